@@ -1,0 +1,173 @@
+/*
+ * iron_b200 -- C ABI of the B200 (sm_100a) operator library.
+ *
+ * The reference (amd/IRON) has no C FFI: its device boundary is the Python operator
+ * class (`Operator.__call__` / `Operator.step`, iron/common/declare/operator.py:126-136,
+ * :619-637) whose `build()`/`sequence()` halves lower to AIE designs.  On B200 those
+ * halves become kernel-launch wrappers that call the entry points declared here, one
+ * per kernel family.  Each comment names the reference operator the entry replaces.
+ *
+ * Conventions
+ *   - every pointer is a CUDA device pointer unless its name starts with `h_`;
+ *   - bf16 tensors are dense, row-major, 16-byte aligned at their base;
+ *   - `stream` is a `cudaStream_t` passed as `void*` (NULL = the legacy default stream);
+ *   - the library allocates nothing: outputs, workspaces and the arena are the caller's;
+ *   - every launch is stream-ordered and may be captured in a CUDA graph;
+ *   - a `const int* d_*` argument, when non-NULL, overrides the immediate of the same
+ *     name with a value read on the device at run time, so a captured graph can be
+ *     replayed with new per-call values (the reference's per-call `Value`s,
+ *     iron/common/declare/value.py:25-114);
+ *   - return value: IRON_OK or a negative IRON_ERR_* code; nothing throws or aborts.
+ */
+#ifndef IRON_B200_H
+#define IRON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* iron_stream_t;
+
+enum {
+  IRON_OK = 0,
+  IRON_ERR_SHAPE = -1,       /* a size the kernel family refuses */
+  IRON_ERR_ALIGN = -2,       /* a pointer or row pitch that is not 16-byte aligned */
+  IRON_ERR_LAUNCH = -3,      /* the CUDA runtime reported a launch error */
+  IRON_ERR_UNSUPPORTED = -4, /* a mode this build does not implement */
+  IRON_ERR_WORKSPACE = -5,   /* the workspace given is too small */
+  IRON_ERR_TIMEOUT = -6      /* a bounded device-side wait gave up (see status word) */
+};
+
+/* Library version and the architecture it was compiled for ("sm_100a"). */
+int iron_version(void);
+const char* iron_arch(void);
+
+/* ------------------------------------------------------------------------------------
+ * GEMV -- replaces iron/operators/gemv.py:79 (`GEMV`, reference :408-417).
+ *   y[b, m] = bf16( sum_k A[b / repeat, m, k] * xn[b, k] ),  f32 accumulation.
+ * A is (num_matrices, M, K) with num_matrices = batches / repeat, x is (batches, K),
+ * y is (batches, M).  Rows >= valid_rows are not written.
+ * Fused prologue (norm_mode): 0 none; 1 xn = RMSNorm(x) unweighted; 2 xn = RMSNorm(x)
+ * times norm_weight (K,) -- with the two bf16 roundings of
+ * iron/common/elementwise.py:676-682.
+ * Fused epilogue: residual (batches, M) non-NULL adds it after y's own rounding,
+ * y = bf16(bf16(acc) + residual), as `ElementwiseAdd` after `GEMV` would.
+ * K must be a multiple of 8 and at most 49152.
+ */
+int iron_gemv_bf16(const void* A, const void* x, void* y, int M, int K, int batches,
+                   int repeat, int valid_rows, int norm_mode, const void* norm_weight,
+                   float eps, const void* residual, iron_stream_t stream);
+
+/* Gate/up projection with SwiGLU -- the chain GEMV, GEMV, SiLU, ElementwiseMul of
+ * iron/lm/blocks.py:697-699 in one pass over both weight matrices:
+ *   y[m] = bf16( bf16(silu(bf16(Wg[m,:] . xn))) * bf16(Wu[m,:] . xn) ).
+ * Same prologue options as iron_gemv_bf16.  Wg, Wu are (M, K); x (K,); y (M,).
+ */
+int iron_gemv_swiglu_bf16(const void* Wg, const void* Wu, const void* x, void* y, int M,
+                          int K, int norm_mode, const void* norm_weight, float eps,
+                          iron_stream_t stream);
+
+/* Decode-step fused QKV projection -- RMSNorm, the three GEMVs, RoPE on q and k and
+ * the two KV-cache writes of iron/lm/blocks.py:627-648 and :486 in one kernel.
+ * Wqkv is ((H + 2G) * D, K): q rows, then k rows, then v rows.  angles is the packed
+ * RoPE table (positions, D) with cos at even and sin at odd columns
+ * (iron/operators/rope.py:58); the row used is `position`.  q_out is (H, D);
+ * k_cache and v_cache are (max_seq, G, D) and row `position` of each is written.
+ */
+int iron_decode_qkv_rope_bf16(const void* Wqkv, const void* x, int K, int norm_mode,
+                              const void* norm_weight, float eps, const void* angles,
+                              int position, const int* d_position, void* q_out,
+                              void* k_cache, void* v_cache, int H, int G, int D,
+                              iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Row-wise and element-wise kernels.
+ */
+
+/* RMSNorm -- iron/operators/rms_norm.py:10 on WeightedRowwise
+ * (iron/common/elementwise.py:619-794): per row n = bf16(x * 1/sqrt(mean(x^2)+eps)),
+ * then y = bf16(n * weight) when weight is non-NULL.  x, y (rows, cols); cols % 8 == 0. */
+int iron_rmsnorm_bf16(const void* x, const void* weight, void* y, int rows, int cols,
+                      float eps, int valid_rows, const int* d_valid_rows,
+                      iron_stream_t stream);
+
+/* RoPE -- iron/operators/rope.py:58 (reference :167-184).  x, y (rows, cols); angles
+ * (angle_rows, cols) packed cos/sin; row r uses angle row
+ * angle_offset + r / (rows / angle_rows).  two_halves != 0 pairs column i with
+ * i + cols/2 (the Hugging Face layout), else columns 2i and 2i+1. */
+int iron_rope_bf16(const void* x, const void* angles, void* y, int rows, int cols,
+                   int angle_rows, int two_halves, int angle_offset,
+                   const int* d_angle_offset, int valid_rows, const int* d_valid_rows,
+                   iron_stream_t stream);
+
+/* Unary / binary element-wise ops over n bf16 elements (n % 8 == 0 not required).
+ * op: see IRON_EW_*.  For the ROW variants b is a row of `cols` elements broadcast
+ * over n / cols rows.  Replaces iron/operators/{silu,elementwise_add,elementwise_mul,
+ * axpy}.py.  Every result is computed in f32 and rounded once. */
+enum {
+  IRON_EW_SILU = 0,     /* y = silu(a) */
+  IRON_EW_ADD = 1,      /* y = a + b */
+  IRON_EW_MUL = 2,      /* y = a * b */
+  IRON_EW_AXPY = 3,     /* y = scalar * a + b */
+  IRON_EW_SILU_MUL = 4, /* y = bf16(silu(a)) * b  (SiLU then ElementwiseMul) */
+  IRON_EW_ROW_ADD = 5,  /* y = a + b[col] */
+  IRON_EW_ROW_MUL = 6,  /* y = a * b[col] */
+  IRON_EW_SIGMOID = 7,  /* y = 1 / (1 + exp(-a)) */
+  IRON_EW_GELU_SIG = 8  /* y = a * sigmoid(1.702 a) */
+};
+int iron_elementwise_bf16(int op, const void* a, const void* b, void* y, long long n,
+                          int cols, float scalar, iron_stream_t stream);
+
+/* Copy / Gather -- iron/operators/copy.py:546 (`Copy`, reference :839-902) and :72
+ * (`Gather`), exact.  Gathers `nrows` rows of `row_bytes` bytes (multiple of 16):
+ *   dst[(dst_row0 + i) * dst_pitch ...] = src[row(i) * src_pitch ...]
+ * where row(i) = ids ? clamp(ids[i], 0, src_rows - 1) : src_row0 + i.  d_src_row0 /
+ * d_dst_row0 / d_nrows override the immediates when non-NULL; nrows is then the
+ * upper bound the grid is sized for. */
+int iron_copy_rows(const void* src, void* dst, const int* ids, int nrows,
+                   const int* d_nrows, long long row_bytes, long long src_pitch,
+                   long long dst_pitch, int src_rows, int src_row0, const int* d_src_row0,
+                   int dst_row0, const int* d_dst_row0, iron_stream_t stream);
+
+/* Greedy draw -- the all-zero draw row of iron/operators/sample.py:106, i.e.
+ * iron/lm/generation.py:97-99: the first index of the largest logit, exact.
+ * logits (n,) bf16.  workspace: iron_argmax_workspace_bytes() bytes, zeroed once by the
+ * caller before first use (the kernel leaves it zeroed).  *token_out receives the id;
+ * when carry_token / carry_position are non-NULL the id is also stored there and
+ * *carry_position is incremented, which is how a captured decode loop carries
+ * (token, position + 1) to its next replay (iron/lm/causal.py:334-349). */
+size_t iron_argmax_workspace_bytes(int n);
+int iron_argmax_bf16(const void* logits, int n, int* token_out, int* carry_token,
+                     int* carry_position, void* workspace, iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Attention.
+ */
+
+/* One-query ("packed") attention over a KV cache -- iron/operators/mha.py:191 with
+ * seq_len == 1 (reference :1073-1116), as iron/lm/blocks.py:491-499 calls it for a
+ * decode step: O[b,h,:] = softmax(scale * Q[b,h,:] . K[b, :n, h / (H/G), :]) . V.
+ * Q, O are (batch, H, D).  K and V share the element strides given: the cache layout
+ * (max_seq, G, D) of iron/lm/blocks.py:460 is seq_stride = G*D, head_stride = D.
+ * n = kv_valid, or d_kv_valid[b * d_kv_valid_stride] + kv_valid_add when d_kv_valid is
+ * non-NULL; clamped to kv_max.  window < 0 attends all n keys, else the query's own
+ * and the `window` before it.  D is 64, 128 or 256.  The keys are split `nsplit` ways
+ * (iron_mha_decode_splits suggests a count); with nsplit > 1 the workspace
+ * (iron_mha_decode_workspace_bytes, 256-byte aligned, zeroed once before first use
+ * and left zeroed by every launch) holds the partial results. */
+int iron_mha_decode_splits(int batch, int G, int kv_len_hint);
+size_t iron_mha_decode_workspace_bytes(int batch, int H, int G, int D, int nsplit);
+int iron_mha_decode_bf16(const void* Q, const void* K, const void* V, void* O, int batch,
+                         int H, int G, int D, int kv_max, long long kv_batch_stride,
+                         long long kv_seq_stride, long long kv_head_stride, int kv_valid,
+                         const int* d_kv_valid, int d_kv_valid_stride, int kv_valid_add,
+                         int window, float scale, int nsplit, void* workspace,
+                         size_t workspace_bytes, iron_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IRON_B200_H */

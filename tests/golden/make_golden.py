@@ -1,0 +1,33 @@
+"""Copy the reference's recorded float32 Hugging Face logits into ``tests/golden/``.
+
+Run once in a container that has the reference tree mounted; the GPU box has no copy of
+it, so the rows travel as this small fixture.  The rows are data the reference's own
+tests judge by (iron/tests/common/goldens/small.npz, keyed by sha256 of the int64 token
+ids, iron/lm/golden.py:88-92): the toy ``SCALED`` Llama on ``filled("random", seed 0)``
+weights, prompt ``default_rng(7).integers(0, 1024, 8)`` then six greedy steps, and the
+multi-chunk prompts of seeds 3 and 4 (iron/tests/support/llama_reference.py:134, :219-224).
+
+    python tests/golden/make_golden.py /root/reference
+"""
+
+import sys
+from pathlib import Path
+
+import numpy as np
+
+SOURCES = {
+    "llama_small.npz": "iron/tests/common/goldens/small.npz",
+}
+
+
+def main(reference: str) -> None:
+    here = Path(__file__).resolve().parent
+    for name, rel in SOURCES.items():
+        with np.load(Path(reference) / rel) as z:
+            rows = {k: z[k] for k in z.files}
+        np.savez_compressed(here / name, **rows)
+        print(name, len(rows), "rows")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
