@@ -1,0 +1,328 @@
+"""Headline benchmark: Llama-3.2-1B-architecture greedy decode, tokens per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode token of the random-init 1B-architecture model (bf16 weights
+N(0, 0.02), 16 layers, hidden 2048, 32/8 heads of 64, MLP 8192, vocabulary 128256, tied
+head) at context 2048 and growing.  `value` is tokens/s with the loop carried on the
+device (CUDA-graph replays, per-call values in HBM); `e2e` is the same through the
+host-facing call (`LlamaEngine.decode`: token in from pinned host memory, drawn token read
+back, every step).  With N > 1 every rank holds a full replica and decodes its own
+sequence (no collective; weak scaling).
+
+`--impl reference` times the CPU restatement of the reference's host graph
+(`oracle.model.NumpyLlama`: numpy float32 arithmetic on bf16 tensors, one rounding per
+operator) on the host cores for a bounded number of tokens.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONTEXT = 2048          # positions already in the caches when decode starts
+MAX_SEQ = 4096
+METRIC = "llama-3.2-1b-arch decode throughput (batch 1, greedy, context 2048+)"
+UNIT = "tokens/s"
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._thread = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                     "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                "sm_max_mhz": float(self.rows[0][1]) if self.rows[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def build_config():
+    import dataclasses
+
+    from iron_b200.applications.llama.model import LLAMA_1B
+
+    return dataclasses.replace(LLAMA_1B, max_seq_len=MAX_SEQ)
+
+
+def device_weights(config, seed: int, device):
+    """Random-init weights N(0, 0.02) (norms one), drawn on the device from ``seed``."""
+    import torch
+
+    from oracle.model import llama_shapes, LlamaShape
+
+    shape = LlamaShape(max_seq_len=config.max_seq_len)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    out = {}
+    for name, dims in llama_shapes(shape).items():
+        if len(dims) >= 2:
+            out[name] = (torch.randn(dims, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        else:
+            out[name] = torch.ones(dims, device=device, dtype=torch.bfloat16)
+    return out
+
+
+def fill_caches(engine, seed: int):
+    """Stand-in for the 2048-token prompt: caches filled N(0, 1) up to CONTEXT."""
+    import torch
+
+    gen = torch.Generator(device=engine.device).manual_seed(seed)
+    for l in engine.layers:
+        for name in ("k", "v"):
+            l[name][:, :CONTEXT].copy_(torch.randn(l[name][:, :CONTEXT].shape, generator=gen,
+                                                   device=engine.device).to(torch.bfloat16))
+
+
+def time_dominant_kernel(engine, peak_gbs: float, peak_kind: str) -> dict:
+    """CUDA-event timing of the gate/up SwiGLU GEMV (43 % of the step's bytes), cycling
+    through the 16 layers' weights so every launch streams from HBM."""
+    import torch
+
+    from iron_b200 import kernels as K
+
+    c = engine.c
+    x, act = engine.x1[0], engine.act[0]
+    x.copy_(torch.randn(c.hidden_size, device=engine.device).to(torch.bfloat16))
+
+    def sweep():
+        for l in engine.layers:
+            K.gemv_swiglu(l["wg"], l["wu"], x, act, norm_weight=l["ln2"], eps=c.eps)
+
+    for _ in range(3):
+        sweep()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sweep()
+    g.replay()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(reps):
+        g.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    per_launch_s = start.elapsed_time(stop) / 1e3 / (reps * len(engine.layers))
+    bytes_per_launch = 2 * c.intermediate_size * c.hidden_size * 2
+    achieved = bytes_per_launch / per_launch_s / 1e9
+    return {"bound": "hbm", "kernel": "gemv_kernel<SWIGLU> (gate/up GEMV + SiLU + mul)",
+            "achieved": round(achieved, 1), "peak": peak_gbs, "peak_kind": peak_kind,
+            "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
+            "bytes_per_launch": bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 2),
+            "traffic": None}
+
+
+def cpu_baseline(tokens: int = 2) -> dict:
+    """The oracle decoder on the host cores for a bounded number of decode tokens."""
+    import numpy as np
+
+    from oracle import model as M
+
+    shape = M.LlamaShape(max_seq_len=CONTEXT + 64)
+    t0 = time.perf_counter()
+    weights = M.filled_normal(M.llama_shapes(shape), 3001)
+    model = M.NumpyLlama(shape, weights)
+    rng = np.random.default_rng(3002)
+    for k, v in zip(model.keys, model.values):
+        k[:CONTEXT] = rng.standard_normal(k[:CONTEXT].shape, dtype=np.float32).astype(k.dtype)
+        v[:CONTEXT] = k[:CONTEXT]
+    setup = time.perf_counter() - t0
+    tok = 1
+    model.forward([tok], CONTEXT)  # warm-up: page in, BLAS threads up
+    t0 = time.perf_counter()
+    for i in range(tokens):
+        logits = model.forward([tok], CONTEXT + 1 + i)
+        tok = int(np.argmax(logits.astype(np.float32)))
+    dt = time.perf_counter() - t0
+    cores = len(os.sched_getaffinity(0))
+    return {"value": round(tokens / dt, 4), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{tokens} greedy decode tokens of the same 1B-architecture model at context "
+                      f"{CONTEXT} (numpy float32 restatement of the reference's host graph, "
+                      f"{setup:.0f}s weight draw excluded)"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_baseline(tokens=max(1, min(args.steps, 3)))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(1e3 / base["value"], 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic",
+            "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "configs[2]: Llama-3.2-1B architecture, random-init bf16 N(0,0.02), tied head; "
+                        "decode after a 2048-position context, batch 1 per GPU",
+            "context": CONTEXT, "replicas": n_gpus,
+            "l2": "every step streams 2.47 GB of weights, far more than the 126 MB L2",
+            "prompt": "KV caches filled N(0,1) for positions < 2048 (stands in for the prefill)"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from __graft_entry__ import build
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path); "
+                           "use --impl reference for the CPU baseline")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if rank == 0:
+        build()
+    if world > 1:
+        dist.barrier()
+
+    from iron_b200.lm.engine import LlamaEngine
+
+    config = build_config()
+    weights = device_weights(config, 3001, device)
+    engine = LlamaEngine(config, weights, device=device, kv_len_hint=CONTEXT + args.steps)
+    del weights
+    fill_caches(engine, 3002 + rank)
+    engine.capture()
+    warm = max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-carried loop: inputs resident, one graph replay per token ----
+    engine.set_call(1, CONTEXT)
+    for _ in range(warm):
+        engine.step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    engine.set_call(1, CONTEXT)
+    barrier()
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            engine.step()
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+
+    # ---- host-facing call: token from pinned host memory in, drawn token out ----
+    tok = 1
+    for i in range(warm):
+        tok = engine.decode(tok, CONTEXT + i)
+    barrier()
+    tok = 1
+    start.record()
+    for i in range(args.steps):
+        tok = engine.decode(tok, CONTEXT + i)
+    stop.record()
+    barrier()
+    ms_e2e = start.elapsed_time(stop)
+
+    times = torch.tensor([ms, ms_e2e], device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = times.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, kind = measured_peaks()
+    value = world * args.steps / (ms / 1e3)
+    e2e = world * args.steps / (ms_e2e / 1e3)
+    step_bytes = engine.weight_bytes_per_token + (CONTEXT + args.steps // 2) * 32768
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": warm, "ms_per_step": round(ms / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": 64,
+                "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e / args.steps, 4)},
+        "gpu_launches": engine.launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": time_dominant_kernel(engine, peak, kind),
+        "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes,
+                          "achieved": round(step_bytes / (ms / args.steps / 1e3) / 1e9, 1),
+                          "peak": peak, "unit": "GB/s",
+                          "frac": round(step_bytes / (ms / args.steps / 1e3) / 1e9 / peak, 4)},
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -135,13 +135,16 @@ int iron_copy_rows(const void* src, void* dst, const int* ids, int nrows,
 /* Greedy draw -- the all-zero draw row of iron/operators/sample.py:106, i.e.
  * iron/lm/generation.py:97-99: the first index of the largest logit, exact.
  * logits (n,) bf16.  workspace: iron_argmax_workspace_bytes() bytes, zeroed once by the
- * caller before first use (the kernel leaves it zeroed).  *token_out receives the id;
- * when carry_token / carry_position are non-NULL the id is also stored there and
- * *carry_position is incremented, which is how a captured decode loop carries
- * (token, position + 1) to its next replay (iron/lm/causal.py:334-349). */
+ * caller before first use (the kernel leaves it zeroed).  token_out[*d_out_index]
+ * (index 0 when d_out_index is NULL) receives the id -- `drawn[position]` of
+ * iron/lm/causal.py:340-347; when carry_token / carry_position are non-NULL the id is
+ * also stored there and *carry_position is incremented afterwards, which is how a
+ * captured decode loop carries (token, position + 1) to its next replay
+ * (iron/lm/causal.py:348). */
 size_t iron_argmax_workspace_bytes(int n);
-int iron_argmax_bf16(const void* logits, int n, int* token_out, int* carry_token,
-                     int* carry_position, void* workspace, iron_stream_t stream);
+int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out_index,
+                     int* carry_token, int* carry_position, void* workspace,
+                     iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Attention.

@@ -204,8 +204,8 @@ constexpr int kArgmaxBlocks = kSMs * 2;
 
 // workspace layout: [0] u32 arrival counter, [8 ..] u64 partial keys per block
 __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int n,
-                                                     int* token_out, int* carry_token,
-                                                     int* carry_position,
+                                                     int* token_out, const int* d_out_index,
+                                                     int* carry_token, int* carry_position,
                                                      unsigned long long* workspace) {
   __shared__ unsigned long long sred[8];
   __shared__ bool last;
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __rest
     if (threadIdx.x == 0) {
       for (int w = 1; w < 8; ++w) b = umax64(b, sred[w]);
       const int tok = (int)(~(uint32_t)(b & 0xffffffffull));
-      *token_out = tok;
+      token_out[d_out_index ? *d_out_index : 0] = tok;
       if (carry_token) *carry_token = tok;
       if (carry_position) *carry_position += 1;
       *counter = 0;  // leave the workspace ready for the next launch
@@ -368,13 +368,14 @@ extern "C" size_t iron_argmax_workspace_bytes(int n) {
   return sizeof(unsigned long long) * (1 + kArgmaxBlocks);
 }
 
-extern "C" int iron_argmax_bf16(const void* logits, int n, int* token_out, int* carry_token,
-                                int* carry_position, void* workspace, iron_stream_t stream) {
+extern "C" int iron_argmax_bf16(const void* logits, int n, int* token_out,
+                                const int* d_out_index, int* carry_token, int* carry_position,
+                                void* workspace, iron_stream_t stream) {
   if (n <= 0 || !token_out || !workspace) return IRON_ERR_SHAPE;
   if (!aligned16(logits) || (reinterpret_cast<uintptr_t>(workspace) & 7)) return IRON_ERR_ALIGN;
   int grid = (n / 8 + 255) / 256;
   grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
   return launch_pdl(argmax_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
-                    (const __nv_bfloat16*)logits, n, token_out, carry_token, carry_position,
-                    (unsigned long long*)workspace);
+                    (const __nv_bfloat16*)logits, n, token_out, d_out_index, carry_token,
+                    carry_position, (unsigned long long*)workspace);
 }

@@ -127,11 +127,12 @@ def argmax_workspace(device) -> torch.Tensor:
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
-def argmax(logits, token_out, workspace, *, carry_token=None, carry_position=None):
-    """Greedy draw: first index of the maximum, written to ``token_out`` (int32 device scalar)."""
+def argmax(logits, token_out, workspace, *, d_out_index=None, carry_token=None,
+           carry_position=None):
+    """Greedy draw: first index of the maximum, written to ``token_out[*d_out_index]``."""
     _bf16(logits)
-    call("iron_argmax_bf16", _ptr(logits), logits.numel(), _ptr(token_out), _ptr(carry_token),
-         _ptr(carry_position), _ptr(workspace), _stream())
+    call("iron_argmax_bf16", _ptr(logits), logits.numel(), _ptr(token_out), _ptr(d_out_index),
+         _ptr(carry_token), _ptr(carry_position), _ptr(workspace), _stream())
     return token_out
 
 

@@ -1,0 +1,244 @@
+"""The Llama-architecture decoder as fused sm_100a kernels over one device arena.
+
+This is what a compiled ``CausalLM`` graph of the reference becomes on B200
+(iron/lm/causal.py:271-349 recorded over iron/lm/blocks.py:627-733): the reference's 18
+operator steps per layer run as five kernels,
+
+    1. RMSNorm + fused q/k/v GEMV + RoPE + KV-cache write      (iron_decode_qkv_rope_bf16)
+    2. one-query attention, split over the keys                (iron_mha_decode_bf16)
+    3. o_proj GEMV + residual add                              (iron_gemv_bf16)
+    4. RMSNorm + gate/up GEMV + SiLU + multiply                (iron_gemv_swiglu_bf16)
+    5. down_proj GEMV + residual add                           (iron_gemv_bf16)
+
+between an embedding-row gather and the final norm + tied-head GEMV + greedy draw, all
+captured in one CUDA graph.  The per-call values (token, position) live in a small device
+buffer the last kernel updates, so ``generate`` replays the graph once per token with no
+host round trip, as the reference's device-carried loop does
+(iron/common/graph/carried.py:189-276).
+
+Weights, KV caches and intermediates are slices of one HBM allocation planned by
+``iron_b200.arena.ArenaPlan``.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from ..arena import ArenaPlan
+from .config import DecoderConfig
+
+BF16 = torch.bfloat16
+
+
+def _as_device_bf16(a, out: torch.Tensor) -> None:
+    """Copy ``a`` (numpy bf16 via ml_dtypes, or a torch tensor) into arena slice ``out``."""
+    if isinstance(a, torch.Tensor):
+        out.copy_(a.to(BF16).reshape(out.shape))
+        return
+    a = np.ascontiguousarray(a)
+    if a.dtype.name == "bfloat16":
+        t = torch.from_numpy(a.view(np.int16)).view(BF16)
+    else:
+        t = torch.from_numpy(a.astype(np.float32)).to(BF16)
+    out.copy_(t.reshape(out.shape))
+
+
+class LlamaEngine:
+    """A decoder of ``config``'s shape on ``weights`` (Hugging Face checkpoint names).
+
+    ``batch`` independent sequences share the weights and hold a KV cache each.
+    """
+
+    def __init__(self, config: DecoderConfig, weights: dict, device="cuda", batch: int = 1,
+                 kv_len_hint: int | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("LlamaEngine needs a CUDA device: there is no CPU path")
+        self.c, self.device, self.batch = config, torch.device(device), batch
+        c = config
+        E, F, V, L = c.hidden_size, c.intermediate_size, c.vocab_size, c.num_hidden_layers
+        H, G, D, S = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.max_seq_len
+        self.kv_len_hint = kv_len_hint or S
+
+        # ---- plan the arena: residents first, then the decode step's transients ----
+        plan = ArenaPlan()
+        sizes: dict[str, int] = {}
+
+        def res(name, shape, dtype_bytes=2):
+            sizes[name] = int(np.prod(shape)) * dtype_bytes
+            return name
+
+        res("embed", (V, E)); res("norm", (E,)); res("angles", (S, D))
+        if not c.tie_word_embeddings:
+            res("head", (V, E))
+        for i in range(L):
+            res(f"l{i}.ln1", (E,)); res(f"l{i}.wqkv", ((H + 2 * G) * D, E))
+            res(f"l{i}.wo", (E, H * D)); res(f"l{i}.ln2", (E,))
+            res(f"l{i}.wg", (F, E)); res(f"l{i}.wu", (F, E)); res(f"l{i}.wd", (E, F))
+            res(f"l{i}.k", (batch, S, G, D)); res(f"l{i}.v", (batch, S, G, D))
+        res("values", (16,), 4); res("drawn", (batch, S), 4)
+        residents = {n: n for n in sizes}
+        trans = {"x0": (batch, E), "x1": (batch, E), "q": (batch, H * D), "att": (batch, H * D),
+                 "act": (batch, F), "logits": (batch, V)}
+        for n, shape in trans.items():
+            sizes[n] = int(np.prod(shape)) * 2
+        # the decode step touches every transient in each layer: all live together
+        spans = plan.place_version([list(trans)], sizes, residents)
+        self.plan = plan
+        self.arena = torch.empty(plan.size, dtype=torch.uint8, device=self.device)
+        self.arena.zero_()
+
+        def view(name, shape, dtype=BF16):
+            s = spans[name]
+            return self.arena[s.offset : s.offset + s.size].view(dtype).view(*shape)
+
+        self.embed, self.norm, self.angles = view("embed", (V, E)), view("norm", (E,)), view("angles", (S, D))
+        self.head = self.embed if c.tie_word_embeddings else view("head", (V, E))
+        self.layers = []
+        for i in range(L):
+            self.layers.append(dict(
+                ln1=view(f"l{i}.ln1", (E,)), wqkv=view(f"l{i}.wqkv", ((H + 2 * G) * D, E)),
+                wo=view(f"l{i}.wo", (E, H * D)), ln2=view(f"l{i}.ln2", (E,)),
+                wg=view(f"l{i}.wg", (F, E)), wu=view(f"l{i}.wu", (F, E)), wd=view(f"l{i}.wd", (E, F)),
+                k=view(f"l{i}.k", (batch, S, G, D)), v=view(f"l{i}.v", (batch, S, G, D))))
+        self.values = view("values", (16,), torch.int32)   # [token, position, ...]
+        self.drawn = view("drawn", (batch, S), torch.int32)
+        self.x0, self.x1 = view("x0", (batch, E)), view("x1", (batch, E))
+        self.q, self.att = view("q", (batch, H, D)), view("att", (batch, H, D))
+        self.act, self.logits_buf = view("act", (batch, F)), view("logits", (batch, V))
+
+        self._load(weights)
+        self.nsplit, self.mha_ws = K.mha_decode_plan(batch, H, G, D, self.kv_len_hint, self.device)
+        self.argmax_ws = K.argmax_workspace(self.device)
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self._h_values = torch.zeros(16, dtype=torch.int32).pin_memory()
+        self._h_token = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    # ------------------------------------------------------------------ weights
+    def _load(self, w: dict) -> None:
+        c = self.c
+        _as_device_bf16(w["model.embed_tokens.weight"], self.embed)
+        _as_device_bf16(w["model.norm.weight"], self.norm)
+        if not c.tie_word_embeddings:
+            _as_device_bf16(w["lm_head.weight"], self.head)
+        _as_device_bf16(c.angles().astype(np.float32), self.angles)
+        Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+        for i, l in enumerate(self.layers):
+            p = f"model.layers.{i}"
+            _as_device_bf16(w[f"{p}.input_layernorm.weight"], l["ln1"])
+            _as_device_bf16(w[f"{p}.self_attn.q_proj.weight"], l["wqkv"][:Q])
+            _as_device_bf16(w[f"{p}.self_attn.k_proj.weight"], l["wqkv"][Q : Q + KV])
+            _as_device_bf16(w[f"{p}.self_attn.v_proj.weight"], l["wqkv"][Q + KV :])
+            _as_device_bf16(w[f"{p}.self_attn.o_proj.weight"], l["wo"])
+            _as_device_bf16(w[f"{p}.post_attention_layernorm.weight"], l["ln2"])
+            _as_device_bf16(w[f"{p}.mlp.gate_proj.weight"], l["wg"])
+            _as_device_bf16(w[f"{p}.mlp.up_proj.weight"], l["wu"])
+            _as_device_bf16(w[f"{p}.mlp.down_proj.weight"], l["wd"])
+
+    # ------------------------------------------------------------------ decode step
+    @property
+    def launches_per_step(self) -> int:
+        """Kernels one decode step launches: gather, five per layer, head, draw."""
+        return 1 + 5 * self.c.num_hidden_layers + 2
+
+    @property
+    def weight_bytes_per_token(self) -> int:
+        """Bytes of weights one decode step streams (the HBM roofline's numerator)."""
+        c = self.c
+        E, F, V = c.hidden_size, c.intermediate_size, c.vocab_size
+        Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+        layer = ((Q + 2 * KV) * E + E * Q + 3 * F * E) * 2
+        return c.num_hidden_layers * layer + V * E * 2
+
+    def _decode_launches(self) -> None:
+        """Launch one decode step on the current stream, reading (token, position) from
+        the device values buffer and leaving (drawn token, position + 1) there."""
+        c = self.c
+        H, G, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        d_token, d_pos = self.values[0:1], self.values[1:2]
+        E2 = c.hidden_size * 2
+        x, y = self.x0[0], self.x1[0]
+        K.copy_rows(self.embed, x, ids=d_token, nrows=1, row_bytes=E2, src_rows=c.vocab_size)
+        for l in self.layers:
+            K.decode_qkv_rope(l["wqkv"], x, self.angles, l["k"][0], l["v"][0], self.q[0],
+                              H=H, G=G, D=D, d_position=d_pos, norm_weight=l["ln1"], eps=c.eps)
+            K.mha_decode(self.q, l["k"], l["v"], self.att, d_kv_valid=d_pos, kv_valid_add=1,
+                         window=c.window, scale=c.attention_scale, nsplit=self.nsplit,
+                         workspace=self.mha_ws)
+            K.gemv(l["wo"], self.att[0].view(-1), y, residual=x)
+            K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
+            K.gemv(l["wd"], self.act[0], x, residual=y)
+        K.gemv(self.head, x, self.logits_buf[0], norm_weight=self.norm, eps=c.eps)
+        K.argmax(self.logits_buf[0], self.drawn[0], self.argmax_ws, d_out_index=d_pos,
+                 carry_token=d_token, carry_position=d_pos)
+
+    def capture(self) -> None:
+        """Capture the decode step as one CUDA graph (idempotent)."""
+        if self._graph is not None:
+            return
+        saved = self.values.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # warm up outside capture: lazy module loading
+            self.set_call(0, 0)
+            self._decode_launches()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        self.set_call(0, 0)
+        with torch.cuda.graph(g):
+            self._decode_launches()
+        self._graph = g
+        self.values.copy_(saved)
+        for l in self.layers:   # the warm-up wrote position 0 of the caches
+            l["k"][:, 0].zero_(); l["v"][:, 0].zero_()
+        torch.cuda.synchronize()
+
+    def set_call(self, token: int, position: int) -> None:
+        """Write the per-call values (one small pinned-host to device copy)."""
+        if not 0 <= position < self.c.max_seq_len:
+            raise IndexError(f"position {position} is outside the {self.c.max_seq_len}-row caches")
+        if not 0 <= token < self.c.vocab_size:
+            raise IndexError(f"token {token} is outside the {self.c.vocab_size}-row vocabulary")
+        self._h_values[0], self._h_values[1] = int(token), int(position)
+        self.values.copy_(self._h_values, non_blocking=True)
+
+    def step(self) -> None:
+        """Replay one decode step (stream-ordered; no host synchronisation)."""
+        self.capture()
+        self._graph.replay()
+
+    def decode(self, token: int, position: int) -> int:
+        """One decode step from the host: token in, drawn token out (both cross PCIe)."""
+        self.set_call(token, position)
+        self.step()
+        self._h_token.copy_(self.values[0:1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(self._h_token[0])
+
+    def logits(self) -> np.ndarray:
+        """The last step's logits as float32 on the host."""
+        return self.logits_buf[0].float().cpu().numpy()
+
+    def generate(self, token: int, position: int, steps: int) -> list[int]:
+        """``steps`` greedy tokens, the loop carried on the device: one replay per token."""
+        if position + steps > self.c.max_seq_len:
+            raise IndexError("the run would pass the end of the caches")
+        self.set_call(token, position)
+        self.capture()
+        for _ in range(steps):
+            self._graph.replay()
+        out = self.drawn[0, position : position + steps].cpu()
+        return out.tolist()
+
+    def feed(self, tokens, start: int = 0) -> np.ndarray:
+        """Run ``tokens`` one decode step at a time from ``start`` (teacher-forced);
+        returns the logits after the last."""
+        for i, t in enumerate(tokens):
+            self.set_call(int(t), start + i)
+            self.step()
+        return self.logits()
