@@ -45,6 +45,12 @@ enum {
 int iron_version(void);
 const char* iron_arch(void);
 
+/* Every kernel is launched with the programmatic-stream-serialization attribute, so a
+ * kernel's weight prefetch may overlap the tail of the kernel before it (each kernel
+ * still waits for its predecessor's results before reading them).  iron_set_pdl(0)
+ * turns the attribute off process-wide, e.g. to bisect a scheduling problem. */
+void iron_set_pdl(int enabled);
+
 /* ------------------------------------------------------------------------------------
  * GEMV -- replaces iron/operators/gemv.py:79 (`GEMV`, reference :408-417).
  *   y[b, m] = bf16( sum_k A[b / repeat, m, k] * xn[b, k] ),  f32 accumulation.
@@ -103,6 +109,18 @@ int iron_rope_bf16(const void* x, const void* angles, void* y, int rows, int col
                    const int* d_angle_offset, int valid_rows, const int* d_valid_rows,
                    iron_stream_t stream);
 
+/* Prompt-chunk RoPE and KV-cache write -- the two RoPE steps and the two bounded cache
+ * writes `cache[start : start + C][:rows] = x` of iron/lm/blocks.py:642-644 and :483-484
+ * in one pass over a fused projection's output.  qkv is (rows, (H + 2G) * D) with row
+ * pitch `pitch` (q heads, k heads, v heads); q is rotated in place, k is rotated into
+ * k_cache[start + r] and v copied into v_cache[start + r] (caches (max_seq, G, D)).
+ * Row r uses angle row angle_start + r.  d_rows / d_start / d_angle_start override on
+ * the device. */
+int iron_rope_kv_write_bf16(void* qkv, long long pitch, const void* angles, void* k_cache,
+                            void* v_cache, int rows, const int* d_rows, int H, int G, int D,
+                            int start, const int* d_start, int angle_start,
+                            const int* d_angle_start, iron_stream_t stream);
+
 /* Unary / binary element-wise ops over n bf16 elements (n % 8 == 0 not required).
  * op: see IRON_EW_*.  For the ROW variants b is a row of `cols` elements broadcast
  * over n / cols rows.  Replaces iron/operators/{silu,elementwise_add,elementwise_mul,
@@ -147,6 +165,60 @@ int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out
                      iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * GEMM -- replaces iron/operators/gemm.py:143 (`GEMM`, reference :696-702) and
+ * iron/operators/flm/gemm/op.py:128 (`ProjectionGEMM`, reference :1335-1346, output
+ * stage iron/operators/flm/gemm/design.py:92-112), which `F.linear` records for a
+ * prompt chunk (iron/functional.py:50-60).
+ *   C = epilogue( bf16( A[:valid_rows, :valid_k] @ B[:valid_k] ) ) (+ residual)
+ * A is (M, K) row-major with row pitch lda.  B is (N, K) when b_col_maj (a checkpoint's
+ * (out, in) weight) else (K, N), row pitch ldb.  C is (M, N), or (N, M) when c_col_maj,
+ * pitch ldc; bf16, or f32 when out_f32 (no epilogue then).  Accumulation is f32 in
+ * tensor memory (tcgen05.mma), rounded once.  epilogue: 0 none, 1 x*sigmoid(1.702x),
+ * 2 silu, 3 sigmoid, applied to the rounded product as the reference does.  residual
+ * (same layout as C, bf16) is added after the rounding, as ElementwiseAdd would.
+ * Rows >= valid_rows (d_valid_rows overrides on the device) are neither computed nor
+ * written.  lda, ldb multiples of 8; bases 16-byte aligned.  d_status (optional device
+ * int) receives IRON_ERR_TIMEOUT if a bounded pipeline wait gave up.
+ */
+int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda,
+                   int ldb, int ldc, int b_col_maj, int c_col_maj, int valid_rows,
+                   const int* d_valid_rows, int valid_k, int epilogue, const void* residual,
+                   int out_f32, int* d_status, iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Mamba2.
+ */
+
+/* Selective scan -- iron/operators/selective_scan.py:46 (reference :367-383).  Per batch
+ * entry and row t < valid_rows: x = xbc[t, :H*P] as (H, P); B, C = the two halves of
+ * xbc[t, H*P:], each (G, N), head h reading group h / (H/G);
+ *   step = softplus(dt[t, h] + dt_bias[h]);  state = exp(step * A[h]) * state + step * x (x) B;
+ *   y[t] = state . C + D[h] * x,
+ * float32 throughout, y rounded once to bf16.  head is (H, 3) f32 = (dt_bias, A, D);
+ * state / final_state are (batch, H, P, N) f32 (state NULL = zeros, final_state NULL =
+ * not wanted).  xbc (batch, rows, H*P + 2*G*N), dt (batch, rows, H), y (batch, rows, H*P),
+ * all dense.  Rows >= valid_rows of y are zeros.  N is 16, 32, 64 or 128; P % 8 == 0.
+ * The reference operator has no batch axis: batch > 1 is the independent-sequence axis. */
+int iron_selective_scan_bf16(const void* xbc, const void* dt, const void* head,
+                             const void* state, void* y, void* final_state, int batch,
+                             int rows, int heads, int head_dim, int state_size, int groups,
+                             int valid_rows, const int* d_valid_rows, iron_stream_t stream);
+
+/* Short causal depth-wise convolution -- iron/functional.py:147-180 (`F.causal_conv1d`) with
+ * the bias of iron/lm/causal.py:163 and the SiLU of
+ * iron/applications/granite_hybrid/model.py:128 optionally fused:
+ *   y[t, c] = sum_k taps[k, c] * xx[t + k, c],  xx = history (K-1 rows) ++ x,
+ * each product and each partial sum rounded to bf16 as the recorded RowwiseMul /
+ * ElementwiseAdd steps do; decode_order != 0 sums the newest tap first (the one-row form).
+ * new_history receives the K-1 rows ending the valid run (may alias history).  x, y
+ * (batch, rows, channels); taps (K, channels); K is 2, 3 or 4; channels % 8 == 0. */
+int iron_causal_conv1d_bf16(const void* x, const void* taps, const void* bias,
+                            const void* history, void* new_history, void* y, int batch,
+                            int rows, int channels, int kernel, int valid_rows,
+                            const int* d_valid_rows, int decode_order, int silu,
+                            iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * Attention.
  */
 
@@ -157,18 +229,41 @@ int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out
  * (max_seq, G, D) of iron/lm/blocks.py:460 is seq_stride = G*D, head_stride = D.
  * n = kv_valid, or d_kv_valid[b * d_kv_valid_stride] + kv_valid_add when d_kv_valid is
  * non-NULL; clamped to kv_max.  window < 0 attends all n keys, else the query's own
- * and the `window` before it.  D is 64, 128 or 256.  The keys are split `nsplit` ways
- * (iron_mha_decode_splits suggests a count); with nsplit > 1 the workspace
- * (iron_mha_decode_workspace_bytes, 256-byte aligned, zeroed once before first use
- * and left zeroed by every launch) holds the partial results. */
+ * and the `window` before it.  D is 64, 128 or 256.  The keys are split over a
+ * thread-block cluster of nsplit CTAs (1, 2, 4 or 8; iron_mha_decode_splits suggests
+ * one); partial results meet in distributed shared memory, so no workspace is needed.
+ * stable_prefix != 0 promises that the kernel launched just before this one on the
+ * stream wrote at most row n-1 of K and V (true of a decode step), which lets the key
+ * loads start before that kernel has finished. */
 int iron_mha_decode_splits(int batch, int G, int kv_len_hint);
-size_t iron_mha_decode_workspace_bytes(int batch, int H, int G, int D, int nsplit);
 int iron_mha_decode_bf16(const void* Q, const void* K, const void* V, void* O, int batch,
                          int H, int G, int D, int kv_max, long long kv_batch_stride,
                          long long kv_seq_stride, long long kv_head_stride, int kv_valid,
                          const int* d_kv_valid, int d_kv_valid_stride, int kv_valid_add,
-                         int window, float scale, int nsplit, void* workspace,
-                         size_t workspace_bytes, iron_stream_t stream);
+                         int window, float scale, int nsplit, int stable_prefix,
+                         iron_stream_t stream);
+
+/* Multi-query attention -- iron/operators/mha.py:191 with seq_len > 1 (reference
+ * :1073-1116), as iron/lm/blocks.py:491-499 calls it for a prompt chunk.  The q_tokens
+ * queries are the last rows of the kv_tokens keys (position of query i is
+ * kv_tokens - q_tokens + i); causal keeps keys <= position, window >= 0 keeps keys
+ * within `window` positions (both sides when not causal).  Output rows in
+ * [q_tokens, q_rows) are written as zeros and keys >= kv_tokens are masked
+ * (iron/operators/mha.py:1076-1096).  Q, O and K/V (K and V share theirs) each have
+ * element strides (batch, row, head): a (rows, heads, D) layout has row stride heads*D
+ * and head stride D; Q may be a view into a wider fused projection (larger row stride).
+ * d_q_tokens / d_kv_tokens (+ kv_tokens_add) override the bounds on the device.
+ * D is 64 or 128. */
+int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, int batch,
+                          int H, int G, int D, int q_rows, int kv_rows,
+                          long long q_batch_stride, long long q_row_stride,
+                          long long q_head_stride, long long o_batch_stride,
+                          long long o_row_stride, long long o_head_stride,
+                          long long kv_batch_stride,
+                          long long kv_row_stride, long long kv_head_stride, int q_tokens,
+                          const int* d_q_tokens, int kv_tokens, const int* d_kv_tokens,
+                          int kv_tokens_add, int causal, int window, float scale,
+                          iron_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -39,23 +39,34 @@ _P, _I, _L, _F, _Z = c_void_p, c_int, c_longlong, c_float, c_size_t
 SIGNATURES: dict[str, tuple] = {
     "iron_version": (_I, []),
     "iron_arch": (c_char_p, []),
+    "iron_set_pdl": (None, [_I]),
     "iron_gemv_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _P, _P]),
     "iron_gemv_swiglu_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _F, _P]),
     "iron_decode_qkv_rope_bf16": (
         _I,
         [_P, _P, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
     ),
+    "iron_gemm_bf16": (
+        _I,
+        [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _I, _P, _P],
+    ),
     "iron_rmsnorm_bf16": (_I, [_P, _P, _P, _I, _I, _F, _I, _P, _P]),
     "iron_rope_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
+    "iron_rope_kv_write_bf16": (_I, [_P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P, _P]),
     "iron_elementwise_bf16": (_I, [_I, _P, _P, _P, _L, _I, _F, _P]),
     "iron_copy_rows": (_I, [_P, _P, _P, _I, _P, _L, _L, _L, _I, _I, _P, _I, _P, _P]),
     "iron_argmax_workspace_bytes": (_Z, [_I]),
     "iron_argmax_bf16": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
     "iron_mha_decode_splits": (_I, [_I, _I, _I]),
-    "iron_mha_decode_workspace_bytes": (_Z, [_I, _I, _I, _I, _I]),
     "iron_mha_decode_bf16": (
         _I,
-        [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _P, _I, _I, _I, _F, _I, _P, _Z, _P],
+        [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _P, _I, _I, _I, _F, _I, _I, _P],
+    ),
+    "iron_selective_scan_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
+    "iron_causal_conv1d_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P]),
+    "iron_mha_prefill_bf16": (
+        _I,
+        [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _I, _P, _I, _I, _I, _F, _P],
     ),
 }
 

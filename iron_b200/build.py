@@ -75,7 +75,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     if force or jobs or _stale(LIB, objs):
         # The default (static) CUDA runtime: the library brings its own and shares the
         # process's primary context with torch.
-        cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcuda"]
+        cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objs)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")

@@ -62,6 +62,10 @@ __device__ __forceinline__ uint4 ld_cached(const void* p) {
   return *reinterpret_cast<const uint4*>(p);
 }
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
 // ---- reductions -----------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -94,6 +98,16 @@ __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.laun
 
 // SiLU as the reference's chain computes it: f32 x*sigmoid(x), rounded once to bf16.
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+// Programmatic dependent launch can be switched off process-wide (iron_set_pdl): every
+// launch helper asks here how many launch attributes to attach.
+int pdl_attr_count();
+inline void fill_pdl_attr(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr) {
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_attr_count();
+}
 
 inline int check_launch() {
   cudaError_t e = cudaGetLastError();

@@ -1,0 +1,462 @@
+// bf16 GEMM on the 5th-generation tensor cores: C = epilogue(A @ B), f32 accumulation.
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0      TMA producer: A (128 x 64) and B (BN x 64) tiles, 128-byte swizzle,
+//               into a ring of shared-memory stages (mbarrier full/empty pairs)
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M 128, N BN, K 16) on
+//               shared-memory descriptors, accumulating in tensor memory; tcgen05.commit
+//               releases each stage and signals the finished accumulator
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per
+//               thread), round to bf16, apply the fused output stage, store
+// Two accumulators (2 x BN of the 512 TMEM columns) let the MMA warp start the next tile
+// while the epilogue drains the previous one.  Tiles are walked M-fastest so the CTAs
+// running together share one B (weight) tile through L2.
+//
+// Every wait on an mbarrier is bounded by a wall-clock limit; a wait that gives up sets
+// an abort flag that unwinds all three roles, the producer drains its in-flight copies,
+// tensor memory is freed, and the host finds IRON_ERR_TIMEOUT in the status word.
+// No cluster launch and no multicast: every CTA loads its own operands.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace iron {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes: one swizzle-atom row
+constexpr int UK = 16;  // K of one tcgen05.mma for 16-bit operands
+constexpr int kGemmThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+enum { EPI_NONE = 0, EPI_GELU = 1, EPI_SILU = 2, EPI_SIGMOID = 3 };
+
+struct GemmParams {
+  void* C;
+  const __nv_bfloat16* residual;
+  int M, N, K;          // K already bounded by the caller (tensor maps zero-fill past it)
+  int ldc;              // elements between rows of C (or between columns when transposed)
+  int valid;            // rows of A / C computed
+  const int* d_valid;
+  int epilogue;
+  int out_f32;
+  int c_transposed;     // C is (N, M)
+  int b_n_major;        // B is (K, N) row-major
+  int* status;          // optional device word: receives IRON_ERR_TIMEOUT
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Wait for the phase of `parity` to complete; false when aborted or out of time.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format: version 1, 128-byte swizzle).
+// Addresses and offsets are in 16-byte units.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for Blackwell
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor for kind::f16: bf16 x bf16 -> f32, A K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool b_n_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_n_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ float epilogue_apply(int mode, float c) {
+  // c is already rounded to bf16; the activation's sigmoid is rounded to bf16 before
+  // the product, as the reference's output stage does.
+  switch (mode) {
+    case EPI_GELU: return __fmul_rn(c, 1.0f / (1.0f + expf(-__fmul_rn(1.702f, c))));
+    case EPI_SILU: return __fmul_rn(c, round_bf16(1.0f / (1.0f + expf(-c))));
+    case EPI_SIGMOID: return 1.0f / (1.0f + expf(-c));
+    default: return c;
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;                         // [kStages]
+  uint64_t* empty = bars + Cfg::kStages;         // [kStages]
+  uint64_t* acc_full = bars + 2 * Cfg::kStages;  // [2]
+  uint64_t* acc_empty = acc_full + 2;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 128); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  if (warp == 1) {  // the MMA warp owns tensor memory: all 512 columns (one CTA per SM)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // A and (for b_n_major) B are inputs the previous kernel may have produced.
+  pdl_wait();
+
+  int valid = p.d_valid ? min(*p.d_valid, p.M) : p.valid;
+  valid = max(valid, 0);
+  const int m_tiles = (valid + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total = m_tiles * n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty + s, phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * Cfg::kStageBytes;
+          uint8_t* b_dst = a_dst + Cfg::kABytes;
+          mbar_expect_tx(full + s, Cfg::kStageBytes);
+          tma_load_2d(a_dst, &map_a, kb * BK, m0, full + s);
+          if (!p.b_n_major) {
+            tma_load_2d(b_dst, &map_b, kb * BK, n0, full + s);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(b_dst + c * (64 * BK * 2), &map_b, n0 + c * 64, kb * BK, full + s);
+          }
+          ++issued;
+          if (++s == Cfg::kStages) { s = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Unwinding: let every copy already issued land before the CTA leaves.
+        const int outstanding = min(issued, Cfg::kStages);
+        int ss = s;
+        uint32_t ph = phase;
+        for (int i = 0; i < outstanding; ++i) {
+          if (--ss < 0) { ss = Cfg::kStages - 1; ph ^= 1; }
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try_wait(full + ss, ph) && global_ns() - t0 < kWaitLimitNs) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BN, p.b_n_major != 0);
+      int s = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full + s, phase, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t b_addr = a_addr + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            // K-major: 128-byte rows, 8-row groups 1024 bytes apart, 32 bytes per K step.
+            const uint64_t a_desc = make_desc(a_addr + k * UK * 2, 16, 1024);
+            // N-major B: 64-column chunks 8 KB apart, 8-row K groups 1024 bytes apart,
+            // one K step is 16 rows of 128 bytes.
+            const uint64_t b_desc = p.b_n_major ? make_desc(b_addr + k * UK * 128, 64 * BK * 2, 1024)
+                                                : make_desc(b_addr + k * UK * 2, 16, 1024);
+            tcgen05_mma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+          }
+          tcgen05_commit(empty + s);  // the stage is free once these MMAs have read it
+          if (++s == Cfg::kStages) { s = 0; phase ^= 1; }
+        }
+        if (ok) tcgen05_commit(acc_full + acc);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int group = warp & 3;  // the TMEM lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+      if (!mbar_wait(acc_full + acc, acc_phase, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = m0 + group * 32 + lane;
+      const bool row_live = row < valid;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_live || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (!p.out_f32) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = epilogue_apply(p.epilogue, round_bf16(v[j]));
+        }
+        const bool full_chunk = col0 + 32 <= p.N;
+        if (!p.c_transposed) {
+          const size_t off = (size_t)row * p.ldc + col0;
+          if (p.residual) {
+            if (full_chunk) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float f[8];
+                unpack8(ld_cached(p.residual + off + q * 8), f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(round_bf16(v[q * 8 + j]), f[j]);
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(p.residual[off + j]));
+            }
+          }
+          if (p.out_f32) {
+            float* dst = reinterpret_cast<float*>(p.C) + off;
+            if (full_chunk && (p.ldc & 3) == 0) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+            if (full_chunk && (p.ldc & 7) == 0) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = pack8(v + q * 8);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        } else {
+          // C is (N, M): lanes hold consecutive rows, so each column is a coalesced run.
+          for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+            const size_t off = (size_t)(col0 + j) * p.ldc + row;
+            float x = v[j];
+            if (p.residual) x = __fadd_rn(round_bf16(x), __bfloat162float(p.residual[off]));
+            if (p.out_f32) reinterpret_cast<float*>(p.C)[off] = x;
+            else reinterpret_cast<__nv_bfloat16*>(p.C)[off] = __float2bfloat16_rn(x);
+          }
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(acc_empty + acc);
+    }
+  }
+
+  pdl_launch();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = IRON_ERR_TIMEOUT;
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// A 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows `pitch` elements apart.
+static bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
+                     uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {pitch * 2};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_rows,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) !=
+        cudaSuccess)
+      return IRON_ERR_LAUNCH;
+    configured = true;
+  }
+  const int tiles = ((max_rows + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles < kSMs ? (tiles < 1 ? 1 : tiles) : kSMs);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN>, ma, mb, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+}
+
+}  // namespace iron
+
+using namespace iron;
+
+extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                              int ldc, int b_col_maj, int c_col_maj, int valid_rows, const int* d_valid_rows,
+                              int valid_k, int epilogue, const void* residual, int out_f32, int* d_status,
+                              iron_stream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > M || valid_k < 0 || valid_k > K) return IRON_ERR_SHAPE;
+  if (epilogue < EPI_NONE || epilogue > EPI_SIGMOID) return IRON_ERR_SHAPE;
+  if (out_f32 && epilogue != EPI_NONE) return IRON_ERR_UNSUPPORTED;
+  // TMA: 16-byte aligned bases and row pitches
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return IRON_ERR_ALIGN;
+  if ((lda & 7) || (ldb & 7)) return IRON_ERR_ALIGN;
+  if (lda < K || ldb < (b_col_maj ? K : N) || ldc < (c_col_maj ? M : N)) return IRON_ERR_SHAPE;
+  if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
+  if (valid_k == 0) return IRON_ERR_SHAPE;
+
+  // BN: the widest tile that still yields at least one wave of CTAs
+  const int m_tiles = (M + BM - 1) / BM;
+  int bn = 256;
+  if (N <= 64 || (long long)m_tiles * ((N + 255) / 256) < kSMs / 2) bn = 128;
+  if (N <= 64 || (bn == 128 && (long long)m_tiles * ((N + 127) / 128) < kSMs / 2)) bn = 64;
+
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, (uint64_t)valid_k, (uint64_t)M, (uint64_t)lda, BK, BM)) return IRON_ERR_LAUNCH;
+  bool okb;
+  if (b_col_maj) okb = make_map(&mb, B, (uint64_t)valid_k, (uint64_t)N, (uint64_t)ldb, BK, bn);
+  else okb = make_map(&mb, B, (uint64_t)N, (uint64_t)valid_k, (uint64_t)ldb, 64, BK);
+  if (!okb) return IRON_ERR_LAUNCH;
+
+  GemmParams p = {};
+  p.C = C; p.residual = (const __nv_bfloat16*)residual;
+  p.M = M; p.N = N; p.K = valid_k; p.ldc = ldc;
+  p.valid = valid_rows; p.d_valid = d_valid_rows;
+  p.epilogue = epilogue; p.out_f32 = out_f32; p.c_transposed = c_col_maj; p.b_n_major = !b_col_maj;
+  p.status = d_status;
+  const int max_rows = d_valid_rows ? M : valid_rows;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256>(ma, mb, p, max_rows, s);
+  if (bn == 128) return launch_gemm<128>(ma, mb, p, max_rows, s);
+  return launch_gemm<64>(ma, mb, p, max_rows, s);
+}

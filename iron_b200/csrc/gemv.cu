@@ -12,6 +12,8 @@
 //
 // The optional prologue recomputes RMSNorm(x) per CTA (x is a few KB and L2-resident),
 // with the reference's two bf16 roundings (norm, then weight).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace iron {
@@ -39,7 +41,7 @@ struct GemvParams {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 2;         // 256-bit loads per row per work item (4 for 128-bit loads)
 
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc) {
   acc = fmaf(bf16_lo(a.x), bf16_lo(b.x), acc);
@@ -53,9 +55,87 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc)
   return acc;
 }
 
+// One work item of a warp: kItem 16-byte chunks per lane of each of the pair's two rows
+// (2 KB per row per warp), held in registers between issue and use.
+constexpr int kItem = 4;
+struct Item {
+  uint4 a[kItem], b[kItem];
+};
+
 // WIDE: K % 16 == 0 and 32-byte aligned rows, so the weights move as 256-bit loads.
+// Lane `lane` owns chunks (c0 + lane*2 + {0,1}) and (c0 + 64 + lane*2 + {0,1}) when WIDE,
+// else chunks c0 + lane + 32*u.
+template <bool WIDE>
+__device__ __forceinline__ void issue(Item& it, const uint4* qa, const uint4* qb, int c0, int lane,
+                                      int c_hi, bool live) {
+#pragma unroll
+  for (int u = 0; u < kItem; ++u) { it.a[u] = make_uint4(0, 0, 0, 0); it.b[u] = make_uint4(0, 0, 0, 0); }
+  if (!live) return;
+  if (WIDE) {
+#pragma unroll
+    for (int u = 0; u < kItem / 2; ++u) {
+      const int c = c0 + 64 * u + 2 * lane;
+      if (c < c_hi) {
+        ld_stream256(qa + c, it.a[2 * u], it.a[2 * u + 1]);
+        ld_stream256(qb + c, it.b[2 * u], it.b[2 * u + 1]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < kItem; ++u) {
+      const int c = c0 + 32 * u + lane;
+      if (c < c_hi) {
+        it.a[u] = ld_stream(qa + c);
+        it.b[u] = ld_stream(qb + c);
+      }
+    }
+  }
+}
+
+template <bool WIDE>
+__device__ __forceinline__ void consume(const Item& it, const uint4* xs, int c0, int lane, int c_hi,
+                                        float& acc0, float& acc1) {
+#pragma unroll
+  for (int u = 0; u < kItem; ++u) {
+    const int c = WIDE ? (c0 + 64 * (u >> 1) + 2 * lane + (u & 1)) : (c0 + 32 * u + lane);
+    if (c < c_hi) {
+      const uint4 xv = xs[c];
+      acc0 = dot8(it.a[u], xv, acc0);
+      acc1 = dot8(it.b[u], xv, acc1);
+    }
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ void pair_rows(const GemvParams& p, const __nv_bfloat16* A, int pair, int half,
+                                          int& ra, int& rb, const uint4*& qa, const uint4*& qb) {
+  const int K = p.K;
+  const __nv_bfloat16 *pa, *pb;
+  if (MODE == GEMV_PLAIN) {
+    ra = 2 * pair; rb = ra + 1;
+    pa = A + (size_t)ra * K;
+    pb = (rb < p.rows) ? pa + K : pa;
+  } else if (MODE == GEMV_SWIGLU) {
+    ra = rb = pair;
+    pa = A + (size_t)ra * K;
+    pb = p.A2 + (size_t)ra * K;
+  } else {
+    const int head = pair / half, i = pair - head * half;
+    ra = head * p.D + i; rb = ra + half;
+    pa = A + (size_t)ra * K;
+    pb = A + (size_t)rb * K;
+  }
+  qa = reinterpret_cast<const uint4*>(pa);
+  qb = reinterpret_cast<const uint4*>(pb);
+}
+
+// The grid is persistent (at most two CTAs per SM).  A warp's first weight loads are
+// issued before anything else -- they do not depend on the previous kernel -- so with
+// programmatic dependent launch the weight stream of this kernel overlaps the tail of
+// the one before it; the activation vector is staged (and normalised) while those
+// loads are in flight, and every later item is prefetched one step ahead of its use.
 template <int MODE, bool WIDE>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ uint4 smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K, nch = K >> 3;
@@ -63,11 +143,35 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
   float* red = reinterpret_cast<float*>(smem + nch);  // 32 floats for block_sum
   float* part = red + 32;                             // kWarps x 2 partial sums
 
+  pdl_launch();
+
   const int batch = blockIdx.y;
   const size_t mat = (size_t)(batch / p.repeat) * (size_t)p.M * (size_t)K;
   const __nv_bfloat16* A = p.A + mat;
 
-  // The activation vector is the previous kernel's output: wait for it, nothing else.
+  const int KS = p.ksplit;
+  const int groups = kWarps / KS;       // row pairs in flight per CTA
+  const int g = warp / KS, ks = warp % KS;
+  constexpr int kStep = 32 * kItem;     // chunks one item covers
+  const int per = ((nch + KS - 1) / KS + 1) & ~1;  // even, so 256-bit loads stay aligned
+  const int ch_lo = min(nch, ks * per);
+  const int ch_hi = min(nch, ch_lo + per);
+
+  int npairs, half = 0;
+  if (MODE == GEMV_PLAIN) npairs = (p.rows + 1) >> 1;
+  else if (MODE == GEMV_SWIGLU) npairs = p.rows;
+  else { half = p.D >> 1; npairs = p.rows >> 1; }
+  const int stride = gridDim.x * groups;
+
+  int base = blockIdx.x * groups;
+  int ra = 0, rb = 0;
+  const uint4 *qa = nullptr, *qb = nullptr;
+  bool live = base + g < npairs;
+  if (live) pair_rows<MODE>(p, A, base + g, half, ra, rb, qa, qb);
+  Item cur;
+  issue<WIDE>(cur, qa, qb, ch_lo, lane, ch_hi, live && ch_lo < ch_hi);
+
+  // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
 
   // ---- stage x (optionally RMS-normalised) into shared memory ----
@@ -104,89 +208,20 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
     }
     __syncthreads();
   }
-  pdl_launch();
 
-  const int KS = p.ksplit;
-  const int groups = kWarps / KS;       // row pairs in flight per CTA
-  const int g = warp / KS, ks = warp % KS;
-  const int nvec = WIDE ? (nch >> 1) : nch;  // loads per row
-  const int per = (nvec + KS - 1) / KS;
-  const int ch_lo = ks * per;
-  const int ch_hi = min(nvec, ch_lo + per);
-
-  int npairs, half = 0;
-  if (MODE == GEMV_PLAIN) npairs = (p.rows + 1) >> 1;
-  else if (MODE == GEMV_SWIGLU) npairs = p.rows;
-  else { half = p.D >> 1; npairs = p.rows >> 1; }
-
-  for (int base = blockIdx.x * groups; base < npairs; base += gridDim.x * groups) {
-    const int pair = base + g;
-    const bool live = pair < npairs;
-    int ra = 0, rb = 0;
-    const __nv_bfloat16 *pa = A, *pb = A;
-    if (live) {
-      if (MODE == GEMV_PLAIN) {
-        ra = 2 * pair; rb = ra + 1;
-        pa = A + (size_t)ra * K;
-        pb = (rb < p.rows) ? pa + K : pa;
-      } else if (MODE == GEMV_SWIGLU) {
-        ra = rb = pair;
-        pa = A + (size_t)ra * K;
-        pb = p.A2 + (size_t)ra * K;
-      } else {
-        const int head = pair / half, i = pair - head * half;
-        ra = head * p.D + i; rb = ra + half;
-        pa = A + (size_t)ra * K;
-        pb = A + (size_t)rb * K;
-      }
-    }
+  for (; base < npairs; base += stride) {
     float acc0 = 0.f, acc1 = 0.f;
-    if (live) {
-      const uint4* qa = reinterpret_cast<const uint4*>(pa);
-      const uint4* qb = reinterpret_cast<const uint4*>(pb);
-      for (int c = ch_lo + lane; c < ch_hi; c += 32 * kUnroll) {
-        if (WIDE) {
-          uint4 a0[kUnroll][2], a1[kUnroll][2];
-#pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int cc = c + 32 * u;
-            if (cc < ch_hi) {
-              ld_stream256(qa + 2 * cc, a0[u][0], a0[u][1]);
-              ld_stream256(qb + 2 * cc, a1[u][0], a1[u][1]);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int cc = c + 32 * u;
-            if (cc < ch_hi) {
-              const uint4 x0 = xs[2 * cc], x1 = xs[2 * cc + 1];
-              acc0 = dot8(a0[u][0], x0, acc0);
-              acc1 = dot8(a1[u][0], x0, acc1);
-              acc0 = dot8(a0[u][1], x1, acc0);
-              acc1 = dot8(a1[u][1], x1, acc1);
-            }
-          }
-        } else {
-          uint4 a0[kUnroll], a1[kUnroll];
-#pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int cc = c + 32 * u;
-            if (cc < ch_hi) {
-              a0[u] = ld_stream(qa + cc);
-              a1[u] = ld_stream(qb + cc);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int cc = c + 32 * u;
-            if (cc < ch_hi) {
-              const uint4 xv = xs[cc];
-              acc0 = dot8(a0[u], xv, acc0);
-              acc1 = dot8(a1[u], xv, acc1);
-            }
-          }
-        }
-      }
+    // the next pair of this warp (its first item is prefetched during this pair's last)
+    const bool live_n = base + stride + g < npairs;
+    int ra_n = 0, rb_n = 0;
+    const uint4 *qa_n = nullptr, *qb_n = nullptr;
+    if (live_n) pair_rows<MODE>(p, A, base + stride + g, half, ra_n, rb_n, qa_n, qb_n);
+    for (int c0 = ch_lo; c0 < ch_hi; c0 += kStep) {
+      Item nxt;
+      if (c0 + kStep < ch_hi) issue<WIDE>(nxt, qa, qb, c0 + kStep, lane, ch_hi, live);
+      else issue<WIDE>(nxt, qa_n, qb_n, ch_lo, lane, ch_hi, live_n);
+      consume<WIDE>(cur, xs, c0, lane, ch_hi, acc0, acc1);
+      cur = nxt;
     }
     acc0 = warp_sum(acc0);
     acc1 = warp_sum(acc1);
@@ -233,6 +268,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
         dst[i + half] = __float2bfloat16_rn(x2);
       }
     }
+    live = live_n; ra = ra_n; rb = rb_n; qa = qa_n; qb = qb_n;
   }
 }
 
@@ -247,19 +283,33 @@ static int launch_gemv_w(GemvParams& p, int npairs, int batches, cudaStream_t st
     configured = true;
   }
   const int nch = p.K >> 3;
-  const int nvec = WIDE ? nch >> 1 : nch;
-  // Split K across warps until the grid covers the machine twice over, as long as each
-  // warp keeps at least half an unrolled pass (64 loads) of its own.
-  int ks = 1;
-  while (ks < kWarps && (npairs * ks + kWarps - 1) / kWarps < 2 * kSMs &&
-         nvec / (ks * 2) >= 16 * kUnroll)
-    ks *= 2;
-  p.ksplit = ks;
-  const int groups = kWarps / ks;
-  int ctas = (npairs + groups - 1) / groups;
+  constexpr int kStep = 32 * kItem;
+  static const int per_sm = [] {
+    const char* e = getenv("IRON_GEMV_CTAS_PER_SM");
+    const int v = e ? atoi(e) : 2;
+    return v >= 1 && v <= 2 ? v : 2;
+  }();
+  const int slots = per_sm * kSMs;  // resident CTAs
+  // Split K across the warps of a CTA (each keeps at least one full item) while that
+  // evens out the last wave: pick the split with the least idle warp-time.
+  int best_ks = 1;
+  double best_eff = -1.0;
+  for (int ks = 1; ks <= kWarps; ks *= 2) {
+    if (ks > 1 && nch / ks < kStep) break;
+    const long long cta_iters = ((long long)npairs * ks + kWarps - 1) / kWarps;
+    const long long waves = (cta_iters + slots - 1) / slots;
+    const double eff = (double)cta_iters / (double)(waves * slots);
+    const double fill = cta_iters >= slots ? 1.0 : (double)cta_iters / slots;
+    const double score = cta_iters >= slots ? eff : fill * 0.9;
+    if (score > best_eff + 0.02) { best_eff = score; best_ks = ks; }
+  }
+  p.ksplit = best_ks;
+  const int groups = kWarps / best_ks;
+  const long long cta_iters = (npairs + groups - 1) / groups;
+  const long long waves = (cta_iters + slots - 1) / slots;
+  int ctas = (int)((cta_iters + waves - 1) / waves);  // equal work per CTA
+  if (batches > 1) ctas = (int)(cta_iters < slots ? cta_iters : slots);
   ctas = ctas < 1 ? 1 : ctas;
-  const int cap = kSMs * 8;
-  if (ctas > cap) ctas = cap;
   const size_t smem = (size_t)nch * 16 + (32 + 2 * kWarps) * sizeof(float);
   if (smem > (size_t)kMaxSmem) return IRON_ERR_SHAPE;
 
@@ -269,10 +319,7 @@ static int launch_gemv_w(GemvParams& p, int npairs, int batches, cudaStream_t st
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  fill_pdl_attr(cfg, attr);
   if (cudaLaunchKernelEx(&cfg, gemv_kernel<MODE, WIDE>, p) != cudaSuccess) return IRON_ERR_LAUNCH;
   return IRON_OK;
 }

@@ -102,6 +102,56 @@ __global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* __restri
   }
 }
 
+// ---------------------------------------------------------------- prompt-chunk RoPE + KV write
+// qkv is (rows, (H + 2G) * D) with row pitch `pitch`: q heads, then k heads, then v heads.
+// q is rotated in place, k is rotated into k_cache[start + row], v copied into
+// v_cache[start + row].  One thread per 8 rotation pairs (or 16 copied elements).
+__global__ void __launch_bounds__(256) rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long pitch,
+                                                      const __nv_bfloat16* __restrict__ angles,
+                                                      __nv_bfloat16* __restrict__ k_cache,
+                                                      __nv_bfloat16* __restrict__ v_cache, int rows,
+                                                      const int* d_rows, int H, int G, int D, int start,
+                                                      const int* d_start, int angle_start,
+                                                      const int* d_angle_start) {
+  pdl_wait();
+  pdl_launch();
+  if (d_rows) rows = min(*d_rows, rows);
+  if (d_start) start = *d_start;
+  if (d_angle_start) angle_start = *d_angle_start;
+  const int half = D >> 1, per_head = half >> 3, heads = H + 2 * G;
+  const long long total = (long long)rows * heads * per_head;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int pg = (int)(idx % per_head);
+    const int hh = (int)((idx / per_head) % heads);
+    const int r = (int)(idx / ((long long)per_head * heads));
+    const int i0 = pg * 8;
+    __nv_bfloat16* src = qkv + (long long)r * pitch + (long long)hh * D;
+    float a[8], b[8];
+    unpack8(ld_cached(src + i0), a);
+    unpack8(ld_cached(src + half + i0), b);
+    if (hh < H + G) {
+      const __nv_bfloat16* ar = angles + (size_t)(angle_start + r) * D;
+      float cs[16];
+      unpack8(ld_cached(ar + 2 * i0), cs);
+      unpack8(ld_cached(ar + 2 * i0 + 8), cs + 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = cs[2 * j], s = cs[2 * j + 1];
+        const float ya = __fsub_rn(__fmul_rn(a[j], c), __fmul_rn(b[j], s));
+        const float yb = __fadd_rn(__fmul_rn(b[j], c), __fmul_rn(a[j], s));
+        a[j] = ya; b[j] = yb;
+      }
+    }
+    __nv_bfloat16* dst;
+    if (hh < H) dst = src;
+    else if (hh < H + G) dst = k_cache + ((size_t)(start + r) * G + (hh - H)) * D;
+    else dst = v_cache + ((size_t)(start + r) * G + (hh - H - G)) * D;
+    *reinterpret_cast<uint4*>(dst + i0) = pack8(a);
+    *reinterpret_cast<uint4*>(dst + half + i0) = pack8(b);
+  }
+}
+
 // ---------------------------------------------------------------- element-wise
 __device__ __forceinline__ float ew_apply(int op, float a, float b, float s) {
   switch (op) {
@@ -264,10 +314,7 @@ static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  fill_pdl_attr(cfg, attr);
   return cudaLaunchKernelEx(&cfg, kernel, args...) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
@@ -282,6 +329,9 @@ static int grid_for(long long work_items, int threads) {
 
 using namespace iron;
 
+static int g_pdl_enabled = 1;
+namespace iron { int pdl_attr_count() { return g_pdl_enabled ? 1 : 0; } }
+extern "C" void iron_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
 extern "C" int iron_version(void) { return 100; }
 extern "C" const char* iron_arch(void) { return "sm_100a"; }
 
@@ -378,4 +428,20 @@ extern "C" int iron_argmax_bf16(const void* logits, int n, int* token_out,
   return launch_pdl(argmax_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
                     (const __nv_bfloat16*)logits, n, token_out, d_out_index, carry_token,
                     carry_position, (unsigned long long*)workspace);
+}
+
+extern "C" int iron_rope_kv_write_bf16(void* qkv, long long pitch, const void* angles, void* k_cache,
+                                       void* v_cache, int rows, const int* d_rows, int H, int G, int D,
+                                       int start, const int* d_start, int angle_start,
+                                       const int* d_angle_start, iron_stream_t stream) {
+  if (rows < 0 || H <= 0 || G <= 0 || D < 16 || (D & 15)) return IRON_ERR_SHAPE;
+  if (pitch < (long long)(H + 2 * G) * D || (pitch & 7)) return IRON_ERR_SHAPE;
+  if (start < 0 || angle_start < 0) return IRON_ERR_SHAPE;
+  if (!aligned16(qkv) || !aligned16(angles) || !aligned16(k_cache) || !aligned16(v_cache)) return IRON_ERR_ALIGN;
+  if (rows == 0) return IRON_OK;
+  const long long items = (long long)rows * (H + 2 * G) * (D / 16);
+  return launch_pdl(rope_kv_kernel, dim3(grid_for(items, 256)), dim3(256), (cudaStream_t)stream,
+                    (__nv_bfloat16*)qkv, pitch, (const __nv_bfloat16*)angles, (__nv_bfloat16*)k_cache,
+                    (__nv_bfloat16*)v_cache, rows, d_rows, H, G, D, start, d_start, angle_start,
+                    d_angle_start);
 }

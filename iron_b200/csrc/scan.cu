@@ -1,0 +1,372 @@
+// Mamba2: the selective-scan recurrence and the short causal depth-wise convolution.
+//
+// Selective scan.  The recurrence is sequential in time and independent over
+// (batch, head, head_dim row); float32 throughout, y rounded once, as the reference's.
+// A CTA of 128 threads owns one head and up to 64 rows of its (head_dim x state_size)
+// state: thread (p, half) keeps half of row p's state in registers (packed f32x2
+// arithmetic), so a time step costs two packed FMAs and one packed multiply per state
+// pair and a single shuffle per row -- no cross-lane reduction tree.  The step's B, C,
+// x and dt are staged 16 time steps at a time through shared memory (converted to f32
+// once per CTA, the next block's global loads in flight while the current block
+// computes), and y leaves through a shared tile so stores are 128-byte rows.
+//
+// Causal conv.  y[t] = sum_k taps[k] * x[t - K + 1 + k] per channel, the K - 1 rows before
+// the call read from a history buffer, with the reference's operator chain roundings
+// (each product and each partial sum rounded to bf16), optional bias and SiLU fused.
+#include "common.cuh"
+
+namespace iron {
+
+constexpr int kScanThreads = 128;
+constexpr int kTB = 16;   // time steps staged per block
+constexpr int kPT = 64;   // head_dim rows per CTA
+
+struct ScanParams {
+  const __nv_bfloat16* xbc;   // (B, rows, width): x (H*P) | B (G*N) | C (G*N)
+  const __nv_bfloat16* dt;    // (B, rows, H)
+  const float* head;          // (H, 3): dt_bias, A, D
+  const float* state;         // (B, H, P, N) or null: zeros
+  __nv_bfloat16* y;           // (B, rows, H*P)
+  float* final_state;         // (B, H, P, N) or null
+  int rows, H, P, G, width;
+  int valid;
+  const int* d_valid;
+  long long xbc_batch, dt_batch, y_batch, state_batch;  // element strides
+};
+
+__device__ __forceinline__ float softplus_f32(float v) {
+  // logaddexp(0, v) = max(v, 0) + log1p(exp(-|v|))
+  return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v)));
+}
+
+template <int N>
+__global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const ScanParams p) {
+  constexpr int NH = N / 2;        // states per thread
+  constexpr int CB = N / 8;        // 16-byte chunks per B (or C) row
+  constexpr int kBC = (kTB * CB + kScanThreads - 1) / kScanThreads;  // chunks per thread per block
+  __shared__ __align__(16) float sB[2][kTB][N];
+  __shared__ __align__(16) float sC[2][kTB][N];
+  __shared__ __align__(16) float sX[2][kTB][kPT];
+  __shared__ float2 sDt[2][kTB];   // (step, exp(step * A))
+  __shared__ __align__(16) __nv_bfloat16 sY[kTB][kPT];
+
+  const int tid = threadIdx.x, p_local = tid >> 1, half = tid & 1;
+  const int ptiles = (p.P + kPT - 1) / kPT;
+  const int h = blockIdx.x / ptiles, p0 = (blockIdx.x - h * ptiles) * kPT;
+  const int b = blockIdx.y;
+  const int grp = h / (p.H / p.G);
+  const int pcount = min(kPT, p.P - p0);
+  const bool row_live = p_local < pcount;
+  const int inner = p.H * p.P;
+
+  pdl_wait();
+  pdl_launch();
+  int valid = p.d_valid ? min(*p.d_valid, p.rows) : p.valid;
+  valid = max(valid, 0);
+
+  const float dt_bias = p.head[h * 3], A = p.head[h * 3 + 1], Dh = p.head[h * 3 + 2];
+  const __nv_bfloat16* xbc = p.xbc + (size_t)b * p.xbc_batch;
+  const __nv_bfloat16* dtp = p.dt + (size_t)b * p.dt_batch;
+  __nv_bfloat16* yb = p.y + (size_t)b * p.y_batch;
+
+  float2 s[NH / 2];
+  if (row_live && p.state) {
+    const float* src = p.state + (size_t)b * p.state_batch + ((size_t)h * p.P + p0 + p_local) * N + half * NH;
+#pragma unroll
+    for (int i = 0; i < NH / 2; ++i) s[i] = *reinterpret_cast<const float2*>(src + 2 * i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < NH / 2; ++i) s[i] = make_float2(0.f, 0.f);
+  }
+
+  // registers holding the next block's raw rows while the current block computes
+  uint4 rB[kBC], rC[kBC], rX;
+  float rDt = 0.f;
+  auto fetch = [&](int t0) {
+#pragma unroll
+    for (int i = 0; i < kBC; ++i) {
+      const int idx = tid + i * kScanThreads;
+      const int tt = idx / CB, c = idx - tt * CB;
+      rB[i] = make_uint4(0, 0, 0, 0); rC[i] = make_uint4(0, 0, 0, 0);
+      if (idx < kTB * CB && t0 + tt < valid) {
+        const __nv_bfloat16* row = xbc + (size_t)(t0 + tt) * p.width + inner;
+        rB[i] = ld_cached(row + (size_t)grp * N + c * 8);
+        rC[i] = ld_cached(row + (size_t)(p.G + grp) * N + c * 8);
+      }
+    }
+    {
+      const int tt = tid >> 3, c = tid & 7;  // 16 steps x 8 chunks of 8 rows
+      rX = make_uint4(0, 0, 0, 0);
+      if (t0 + tt < valid && c * 8 < pcount) {
+        const __nv_bfloat16* src = xbc + (size_t)(t0 + tt) * p.width + (size_t)h * p.P + p0 + c * 8;
+        if (c * 8 + 8 <= pcount && (((p.width | (h * p.P + p0)) & 7) == 0)) {
+          rX = ld_cached(src);
+        } else {
+          uint16_t e[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int j = 0; j < 8 && c * 8 + j < pcount; ++j) e[j] = __bfloat16_as_ushort(src[j]);
+          rX = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+        }
+      }
+    }
+    if (tid < kTB) rDt = (t0 + tid < valid) ? __bfloat162float(dtp[(size_t)(t0 + tid) * p.H + h]) : 0.f;
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < kBC; ++i) {
+      const int idx = tid + i * kScanThreads;
+      if (idx < kTB * CB) {
+        const int tt = idx / CB, c = idx - tt * CB;
+        float f[8];
+        unpack8(rB[i], f);
+        *reinterpret_cast<float4*>(&sB[buf][tt][c * 8]) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(&sB[buf][tt][c * 8 + 4]) = make_float4(f[4], f[5], f[6], f[7]);
+        unpack8(rC[i], f);
+        *reinterpret_cast<float4*>(&sC[buf][tt][c * 8]) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(&sC[buf][tt][c * 8 + 4]) = make_float4(f[4], f[5], f[6], f[7]);
+      }
+    }
+    {
+      const int tt = tid >> 3, c = tid & 7;
+      float f[8];
+      unpack8(rX, f);
+      *reinterpret_cast<float4*>(&sX[buf][tt][c * 8]) = make_float4(f[0], f[1], f[2], f[3]);
+      *reinterpret_cast<float4*>(&sX[buf][tt][c * 8 + 4]) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+    if (tid < kTB) {
+      const float step = softplus_f32(rDt + dt_bias);
+      sDt[buf][tid] = make_float2(step, expf(step * A));
+    }
+  };
+
+  fetch(0);
+  stage(0);
+  __syncthreads();
+
+  for (int t0 = 0, blk = 0; t0 < p.rows; t0 += kTB, ++blk) {
+    const int buf = blk & 1;
+    const bool more = t0 + kTB < valid;
+    if (more) fetch(t0 + kTB);
+    const int steps = min(kTB, valid - t0);  // <= 0 past the bound: rows of zeros
+    for (int tt = 0; tt < kTB; ++tt) {
+      float yv = 0.f;
+      if (tt < steps) {
+        const float2 sd = sDt[buf][tt];
+        const float xv = sX[buf][tt][p_local];
+        const float xdt = sd.x * xv;
+        const float2 dA2 = make_float2(sd.y, sd.y), xdt2 = make_float2(xdt, xdt);
+        float2 acc = make_float2(0.f, 0.f);
+        const float4* Bp = reinterpret_cast<const float4*>(&sB[buf][tt][half * NH]);
+        const float4* Cp = reinterpret_cast<const float4*>(&sC[buf][tt][half * NH]);
+#pragma unroll
+        for (int i = 0; i < NH / 4; ++i) {
+          const float4 bv = Bp[i], cv = Cp[i];
+          s[2 * i] = __ffma2_rn(dA2, s[2 * i], __fmul2_rn(xdt2, make_float2(bv.x, bv.y)));
+          s[2 * i + 1] = __ffma2_rn(dA2, s[2 * i + 1], __fmul2_rn(xdt2, make_float2(bv.z, bv.w)));
+          acc = __ffma2_rn(s[2 * i], make_float2(cv.x, cv.y), acc);
+          acc = __ffma2_rn(s[2 * i + 1], make_float2(cv.z, cv.w), acc);
+        }
+        yv = acc.x + acc.y;
+        yv += __shfl_xor_sync(0xffffffffu, yv, 1);
+        yv = fmaf(Dh, xv, yv);
+      } else {
+        (void)__shfl_xor_sync(0xffffffffu, yv, 1);
+      }
+      if (half == 0) sY[tt][p_local] = __float2bfloat16_rn(yv);
+    }
+    __syncthreads();
+    // y tile out: 16 rows x up to 64 columns
+    {
+      const int tt = tid >> 3, c = tid & 7;
+      if (t0 + tt < p.rows && c * 8 < pcount) {
+        __nv_bfloat16* dst = yb + (size_t)(t0 + tt) * inner + (size_t)h * p.P + p0 + c * 8;
+        if (c * 8 + 8 <= pcount && ((inner | (h * p.P + p0)) & 7) == 0) {
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sY[tt][c * 8]);
+        } else {
+          for (int j = 0; j < 8 && c * 8 + j < pcount; ++j) dst[j] = sY[tt][c * 8 + j];
+        }
+      }
+    }
+    if (more) stage(buf ^ 1);
+    __syncthreads();
+  }
+
+  if (row_live && p.final_state) {
+    float* dst = p.final_state + (size_t)b * p.state_batch + ((size_t)h * p.P + p0 + p_local) * N + half * NH;
+#pragma unroll
+    for (int i = 0; i < NH / 2; ++i) *reinterpret_cast<float2*>(dst + 2 * i) = s[i];
+  }
+}
+
+// ---------------------------------------------------------------- causal conv
+struct ConvParams {
+  const __nv_bfloat16* x;        // (B, rows, C)
+  const __nv_bfloat16* taps;     // (K, C)
+  const __nv_bfloat16* bias;     // (C) or null
+  const __nv_bfloat16* history;  // (B, K-1, C) or null: zeros
+  __nv_bfloat16* new_history;    // (B, K-1, C) or null
+  __nv_bfloat16* y;              // (B, rows, C)
+  int rows, C, K;
+  int valid;
+  const int* d_valid;
+  int decode_order;              // sum the newest tap first (the one-row form's order)
+  int silu;
+  long long x_batch, y_batch, hist_batch;
+};
+
+// One thread per 8 channels, marching down the rows with the last K-1 inputs in registers.
+template <int K>
+__global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
+  pdl_wait();
+  pdl_launch();
+  int valid = p.d_valid ? min(*p.d_valid, p.rows) : p.valid;
+  valid = max(valid, 0);
+  const int cg8 = p.C >> 3;
+  const int rows_per = (p.rows + gridDim.y - 1) / gridDim.y;
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 >= cg8) return;
+  const int b = blockIdx.z;
+  const int r_lo = blockIdx.y * rows_per, r_hi = min(p.rows, r_lo + rows_per);
+  const __nv_bfloat16* x = p.x + (size_t)b * p.x_batch + c8 * 8;
+  const __nv_bfloat16* hist = p.history ? p.history + (size_t)b * p.hist_batch + c8 * 8 : nullptr;
+  __nv_bfloat16* y = p.y + (size_t)b * p.y_batch + c8 * 8;
+
+  float w[K][8], win[K][8], bias[8];
+#pragma unroll
+  for (int k = 0; k < K; ++k) unpack8(ld_cached(p.taps + (size_t)k * p.C + c8 * 8), w[k]);
+  if (p.bias) unpack8(ld_cached(p.bias + c8 * 8), bias);
+  // row index r of the concatenation history ++ x is (r - (K-1)) of x
+  auto input_row = [&](int r, float* f) {
+    if (r >= 0) {
+      if (r < valid) unpack8(ld_cached(x + (size_t)r * p.C), f);
+      else { for (int j = 0; j < 8; ++j) f[j] = 0.f; }
+    } else if (hist) {
+      unpack8(ld_cached(hist + (size_t)(r + K - 1) * p.C), f);
+    } else {
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) input_row(r_lo - (K - 1) + k, win[k]);
+  for (int r = r_lo; r < r_hi; ++r) {
+    input_row(r, win[K - 1]);
+    float out[8];
+    if (r < valid) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float acc;
+        if (p.decode_order) {
+          acc = round_bf16(__fmul_rn(win[K - 1][j], w[K - 1][j]));
+#pragma unroll
+          for (int k = 0; k < K - 1; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
+        } else {
+          acc = round_bf16(__fmul_rn(win[0][j], w[0][j]));
+#pragma unroll
+          for (int k = 1; k < K; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
+        }
+        if (p.bias) acc = round_bf16(__fadd_rn(acc, bias[j]));
+        if (p.silu) acc = silu_f32(acc);
+        out[j] = acc;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out[j] = 0.f;
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)r * p.C) = pack8(out);
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+  }
+  // the K-1 rows ending the valid run become the next call's history
+  if (p.new_history && blockIdx.y == 0) {
+    __nv_bfloat16* nh = p.new_history + (size_t)b * p.hist_batch + c8 * 8;
+    uint4 keep[K - 1];
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) {
+      float f[8];
+      input_row(valid - (K - 1) + k, f);
+      keep[k] = pack8(f);
+    }
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) *reinterpret_cast<uint4*>(nh + (size_t)k * p.C) = keep[k];
+  }
+}
+
+template <typename... Args>
+static int launch_scan_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  return cudaLaunchKernelEx(&cfg, kernel, args...) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+}
+
+}  // namespace iron
+
+using namespace iron;
+
+extern "C" int iron_selective_scan_bf16(const void* xbc, const void* dt, const void* head, const void* state,
+                                        void* y, void* final_state, int batch, int rows, int heads,
+                                        int head_dim, int state_size, int groups, int valid_rows,
+                                        const int* d_valid_rows, iron_stream_t stream) {
+  if (batch <= 0 || rows <= 0 || heads <= 0 || groups <= 0 || heads % groups) return IRON_ERR_SHAPE;
+  if (head_dim <= 0 || (head_dim & 7)) return IRON_ERR_SHAPE;
+  if (state_size != 16 && state_size != 32 && state_size != 64 && state_size != 128) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > rows) return IRON_ERR_SHAPE;
+  if (!aligned16(xbc) || !aligned16(y) || !aligned16(head)) return IRON_ERR_ALIGN;
+  if ((state && !aligned16(state)) || (final_state && !aligned16(final_state))) return IRON_ERR_ALIGN;
+  ScanParams p = {};
+  p.xbc = (const __nv_bfloat16*)xbc; p.dt = (const __nv_bfloat16*)dt; p.head = (const float*)head;
+  p.state = (const float*)state; p.y = (__nv_bfloat16*)y; p.final_state = (float*)final_state;
+  p.rows = rows; p.H = heads; p.P = head_dim; p.G = groups;
+  p.width = heads * head_dim + 2 * groups * state_size;
+  if (p.width & 7) return IRON_ERR_SHAPE;
+  p.valid = valid_rows; p.d_valid = d_valid_rows;
+  p.xbc_batch = (long long)rows * p.width; p.dt_batch = (long long)rows * heads;
+  p.y_batch = (long long)rows * heads * head_dim;
+  p.state_batch = (long long)heads * head_dim * state_size;
+  const dim3 grid(heads * ((head_dim + kPT - 1) / kPT), batch), block(kScanThreads);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (state_size) {
+    case 16: return launch_scan_pdl(selective_scan_kernel<16>, grid, block, s, p);
+    case 32: return launch_scan_pdl(selective_scan_kernel<32>, grid, block, s, p);
+    case 64: return launch_scan_pdl(selective_scan_kernel<64>, grid, block, s, p);
+    default: return launch_scan_pdl(selective_scan_kernel<128>, grid, block, s, p);
+  }
+}
+
+extern "C" int iron_causal_conv1d_bf16(const void* x, const void* taps, const void* bias, const void* history,
+                                       void* new_history, void* y, int batch, int rows, int channels,
+                                       int kernel, int valid_rows, const int* d_valid_rows, int decode_order,
+                                       int silu, iron_stream_t stream) {
+  if (batch <= 0 || rows <= 0 || channels <= 0 || (channels & 7)) return IRON_ERR_SHAPE;
+  if (kernel < 2 || kernel > 4) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > rows) return IRON_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(taps) || !aligned16(y)) return IRON_ERR_ALIGN;
+  if ((bias && !aligned16(bias)) || (history && !aligned16(history)) || (new_history && !aligned16(new_history)))
+    return IRON_ERR_ALIGN;
+  ConvParams p = {};
+  p.x = (const __nv_bfloat16*)x; p.taps = (const __nv_bfloat16*)taps; p.bias = (const __nv_bfloat16*)bias;
+  p.history = (const __nv_bfloat16*)history; p.new_history = (__nv_bfloat16*)new_history;
+  p.y = (__nv_bfloat16*)y;
+  p.rows = rows; p.C = channels; p.K = kernel; p.valid = valid_rows; p.d_valid = d_valid_rows;
+  p.decode_order = decode_order; p.silu = silu;
+  p.x_batch = p.y_batch = (long long)rows * channels;
+  p.hist_batch = (long long)(kernel - 1) * channels;
+  // rows are cut into segments so a long prompt fills the machine; each segment re-reads
+  // the K-1 rows before it
+  const int cgroups = (channels / 8 + 127) / 128;
+  int segs = (2 * kSMs) / (cgroups * batch);
+  segs = segs < 1 ? 1 : segs;
+  const int max_segs = (rows + 63) / 64;
+  if (segs > max_segs) segs = max_segs;
+  const dim3 grid(cgroups, segs, batch), block(128);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (kernel) {
+    case 2: return launch_scan_pdl(causal_conv_kernel<2>, grid, block, s, p);
+    case 3: return launch_scan_pdl(causal_conv_kernel<3>, grid, block, s, p);
+    default: return launch_scan_pdl(causal_conv_kernel<4>, grid, block, s, p);
+  }
+}

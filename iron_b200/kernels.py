@@ -136,22 +136,19 @@ def argmax(logits, token_out, workspace, *, d_out_index=None, carry_token=None,
     return token_out
 
 
-def mha_decode_plan(batch, H, G, D, kv_len_hint, device, nsplit=None):
-    """Pick a split count and allocate (zeroed) the workspace it needs."""
-    lib = _lib.load()
-    if nsplit is None:
-        nsplit = lib.iron_mha_decode_splits(batch, G, kv_len_hint)
-    nbytes = lib.iron_mha_decode_workspace_bytes(batch, H, G, D, nsplit)
-    return nsplit, torch.zeros(nbytes, dtype=torch.uint8, device=device)
+def mha_decode_splits(batch, G, kv_len_hint) -> int:
+    """The cluster size (key splits) suggested for a context of ``kv_len_hint`` keys."""
+    return _lib.load().iron_mha_decode_splits(batch, G, kv_len_hint)
 
 
 def mha_decode(Q, K, V, out=None, *, kv_valid=None, d_kv_valid=None, per_batch=False,
-               kv_valid_add=0, window=None, scale=None, nsplit=1, workspace=None,
-               kv_interleaved=True):
+               kv_valid_add=0, window=None, scale=None, nsplit=None, kv_interleaved=True,
+               stable_prefix=False):
     """One query per (batch, head) over the first ``kv_valid`` keys.
 
     ``Q`` (B, H, D) or (H, D).  ``K``/``V``: (B?, S, G, D) when ``kv_interleaved`` else
-    (B?, G, S, D).
+    (B?, G, S, D).  ``stable_prefix``: only the newest cache row was written by the
+    kernel launched just before (a decode step).
     """
     _bf16(Q, K, V)
     q3 = Q if Q.dim() == 3 else Q.unsqueeze(0)
@@ -166,10 +163,131 @@ def mha_decode(Q, K, V, out=None, *, kv_valid=None, d_kv_valid=None, per_batch=F
     batch_stride = S * G * D if k4.shape[0] > 1 or B == 1 else 0
     if out is None:
         out = torch.empty_like(Q)
+    if nsplit is None:
+        nsplit = mha_decode_splits(B, G, S if kv_valid is None else int(kv_valid))
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
     call("iron_mha_decode_bf16", _ptr(Q), _ptr(K), _ptr(V), _ptr(out), B, H, G, D, S,
          batch_stride, seq_stride, head_stride, S if kv_valid is None else int(kv_valid),
          _ptr(d_kv_valid), 1 if per_batch else 0, int(kv_valid_add),
-         -1 if window is None else int(window), scale, int(nsplit), _ptr(workspace),
-         0 if workspace is None else workspace.numel(), _stream())
+         -1 if window is None else int(window), scale, int(nsplit), int(bool(stable_prefix)),
+         _stream())
+    return out
+
+
+EPILOGUES = dict(none=0, gelu=1, silu=2, sigmoid=3)
+
+
+def gemm(A, B, out=None, *, b_col_maj=False, c_col_maj=False, valid=None, d_valid=None,
+         valid_k=None, epilogue="none", residual=None, out_f32=False, status=None):
+    """``epilogue(bf16(A @ B))`` on the tensor cores (tcgen05, f32 accumulation in TMEM).
+
+    ``A`` (M, K); ``B`` (N, K) when ``b_col_maj`` (a checkpoint's (out, in) weight) else
+    (K, N); the result is (M, N), or (N, M) when ``c_col_maj``.
+    """
+    _bf16(A, B, residual)
+    M, Kd = A.shape
+    N = B.shape[0] if b_col_maj else B.shape[1]
+    if (B.shape[1] if b_col_maj else B.shape[0]) != Kd:
+        raise ValueError(f"gemm: A {tuple(A.shape)} and B {tuple(B.shape)} do not chain")
+    if out is None:
+        out = torch.empty((N, M) if c_col_maj else (M, N),
+                          dtype=torch.float32 if out_f32 else torch.bfloat16, device=A.device)
+    call("iron_gemm_bf16", _ptr(A), _ptr(B), _ptr(out), M, N, Kd, A.stride(0), B.stride(0),
+         out.stride(0), int(b_col_maj), int(c_col_maj), M if valid is None else int(valid),
+         _ptr(d_valid), Kd if valid_k is None else int(valid_k), EPILOGUES[epilogue],
+         _ptr(residual), int(out_f32), _ptr(status), _stream())
+    return out
+
+
+def mha_prefill(Q, K, V, out=None, *, q_tokens=None, d_q_tokens=None, kv_tokens=None,
+                d_kv_tokens=None, kv_tokens_add=0, causal=True, window=None, scale=None,
+                heads_interleaved=True, kv_interleaved=True, q_row_stride=None):
+    """Attention of ``Q``'s rows over ``K``/``V``, the queries the keys' last rows.
+
+    ``Q`` (rows, H, D) when ``heads_interleaved`` else (H, rows, D); ``K``/``V`` (rows, G, D)
+    when ``kv_interleaved`` else (G, rows, D); an optional leading batch axis on all.
+    """
+    _bf16(Q, K, V)
+    if q_row_stride is not None:
+        # Q is a strided view (rows, H, D) into a wider fused projection: rows are
+        # `q_row_stride` elements apart and O is dense (rows, H, D).
+        rows, H, D = Q.shape
+        kv_rows, G = K.shape[0], K.shape[1]
+        if out is None:
+            out = torch.empty((rows, H, D), dtype=torch.bfloat16, device=Q.device)
+        scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+        if not (K.is_contiguous() and V.is_contiguous() and out.is_contiguous()):
+            raise ValueError("K, V and the output must be contiguous")
+        call("iron_mha_prefill_bf16", Q.data_ptr(), _ptr(K), _ptr(V), _ptr(out), 1, H, G, D, rows,
+             kv_rows, 0, int(q_row_stride), D, 0, H * D, D, 0, G * D, D,
+             rows if q_tokens is None else int(q_tokens), _ptr(d_q_tokens),
+             kv_rows if kv_tokens is None else int(kv_tokens), _ptr(d_kv_tokens), int(kv_tokens_add),
+             int(bool(causal)), -1 if window is None else int(window), scale, _stream())
+        return out
+    q4 = Q if Q.dim() == 4 else Q.unsqueeze(0)
+    k4 = K if K.dim() == 4 else K.unsqueeze(0)
+    B = q4.shape[0]
+    if heads_interleaved:
+        rows, H, D = q4.shape[1:]
+        q_row, q_head = H * D, D
+    else:
+        H, rows, D = q4.shape[1:]
+        q_row, q_head = D, rows * D
+    if kv_interleaved:
+        kv_rows, G = k4.shape[1], k4.shape[2]
+        kv_row, kv_head = G * D, D
+    else:
+        G, kv_rows = k4.shape[1], k4.shape[2]
+        kv_row, kv_head = D, kv_rows * D
+    if out is None:
+        out = torch.empty_like(Q)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    call("iron_mha_prefill_bf16", _ptr(Q), _ptr(K), _ptr(V), _ptr(out), B, H, G, D, rows, kv_rows,
+         rows * H * D, q_row, q_head, rows * H * D, q_row, q_head, kv_rows * G * D, kv_row, kv_head,
+         rows if q_tokens is None else int(q_tokens), _ptr(d_q_tokens),
+         kv_rows if kv_tokens is None else int(kv_tokens), _ptr(d_kv_tokens), int(kv_tokens_add),
+         int(bool(causal)), -1 if window is None else int(window), scale, _stream())
+    return out
+
+
+def rope_kv_write(qkv, angles, k_cache, v_cache, *, rows, H, G, D, start=0, angle_start=None,
+                  d_rows=None, d_start=None, d_angle_start=None):
+    """Rotate q in place and write rotated k and v rows into the caches at ``start``."""
+    _bf16(qkv, angles, k_cache, v_cache)
+    call("iron_rope_kv_write_bf16", _ptr(qkv), qkv.stride(0), _ptr(angles), _ptr(k_cache),
+         _ptr(v_cache), int(rows), _ptr(d_rows), H, G, D, int(start), _ptr(d_start),
+         int(start if angle_start is None else angle_start), _ptr(d_angle_start), _stream())
+    return qkv
+
+
+def selective_scan(xbc, dt, head, state=None, *, heads, head_dim, state_size, groups=1, valid=None,
+                   d_valid=None, want_final=True):
+    """Mamba2's recurrence; returns ``(y bf16, final f32)``.  A leading batch axis is optional."""
+    _bf16(xbc, dt)
+    batched = xbc.dim() == 3
+    B = xbc.shape[0] if batched else 1
+    rows = xbc.shape[-2]
+    inner = heads * head_dim
+    y = torch.empty((*xbc.shape[:-1], inner), dtype=torch.bfloat16, device=xbc.device)
+    shape = (B, heads, head_dim, state_size) if batched else (heads, head_dim, state_size)
+    final = torch.empty(shape, dtype=torch.float32, device=xbc.device) if want_final else None
+    if head.dtype != torch.float32 or (state is not None and state.dtype != torch.float32):
+        raise TypeError("head and state are float32")
+    call("iron_selective_scan_bf16", _ptr(xbc), _ptr(dt), _ptr(head), _ptr(state), _ptr(y), _ptr(final),
+         B, rows, heads, head_dim, state_size, groups, rows if valid is None else int(valid),
+         _ptr(d_valid), _stream())
+    return y, final
+
+
+def causal_conv1d(x, taps, *, bias=None, history=None, new_history=None, out=None, valid=None,
+                  d_valid=None, decode_order=False, silu=False):
+    """Depth-wise causal conv over ``x`` (rows, C) or (B, rows, C) with ``taps`` (K, C)."""
+    _bf16(x, taps, bias, history, new_history)
+    B = x.shape[0] if x.dim() == 3 else 1
+    rows, C = x.shape[-2], x.shape[-1]
+    if out is None:
+        out = torch.empty_like(x)
+    call("iron_causal_conv1d_bf16", _ptr(x), _ptr(taps), _ptr(bias), _ptr(history), _ptr(new_history),
+         _ptr(out), B, rows, C, taps.shape[0], rows if valid is None else int(valid), _ptr(d_valid),
+         int(bool(decode_order)), int(bool(silu)), _stream())
     return out

@@ -88,6 +88,25 @@ class LlamaEngine:
             sizes[n] = int(np.prod(shape)) * 2
         # the decode step touches every transient in each layer: all live together
         spans = plan.place_version([list(trans)], sizes, residents)
+        # The prompt-chunk version: the same residents at the same offsets, its own
+        # transients (one batch entry at a time) placed by live range, so the attention
+        # buffers share bytes with the gated MLP's.
+        C = min(c.prefill_chunk, S)
+        self.chunk = C
+        QKV = (H + 2 * G) * D
+        ptrans = {"p.ids": (C, 2), "p.x": (C, E), "p.h": (C, E), "p.y": (C, E), "p.qkv": (C, QKV),
+                  "p.att": (C, H * D), "p.gate": (C, F), "p.up": (C, F)}
+        psizes = dict(sizes)
+        for n in trans:
+            psizes.pop(n)
+        for n, shape in ptrans.items():
+            psizes[n] = int(np.prod(shape)) * 2
+        psteps = [["p.ids", "p.x"], ["p.x", "p.h"], ["p.h", "p.qkv"], ["p.qkv", "p.att"],
+                  ["p.att", "p.x", "p.y"], ["p.y", "p.h"], ["p.h", "p.gate"], ["p.h", "p.up"],
+                  ["p.gate", "p.up"], ["p.gate", "p.y", "p.x"]]
+        # within a layer p.x and p.y stay live across the loop: mark them touched last too
+        psteps.append(["p.x", "p.y"])
+        spans.update(plan.place_version(psteps, psizes, {n: n for n in residents}))
         self.plan = plan
         self.arena = torch.empty(plan.size, dtype=torch.uint8, device=self.device)
         self.arena.zero_()
@@ -110,12 +129,22 @@ class LlamaEngine:
         self.x0, self.x1 = view("x0", (batch, E)), view("x1", (batch, E))
         self.q, self.att = view("q", (batch, H, D)), view("att", (batch, H, D))
         self.act, self.logits_buf = view("act", (batch, F)), view("logits", (batch, V))
+        self.p_ids = view("p.ids", (C,), torch.int32)
+        self.p_x, self.p_h, self.p_y = view("p.x", (C, E)), view("p.h", (C, E)), view("p.y", (C, E))
+        self.p_qkv, self.p_att = view("p.qkv", (C, QKV)), view("p.att", (C, H * D))
+        self.p_gate, self.p_up = view("p.gate", (C, F)), view("p.up", (C, F))
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
         self._load(weights)
-        self.nsplit, self.mha_ws = K.mha_decode_plan(batch, H, G, D, self.kv_len_hint, self.device)
+        self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
         self._graph: torch.cuda.CUDAGraph | None = None
-        self._h_values = torch.zeros(16, dtype=torch.int32).pin_memory()
+        # Per-call values are staged in a ring of pinned slots: a slot is rewritten only
+        # after the copy that read it has completed, so calls can be queued without a
+        # host synchronisation between them.
+        self._ring = [torch.zeros(16, dtype=torch.int32).pin_memory() for _ in range(32)]
+        self._ring_done: list[torch.cuda.Event | None] = [None] * len(self._ring)
+        self._ring_at = 0
         self._h_token = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     # ------------------------------------------------------------------ weights
@@ -168,13 +197,90 @@ class LlamaEngine:
                               H=H, G=G, D=D, d_position=d_pos, norm_weight=l["ln1"], eps=c.eps)
             K.mha_decode(self.q, l["k"], l["v"], self.att, d_kv_valid=d_pos, kv_valid_add=1,
                          window=c.window, scale=c.attention_scale, nsplit=self.nsplit,
-                         workspace=self.mha_ws)
+                         stable_prefix=True)
             K.gemv(l["wo"], self.att[0].view(-1), y, residual=x)
             K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
             K.gemv(l["wd"], self.act[0], x, residual=y)
         K.gemv(self.head, x, self.logits_buf[0], norm_weight=self.norm, eps=c.eps)
         K.argmax(self.logits_buf[0], self.drawn[0], self.argmax_ws, d_out_index=d_pos,
                  carry_token=d_token, carry_position=d_pos)
+
+    # ------------------------------------------------------------------ prompt chunk
+    @property
+    def launches_per_chunk(self) -> int:
+        """Kernels one prompt chunk launches: gather, eleven per layer, row pick, head, draw."""
+        return 1 + 11 * self.c.num_hidden_layers + 3
+
+    def prefill_chunk(self, tokens, start: int, seq: int = 0) -> None:
+        """Run one prompt chunk (at most ``prefill_chunk`` tokens) at positions ``start...``.
+
+        What the reference's prompt-chunk version records (iron/lm/causal.py:289-332):
+        embedding rows, then per layer RMSNorm, the fused q/k/v projection on the tensor
+        cores, RoPE and the bounded cache write, causal attention of the chunk's rows over
+        the cache, o_proj with the residual, RMSNorm, gate and up projections, SiLU and
+        product, down_proj with the residual; only the last row goes through the head.
+        Leaves (drawn token, start + rows) in the per-call values.
+        """
+        c = self.c
+        tokens = np.asarray(tokens).reshape(-1)
+        n = len(tokens)
+        if not 0 < n <= self.chunk:
+            raise ValueError(f"a prompt chunk holds 1 to {self.chunk} tokens, not {n}")
+        if start < 0 or start + n > c.max_seq_len:
+            raise IndexError(f"positions {start}..{start + n} leave the {c.max_seq_len}-row caches")
+        if tokens.min() < 0 or tokens.max() >= c.vocab_size:
+            raise IndexError("a token id is outside the vocabulary")
+        H, G, D, E, F = (c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.hidden_size,
+                         c.intermediate_size)
+        ids_host = torch.from_numpy(tokens.astype(np.int32)).pin_memory()
+        self.p_ids[:n].copy_(ids_host, non_blocking=True)
+        x, h, y = self.p_x[:n], self.p_h[:n], self.p_y[:n]
+        qkv, att, gate, up = self.p_qkv[:n], self.p_att[:n], self.p_gate[:n], self.p_up[:n]
+        K.copy_rows(self.embed, x, ids=self.p_ids, nrows=n, row_bytes=E * 2, src_rows=c.vocab_size)
+        for l in self.layers:
+            K.rms_norm(x, l["ln1"], h, eps=c.eps)
+            K.gemm(h, l["wqkv"], qkv, b_col_maj=True, status=self.status)
+            K.rope_kv_write(qkv, self.angles, l["k"][seq], l["v"][seq], rows=n, H=H, G=G, D=D, start=start)
+            K.mha_prefill(qkv.view(n, H + 2 * G, D)[:, :H], l["k"][seq], l["v"][seq], att.view(n, H, D),
+                          q_tokens=n, kv_tokens=start + n, window=c.window, scale=c.attention_scale,
+                          q_row_stride=qkv.stride(0))
+            K.gemm(att, l["wo"], y, b_col_maj=True, residual=x, status=self.status)
+            K.rms_norm(y, l["ln2"], h, eps=c.eps)
+            K.gemm(h, l["wg"], gate, b_col_maj=True, status=self.status)
+            K.gemm(h, l["wu"], up, b_col_maj=True, status=self.status)
+            K.elementwise("silu_mul", gate, up, gate)
+            K.gemm(gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
+        last = self.x0[seq]
+        K.copy_rows(x, last, nrows=1, row_bytes=E * 2, src_row0=n - 1)
+        K.gemv(self.head, last, self.logits_buf[seq], norm_weight=self.norm, eps=c.eps)
+        self.set_call(0, start + n - 1)
+        K.argmax(self.logits_buf[seq], self.drawn[seq], self.argmax_ws, d_out_index=self.values[1:2],
+                 carry_token=self.values[0:1], carry_position=self.values[1:2])
+
+    def prefill(self, tokens, start: int = 0, seq: int = 0) -> np.ndarray:
+        """Run a prompt of any length in chunks from ``start``; the logits after its last token."""
+        tokens = np.asarray(tokens).reshape(-1)
+        for s in range(0, len(tokens), self.chunk):
+            self.prefill_chunk(tokens[s : s + self.chunk], start + s, seq)
+        out = self.logits_buf[seq].float().cpu().numpy()
+        if int(self.status.item()) != 0:
+            raise RuntimeError("a GEMM pipeline wait gave up (IRON_ERR_TIMEOUT)")
+        return out
+
+    def complete(self, prompt, steps: int) -> list[int]:
+        """Greedy continuation: prompt in chunks, then ``steps - 1`` device-carried decode steps.
+
+        Returns the ``steps`` tokens drawn (the first comes from the prompt's last row).
+        """
+        prompt = np.asarray(prompt).reshape(-1)
+        n = len(prompt)
+        if n + steps > self.c.max_seq_len:
+            raise IndexError("the run would pass the end of the caches")
+        self.prefill(prompt)
+        self.capture()
+        for _ in range(steps - 1):
+            self._graph.replay()
+        return self.drawn[0, n - 1 : n - 1 + steps].cpu().tolist()
 
     def capture(self) -> None:
         """Capture the decode step as one CUDA graph (idempotent)."""
@@ -204,8 +310,16 @@ class LlamaEngine:
             raise IndexError(f"position {position} is outside the {self.c.max_seq_len}-row caches")
         if not 0 <= token < self.c.vocab_size:
             raise IndexError(f"token {token} is outside the {self.c.vocab_size}-row vocabulary")
-        self._h_values[0], self._h_values[1] = int(token), int(position)
-        self.values.copy_(self._h_values, non_blocking=True)
+        i = self._ring_at
+        self._ring_at = (i + 1) % len(self._ring)
+        if self._ring_done[i] is not None:
+            self._ring_done[i].synchronize()
+        slot = self._ring[i]
+        slot[0], slot[1] = int(token), int(position)
+        self.values.copy_(slot, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self._ring_done[i] = done
 
     def step(self) -> None:
         """Replay one decode step (stream-ordered; no host synchronisation)."""

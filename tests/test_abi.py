@@ -27,6 +27,7 @@ def test_bad_shapes_are_refused_before_any_launch():
     assert lib.iron_gemv_bf16(None, None, None, 16, 12, 1, 1, 16, 0, None, 1e-5, None, None) == -1
     assert lib.iron_rope_bf16(None, None, None, 4, 24, 4, 1, 0, None, 4, None, None) == -1
     assert lib.iron_mha_decode_bf16(None, None, None, None, 1, 6, 4, 64, 8, 0, 256, 64, 8, None, 0, 0,
-                                    -1, 0.125, 1, None, 0, None) == -1
-    assert lib.iron_mha_decode_workspace_bytes(1, 32, 8, 64, 8) > 0
-    assert lib.iron_mha_decode_splits(1, 8, 2048) >= 1
+                                    -1, 0.125, 1, 0, None) == -1
+    assert lib.iron_mha_decode_splits(1, 8, 2048) == 8
+    assert lib.iron_gemm_bf16(None, None, None, 0, 8, 8, 8, 8, 8, 1, 0, 0, None, 8, 0, None, 0, None,
+                              None) == -1

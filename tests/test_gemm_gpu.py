@@ -1,0 +1,118 @@
+"""The tcgen05 GEMM against the oracle's GEMM / ProjectionGEMM references (B200).
+
+Tolerance is the reference's own bound, ``2 * 2^-8 * |A| @ |B|`` elementwise
+(iron/operators/gemm.py:704-735, HIGHEST precision), plus the north-star bound.
+"""
+
+import numpy as np
+import pytest
+from ml_dtypes import bfloat16
+
+from iron_b200.verify import Tolerance, compare
+from oracle import ops
+from tests.util import assert_north_star, normal, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from iron_b200 import kernels
+
+    return kernels
+
+
+def check(got, A, B, want, b_col_maj=False, c_col_maj=False, what=""):
+    bound = ops.gemm_bound(A, B, b_col_maj=b_col_maj, c_col_maj=c_col_maj)
+    v = compare(got, want, Tolerance.bounded(lambda *a: bound), bound=bound)
+    assert v, f"{what}: {v.detail}"
+
+
+CASES = [
+    # M, N, K -- the reference's GEMM cases are multiples of 64; ragged ones added
+    (128, 64, 64), (128, 256, 64), (256, 256, 256), (2048, 2048, 2048), (2048, 512, 2048),
+    (384, 1536, 768), (200, 96, 136), (130, 520, 72), (64, 8192, 2048), (2048, 2048, 8192),
+]
+
+
+@pytest.mark.parametrize("M,N,Kd", CASES)
+@pytest.mark.parametrize("b_col_maj", [True, False])
+def test_gemm_matches_reference(K, M, N, Kd, b_col_maj):
+    rng = np.random.default_rng(1001)
+    A = normal(rng, (M, Kd), 1 / np.sqrt(Kd))
+    B = normal(rng, (N, Kd) if b_col_maj else (Kd, N), 1.0)
+    if not b_col_maj and N % 8:
+        pytest.skip("row pitch of B must be a multiple of 8")
+    want = ops.gemm(A, B, b_col_maj=b_col_maj)
+    got = to_numpy(K.gemm(to_torch(A), to_torch(B), b_col_maj=b_col_maj))
+    check(got, A, B, want, b_col_maj, what=f"{M}x{N}x{Kd} b_col_maj={b_col_maj}")
+
+
+def test_config1_gemm_2048_cubed_within_the_north_star_bound(K):
+    rng = np.random.default_rng(1001)
+    A = normal(rng, (2048, 2048), 1 / np.sqrt(2048))
+    B = normal(np.random.default_rng(1002), (2048, 2048), 1 / np.sqrt(2048))
+    for b_col_maj in (False, True):
+        want = ops.gemm(A, B, b_col_maj=b_col_maj)
+        got = to_numpy(K.gemm(to_torch(A), to_torch(B), b_col_maj=b_col_maj))
+        assert_north_star(got, want, f"b_col_maj={b_col_maj}")
+
+
+def test_bounded_rows_are_neither_computed_nor_written(K):
+    import torch
+
+    rng = np.random.default_rng(3)
+    A, B = normal(rng, (512, 256), 1 / 16), normal(rng, (384, 256))
+    out = torch.full((512, 384), 5.0, dtype=torch.bfloat16, device="cuda")
+    nv = torch.tensor([300], dtype=torch.int32, device="cuda")
+    K.gemm(to_torch(A), to_torch(B), out, b_col_maj=True, d_valid=nv)
+    got = to_numpy(out)
+    check(got[:300], A[:300], B, ops.gemm(A[:300], B, b_col_maj=True), True)
+    assert (got[300:].astype(np.float32) == 5.0).all()
+
+
+def test_bounded_k(K):
+    rng = np.random.default_rng(4)
+    A, B = normal(rng, (256, 512), 1 / 16), normal(rng, (512, 256))
+    got = to_numpy(K.gemm(to_torch(A), to_torch(B), valid_k=200))
+    check(got, A[:, :200], B[:200], ops.gemm(A, B, valid_k=200))
+
+
+@pytest.mark.parametrize("epilogue", ["silu", "sigmoid"])
+def test_projection_gemm_output_stage(K, epilogue):
+    rng = np.random.default_rng(5)
+    A, W = normal(rng, (256, 512), 1 / 16), normal(rng, (768, 512))
+    want = ops.projection_gemm(A, W, epilogue=epilogue)
+    got = to_numpy(K.gemm(to_torch(A), to_torch(W), b_col_maj=True, epilogue=epilogue))
+    # The reference states no tolerance for an activated GEMM (flm/gemm/op.py:1355-1356):
+    # a one-ulp difference of the rounded product is amplified by the activation's own
+    # two roundings.
+    v = compare(got, want, Tolerance.relative(0.02, atol=2e-2))
+    assert v, v.detail
+
+
+def test_residual_and_transposed_and_f32_outputs(K):
+    rng = np.random.default_rng(6)
+    A, W = normal(rng, (300, 256), 1 / 16), normal(rng, (520, 256))
+    res = normal(rng, (300, 520))
+    want = ops.add(res, ops.gemm(A, W, b_col_maj=True))
+    got = to_numpy(K.gemm(to_torch(A), to_torch(W), b_col_maj=True, residual=to_torch(res)))
+    v = compare(got, want, Tolerance.bf16_ulps(2, atol=2e-2))
+    assert v, v.detail
+    wantT = ops.gemm(A, W, b_col_maj=True, c_col_maj=True)
+    gotT = to_numpy(K.gemm(to_torch(A), to_torch(W), b_col_maj=True, c_col_maj=True))
+    check(gotT, A, W, wantT, True, True)
+    want32 = ops.gemm(A, W, b_col_maj=True, output_dtype=np.float32)
+    got32 = to_numpy(K.gemm(to_torch(A), to_torch(W), b_col_maj=True, out_f32=True))
+    assert np.allclose(got32, want32, rtol=1e-4, atol=1e-4)
+
+
+def test_no_pipeline_wait_gave_up(K):
+    import torch
+
+    rng = np.random.default_rng(7)
+    A, W = normal(rng, (1024, 1024), 1 / 32), normal(rng, (1024, 1024))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K.gemm(to_torch(A), to_torch(W), b_col_maj=True, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
