@@ -112,7 +112,7 @@ def compare(actual, expected, tolerance: Tolerance, bound=None) -> Verdict:
             ok |= diff < tol.atol
     else:
         floor = float(np.finfo(np.float32).tiny) if tol.atol is None else tol.atol
-        ok = (diff < (tol.rtol or 0.0) * (np.abs(a) + np.abs(e))) | (diff < floor)
+        ok = (diff < (tol.rtol or 0.0) * (np.abs(a) + np.abs(e))) | (diff < floor) | (diff == 0)
     if tol.range_frac is not None and tol.kind in ("relative", "ulps"):
         finite = np.isfinite(e)
         scale = float(np.max(np.abs(e[finite]))) if finite.any() else 0.0
