@@ -70,3 +70,23 @@ LLAMA_3B = LlamaConfig(
     max_seq_len=131072, eps=1e-5, precision=Precision.HIGH,
     rope_scaling=Llama3RopeScaling(32.0, 1.0, 4.0, 8192),
 )
+
+
+def _llama():
+    from ...lm.causal import CausalLM
+
+    class Llama(CausalLM):
+        """Llama 3 on ``config``'s shape and a checkpoint's ``weights``."""
+
+        config_class = LlamaConfig
+
+    return Llama
+
+
+def __getattr__(name):
+    # ``Llama`` needs the graph layer; keep the config importable without it
+    if name == "Llama":
+        cls = _llama()
+        globals()["Llama"] = cls
+        return cls
+    raise AttributeError(name)

@@ -160,7 +160,7 @@ class Declaration:
         return out
 
     def infer(self, inputs: Mapping[str, tuple[int, ...]], outputs: Mapping[str, tuple[int, ...]] | None = None,
-              **given) -> dict[str, Any]:
+              keep_derived: bool = False, **given) -> dict[str, Any]:
         """Solve construction fields from operand shapes (iron/common/graph/record.py:819-833).
 
         A dim that is a nullable param may be absent from a shape; the first assignment
@@ -188,7 +188,7 @@ class Declaration:
                 for d, extent in zip(kept, shape):
                     if isinstance(d, Field):
                         f = self.members[d.name]
-                        if f.derive is not None and f.kind == "param":
+                        if f.derive is not None and f.kind == "param" and not keep_derived:
                             continue  # checked after construction
                         if trial.setdefault(d.name, int(extent)) != int(extent):
                             ok = False
@@ -199,6 +199,8 @@ class Declaration:
                     break
             if not done:
                 raise ValueError(f"{name}: shape {tuple(shape)} contradicts the other operands")
+        if keep_derived:
+            return solved
         return {k: v for k, v in solved.items() if k not in self.members or self.members[k].derive is None}
 
 

@@ -1,0 +1,116 @@
+"""``CausalLM``: a decoder and its head as one graph with two versions
+(iron/lm/causal.py:166-400): the decode step (no inputs: the token and position are
+per-call values) and the prompt chunk (``ids`` of ``prefill_chunk`` int32, bounded per call
+by ``rows``).  Both write the same KV-cache states.
+
+``logits(tokens)`` runs the compiled versions on the device; ``reference_logits(tokens)``
+runs the same recordings on the host with every operator's numpy reference (the
+reference's ``OnHost``, iron/lm/model.py:667-695); ``engine()`` returns the fused decoder
+the same weights run on when throughput matters.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+from ml_dtypes import bfloat16
+
+from ..graph import Carried, Graph, Scratchpad, carry, state, walk
+from ..operators.copy import Copy
+from ..operators.sample import ROW_WORDS, Sample
+from .blocks import Call, DecoderLayer, Embedding, Linear, RMSNorm, Rope
+from .config import DecoderConfig
+
+
+class Decoder(Graph):
+    def __init__(self, c: DecoderConfig, layer_class=DecoderLayer):
+        self.embed_tokens = Embedding(c.vocab_size, c.hidden_size)
+        self.layers = [layer_class(c, i) for i in range(c.num_hidden_layers)]
+        self.norm = RMSNorm(c.hidden_size, c.eps)
+
+
+class CausalLM(Graph):
+    """A causal language model on ``config``'s shape and a checkpoint's ``weights`` (by name)."""
+
+    layer_class = DecoderLayer
+
+    def __init__(self, config: DecoderConfig, weights: dict):
+        self.config = config
+        self.rotary_emb = None if config.rope_theta is None else Rope(config)
+        self.draws = state((config.max_seq_len, ROW_WORDS), np.int32)
+        self.drawn = state((config.max_seq_len,), np.int32)
+        self.model = Decoder(config, self.layer_class)
+        for layer in self.model.layers:
+            layer.rope = self.rotary_emb
+        self.lm_head = Linear(config.hidden_size, config.vocab_size, False, precision=config.precision)
+        if config.tie_word_embeddings:
+            self.lm_head.weight = self.model.embed_tokens.weight
+        self.load_state_dict(weights)
+        self._weights = weights
+        self._held = 0   # positions the caches hold (device path)
+        self._held_ref = 0
+
+    def body(self, ids=None, *, token: Carried[np.int32] = np.int32(0), position: Carried[np.int32] = np.int32(0),
+             start: Scratchpad[np.int32] = np.int32(0), rows: Scratchpad[np.int32] = np.int32(1)):
+        c = self.config
+        prompt = ids is not None
+        call = Call(prompt=prompt, start=start if prompt else position, rows=rows, position=position,
+                    ids=ids[:rows] if prompt else token, token=token)
+        if prompt:
+            x = self.model.embed_tokens(call.ids)
+        else:
+            x = Copy.step(self.model.embed_tokens.weight[token]).reshape(1, c.hidden_size)
+        if self.rotary_emb is not None:
+            call.ropes[self.rotary_emb] = self.rotary_emb.rows(call)
+        for layer in self.model.layers:
+            x = layer(x, call)
+        if prompt:
+            x = Copy.step(x[rows - 1]).reshape(1, c.hidden_size)   # the last row's logits alone
+        logits = self.lm_head(self.model.norm(x))
+        drawn = Sample.step(logits.reshape(c.vocab_size), self.draws, self.drawn, at=position, vocab=c.vocab_size)
+        return logits, carry(token=drawn[position], position=position + 1)
+
+    # ---- running ----
+    def shapes(self) -> list[dict]:
+        return [{}, dict(ids=((self.config.prefill_chunk,), np.int32))]
+
+    def _chunks(self, n: int, start: int):
+        C = self.config.prefill_chunk
+        s = start
+        while s < start + n:
+            e = min(start + n, (s // C + 1) * C)
+            yield s, e
+            s = e
+
+    def _run(self, tokens, start: int, on_host: bool):
+        c = self.config
+        tokens = np.asarray(tokens).reshape(-1)
+        if start + len(tokens) > c.max_seq_len:
+            raise IndexError(f"{start + len(tokens)} positions do not fit the {c.max_seq_len}-row caches")
+        out = None
+        if len(tokens) == 1:
+            kw = dict(token=int(tokens[0]), position=start)
+            out = self.reference(**kw) if on_host else self.compile()(**kw)
+        else:
+            C = c.prefill_chunk
+            for s, e in self._chunks(len(tokens), start):
+                ids = np.zeros(C, np.int32)
+                ids[: e - s] = tokens[s - start : e - start]
+                kw = dict(position=e - 1, start=s, rows=e - s)
+                out = self.reference(ids, **kw) if on_host else self.compile(ids=((C,), np.int32))(ids, **kw)
+        logits, carried = out
+        logits = logits if isinstance(logits, np.ndarray) else logits.numpy()
+        return np.asarray(logits, np.float32).reshape(-1), carried
+
+    def logits(self, tokens, start: int = 0) -> np.ndarray:
+        """Float32 logits after the last of ``tokens`` run at positions ``start...`` on the device."""
+        return self._run(tokens, start, on_host=False)[0]
+
+    def reference_logits(self, tokens, start: int = 0) -> np.ndarray:
+        """The same on the host: every recorded step's numpy reference."""
+        return self._run(tokens, start, on_host=True)[0]
+
+    def engine(self, **kwargs):
+        """The fused decoder on the same weights (five kernels a layer, one CUDA graph a step)."""
+        from .engine import LlamaEngine
+
+        return LlamaEngine(self.config, self._weights, **kwargs)

@@ -286,7 +286,10 @@ class LlamaEngine:
         """Capture the decode step as one CUDA graph (idempotent)."""
         if self._graph is not None:
             return
+        # the warm-up and the capture run a step at position 0: keep what they overwrite
         saved = self.values.clone()
+        rows = [(l["k"][:, 0].clone(), l["v"][:, 0].clone()) for l in self.layers]
+        drawn0 = self.drawn[:, 0].clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):  # warm up outside capture: lazy module loading
@@ -300,8 +303,9 @@ class LlamaEngine:
             self._decode_launches()
         self._graph = g
         self.values.copy_(saved)
-        for l in self.layers:   # the warm-up wrote position 0 of the caches
-            l["k"][:, 0].zero_(); l["v"][:, 0].zero_()
+        for l, (k0, v0) in zip(self.layers, rows):
+            l["k"][:, 0].copy_(k0); l["v"][:, 0].copy_(v0)
+        self.drawn[:, 0].copy_(drawn0)
         torch.cuda.synchronize()
 
     def set_call(self, token: int, position: int) -> None:

@@ -1,0 +1,203 @@
+"""Graphs without a device: per-call expressions, handle views, recording, host reference.
+
+The contracts iron/tests/common/test_graph.py pins in the reference: what a per-call value
+may and may not do (:534-600, :898-945), the Llama decode and prompt recordings
+(:405-511: 18 steps a layer; 7 projection GEMMs a layer for a prompt chunk), errors
+raised before any dispatch, and the model's host path against the reference's golden
+logits (iron/tests/support/llama_reference.py:179-224).
+"""
+
+import dataclasses
+from pathlib import Path
+
+import numpy as np
+import pytest
+from ml_dtypes import bfloat16
+
+import iron_b200 as iron
+from iron_b200 import functional as F
+from iron_b200.graph import Expr
+from iron_b200.graph.expr import evaluate
+from oracle import model as M
+from tests.test_oracle_golden import assert_close
+
+GOLDEN = Path(__file__).parent / "golden" / "llama_small.npz"
+
+
+def test_per_call_expressions_are_closed_under_what_indices_need():
+    p = Expr("position")
+    assert (p + 1).evaluate({"position": 5}) == 6
+    assert (p * 4 + 3).evaluate({"position": 5}) == 23
+    assert ((p - 1) // 256 + 1).evaluate({"position": 600}) == 3
+    assert (p // 4 // 8).evaluate({"position": 1000}) == 1000 // 32
+    assert (p % 64).evaluate({"position": 130}) == 2
+    assert (p + p * 2).evaluate({"position": 7}) == 21
+    assert iron.clamp(p - 10, lo=0).evaluate({"position": 3}) == 0
+    assert (p + 1).difference(p) == 1 and (p * 2).difference(p) is None
+    for bad in (lambda: p // 3, lambda: p % 48, lambda: p < 3, lambda: bool(p), lambda: p * Expr("rows"),
+                lambda: p + Expr("rows"), lambda: int(p), lambda: iron.clamp(p, hi=4) + 1):
+        with pytest.raises(TypeError):
+            bad()
+    with pytest.raises(TypeError):
+        (p + 1).evaluate({})
+
+
+class FeedForward(iron.Graph):
+    def __init__(self, E, H):
+        self.norm = iron.param(E)
+        self.gate, self.up, self.down = iron.param(H, E), iron.param(H, E), iron.param(E, H)
+        self.cache = iron.state((16, E))
+
+    def body(self, x, *, position: iron.Scratchpad[np.int32], rows: iron.Scratchpad[np.int32] = np.int32(1)):
+        h = F.rms_norm(x, (x.shape[-1],), self.norm, 1e-5)
+        y = x + F.linear(F.silu(F.linear(h, self.gate)) * F.linear(h, self.up), self.down)
+        self.cache[position] = y.reshape(y.shape[-1])
+        return y, iron.carry(position=position + 1)
+
+
+def loaded(seed=0):
+    rng = np.random.default_rng(seed)
+    g = FeedForward(64, 128)
+    g.load_state_dict({"norm": (1 + rng.standard_normal(64) / 10).astype(bfloat16),
+                       "gate": (rng.standard_normal((128, 64)) / 8).astype(bfloat16),
+                       "up": (rng.standard_normal((128, 64)) / 8).astype(bfloat16),
+                       "down": (rng.standard_normal((64, 128)) / 11).astype(bfloat16)})
+    return g, rng.standard_normal((1, 64)).astype(bfloat16)
+
+
+def test_a_body_records_operator_steps_and_its_reference_runs_them():
+    from oracle import ops
+
+    g, x = loaded()
+    rec = g.record(x=((1, 64), bfloat16))
+    assert [s.op.name for s in rec.steps] == ["RMSNorm", "GEMV", "SiLU", "GEMV", "ElementwiseMul", "GEMV",
+                                               "ElementwiseAdd", "Copy"]
+    y, carried = g.reference(x, position=3)
+    h = ops.rms_norm(x, np.asarray(g.norm), 1e-5)
+    act = ops.mul(ops.silu(ops.gemv(np.asarray(g.gate), h[0])), ops.gemv(np.asarray(g.up), h[0]))
+    want = ops.add(x, ops.gemv(np.asarray(g.down), act).reshape(1, 64))
+    assert np.array_equal(y, want) and carried == {"position": 4}
+    assert np.array_equal(g.cache.host.reshape(16, 64)[3], want[0])
+    assert not g.cache.host.reshape(16, 64)[[0, 1, 2, 4]].astype(np.float32).any()
+
+
+def test_bad_calls_are_refused_before_anything_runs():
+    g, x = loaded()
+    with pytest.raises(IndexError):
+        g.reference(x, position=16)          # a row past the state
+    with pytest.raises(TypeError):
+        g.reference(x, position=1.5)         # per-call values are integers
+    with pytest.raises(TypeError):
+        g.reference(x)                       # a value without a default is needed
+    with pytest.raises(TypeError):
+        g.reference(x, position=1, tokens=3)  # an unknown value
+    with pytest.raises(TypeError):
+        FeedForward(64, 128).reference(x, position=0)  # params never loaded
+    with pytest.raises(KeyError):
+        FeedForward(64, 128).load_state_dict({})
+    with pytest.raises(TypeError):
+        g(x)                                 # a graph is compiled, or called in a body
+
+
+def test_handle_views_carry_bounds_through_reshapes_and_refuse_what_is_not_a_view():
+    class Views(iron.Graph):
+        def __init__(self):
+            self.table = iron.weight(np.arange(64 * 8, dtype=np.float32).reshape(64, 8).astype(bfloat16))
+            self.log = {}
+
+        def body(self, x, *, rows: iron.Scratchpad[np.int32], start: iron.Scratchpad[np.int32]):
+            b = x[:rows]
+            self.log["bound"] = b.valid
+            self.log["merged"] = b.reshape(x.shape[0] * 2, x.shape[1] // 2).valid
+            self.log["split"] = b.reshape(x.shape[0] * 2, x.shape[1] // 2).reshape(x.shape).valid
+            run = self.table[start : start + 4]
+            self.log["run"] = (run.shape, run.offset)
+            for bad in (lambda: x[:, :4], lambda: x[::2], lambda: self.table[start : start * 2],
+                        lambda: x[:rows][:rows]):
+                with pytest.raises(TypeError):
+                    bad()
+            with pytest.raises(IndexError):
+                x[99]
+            return x
+
+    from iron_b200.operators.copy import Copy
+
+    v = Views()
+    v.record(x=((8, 16), bfloat16))
+    rows = Expr("rows")
+    assert v.log["bound"] == {0: rows} and v.log["merged"] == {0: rows * 2} and v.log["split"] == {0: rows}
+    assert v.log["run"][0] == (4, 8) and evaluate(v.log["run"][1], {"start": 5}) == 40
+
+
+@pytest.fixture(scope="module")
+def llama():
+    from iron_b200.applications.llama.model import Llama, Llama3RopeScaling, LlamaConfig
+
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=512, num_hidden_layers=2, num_attention_heads=16,
+                      num_key_value_heads=4, head_dim=64, intermediate_size=2048, rope_theta=500000.0,
+                      max_seq_len=256, eps=1e-5, prefill_chunk=256,
+                      rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 64))
+    weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
+    with np.load(GOLDEN) as z:
+        golden = {k: z[k] for k in z.files}
+    return Llama, cfg, weights, golden
+
+
+def test_llama_records_the_reference_step_sequence(llama):
+    Llama, cfg, weights, _ = llama
+    model = Llama(cfg, weights)
+    decode = [s.op.name for s in model.record().steps]
+    layer = ["RMSNorm", "GEMV", "GEMV", "GEMV", "RoPE", "RoPE", "Copy", "Copy", "MHA", "GEMV", "ElementwiseAdd",
+             "RMSNorm", "GEMV", "SiLU", "GEMV", "ElementwiseMul", "GEMV", "ElementwiseAdd"]
+    assert decode == ["Copy", "Copy"] + layer * 2 + ["RMSNorm", "GEMV", "Sample"]
+    prompt = model.record(ids=((256,), np.int32)).steps
+    assert sum(s.op.name == "ProjectionGEMM" for s in prompt) == 7 * 2      # seven a layer
+    mha = next(s for s in prompt if s.op.name == "MHA")
+    assert evaluate(mha.values["valid"], dict(rows=9, position=20)) == 9
+    assert evaluate(mha.values["kv_valid"], dict(rows=9, position=20)) == 21
+
+
+def test_llama_host_path_matches_the_oracle_bit_for_bit_and_the_golden_logits(llama):
+    Llama, cfg, weights, golden = llama
+    model = Llama(cfg, weights)
+    oracle = M.NumpyLlama(M.SCALED, weights)
+    prompt = np.random.default_rng(7).integers(0, 1024, 8)
+    got = model.reference_logits(prompt)
+    assert np.array_equal(got, oracle.forward(prompt, 0).astype(np.float32))
+    assert_close(got, golden[M.golden_key(prompt)])
+    tokens = prompt
+    for step in range(3):
+        nxt = int(golden[M.golden_key(tokens)].argmax())
+        got = model.reference_logits([nxt], len(tokens))
+        assert np.array_equal(got, oracle.forward([nxt], len(tokens)).astype(np.float32))
+        tokens = np.append(tokens, nxt)
+        assert_close(got, golden[M.golden_key(tokens)], f"step {step}")
+
+
+def test_arena_plan_shares_transients_and_pins_residents():
+    from iron_b200.arena import ArenaPlan, Live, place
+
+    plan = ArenaPlan()
+    sizes = {"w": 1000, "kv": 5000, "a": 4096, "b": 4096, "c": 4096}
+    spans = plan.place_version([["a"], ["a", "b"], ["b", "c"], ["c"]], sizes, {"w": "W", "kv": "KV"})
+    assert spans["a"].offset == spans["c"].offset                    # live ranges do not overlap
+    assert not spans["a"].overlaps(spans["b"]) and not spans["b"].overlaps(spans["c"])
+    fixed = [spans["w"], spans["kv"]]
+    assert all(not t.overlaps(f) for t in (spans["a"], spans["b"], spans["c"]) for f in fixed)
+    again = plan.place_version([["x"]], {"kv": 5000, "x": 64}, {"kv": "KV"})
+    assert again["kv"].offset == spans["kv"].offset                  # one offset in every version
+    with pytest.raises(ValueError):
+        plan.place_version([[]], {"kv": 6000}, {"kv": "KV"})
+    assert all(s.offset % 256 == 0 for s in (*spans.values(), *again.values()))
+    # randomized: nothing live together ever overlaps
+    rng = np.random.default_rng(0)
+    for _ in range(20):
+        n = int(rng.integers(2, 12))
+        ranges = {f"t{i}": Live(*sorted(rng.integers(0, 10, 2).tolist())) for i in range(n)}
+        szs = {k: int(rng.integers(1, 5000)) for k in ranges}
+        placed, top = place(ranges, szs)
+        for a in placed:
+            for b in placed:
+                if a < b and ranges[a].overlaps(ranges[b]):
+                    assert not placed[a].overlaps(placed[b])
+        assert top == max(s.end for s in placed.values())

@@ -1,0 +1,73 @@
+"""Compiled graphs on the device against their own host reference and the golden logits (B200)."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+from ml_dtypes import bfloat16
+
+from oracle import model as M
+from tests.test_graph_cpu import FeedForward, loaded
+from tests.test_oracle_golden import assert_close
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).parent / "golden" / "llama_small.npz"
+
+
+def test_a_compiled_graph_replays_with_new_per_call_values():
+    g, x = loaded()
+    ref, _ = loaded()
+    version = g.compile(x=((1, 64), bfloat16))
+    for position in (3, 7, 3, 15):
+        y, carried = version(x, position=position)
+        want, want_carried = ref.reference(x, position=position)
+        got = y.numpy().astype(np.float32)
+        assert np.abs(got - want.astype(np.float32)).max() <= 2e-2 and carried == want_carried
+        x = (x.astype(np.float32) * 0.5 + 0.1).astype(bfloat16)
+    cache = version.read(g.cache).astype(np.float32)
+    want_cache = ref.cache.host.reshape(16, 64).astype(np.float32)
+    assert np.abs(cache - want_cache).max() <= 2e-2
+    assert not cache[[0, 1, 2, 4, 5, 6]].any()
+    assert g.compile(x=((1, 64), bfloat16)) is version
+    with pytest.raises(ValueError, match="a new shape is a new compile"):
+        version(np.zeros((2, 64), bfloat16), position=0)
+    with pytest.raises(TypeError):
+        version(x.astype(np.float32), position=0)
+    with pytest.raises(IndexError):
+        version(x, position=16)
+    with pytest.raises(TypeError):
+        version(x)
+
+
+def test_llama_compiled_graphs_match_the_golden_logits_prompt_then_decode():
+    from iron_b200.applications.llama.model import Llama, Llama3RopeScaling, LlamaConfig
+
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=512, num_hidden_layers=2, num_attention_heads=16,
+                      num_key_value_heads=4, head_dim=64, intermediate_size=2048, rope_theta=500000.0,
+                      max_seq_len=256, eps=1e-5, prefill_chunk=256,
+                      rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 64))
+    weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
+    with np.load(GOLDEN) as z:
+        golden = {k: z[k] for k in z.files}
+    model = Llama(cfg, weights)
+    prompt = np.random.default_rng(7).integers(0, 1024, 8)
+    got = model.logits(prompt)
+    assert_close(got, golden[M.golden_key(prompt)])
+    host = Llama(cfg, weights).reference_logits(prompt)
+    assert np.abs(got - host).max() <= 0.02 * np.abs(host).max() and got.argmax() == host.argmax()
+    tokens = prompt
+    for step in range(6):
+        nxt = int(golden[M.golden_key(tokens)].argmax())
+        got = model.logits([nxt], len(tokens))
+        tokens = np.append(tokens, nxt)
+        assert_close(got, golden[M.golden_key(tokens)], f"step {step}")
+    # the two versions share one arena: the prompt's caches are the decode step's
+    assert len(model.__dict__["_versions"]) == 2
+    # the fused engine on the same weights draws the same greedy tokens
+    engine = model.engine(kv_len_hint=64)
+    want = []
+    tokens = prompt
+    for _ in range(4):
+        want.append(int(golden[M.golden_key(tokens)].argmax()))
+        tokens = np.append(tokens, want[-1])
+    assert engine.complete(prompt, 4) == want
