@@ -238,6 +238,75 @@ def workload_config(n_gpus: int) -> dict:
             "prompt": "2048 uniform-random token ids run as one prompt chunk; decode continues from its caches"}
 
 
+def run_tp(args, rank: int, world: int, device) -> None:
+    """Llama-3.2-3B architecture, decode of one token at position 4096 and on, batch 1,
+    QKV/O/MLP weights tensor-parallel over the ranks with an all-reduce after o_proj and
+    down_proj.  Every rank draws the same full weights from one seed and keeps its shard."""
+    import dataclasses
+
+    import torch
+    import torch.distributed as dist
+
+    from iron_b200.applications.llama.model import LLAMA_3B
+    from iron_b200.lm.engine import LlamaEngine
+
+    ctx = 4096
+    config = dataclasses.replace(LLAMA_3B, max_seq_len=ctx + 512)
+    gen = torch.Generator(device=device).manual_seed(4001)
+    from oracle.model import LlamaShape, llama_shapes
+
+    shape = LlamaShape(hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8,
+                       head_dim=128, intermediate_size=8192, max_seq_len=config.max_seq_len)
+    weights = {}
+    for name, dims in llama_shapes(shape).items():
+        weights[name] = ((torch.randn(dims, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+                         if len(dims) >= 2 else torch.ones(dims, device=device, dtype=torch.bfloat16))
+    engine = LlamaEngine(config, weights, device=device, kv_len_hint=ctx + args.steps, tp_rank=rank, tp_size=world)
+    del weights
+    gen = torch.Generator(device=device).manual_seed(4002)
+    for l in engine.layers:
+        for name in ("k", "v"):
+            l[name][:, :ctx].copy_(torch.randn(l[name][:, :ctx].shape, generator=gen, device=device).to(torch.bfloat16))
+    engine.capture()
+    warm = max(args.warmup, 3)
+    engine.set_call(1, ctx)
+    for _ in range(warm):
+        engine.step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    engine.set_call(1, ctx)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.steps):
+        engine.step()
+    stop.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank != 0:
+        return
+    peak, kind = measured_peaks()
+    step_bytes = engine.weight_bytes_per_token + (ctx + args.steps // 2) * 2 * 28 * (8 // world) * 128 * 2
+    print(json.dumps({
+        "metric": "llama-3.2-3b-arch decode throughput (batch 1, context 4096, tensor parallel)",
+        "value": round(args.steps / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "configs[3]: Llama-3.2-3B architecture decode, 4096-token KV cache N(0,1), "
+                               "batch 1, tensor parallel with NCCL all-reduce", "tp": world},
+        "gpu_launches": (engine.launches_per_step + (4 * 28 if world > 1 else 0)) * args.steps,
+        "per_rank_roofline": {"bound": "hbm", "bytes_per_step": step_bytes,
+                              "achieved": round(step_bytes / (ms / args.steps / 1e3) / 1e9, 1),
+                              "peak": peak, "unit": "GB/s",
+                              "frac": round(step_bytes / (ms / args.steps / 1e3) / 1e9 / peak, 4)},
+        "all_reduces_per_step": 56 if world > 1 else 0}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -245,6 +314,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="llama1b", choices=["llama1b", "llama3b-tp"],
+                    help="llama1b: the headline decode, one replica per GPU; llama3b-tp: the 3B "
+                         "architecture tensor-parallel over --gpus ranks at context 4096")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -272,6 +344,11 @@ def main() -> None:
 
     from iron_b200.lm.engine import LlamaEngine
 
+    if args.workload == "llama3b-tp":
+        run_tp(args, rank, world, device)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     config = build_config()
     weights = device_weights(config, 3001, device)
     engine = LlamaEngine(config, weights, device=device, kv_len_hint=CONTEXT + args.steps)

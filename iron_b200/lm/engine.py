@@ -48,6 +48,30 @@ def _as_device_bf16(a, out: torch.Tensor) -> None:
     out.copy_(t.reshape(out.shape))
 
 
+@dataclasses.dataclass(frozen=True)
+class ShardLayout:
+    """What one tensor-parallel rank holds of each projection."""
+
+    heads: int
+    kv_heads: int
+    ffn: int
+    q_rows: slice      # rows of q_proj (and columns of o_proj)
+    kv_rows: slice     # rows of k_proj and v_proj
+    ffn_rows: slice    # rows of gate/up_proj (and columns of down_proj)
+
+
+def shard_layout(c: DecoderConfig, rank: int, size: int) -> ShardLayout:
+    """Split heads and MLP rows ``size`` ways; raises ``ValueError`` when they do not divide."""
+    H, G, D, F = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.intermediate_size
+    if not 0 <= rank < size:
+        raise ValueError(f"rank {rank} is outside 0..{size - 1}")
+    if H % size or G % size or F % size or (F // size) % 8:
+        raise ValueError(f"{H} heads, {G} KV heads and {F} MLP rows do not split {size} ways")
+    h, g, f = H // size, G // size, F // size
+    return ShardLayout(h, g, f, slice(rank * h * D, (rank + 1) * h * D),
+                       slice(rank * g * D, (rank + 1) * g * D), slice(rank * f, (rank + 1) * f))
+
+
 class LlamaEngine:
     """A decoder of ``config``'s shape on ``weights`` (Hugging Face checkpoint names).
 
@@ -55,13 +79,20 @@ class LlamaEngine:
     """
 
     def __init__(self, config: DecoderConfig, weights: dict, device="cuda", batch: int = 1,
-                 kv_len_hint: int | None = None):
+                 kv_len_hint: int | None = None, tp_rank: int = 0, tp_size: int = 1, tp_group=None):
         if not torch.cuda.is_available():
             raise RuntimeError("LlamaEngine needs a CUDA device: there is no CPU path")
         self.c, self.device, self.batch = config, torch.device(device), batch
         c = config
-        E, F, V, L = c.hidden_size, c.intermediate_size, c.vocab_size, c.num_hidden_layers
-        H, G, D, S = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.max_seq_len
+        E, V, L = c.hidden_size, c.vocab_size, c.num_hidden_layers
+        D, S = c.head_dim, c.max_seq_len
+        # Tensor parallelism: this rank holds heads [rank*H/t, ...) of q/k/v and o_proj's
+        # matching columns, rows [rank*F/t, ...) of gate/up and down_proj's matching
+        # columns; o_proj and down_proj produce partial sums that one all-reduce completes.
+        self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
+        layout = shard_layout(c, tp_rank, tp_size)
+        H, G, F = layout.heads, layout.kv_heads, layout.ffn
+        self.H, self.G, self.F = H, G, F
         self.kv_len_hint = kv_len_hint or S
 
         # ---- plan the arena: residents first, then the decode step's transients ----
@@ -83,7 +114,7 @@ class LlamaEngine:
         res("values", (16,), 4); res("drawn", (batch, S), 4)
         residents = {n: n for n in sizes}
         trans = {"x0": (batch, E), "x1": (batch, E), "q": (batch, H * D), "att": (batch, H * D),
-                 "act": (batch, F), "logits": (batch, V)}
+                 "act": (batch, F), "logits": (batch, V), "part": (batch, E)}
         for n, shape in trans.items():
             sizes[n] = int(np.prod(shape)) * 2
         # the decode step touches every transient in each layer: all live together
@@ -95,7 +126,7 @@ class LlamaEngine:
         self.chunk = C
         QKV = (H + 2 * G) * D
         ptrans = {"p.ids": (C, 2), "p.x": (C, E), "p.h": (C, E), "p.y": (C, E), "p.qkv": (C, QKV),
-                  "p.att": (C, H * D), "p.gate": (C, F), "p.up": (C, F)}
+                  "p.att": (C, H * D), "p.gate": (C, F), "p.up": (C, F), "p.part": (C, E)}
         psizes = dict(sizes)
         for n in trans:
             psizes.pop(n)
@@ -105,7 +136,8 @@ class LlamaEngine:
                   ["p.att", "p.x", "p.y"], ["p.y", "p.h"], ["p.h", "p.gate"], ["p.h", "p.up"],
                   ["p.gate", "p.up"], ["p.gate", "p.y", "p.x"]]
         # within a layer p.x and p.y stay live across the loop: mark them touched last too
-        psteps.append(["p.x", "p.y"])
+        psteps.append(["p.x", "p.y", "p.part"])
+        psteps[4].append("p.part")
         spans.update(plan.place_version(psteps, psizes, {n: n for n in residents}))
         self.plan = plan
         self.arena = torch.empty(plan.size, dtype=torch.uint8, device=self.device)
@@ -129,6 +161,7 @@ class LlamaEngine:
         self.x0, self.x1 = view("x0", (batch, E)), view("x1", (batch, E))
         self.q, self.att = view("q", (batch, H, D)), view("att", (batch, H, D))
         self.act, self.logits_buf = view("act", (batch, F)), view("logits", (batch, V))
+        self.part, self.p_part = view("part", (batch, E)), view("p.part", (C, E))
         self.p_ids = view("p.ids", (C,), torch.int32)
         self.p_x, self.p_h, self.p_y = view("p.x", (C, E)), view("p.h", (C, E)), view("p.y", (C, E))
         self.p_qkv, self.p_att = view("p.qkv", (C, QKV)), view("p.att", (C, H * D))
@@ -155,18 +188,25 @@ class LlamaEngine:
         if not c.tie_word_embeddings:
             _as_device_bf16(w["lm_head.weight"], self.head)
         _as_device_bf16(c.angles().astype(np.float32), self.angles)
-        Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+        lay = shard_layout(c, self.tp_rank, self.tp_size)
+        Q, KV = lay.heads * c.head_dim, lay.kv_heads * c.head_dim
         for i, l in enumerate(self.layers):
             p = f"model.layers.{i}"
             _as_device_bf16(w[f"{p}.input_layernorm.weight"], l["ln1"])
-            _as_device_bf16(w[f"{p}.self_attn.q_proj.weight"], l["wqkv"][:Q])
-            _as_device_bf16(w[f"{p}.self_attn.k_proj.weight"], l["wqkv"][Q : Q + KV])
-            _as_device_bf16(w[f"{p}.self_attn.v_proj.weight"], l["wqkv"][Q + KV :])
-            _as_device_bf16(w[f"{p}.self_attn.o_proj.weight"], l["wo"])
+            _as_device_bf16(w[f"{p}.self_attn.q_proj.weight"][lay.q_rows], l["wqkv"][:Q])
+            _as_device_bf16(w[f"{p}.self_attn.k_proj.weight"][lay.kv_rows], l["wqkv"][Q : Q + KV])
+            _as_device_bf16(w[f"{p}.self_attn.v_proj.weight"][lay.kv_rows], l["wqkv"][Q + KV :])
+            _as_device_bf16(w[f"{p}.self_attn.o_proj.weight"][:, lay.q_rows], l["wo"])
             _as_device_bf16(w[f"{p}.post_attention_layernorm.weight"], l["ln2"])
-            _as_device_bf16(w[f"{p}.mlp.gate_proj.weight"], l["wg"])
-            _as_device_bf16(w[f"{p}.mlp.up_proj.weight"], l["wu"])
-            _as_device_bf16(w[f"{p}.mlp.down_proj.weight"], l["wd"])
+            _as_device_bf16(w[f"{p}.mlp.gate_proj.weight"][lay.ffn_rows], l["wg"])
+            _as_device_bf16(w[f"{p}.mlp.up_proj.weight"][lay.ffn_rows], l["wu"])
+            _as_device_bf16(w[f"{p}.mlp.down_proj.weight"][:, lay.ffn_rows], l["wd"])
+
+    def _all_reduce(self, t: torch.Tensor) -> None:
+        """Sum ``t`` over the tensor-parallel ranks in place (NCCL; stream-ordered, capturable)."""
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.tp_group)
 
     # ------------------------------------------------------------------ decode step
     @property
@@ -181,16 +221,17 @@ class LlamaEngine:
         E, F, V = c.hidden_size, c.intermediate_size, c.vocab_size
         Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
         layer = ((Q + 2 * KV) * E + E * Q + 3 * F * E) * 2
-        return c.num_hidden_layers * layer + V * E * 2
+        return c.num_hidden_layers * layer // self.tp_size + V * E * 2
 
     def _decode_launches(self) -> None:
         """Launch one decode step on the current stream, reading (token, position) from
         the device values buffer and leaving (drawn token, position + 1) there."""
         c = self.c
-        H, G, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        H, G, D = self.H, self.G, c.head_dim
         d_token, d_pos = self.values[0:1], self.values[1:2]
         E2 = c.hidden_size * 2
-        x, y = self.x0[0], self.x1[0]
+        x, y, part = self.x0[0], self.x1[0], self.part[0]
+        tp = self.tp_size > 1
         K.copy_rows(self.embed, x, ids=d_token, nrows=1, row_bytes=E2, src_rows=c.vocab_size)
         for l in self.layers:
             K.decode_qkv_rope(l["wqkv"], x, self.angles, l["k"][0], l["v"][0], self.q[0],
@@ -198,6 +239,15 @@ class LlamaEngine:
             K.mha_decode(self.q, l["k"], l["v"], self.att, d_kv_valid=d_pos, kv_valid_add=1,
                          window=c.window, scale=c.attention_scale, nsplit=self.nsplit,
                          stable_prefix=True)
+            if tp:   # partial sums meet in an all-reduce before each residual add
+                K.gemv(l["wo"], self.att[0].view(-1), part)
+                self._all_reduce(part)
+                K.elementwise("add", x, part, y)
+                K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
+                K.gemv(l["wd"], self.act[0], part)
+                self._all_reduce(part)
+                K.elementwise("add", y, part, x)
+                continue
             K.gemv(l["wo"], self.att[0].view(-1), y, residual=x)
             K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
             K.gemv(l["wd"], self.act[0], x, residual=y)
@@ -230,8 +280,9 @@ class LlamaEngine:
             raise IndexError(f"positions {start}..{start + n} leave the {c.max_seq_len}-row caches")
         if tokens.min() < 0 or tokens.max() >= c.vocab_size:
             raise IndexError("a token id is outside the vocabulary")
-        H, G, D, E, F = (c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.hidden_size,
-                         c.intermediate_size)
+        H, G, D, E, F = self.H, self.G, c.head_dim, c.hidden_size, self.F
+        tp = self.tp_size > 1
+        part = self.p_part[:n]
         ids_host = torch.from_numpy(tokens.astype(np.int32)).pin_memory()
         self.p_ids[:n].copy_(ids_host, non_blocking=True)
         x, h, y = self.p_x[:n], self.p_h[:n], self.p_y[:n]
@@ -244,12 +295,22 @@ class LlamaEngine:
             K.mha_prefill(qkv.view(n, H + 2 * G, D)[:, :H], l["k"][seq], l["v"][seq], att.view(n, H, D),
                           q_tokens=n, kv_tokens=start + n, window=c.window, scale=c.attention_scale,
                           q_row_stride=qkv.stride(0))
-            K.gemm(att, l["wo"], y, b_col_maj=True, residual=x, status=self.status)
+            if tp:
+                K.gemm(att, l["wo"], part, b_col_maj=True, status=self.status)
+                self._all_reduce(part)
+                K.elementwise("add", x, part, y)
+            else:
+                K.gemm(att, l["wo"], y, b_col_maj=True, residual=x, status=self.status)
             K.rms_norm(y, l["ln2"], h, eps=c.eps)
             K.gemm(h, l["wg"], gate, b_col_maj=True, status=self.status)
             K.gemm(h, l["wu"], up, b_col_maj=True, status=self.status)
             K.elementwise("silu_mul", gate, up, gate)
-            K.gemm(gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
+            if tp:
+                K.gemm(gate, l["wd"], part, b_col_maj=True, status=self.status)
+                self._all_reduce(part)
+                K.elementwise("add", y, part, x)
+            else:
+                K.gemm(gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
         last = self.x0[seq]
         K.copy_rows(x, last, nrows=1, row_bytes=E * 2, src_row0=n - 1)
         K.gemv(self.head, last, self.logits_buf[seq], norm_weight=self.norm, eps=c.eps)
@@ -360,3 +421,11 @@ class LlamaEngine:
             self.set_call(int(t), start + i)
             self.step()
         return self.logits()
+
+
+def batch_shard(sequences: int, rank: int, size: int) -> range:
+    """The sequences rank ``rank`` of ``size`` decodes when a batch is split with no collective:
+    contiguous runs whose lengths differ by at most one."""
+    base, extra = divmod(sequences, size)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
