@@ -164,6 +164,24 @@ int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out
                      int* carry_token, int* carry_position, void* workspace,
                      iron_stream_t stream);
 
+/* The same greedy draw for callers that cannot give the library a workspace.  It has no
+ * counterpart in the reference.  A caller may be unable to allocate device memory at all: a
+ * thread that must never enter the CUDA allocator (which can lock or synchronise), a plugin
+ * inside a runtime that owns every byte of device memory and offers no hook to ask for more,
+ * or code running where allocation is not permitted.  Here the cross-block scratch is a
+ * fixed array inside the library (a few kilobytes per GPU, held until the process exits), so
+ * the call takes inputs and outputs only and performs no allocation of any kind.
+ *   - n may be at most iron_argmax_noalloc_max_n() (4 194 304); larger n returns
+ *     IRON_ERR_WORKSPACE.
+ *   - The first call on each device looks up the array's device address; make that first
+ *     call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels could overlap on
+ *     the GPU (different streams, no ordering between them) race.  Calls on one stream,
+ *     or otherwise ordered, are safe; each call resets the part that must start at zero. */
+int iron_argmax_noalloc_max_n(void);
+int iron_argmax_bf16_noalloc(const void* logits, int n, int* token_out, const int* d_out_index,
+                             int* carry_token, int* carry_position, iron_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * GEMM -- replaces iron/operators/gemm.py:143 (`GEMM`, reference :696-702) and
  * iron/operators/flm/gemm/op.py:128 (`ProjectionGEMM`, reference :1335-1346, output

@@ -57,6 +57,8 @@ SIGNATURES: dict[str, tuple] = {
     "iron_copy_rows": (_I, [_P, _P, _P, _I, _P, _L, _L, _L, _I, _I, _P, _I, _P, _P]),
     "iron_argmax_workspace_bytes": (_Z, [_I]),
     "iron_argmax_bf16": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
+    "iron_argmax_noalloc_max_n": (_I, []),
+    "iron_argmax_bf16_noalloc": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "iron_mha_decode_splits": (_I, [_I, _I, _I]),
     "iron_mha_decode_bf16": (
         _I,

@@ -445,3 +445,45 @@ extern "C" int iron_rope_kv_write_bf16(void* qkv, long long pitch, const void* a
                     (__nv_bfloat16*)v_cache, rows, d_rows, H, G, D, start, d_start, angle_start,
                     d_angle_start);
 }
+
+// ---------------------------------------------------------------- greedy draw without a workspace
+// Some callers cannot hand the library scratch memory: code that runs where cudaMalloc is not
+// available to it -- a host thread that must not touch the allocator (it would take the
+// allocator's lock or synchronise the device), a plugin bound into a runtime that owns all
+// device memory and exposes no allocation hook, or a caller already inside a region where
+// allocation is illegal.  For them the argmax's cross-block scratch (one arrival counter and
+// one 64-bit partial per block) lives in this file-scope device array instead.  Every GPU that
+// loads the library holds these few kilobytes until the process exits.
+static __device__ __align__(256) unsigned long long g_argmax_scratch[1 + iron::kArgmaxBlocks];
+
+namespace {
+constexpr int kNoAllocMaxN = 1 << 22;  // logits per call this entry point accepts
+constexpr int kMaxDevices = 64;
+unsigned long long* g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+}  // namespace
+
+extern "C" int iron_argmax_noalloc_max_n(void) { return kNoAllocMaxN; }
+
+extern "C" int iron_argmax_bf16_noalloc(const void* logits, int n, int* token_out, const int* d_out_index,
+                                        int* carry_token, int* carry_position, iron_stream_t stream) {
+  if (n <= 0 || !token_out) return IRON_ERR_SHAPE;
+  if (n > kNoAllocMaxN) return IRON_ERR_WORKSPACE;  // more logits than the built-in scratch is stated for
+  if (!aligned16(logits)) return IRON_ERR_ALIGN;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return IRON_ERR_LAUNCH;
+  if (!g_scratch_ptr[dev]) {
+    // In host code `g_argmax_scratch` is only a stand-in for the symbol: its device address
+    // has to be asked for, once per device, with that device current.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_argmax_scratch) != cudaSuccess || !p) return IRON_ERR_LAUNCH;
+    g_scratch_ptr[dev] = static_cast<unsigned long long*>(p);
+  }
+  unsigned long long* scratch = g_scratch_ptr[dev];
+  cudaStream_t s = (cudaStream_t)stream;
+  // The array keeps whatever the last call left: the arrival counter must start at zero.
+  if (cudaMemsetAsync(scratch, 0, sizeof(unsigned long long), s) != cudaSuccess) return IRON_ERR_LAUNCH;
+  int grid = (n / 8 + 255) / 256;
+  grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
+  return launch_pdl(argmax_kernel, dim3(grid), dim3(256), s, (const __nv_bfloat16*)logits, n, token_out,
+                    d_out_index, carry_token, carry_position, scratch);
+}
