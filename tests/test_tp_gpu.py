@@ -1,7 +1,14 @@
-"""Tensor-parallel decode and prefill on two GPUs against the single-GPU engine (NCCL)."""
+"""Tensor-parallel decode and prefill on two GPUs against the single-GPU engine (NCCL).
+
+The ranks are child processes.  A rank that fails reports its traceback through the queue
+and leaves at once (between steps, nothing of its own in flight); the parent then ends the
+other rank on the host rather than letting it wait in a collective, so a failure costs
+seconds, not a process-group timeout.
+"""
 
 import os
 import socket
+import traceback
 
 import numpy as np
 import pytest
@@ -15,7 +22,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _rank(rank: int, size: int, port: int, out):
+def _work(rank: int, size: int, out):
     import torch
     import torch.distributed as dist
 
@@ -23,7 +30,6 @@ def _rank(rank: int, size: int, port: int, out):
     from oracle import model as M
     from tests.test_engine_gpu import toy_config
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=size, device_id=torch.device("cuda", rank))
     weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
@@ -32,18 +38,33 @@ def _rank(rank: int, size: int, port: int, out):
     logits = [tp.prefill(prompt)]
     drawn = tp.complete(prompt, 5)
     logits.append(tp.logits())
+    torch.cuda.synchronize()
     if rank == 0:
         one = LlamaEngine(toy_config(), weights, device="cuda:0", kv_len_hint=64)
         want = [one.prefill(prompt)]
         want_drawn = one.complete(prompt, 5)
         want.append(one.logits())
         err = max(float(np.abs(a - b).max() / np.abs(b).max()) for a, b in zip(logits, want))
-        out.put((err, drawn, want_drawn))
-    dist.barrier()
-    dist.destroy_process_group()
+        out.put(("ok", rank, (err, drawn, want_drawn)))
+    else:
+        out.put(("ok", rank, None))
+
+
+def _rank(rank: int, size: int, port: int, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        _work(rank, size, out)
+    except BaseException:  # noqa: BLE001 -- report and leave; the parent ends the peer
+        out.put(("error", rank, traceback.format_exc()))
+    finally:
+        out.close()
+        out.join_thread()
+        os._exit(0)   # no collective teardown: the peer may already be gone
 
 
 def test_two_way_tensor_parallel_matches_one_gpu():
+    import queue
+
     import torch
     import torch.multiprocessing as mp
 
@@ -52,12 +73,23 @@ def test_two_way_tensor_parallel_matches_one_gpu():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, out), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
-    err, drawn, want = out.get(timeout=10)
+    results = {}
+    try:
+        for _ in range(2):
+            try:
+                kind, rank, payload = out.get(timeout=240)
+            except queue.Empty:
+                pytest.fail(f"a rank did not report within 240 s (reported so far: {sorted(results)})")
+            assert kind == "ok", f"rank {rank} failed:\n{payload}"
+            results[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.kill()
+    err, drawn, want = results[0]
     # partial sums are rounded to bf16 before they meet: close, and the same greedy tokens
     assert err <= 0.02 and drawn == want
