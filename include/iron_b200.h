@@ -51,6 +51,15 @@ const char* iron_arch(void);
  * turns the attribute off process-wide, e.g. to bisect a scheduling problem. */
 void iron_set_pdl(int enabled);
 
+/* A hint for the next GEMV-family or decode-attention launch made by this host thread
+ * (iron_gemv_bf16, iron_gemv_swiglu_bf16, iron_decode_qkv_rope_bf16, iron_mha_decode_bf16):
+ * `bytes` of device memory at `ptr` (16-byte aligned) that kernels launched *after* it will
+ * stream, typically the next projection's weights.  The launch spreads L2 prefetches of that
+ * region over its CTAs and does not wait for them, so HBM keeps working while a
+ * latency-bound kernel runs.  The hint is consumed by that one launch; it never changes a
+ * result.  The reference has no counterpart (its weights stream through shim DMA). */
+int iron_prefetch_hint(const void* ptr, long long bytes);
+
 /* ------------------------------------------------------------------------------------
  * GEMV -- replaces iron/operators/gemv.py:79 (`GEMV`, reference :408-417).
  *   y[b, m] = bf16( sum_k A[b / repeat, m, k] * xn[b, k] ),  f32 accumulation.
@@ -281,6 +290,36 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
                           long long kv_row_stride, long long kv_head_stride, int q_tokens,
                           const int* d_q_tokens, int kv_tokens, const int* d_kv_tokens,
                           int kv_tokens_add, int causal, int window, float scale,
+                          iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * One whole greedy decode step as one persistent kernel -- replaces the decode version the
+ * reference records per call, iron/lm/causal.py:248-287 (embedding gather, per layer
+ * iron/lm/blocks.py:438-470: RMSNorm, q/k/v GEMV, RoPE, cache write, packed attention,
+ * o_proj + residual, RMSNorm, gate/up GEMV, SiLU, product, down_proj + residual; final
+ * RMSNorm, head, argmax iron/operators/sample.py:148).  The same arithmetic and roundings
+ * as the separate entry points above, in one cooperative launch whose phases are
+ * separated by a bounded grid barrier, so the weight stream does not stop between
+ * projections.  Batch 1, one GPU.
+ *   layer_ptrs : DEVICE array of L x 9 pointers per layer, in this order:
+ *                ln1 (E), wqkv ((H+2G)*D x E), wo (E x H*D), ln2 (E), wg (F x E),
+ *                wu (F x E), wd (E x F), k cache (S x G x D), v cache (S x G x D)
+ *   values     : device int32[2] = (token, position); left as (drawn token, position + 1)
+ *   drawn      : device int32[S]; drawn[position] receives the token
+ *   xa, xb (E), q (H*D), act (F), logits (V): bf16 transients, 32-byte aligned
+ *   workspace  : iron_decode_step_workspace_bytes(H, D) bytes, 32-byte aligned, zeroed
+ *                once by the caller.  Byte 128 holds an int status word: 0, or
+ *                IRON_ERR_TIMEOUT after a barrier wait gave up (2 s); it is sticky until the
+ *                caller zeroes it, and a step launched while it is set returns early.
+ *   kv_len_hint: the context length to balance the key split for (0: S).
+ * D is 64 or 128; E, F and H*D multiples of 16.  The launch is cooperative (every CTA
+ * resident); it may be captured in a CUDA graph. */
+size_t iron_decode_step_workspace_bytes(int H, int D);
+int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E, int F, int H, int G, int D,
+                          int V, int S, const void* embed, const void* head,
+                          const void* final_norm, const void* angles, float eps, float scale,
+                          int window, int kv_len_hint, int* values, int* drawn, void* xa,
+                          void* xb, void* q, void* act, void* logits, void* workspace,
                           iron_stream_t stream);
 
 #ifdef __cplusplus

@@ -96,6 +96,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- L2 prefetch of memory a later kernel will stream ------------------------------
+// A launch may carry a hint (iron_prefetch_hint): a region of weights the *next* kernels
+// will read.  Each CTA asks the memory system to pull its slice into L2 with bulk
+// prefetches; nothing waits for them.  Latency-bound kernels (attention over a short
+// context, small GEMVs) leave HBM idle -- the hint fills that time, and the later
+// kernel finds its weights in L2.
+struct PrefetchHint {
+  const char* ptr;
+  long long bytes;
+};
+PrefetchHint take_prefetch_hint();   // host: returns and clears the pending hint
+__device__ __forceinline__ void prefetch_l2_slice(const PrefetchHint& h, int cta, int ctas) {
+  if (h.bytes <= 0) return;
+  constexpr long long kPiece = 16384;
+  long long per = (h.bytes + ctas - 1) / ctas;
+  per = (per + kPiece - 1) / kPiece * kPiece;
+  const long long lo = (long long)cta * per;
+  const long long hi = lo + per < h.bytes ? lo + per : h.bytes;
+  for (long long off = lo; off < hi; off += kPiece) {
+    const unsigned int sz = (unsigned int)((hi - off < kPiece ? hi - off : kPiece) & ~15ll);
+    if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(h.ptr + off), "r"(sz) : "memory");
+  }
+}
+
 // SiLU as the reference's chain computes it: f32 x*sigmoid(x), rounded once to bf16.
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
 

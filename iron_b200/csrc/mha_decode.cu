@@ -39,6 +39,7 @@ struct DecodeParams {
   float scale_log2;         // scale * log2(e)
   int nsplit;
   int stable_prefix;        // rows before the newest are not written by the previous kernel
+  PrefetchHint hint;        // weights a later kernel will stream (may be empty)
 };
 
 template <int D, int GQ>
@@ -60,6 +61,9 @@ __global__ void __launch_bounds__(DecodeCfg<D, GQ>::kThreads) mha_decode_kernel(
   __shared__ float sm_part[GQ][D + 2];  // this CTA's partial: D outputs, max, sum
 
   pdl_launch();
+  if (threadIdx.x == 0)
+    prefetch_l2_slice(p.hint, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                      gridDim.x * gridDim.y * gridDim.z);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x;
   const int chunks = (p.group + GQ - 1) / GQ;
@@ -306,6 +310,7 @@ extern "C" int iron_mha_decode_bf16(const void* Q, const void* K, const void* V,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.nsplit = nsplit;
   p.stable_prefix = stable_prefix;
+  p.hint = take_prefetch_hint();
   cudaStream_t s = (cudaStream_t)stream;
 #define IRON_DEC(DD, QQ) if (D == DD && gq == QQ) return launch_decode<DD, QQ>(p, batch, s);
   IRON_DEC(64, 1) IRON_DEC(64, 2) IRON_DEC(64, 4) IRON_DEC(64, 8)

@@ -329,6 +329,19 @@ static int grid_for(long long work_items, int threads) {
 
 using namespace iron;
 
+static thread_local iron::PrefetchHint g_hint = {nullptr, 0};
+namespace iron {
+PrefetchHint take_prefetch_hint() {
+  PrefetchHint h = g_hint;
+  g_hint = PrefetchHint{nullptr, 0};
+  return h;
+}
+}  // namespace iron
+extern "C" int iron_prefetch_hint(const void* ptr, long long bytes) {
+  if (bytes < 0 || (bytes > 0 && !ptr) || (reinterpret_cast<uintptr_t>(ptr) & 15)) return IRON_ERR_ALIGN;
+  g_hint = iron::PrefetchHint{static_cast<const char*>(ptr), bytes};
+  return IRON_OK;
+}
 static int g_pdl_enabled = 1;
 namespace iron { int pdl_attr_count() { return g_pdl_enabled ? 1 : 0; } }
 extern "C" void iron_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }

@@ -291,3 +291,47 @@ def causal_conv1d(x, taps, *, bias=None, history=None, new_history=None, out=Non
          _ptr(out), B, rows, C, taps.shape[0], rows if valid is None else int(valid), _ptr(d_valid),
          int(bool(decode_order)), int(bool(silu)), _stream())
     return out
+
+
+def prefetch_hint(*tensors) -> None:
+    """Tell the next GEMV-family / decode-attention launch which weights come after it.
+
+    ``tensors`` must be adjacent in memory (one arena run); the launch prefetches the whole
+    run into L2.
+    """
+    ts = [t for t in tensors if t is not None]
+    if not ts:
+        return
+    lo = min(t.data_ptr() for t in ts)
+    hi = max(t.data_ptr() + t.numel() * t.element_size() for t in ts)
+    call("iron_prefetch_hint", lo, hi - lo)
+
+
+def decode_step_workspace(H: int, D: int, device) -> torch.Tensor:
+    """Zeroed workspace of the one-kernel decode step (barrier, status word, partials)."""
+    n = _lib.load().iron_decode_step_workspace_bytes(H, D)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def decode_step_table(layers, device) -> torch.Tensor:
+    """The device table of per-layer pointers ``decode_step`` reads: for every layer
+    ln1, wqkv, wo, ln2, wg, wu, wd, k cache, v cache (cache tensors of one sequence)."""
+    rows = []
+    for l in layers:
+        rows.append([l[n].data_ptr() for n in ("ln1", "wqkv", "wo", "ln2", "wg", "wu", "wd", "k", "v")])
+    return torch.tensor(rows, dtype=torch.int64).to(device)
+
+
+def decode_step(table, *, L, E, F, H, G, D, V, S, embed, head, final_norm, angles, eps, scale,
+                window, kv_len_hint, values, drawn, xa, xb, q, act, logits, workspace):
+    """One greedy decode step in one cooperative launch (token and position in ``values``)."""
+    _bf16(embed, head, final_norm, angles, xa, xb, q, act, logits)
+    call("iron_decode_step_bf16", _ptr(table), L, E, F, H, G, D, V, S, _ptr(embed), _ptr(head),
+         _ptr(final_norm), _ptr(angles), float(eps), float(scale), -1 if window is None else int(window),
+         int(kv_len_hint), _ptr(values), _ptr(drawn), _ptr(xa), _ptr(xb), _ptr(q), _ptr(act),
+         _ptr(logits), _ptr(workspace), _stream())
+
+
+def decode_step_status(workspace: torch.Tensor) -> int:
+    """The step kernel's status word (0, or IRON_ERR_TIMEOUT after a barrier wait gave up)."""
+    return int(workspace[128:132].view(torch.int32).item())

@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 
 import numpy as np
 import torch
@@ -94,6 +95,14 @@ class LlamaEngine:
         H, G, F = layout.heads, layout.kv_heads, layout.ffn
         self.H, self.G, self.F = H, G, F
         self.kv_len_hint = kv_len_hint or S
+        # which launches carry an L2 prefetch hint (bit 0: QKV -> o_proj weights, bit 1:
+        # attention -> gate/up, bit 2: gate/up -> down, bit 3: down -> next layer's QKV)
+        self.prefetch_hints = int(os.environ.get("IRON_PREFETCH_HINTS", "0"))
+        # One sequence on one GPU decodes in one persistent kernel per step; batches and
+        # tensor-parallel shards take the separate launches.  IRON_DECODE_STEP=0 forces the
+        # separate launches (the two paths are compared by the tests).
+        self.fused_step = (batch == 1 and tp_size == 1 and D in (64, 128)
+                           and os.environ.get("IRON_DECODE_STEP", "1") != "0")
 
         # ---- plan the arena: residents first, then the decode step's transients ----
         plan = ArenaPlan()
@@ -171,6 +180,9 @@ class LlamaEngine:
         self._load(weights)
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
+        self.step_ws = K.decode_step_workspace(H, D, self.device)
+        self.step_table = K.decode_step_table(
+            [dict(l, k=l["k"][0], v=l["v"][0]) for l in self.layers], self.device)
         self._graph: torch.cuda.CUDAGraph | None = None
         # Per-call values are staged in a ring of pinned slots: a slot is rewritten only
         # after the copy that read it has completed, so calls can be queued without a
@@ -179,6 +191,7 @@ class LlamaEngine:
         self._ring_done: list[torch.cuda.Event | None] = [None] * len(self._ring)
         self._ring_at = 0
         self._h_token = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._h_status = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     # ------------------------------------------------------------------ weights
     def _load(self, w: dict) -> None:
@@ -211,7 +224,10 @@ class LlamaEngine:
     # ------------------------------------------------------------------ decode step
     @property
     def launches_per_step(self) -> int:
-        """Kernels one decode step launches: gather, five per layer, head, draw."""
+        """Kernels one decode step launches: one persistent kernel, or gather, five per
+        layer, head, draw."""
+        if self.fused_step:
+            return 1
         return 1 + 5 * self.c.num_hidden_layers + 2
 
     @property
@@ -229,16 +245,41 @@ class LlamaEngine:
         c = self.c
         H, G, D = self.H, self.G, c.head_dim
         d_token, d_pos = self.values[0:1], self.values[1:2]
+        if self.fused_step:
+            K.decode_step(self.step_table, L=c.num_hidden_layers, E=c.hidden_size, F=self.F, H=H, G=G,
+                          D=D, V=c.vocab_size, S=c.max_seq_len, embed=self.embed, head=self.head,
+                          final_norm=self.norm, angles=self.angles, eps=c.eps,
+                          scale=c.attention_scale or 1.0 / math.sqrt(D), window=c.window,
+                          kv_len_hint=self.kv_len_hint, values=self.values, drawn=self.drawn[0],
+                          xa=self.x0[0], xb=self.x1[0], q=self.q[0], act=self.act[0],
+                          logits=self.logits_buf[0], workspace=self.step_ws)
+            return
         E2 = c.hidden_size * 2
         x, y, part = self.x0[0], self.x1[0], self.part[0]
         tp = self.tp_size > 1
         K.copy_rows(self.embed, x, ids=d_token, nrows=1, row_bytes=E2, src_rows=c.vocab_size)
-        for l in self.layers:
+        hints = 0 if tp else self.prefetch_hints
+        for i, l in enumerate(self.layers):
+            # Each launch is told which weights follow it, so the latency-bound kernels keep
+            # HBM busy pulling the next projections into L2.
+            if hints & 1:
+                K.prefetch_hint(l["wo"])
             K.decode_qkv_rope(l["wqkv"], x, self.angles, l["k"][0], l["v"][0], self.q[0],
                               H=H, G=G, D=D, d_position=d_pos, norm_weight=l["ln1"], eps=c.eps)
+            if hints & 2:
+                K.prefetch_hint(l["wg"], l["wu"])
             K.mha_decode(self.q, l["k"], l["v"], self.att, d_kv_valid=d_pos, kv_valid_add=1,
                          window=c.window, scale=c.attention_scale, nsplit=self.nsplit,
                          stable_prefix=True)
+            if hints:
+                K.gemv(l["wo"], self.att[0].view(-1), y, residual=x)
+                if hints & 4:
+                    K.prefetch_hint(l["wd"])
+                K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
+                if hints & 8:
+                    K.prefetch_hint(self.layers[i + 1]["wqkv"] if i + 1 < len(self.layers) else self.head[:4096])
+                K.gemv(l["wd"], self.act[0], x, residual=y)
+                continue
             if tp:   # partial sums meet in an all-reduce before each residual add
                 K.gemv(l["wo"], self.att[0].view(-1), part)
                 self._all_reduce(part)
@@ -341,7 +382,9 @@ class LlamaEngine:
         self.capture()
         for _ in range(steps - 1):
             self._graph.replay()
-        return self.drawn[0, n - 1 : n - 1 + steps].cpu().tolist()
+        out = self.drawn[0, n - 1 : n - 1 + steps].cpu().tolist()
+        self.check()
+        return out
 
     def capture(self) -> None:
         """Capture the decode step as one CUDA graph (idempotent)."""
@@ -396,8 +439,19 @@ class LlamaEngine:
         self.set_call(token, position)
         self.step()
         self._h_token.copy_(self.values[0:1], non_blocking=True)
+        if self.fused_step:
+            self._h_status.copy_(self.step_ws[128:132].view(torch.int32), non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if int(self._h_status[0]) != 0:
+            raise RuntimeError("the decode step's grid barrier gave up (IRON_ERR_TIMEOUT)")
         return int(self._h_token[0])
+
+    def check(self) -> None:
+        """Raise if a kernel's bounded wait gave up since the last check (reads two words)."""
+        if int(self.status.item()) != 0:
+            raise RuntimeError("a GEMM pipeline wait gave up (IRON_ERR_TIMEOUT)")
+        if K.decode_step_status(self.step_ws) != 0:
+            raise RuntimeError("the decode step's grid barrier gave up (IRON_ERR_TIMEOUT)")
 
     def logits(self) -> np.ndarray:
         """The last step's logits as float32 on the host."""
@@ -412,6 +466,7 @@ class LlamaEngine:
         for _ in range(steps):
             self._graph.replay()
         out = self.drawn[0, position : position + steps].cpu()
+        self.check()
         return out.tolist()
 
     def feed(self, tokens, start: int = 0) -> np.ndarray:

@@ -39,10 +39,15 @@ def toy_config():
         rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 64))
 
 
-@pytest.fixture(scope="module")
-def case():
+@pytest.fixture(scope="module", params=["one-kernel step", "separate launches"])
+def case(request):
+    """The engine on both of its decode paths: the persistent one-kernel step and the
+    separate launches per projection (what batches and tensor-parallel shards take)."""
     from iron_b200.lm.engine import LlamaEngine
 
+    mp = pytest.MonkeyPatch()
+    mp.setenv("IRON_DECODE_STEP", "1" if request.param == "one-kernel step" else "0")
+    request.addfinalizer(mp.undo)
     weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
     with np.load(GOLDEN) as z:
         golden = {k: z[k] for k in z.files}
