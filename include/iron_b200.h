@@ -298,29 +298,31 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
  * iron/lm/blocks.py:438-470: RMSNorm, q/k/v GEMV, RoPE, cache write, packed attention,
  * o_proj + residual, RMSNorm, gate/up GEMV, SiLU, product, down_proj + residual; final
  * RMSNorm, head, argmax iron/operators/sample.py:148).  The same arithmetic and roundings
- * as the separate entry points above, in one cooperative launch whose phases are
- * separated by a bounded grid barrier, so the weight stream does not stop between
- * projections.  Batch 1, one GPU.
- *   layer_ptrs : DEVICE array of L x 9 pointers per layer, in this order:
+ * as the separate entry points above (dot products in another summation order), in one
+ * cooperative launch, one CTA per SM, whose phases are separated by a bounded grid barrier.
+ * Every warp streams its share of the weights of ALL phases through a private
+ * shared-memory ring filled by bulk asynchronous copies and consumes them on the tensor
+ * cores, so the weight stream does not stop between projections.  Batch 1, one GPU.
+ *   layer_ptrs : DEVICE array of L x 9 pointers per layer, in this order (16-byte aligned):
  *                ln1 (E), wqkv ((H+2G)*D x E), wo (E x H*D), ln2 (E), wg (F x E),
  *                wu (F x E), wd (E x F), k cache (S x G x D), v cache (S x G x D)
  *   values     : device int32[2] = (token, position); left as (drawn token, position + 1)
  *   drawn      : device int32[S]; drawn[position] receives the token
- *   xa, xb (E), q (H*D), act (F), logits (V): bf16 transients, 32-byte aligned
- *   workspace  : iron_decode_step_workspace_bytes(H, D) bytes, 32-byte aligned, zeroed
+ *   xa, xb (E), act (F), logits (V): bf16 transients, 16-byte aligned; on return xa holds
+ *                the residual stream after the last layer and logits the step's logits
+ *   workspace  : iron_decode_step_workspace_bytes(E, H, G, D) bytes, 16-byte aligned, zeroed
  *                once by the caller.  Byte 128 holds an int status word: 0, or
- *                IRON_ERR_TIMEOUT after a barrier wait gave up (2 s); it is sticky until the
- *                caller zeroes it, and a step launched while it is set returns early.
- *   kv_len_hint: the context length to balance the key split for (0: S).
- * D is 64 or 128; E, F and H*D multiples of 16.  The launch is cooperative (every CTA
- * resident); it may be captured in a CUDA graph. */
-size_t iron_decode_step_workspace_bytes(int H, int D);
+ *                IRON_ERR_TIMEOUT after a wait gave up (2 s); it is sticky until the caller
+ *                zeroes it, and a step launched while it is set returns early.
+ * D is 64 or 128; E, F and H*D are multiples of 32 and at most 8192; V is a multiple of 8;
+ * L is at most 64.  The launch is cooperative (every CTA resident); it may be captured in
+ * a CUDA graph. */
+size_t iron_decode_step_workspace_bytes(int E, int H, int G, int D);
 int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E, int F, int H, int G, int D,
                           int V, int S, const void* embed, const void* head,
                           const void* final_norm, const void* angles, float eps, float scale,
-                          int window, int kv_len_hint, int* values, int* drawn, void* xa,
-                          void* xb, void* q, void* act, void* logits, void* workspace,
-                          iron_stream_t stream);
+                          int window, int* values, int* drawn, void* xa, void* xb, void* act,
+                          void* logits, void* workspace, iron_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,37 +1,64 @@
 // One decode step of a Llama-architecture model as ONE persistent kernel.
 //
-// The five kernels a layer takes when launched separately (QKV+RoPE+cache write,
-// attention, o_proj, gate/up+SwiGLU, down_proj) each pay a few microseconds of dependent
-// launch and ramp-up latency, which at batch 1 is as long as the weight streaming itself.
-// Here the whole step -- every layer, the final norm, the head and the greedy draw -- runs
-// as phases of one cooperative grid (two CTAs per SM), separated by a grid-wide barrier
-// that is split in two: a CTA *arrives* when its part of a phase is stored, then issues
-// the first weight loads of the next phase, and only then *waits* for everyone's arrival.
-// The weight stream therefore never stops at a phase boundary.
+// At batch 1 a decode step is a chain of ~80 small dependent operations (per layer: QKV
+// projection + RoPE + cache write, attention, o_proj, gate/up + SwiGLU, down_proj) whose
+// only real cost is streaming 2.5 GB of weights.  Launched one by one, every link of the
+// chain stops the weight stream for a few microseconds.  Here the whole step -- every
+// layer, the final norm, the head and the greedy draw -- runs as phases of one cooperative
+// grid, one CTA per SM, and the weight stream is decoupled from the chain:
 //
-// The barrier is a monotonically increasing counter in global memory (zeroed by a memset
-// node ahead of the kernel).  The launch is cooperative, so every CTA is resident and the
-// barrier cannot deadlock on scheduling; every spin is still bounded by a wall-clock
-// limit, after which the CTA records IRON_ERR_TIMEOUT in the status word and every CTA
-// leaves.  Arithmetic and roundings are those of the separate kernels.
+//   * Every warp owns a private ring of shared-memory slots that the TMA engine fills with
+//     bulk copies (cp.async.bulk + mbarrier complete_tx).  A warp's work items -- 256
+//     columns of 8 consecutive weight rows -- form ONE static sequence over all phases of
+//     the step, so the copies for the next phase are issued, and land, while the CTA is
+//     still waiting for the previous phase to finish everywhere.
+//   * An item is consumed on the tensor cores: the 8 weight rows are the B operand of
+//     mma.sync m16n8k16 (ldmatrix straight from the slot), the activation vector,
+//     replicated over the 16 rows of A, comes from shared memory in fragment order.  A 4 KB
+//     item costs ~50 instructions instead of the ~400 of a SIMT dot product, so the
+//     arithmetic catches up with the prefetched data at several times the HBM rate.
+//   * The narrow projections (q/k/v, o_proj, down_proj) have too few 8-row groups to
+//     occupy the grid, so their reduction dimension is split too: a unit is (row group,
+//     K part), its result an f32 partial in global memory, and the *consumer* of the
+//     projection sums the parts in a fixed order, rounds to bf16 and applies what follows
+//     (residual add and RMSNorm in the next projection's staging; RoPE and the cache write
+//     in the attention phase).  Results do not depend on the grid size or on timing.
+//   * Phases are separated by a grid-wide barrier: a monotonically increasing counter in
+//     global memory (zeroed by a memset node ahead of the kernel).  The launch is
+//     cooperative, so every CTA is resident and the barrier cannot starve; every spin (on
+//     the counter or on an mbarrier) is still bounded by a wall-clock limit, after which the
+//     CTA records IRON_ERR_TIMEOUT in the status word, waits for its own copies in flight and
+//     leaves, and every other CTA follows.
+//
+// Roundings are those of the separate kernels: f32 dot products rounded once to bf16,
+// RMSNorm with its two roundings, RoPE on the rounded projections, the residual added
+// after the rounding, SiLU and the product rounded separately.
 #include <cuda.h>
 
 #include "common.cuh"
-#include "gemv_items.cuh"
 
 namespace iron {
 
-constexpr int kStepThreads = 256;
-constexpr int kStepWarps = kStepThreads / 32;
+constexpr int kStepWarps = 8;
+constexpr int kStepThreads = kStepWarps * 32;
+constexpr int kItemRows = 8;                        // weight rows of one item
+constexpr int kItemCols = 512;                      // columns of one item
+constexpr int kRowPitch = kItemCols * 2 + 16;       // bytes between rows in a slot: ldmatrix
+                                                    // reads 8 rows at once without conflicts
+constexpr int kSlotBytes = kItemRows * kRowPitch;
+constexpr int kSlots = 3;                           // slots in a warp's ring
+constexpr int kStepMaxK = 8192;                     // longest reduction (activation staging)
+constexpr int kStepMaxParts = 8;                    // K parts of a narrow projection
+constexpr int kStepMaxLayers = 64;                  // rows of the layer table in shared memory
 constexpr unsigned long long kStepWaitNs = 2000000000ull;  // 2 s
+constexpr size_t kStepRingBytes = (size_t)kStepWarps * kSlots * kSlotBytes;
+constexpr size_t kStepBarsOff = kStepRingBytes + (size_t)kStepMaxK * 2;
+constexpr size_t kStepTableOff = kStepBarsOff + kStepWarps * kSlots * 8;
+constexpr size_t kStepSmem = kStepTableOff + (size_t)kStepMaxLayers * 9 * sizeof(void*);
 
 struct StepLayer {
   const __nv_bfloat16 *ln1, *wqkv, *wo, *ln2, *wg, *wu, *wd;
   __nv_bfloat16 *k, *v;
-};
-
-struct PhasePlan {
-  int ksplit, ctas;
 };
 
 struct StepParams {
@@ -42,16 +69,25 @@ struct StepParams {
   int window;
   int* values;              // [token, position]; updated at the end
   int* drawn;               // (S)
-  __nv_bfloat16 *xa, *xb, *q, *act, *logits;
-  float* att_part;          // (H, nsplit, D + 2)
+  __nv_bfloat16 *xa, *xb, *act, *logits;
+  float *part_qkv, *part_o, *part_d;   // (parts, rows) f32 partial sums
+  int kp_qkv, kp_o, kp_d;   // K parts of the three narrow projections (powers of two)
+  float* att_part;          // (H, nsplit, D + 4): D outputs, maximum, sum, padding
   int nsplit;
   unsigned int* barrier;
   unsigned long long* best; // one partial argmax key per CTA
   int* status;
-  PhasePlan qkv, o, swiglu, down, headp;
+  unsigned long long* trace; // CTA 0's timestamps: 3 per phase (waited, staged, items done)
 };
 
-// ---- grid barrier, split into arrive and wait ----------------------------------------
+// The layer table is copied to shared memory when the kernel starts: the item cursors look
+// a layer's pointers up at every phase change, on the critical path.
+__device__ __forceinline__ StepLayer* layer_table() {
+  extern __shared__ __align__(128) unsigned char step_smem[];
+  return reinterpret_cast<StepLayer*>(step_smem + kStepTableOff);
+}
+
+// ---- PTX wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -62,6 +98,57 @@ __device__ __forceinline__ unsigned long long step_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ void step_stamp(const StepParams& sp, unsigned int epoch, int which) {
+  if (blockIdx.x == 0 && threadIdx.x == 0 && epoch < 340u) sp.trace[3 * epoch + which] = step_ns();
+}
+__device__ __forceinline__ void step_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void step_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool step_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t step_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+// `bytes` (a multiple of 16) from global to this CTA's shared memory; completion is counted
+// on `bar`.  The weights are read once per step: first in line for eviction from L2.
+__device__ __forceinline__ void step_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar,
+                                               uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void step_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                 uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+// d += a (16x16, rows g and g+8 hold the same vector) * b (16x8)
+__device__ __forceinline__ void step_mma(float (&d)[4], uint32_t a_lo, uint32_t a_hi, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %4, %5, %5}, {%6, %7}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a_lo), "r"(a_hi), "r"(b0), "r"(b1));
+}
+
+// ---- grid barrier, split into arrive and wait ----------------------------------------
 __device__ __forceinline__ void grid_arrive(unsigned int* bar) {
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -103,207 +190,367 @@ __device__ __forceinline__ unsigned long long step_max(unsigned long long a, uns
   return a > b ? a : b;
 }
 
-// Data another CTA wrote earlier in this kernel is read through L2 (L1 is not coherent).
-__device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* p) {
-  return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
-}
-
-enum { PH_PLAIN = 0, PH_SWIGLU = 1, PH_QKV = 2 };
-enum { ST_VECTOR = 0, ST_ATTENTION = 1 };
-
-struct PhaseArgs {
-  const __nv_bfloat16 *A, *A2;       // weights (A2: the up matrix of SWIGLU)
-  const __nv_bfloat16* x;            // ST_VECTOR: the activation vector
-  const __nv_bfloat16* norm_w;       // non-null: RMSNorm(x) * norm_w is staged
-  const __nv_bfloat16* residual;     // PLAIN: added after the rounding
-  __nv_bfloat16* y;
-  int rows, K;                       // output rows, reduction length
-  PhasePlan plan;
-  int stage;                         // ST_*
-  int track_best;                    // PLAIN: keep the greedy maximum of the rows written
-  // QKV
-  __nv_bfloat16 *k_cache, *v_cache;
-  int pos;
-};
-
 struct StepShared {
   int abort;
   float red[32];
-  float part[2 * kStepWarps];
   unsigned long long best[kStepWarps];
   float att_ml[kStepWarps][2];
+  alignas(16) float q[128];             // this CTA's query head: rotated, scaled (attention phase)
+  alignas(16) __nv_bfloat16 knew[128];  // the new cache rows of this CTA's KV head
+  alignas(16) __nv_bfloat16 vnew[128];
 };
 
-// One GEMV-shaped phase.  `xs` holds K/8 16-byte chunks of the staged activation vector.
-// The CTA's first weight item is issued before the wait for the previous phase.
-template <int MODE, bool WIDE>
-__device__ __forceinline__ bool gemv_phase(const StepParams& sp, const PhaseArgs& a, uint4* xs, StepShared& sh,
-                                           unsigned int& epoch, unsigned long long& best) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int K = a.K, nch = K >> 3;
-  const int KS = a.plan.ksplit;
-  const int groups = kStepWarps / KS;
-  const int g = warp / KS, ks = warp % KS;
-  constexpr int kStep = 32 * kItem;
-  const int per = ((nch + KS - 1) / KS + 1) & ~1;
-  const int ch_lo = min(nch, ks * per), ch_hi = min(nch, ch_lo + per);
-  const int half = sp.D >> 1;
-  int npairs;
-  if (MODE == PH_PLAIN) npairs = (a.rows + 1) >> 1;
-  else if (MODE == PH_SWIGLU) npairs = a.rows;
-  else npairs = a.rows >> 1;
-  const bool active = (int)blockIdx.x < a.plan.ctas;
-  const int stride = a.plan.ctas * groups;
+// ---- the static sequence of weight items ----------------------------------------------
+// Phase ids: 4 per layer (QKV, o_proj, gate/up, down_proj), then the head.  The attention
+// phase streams no weights and has no id.  A phase is cut into units that go round the
+// grid's warps; a unit is cut into items of 8 rows x 256 columns.
+//   PH_PART   a unit is (8-row group, K part); the result is an f32 partial per row.
+//   PH_SWIGLU a unit is an 8-row group of the gate matrix followed by the same rows of the
+//             up matrix, over all of K; the result is bf16 silu(gate) * up.
+//   PH_HEAD   a unit is an 8-row group over all of K; the result is a bf16 logit per row.
+enum { PH_PART = 0, PH_SWIGLU = 1, PH_HEAD = 2 };
 
-  auto rows_of = [&](int pair, int& ra, int& rb, const uint4*& qa, const uint4*& qb) {
-    const __nv_bfloat16 *pa, *pb;
-    if (MODE == PH_PLAIN) {
-      ra = 2 * pair; rb = ra + 1;
-      pa = a.A + (size_t)ra * K;
-      pb = (rb < a.rows) ? pa + K : pa;
-    } else if (MODE == PH_SWIGLU) {
-      ra = rb = pair;
-      pa = a.A + (size_t)ra * K;
-      pb = a.A2 + (size_t)ra * K;
-    } else {
-      const int head = pair / half, i = pair - head * half;
-      ra = head * sp.D + i; rb = ra + half;
-      pa = a.A + (size_t)ra * K;
-      pb = a.A + (size_t)rb * K;
-    }
-    qa = reinterpret_cast<const uint4*>(pa);
-    qb = reinterpret_cast<const uint4*>(pb);
-  };
+struct Phase {
+  const __nv_bfloat16 *A, *A2;
+  float* part;       // PH_PART: (parts, rows)
+  int mode, units, K, rows, kshift, part_cols, chunks, nitems, first;
+};
 
-  int base = blockIdx.x * groups;
-  int ra = 0, rb = 0;
-  const uint4 *qa = nullptr, *qb = nullptr;
-  bool live = active && base + g < npairs;
-  if (live) rows_of(base + g, ra, rb, qa, qb);
-  Item cur;
-  issue<WIDE>(cur, qa, qb, ch_lo, lane, ch_hi, live && ch_lo < ch_hi);
+__device__ __forceinline__ Phase load_phase(const StepParams& sp, int pid, int gw, int NW) {
+  Phase ph;
+  const int rows_qkv = (sp.H + 2 * sp.G) * sp.D;
+  const unsigned int u_qkv = (unsigned int)(rows_qkv >> 3) * (unsigned int)sp.kp_qkv;
+  const unsigned int u_o = (unsigned int)(sp.E >> 3) * (unsigned int)sp.kp_o;
+  const unsigned int u_sw = (unsigned int)(sp.F >> 3);
+  const unsigned int u_d = (unsigned int)(sp.E >> 3) * (unsigned int)sp.kp_d;
+  const int layer = pid >> 2, j = pid & 3;
+  unsigned int before = (unsigned int)layer * (u_qkv + u_o + u_sw + u_d);   // units of every earlier phase
+  int parts = 1;
+  ph.A2 = nullptr; ph.part = nullptr;
+  if (layer >= sp.L) {
+    ph.A = sp.head; ph.mode = PH_HEAD; ph.rows = sp.V; ph.K = sp.E;
+  } else {
+    const StepLayer& ly = layer_table()[layer];
+    if (j == 0) { ph.A = ly.wqkv; ph.mode = PH_PART; ph.rows = rows_qkv; ph.K = sp.E; parts = sp.kp_qkv; ph.part = sp.part_qkv; }
+    else if (j == 1) { ph.A = ly.wo; ph.mode = PH_PART; ph.rows = sp.E; ph.K = sp.H * sp.D; parts = sp.kp_o; ph.part = sp.part_o; before += u_qkv; }
+    else if (j == 2) { ph.A = ly.wg; ph.A2 = ly.wu; ph.mode = PH_SWIGLU; ph.rows = sp.F; ph.K = sp.E; before += u_qkv + u_o; }
+    else { ph.A = ly.wd; ph.mode = PH_PART; ph.rows = sp.E; ph.K = sp.F; parts = sp.kp_d; ph.part = sp.part_d; before += u_qkv + u_o + u_sw; }
+  }
+  ph.kshift = 31 - __clz(parts);
+  ph.units = (ph.rows >> 3) << ph.kshift;
+  ph.part_cols = (((ph.K >> ph.kshift) + 31) >> 5) << 5;
+  ph.chunks = (ph.part_cols + kItemCols - 1) / kItemCols;
+  ph.nitems = ph.mode == PH_SWIGLU ? 2 * ph.chunks : ph.chunks;
+  // units go round the grid's warps, each phase starting where the one before stopped
+  const int rot = (int)(before % (unsigned int)NW);
+  ph.first = gw - rot + (gw < rot ? NW : 0);
+  return ph;
+}
 
-  // everything the previous phase wrote is visible after this
-  if (!grid_wait(sp.barrier, epoch, sp.status, &sh.abort)) return false;
+// Where an item's weights are and what it covers.
+struct ItemGeom {
+  const __nv_bfloat16* src;   // first of the 8 row segments
+  int group, kpart, col0, ncols;
+  bool second;                // PH_SWIGLU: the up-matrix half of the unit
+};
+__device__ __forceinline__ ItemGeom item_geom(const Phase& ph, int unit, int item) {
+  ItemGeom g;
+  g.group = unit >> ph.kshift;
+  g.kpart = unit - (g.group << ph.kshift);
+  g.second = ph.mode == PH_SWIGLU && item >= ph.chunks;
+  const int it = g.second ? item - ph.chunks : item;
+  g.col0 = g.kpart * ph.part_cols + it * kItemCols;
+  const int end = min(ph.K, (g.kpart + 1) * ph.part_cols);
+  g.ncols = max(0, min(kItemCols, end - g.col0));
+  g.src = (g.second ? ph.A2 : ph.A) + (size_t)g.group * kItemRows * ph.K + g.col0;
+  return g;
+}
 
-  if (active) {
-    // ---- stage the activation vector ----
-    if (a.stage == ST_VECTOR) {
-      const uint4* xg = reinterpret_cast<const uint4*>(a.x);
-      float ss = 0.f;
-      for (int i = tid; i < nch; i += kStepThreads) {
-        const uint4 v = __ldcg(xg + i);
-        xs[i] = v;
-        if (a.norm_w) {
-          float f[8];
-          unpack8(v, f);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-        }
-      }
-      if (a.norm_w) {
-        const float tot = block_sum(ss, sh.red);
-        const float inv = 1.0f / sqrtf(tot / (float)K + sp.eps);
-        const uint4* wg = reinterpret_cast<const uint4*>(a.norm_w);
-        for (int i = tid; i < nch; i += kStepThreads) {
-          float f[8], w[8];
-          unpack8(xs[i], f);
-          unpack8(ld_cached(wg + i), w);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv) * w[j];
-          xs[i] = pack8(f);
-        }
-      }
-    } else {
-      // the attention phase left (max, sum, D outputs) per head and key split: fold them
-      const int D = sp.D, ns = sp.nsplit;
-      for (int i = tid; i < nch; i += kStepThreads) {
-        const int h = (i * 8) / D, d0 = (i * 8) - h * D;
-        const int PS = D + 4;  // partial stride: D outputs, max, sum, padded to 16 bytes
-        const float* src = sp.att_part + (size_t)h * ns * PS;
-        float M = -INFINITY;
-        for (int s = 0; s < ns; ++s) M = fmaxf(M, __ldcg(src + s * PS + D));
-        float L = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < ns; ++s) {
-          const float ms = __ldcg(src + s * PS + D);
-          const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-          L = fmaf(__ldcg(src + s * PS + D + 1), c, L);
-          const float4 o0 = __ldcg(reinterpret_cast<const float4*>(src + s * PS + d0));
-          const float4 o1 = __ldcg(reinterpret_cast<const float4*>(src + s * PS + d0 + 4));
-          acc[0] = fmaf(o0.x, c, acc[0]); acc[1] = fmaf(o0.y, c, acc[1]);
-          acc[2] = fmaf(o0.z, c, acc[2]); acc[3] = fmaf(o0.w, c, acc[3]);
-          acc[4] = fmaf(o1.x, c, acc[4]); acc[5] = fmaf(o1.y, c, acc[5]);
-          acc[6] = fmaf(o1.z, c, acc[6]); acc[7] = fmaf(o1.w, c, acc[7]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = L > 0.f ? acc[j] / L : 0.f;
-        xs[i] = pack8(acc);
-      }
-    }
-    __syncthreads();
+// A position in a warp's item sequence.
+struct Cursor {
+  Phase ph;
+  int pid, unit, item, idx;
+  bool done;
+};
 
-    for (; base < npairs; base += stride) {
-      float acc0 = 0.f, acc1 = 0.f;
-      const bool live_n = base + stride + g < npairs;
-      int ra_n = 0, rb_n = 0;
-      const uint4 *qa_n = nullptr, *qb_n = nullptr;
-      if (live_n) rows_of(base + stride + g, ra_n, rb_n, qa_n, qb_n);
-      for (int c0 = ch_lo; c0 < ch_hi; c0 += kStep) {
-        Item nxt;
-        if (c0 + kStep < ch_hi) issue<WIDE>(nxt, qa, qb, c0 + kStep, lane, ch_hi, live);
-        else issue<WIDE>(nxt, qa_n, qb_n, ch_lo, lane, ch_hi, live_n);
-        consume<WIDE>(cur, xs, c0, lane, ch_hi, acc0, acc1);
-        cur = nxt;
-      }
-      acc0 = warp_sum(acc0);
-      acc1 = warp_sum(acc1);
-      if (KS > 1) {
-        if (lane == 0) { sh.part[warp * 2] = acc0; sh.part[warp * 2 + 1] = acc1; }
-        __syncthreads();
-        if (ks == 0) {
-          acc0 = 0.f; acc1 = 0.f;
-          for (int s = 0; s < KS; ++s) { acc0 += sh.part[(warp + s) * 2]; acc1 += sh.part[(warp + s) * 2 + 1]; }
-        }
-        __syncthreads();
-      }
-      if (live && ks == 0 && lane == 0) {
-        if (MODE == PH_PLAIN) {
-          float v0 = round_bf16(acc0), v1 = round_bf16(acc1);
-          if (a.residual) {
-            v0 = round_bf16(__fadd_rn(v0, ldcg_bf16(a.residual + ra)));
-            if (rb < a.rows) v1 = round_bf16(__fadd_rn(v1, ldcg_bf16(a.residual + rb)));
-          }
-          a.y[ra] = __float2bfloat16_rn(v0);
-          if (a.track_best) best = step_max(best, step_key(v0, ra));
-          if (rb < a.rows) {
-            a.y[rb] = __float2bfloat16_rn(v1);
-            if (a.track_best) best = step_max(best, step_key(v1, rb));
-          }
-        } else if (MODE == PH_SWIGLU) {
-          const float gate = round_bf16(acc0), up = round_bf16(acc1);
-          const float act = round_bf16(silu_f32(gate));
-          a.y[ra] = __float2bfloat16_rn(__fmul_rn(act, up));
-        } else {
-          const int head = ra / sp.D, i = ra - head * sp.D;
-          float x1 = round_bf16(acc0), x2 = round_bf16(acc1);
-          if (head < sp.H + sp.G) {
-            const __nv_bfloat16* ang = sp.angles + (size_t)a.pos * sp.D;
-            const float c = __bfloat162float(ang[2 * i]), s = __bfloat162float(ang[2 * i + 1]);
-            const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
-            const float y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
-            x1 = y1; x2 = y2;
-          }
-          __nv_bfloat16* dst;
-          if (head < sp.H) dst = a.y + (size_t)head * sp.D;
-          else if (head < sp.H + sp.G) dst = a.k_cache + ((size_t)a.pos * sp.G + (head - sp.H)) * sp.D;
-          else dst = a.v_cache + ((size_t)a.pos * sp.G + (head - sp.H - sp.G)) * sp.D;
-          dst[i] = __float2bfloat16_rn(x1);
-          dst[i + half] = __float2bfloat16_rn(x2);
-        }
-      }
-      live = live_n; ra = ra_n; rb = rb_n; qa = qa_n; qb = qb_n;
+__device__ __forceinline__ void cursor_seek(Cursor& c, const StepParams& sp, int gw, int NW) {
+  // move to the next phase that has a unit for this warp
+  const int NP = 4 * sp.L + 1;
+  while (c.unit >= c.ph.units) {
+    if (++c.pid >= NP) { c.done = true; return; }
+    c.ph = load_phase(sp, c.pid, gw, NW);
+    c.unit = c.ph.first;
+  }
+}
+__device__ __forceinline__ void cursor_start(Cursor& c, const StepParams& sp, int gw, int NW) {
+  c.pid = -1; c.unit = 0; c.item = 0; c.idx = 0; c.done = false;
+  c.ph.units = 0;
+  cursor_seek(c, sp, gw, NW);
+}
+__device__ __forceinline__ void cursor_advance(Cursor& c, const StepParams& sp, int gw, int NW) {
+  ++c.idx;
+  if (++c.item < c.ph.nitems) return;
+  c.item = 0;
+  c.unit += NW;
+  cursor_seek(c, sp, gw, NW);
+}
+
+// What a warp carries through the step: its ring (slots filled by the TMA engine, one
+// mbarrier per slot) and its two positions in the item sequence.
+struct Stream {
+  uint32_t slots;    // shared-memory address of kSlots x kSlotBytes
+  uint64_t* bars;    // kSlots
+  uint64_t policy;
+  Cursor iss, con;   // the next item to start copying / to consume
+  int gw, NW;        // this warp's index in the grid, warps in the grid
+};
+
+// The warp starts the copies of the item at `st.iss` into the slot its index maps to:
+// eight row segments, one per lane.
+__device__ __forceinline__ void ring_issue(const Stream& st, int lane) {
+  const Cursor& c = st.iss;
+  const ItemGeom g = item_geom(c.ph, c.unit, c.item);
+  const int s = c.idx % kSlots;
+  if (lane == 0) step_mbar_expect_tx(st.bars + s, (uint32_t)(kItemRows * g.ncols * 2));
+  __syncwarp();
+  if (lane < kItemRows && g.ncols > 0)
+    step_bulk_load(st.slots + s * kSlotBytes + lane * kRowPitch, g.src + (size_t)lane * c.ph.K,
+                   (uint32_t)g.ncols * 2u, st.bars + s, st.policy);
+}
+
+// Every lane waits for the item with index `idx` to have landed; false when out of time.
+__device__ __forceinline__ bool ring_wait(const Stream& st, int idx, int* status, int* s_abort) {
+  uint64_t* bar = st.bars + idx % kSlots;
+  const uint32_t parity = (uint32_t)(idx / kSlots) & 1u;
+  if (step_mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = step_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (step_mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0 && step_ns() - t0 > kStepWaitNs) {
+      *reinterpret_cast<volatile int*>(status) = IRON_ERR_TIMEOUT;
+      *reinterpret_cast<volatile int*>(s_abort) = 1;
+      return false;
     }
   }
+}
+
+// The staged activation vector lives in shared memory in mma fragment order: within each
+// block of 32 columns (16 words of two bf16) word 4c + t sits at position 4t + c, so that
+// one 16-byte load gives lane t its A operands for two k16 steps.
+__device__ __forceinline__ void store_x8(uint32_t* xs_words, int chunk, const uint4& v) {
+  // `chunk` counts groups of 8 columns: block chunk/4, c = chunk%4, words t = 0..3
+  uint32_t* p = xs_words + (chunk >> 2) * 16 + (chunk & 3);
+  p[0] = v.x; p[4] = v.y; p[8] = v.z; p[12] = v.w;
+}
+
+enum { ST_VECTOR = 0, ST_PARTIAL = 1, ST_ATTENTION = 2 };
+
+struct PhaseArgs {
+  int mode;                          // PH_*
+  int stage;                         // ST_*
+  int K;                             // reduction length (the staged vector)
+  const __nv_bfloat16* x;            // ST_VECTOR: the activation vector
+  const float* parts;                // ST_PARTIAL: (nparts, K) partial sums of the projection before
+  int nparts;
+  const __nv_bfloat16* residual;     // ST_PARTIAL: added after the rounding
+  __nv_bfloat16* keep;               // ST_PARTIAL: the sum is also the new residual stream (CTA 0 stores it)
+  const __nv_bfloat16* norm_w;       // non-null: RMSNorm(x) * norm_w is staged
+  __nv_bfloat16* y;                  // PH_SWIGLU, PH_HEAD: the output vector
+};
+
+// One weight phase: wait for the phase before, stage its result as this phase's activation
+// vector, then every warp consumes the items of phase `pid` in its sequence -- re-arming
+// each slot it frees with the next item of the sequence, whatever phase that belongs to.
+// Whatever does not depend on the phase before (norm weights, the residual vector, which
+// is at least two phases old) is fetched ahead of the wait.
+__device__ __forceinline__ bool weight_phase(const StepParams& sp, int pid, const PhaseArgs& a, Stream& st,
+                                             unsigned char* xs_bytes, StepShared& sh, unsigned int& epoch,
+                                             unsigned long long& best) {
+  constexpr int kIter = (kStepMaxK / 8 + kStepThreads - 1) / kStepThreads;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int K = a.K, nch = K >> 3;
+  uint32_t* xs_words = reinterpret_cast<uint32_t*>(xs_bytes);
+
+  uint4 wreg[kIter], rreg[kIter];
+#pragma unroll
+  for (int k = 0; k < kIter; ++k) {
+    const int i = tid + k * kStepThreads;
+    wreg[k] = make_uint4(0, 0, 0, 0);
+    rreg[k] = make_uint4(0, 0, 0, 0);
+    if (i < nch) {
+      if (a.norm_w) wreg[k] = ld_cached(reinterpret_cast<const uint4*>(a.norm_w) + i);
+      if (a.stage == ST_PARTIAL && a.residual) rreg[k] = __ldcg(reinterpret_cast<const uint4*>(a.residual) + i);
+    }
+  }
+
+  if (!grid_wait(sp.barrier, epoch, sp.status, &sh.abort)) return false;
+  step_stamp(sp, epoch, 0);
+
+  // ---- stage the activation vector ----
+  if (a.stage != ST_ATTENTION) {
+    uint4 xreg[kIter];
+    if (a.stage == ST_VECTOR) {
+#pragma unroll
+      for (int k = 0; k < kIter; ++k) {
+        const int i = tid + k * kStepThreads;
+        xreg[k] = i < nch ? __ldcg(reinterpret_cast<const uint4*>(a.x) + i) : make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      // the projection before left f32 partial sums: add them in a fixed order, round,
+      // add the residual, round -- this is the new residual stream
+#pragma unroll
+      for (int k = 0; k < kIter; ++k) {
+        const int i = tid + k * kStepThreads;
+        xreg[k] = make_uint4(0, 0, 0, 0);
+        if (i < nch) {
+          float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+          for (int p = 0; p < a.nparts; ++p) {
+            const float4 lo = __ldcg(reinterpret_cast<const float4*>(a.parts + (size_t)p * K + i * 8));
+            const float4 hi = __ldcg(reinterpret_cast<const float4*>(a.parts + (size_t)p * K + i * 8 + 4));
+            s[0] += lo.x; s[1] += lo.y; s[2] += lo.z; s[3] += lo.w;
+            s[4] += hi.x; s[5] += hi.y; s[6] += hi.z; s[7] += hi.w;
+          }
+          if (a.residual) {
+            float r[8];
+            unpack8(rreg[k], r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] = __fadd_rn(round_bf16(s[j]), r[j]);
+          }
+          xreg[k] = pack8(s);
+          if (a.keep && blockIdx.x == 0) reinterpret_cast<uint4*>(a.keep)[i] = xreg[k];
+        }
+      }
+    }
+    if (a.norm_w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < kIter; ++k) {
+        float f[8];
+        unpack8(xreg[k], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+      const float tot = block_sum(ss, sh.red);
+      const float inv = 1.0f / sqrtf(tot / (float)K + sp.eps);
+#pragma unroll
+      for (int k = 0; k < kIter; ++k) {
+        float f[8], w[8];
+        unpack8(xreg[k], f);
+        unpack8(wreg[k], w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv) * w[j];
+        xreg[k] = pack8(f);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kIter; ++k) {
+      const int i = tid + k * kStepThreads;
+      if (i < nch) store_x8(xs_words, i, xreg[k]);
+    }
+  } else {
+    // the attention phase left (D outputs, maximum, sum) per head and key split: fold them
+    const int D = sp.D, ns = sp.nsplit, PS = D + 4;
+    for (int i = tid; i < nch; i += kStepThreads) {
+      const int h = (i * 8) / D, d0 = (i * 8) - h * D;
+      const float* src = sp.att_part + (size_t)h * ns * PS;
+      float ms[16], M = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        ms[s] = s < ns ? __ldcg(src + s * PS + D) : -INFINITY;
+        M = fmaxf(M, ms[s]);
+      }
+      float L = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int s = 0; s < ns; ++s) {
+        const float ls = __ldcg(src + s * PS + D + 1);
+        const float4 o0 = __ldcg(reinterpret_cast<const float4*>(src + s * PS + d0));
+        const float4 o1 = __ldcg(reinterpret_cast<const float4*>(src + s * PS + d0 + 4));
+        const float mv = __ldcg(src + s * PS + D);
+        const float c = (mv == -INFINITY) ? 0.f : exp2f(mv - M);
+        L = fmaf(ls, c, L);
+        acc[0] = fmaf(o0.x, c, acc[0]); acc[1] = fmaf(o0.y, c, acc[1]);
+        acc[2] = fmaf(o0.z, c, acc[2]); acc[3] = fmaf(o0.w, c, acc[3]);
+        acc[4] = fmaf(o1.x, c, acc[4]); acc[5] = fmaf(o1.y, c, acc[5]);
+        acc[6] = fmaf(o1.z, c, acc[6]); acc[7] = fmaf(o1.w, c, acc[7]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = L > 0.f ? acc[j] / L : 0.f;
+      store_x8(xs_words, i, pack8(acc));
+    }
+  }
+  __syncthreads();
+  step_stamp(sp, epoch, 1);
+
+  // ---- this warp's items of the phase, on the tensor cores ----
+  float acc[4][4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f; }
+  float gate0 = 0.f, gate1 = 0.f;
+  int dbgn = 0;
+  const uint32_t xs_addr = smem_u32(xs_bytes) + (lane & 3) * 16;
+  while (!st.con.done && st.con.pid == pid) {
+    const Cursor& c = st.con;
+    const bool dbg = blockIdx.x == 0 && tid == 0 && epoch >= 37u && epoch <= 39u;
+    unsigned long long* dt = sp.trace + 700 + (epoch - 37u) * 64 + (dbgn < 12 ? dbgn : 12) * 5;
+    if (dbg) dt[0] = step_ns();
+    if (!ring_wait(st, c.idx, sp.status, &sh.abort)) break;
+    if (dbg) dt[1] = step_ns();
+    const ItemGeom g = item_geom(c.ph, c.unit, c.item);
+    const uint32_t w_addr = st.slots + (c.idx % kSlots) * kSlotBytes + (lane & 7) * kRowPitch + (lane >> 3) * 16;
+    const uint32_t x_addr = xs_addr + (g.col0 >> 5) * 64;
+    const int nb = g.ncols >> 5;
+#pragma unroll
+    for (int b = 0; b < kItemCols / 32; ++b) {
+      if (b < nb) {
+        uint32_t r0, r1, r2, r3;
+        step_ldmatrix_x4(w_addr + b * 64, r0, r1, r2, r3);
+        uint4 xa;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w)
+                     : "r"(x_addr + b * 64));
+        step_mma(acc[(2 * b) & 3], xa.x, xa.y, r0, r1);
+        step_mma(acc[(2 * b + 1) & 3], xa.z, xa.w, r2, r3);
+      }
+    }
+    // the slot is free: start the copies of the item kSlots ahead in the sequence
+    __syncwarp();
+    if (dbg) dt[2] = step_ns() + (unsigned long long)(acc[0][0] == 123.f);
+    if (!st.iss.done) {
+      ring_issue(st, lane);
+      if (dbg) dt[4] = step_ns();
+      cursor_advance(st.iss, sp, st.gw, st.NW);
+    }
+    if (dbg) dt[3] = step_ns();
+    const bool half_done = c.ph.mode == PH_SWIGLU && c.item == c.ph.chunks - 1;
+    if (half_done || c.item == c.ph.nitems - 1) {
+      // every lane (g, t) holds rows 2t and 2t + 1 of the group
+      const float v0 = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
+      const float v1 = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f; }
+      const int row = g.group * kItemRows + 2 * (lane & 3);
+      if (half_done) {
+        gate0 = v0; gate1 = v1;
+      } else if (lane < 4) {
+        if (c.ph.mode == PH_PART) {
+          *reinterpret_cast<float2*>(c.ph.part + (size_t)g.kpart * c.ph.rows + row) = make_float2(v0, v1);
+        } else if (c.ph.mode == PH_HEAD) {
+          const float l0 = round_bf16(v0), l1 = round_bf16(v1);
+          *reinterpret_cast<__nv_bfloat162*>(a.y + row) =
+              __halves2bfloat162(__float2bfloat16_rn(l0), __float2bfloat16_rn(l1));
+          best = step_max(best, step_max(step_key(l0, row), step_key(l1, row + 1)));
+        } else {
+          const float a0 = round_bf16(silu_f32(round_bf16(gate0))), a1 = round_bf16(silu_f32(round_bf16(gate1)));
+          *reinterpret_cast<__nv_bfloat162*>(a.y + row) = __halves2bfloat162(
+              __float2bfloat16_rn(__fmul_rn(a0, round_bf16(v0))), __float2bfloat16_rn(__fmul_rn(a1, round_bf16(v1))));
+        }
+      }
+    }
+    cursor_advance(st.con, sp, st.gw, st.NW);
+    if (dbg) { ++dbgn; }
+  }
+  step_stamp(sp, epoch, 2);
   grid_arrive(sp.barrier);
   ++epoch;
   return true;
@@ -312,14 +559,18 @@ __device__ __forceinline__ bool gemv_phase(const StepParams& sp, const PhaseArgs
 // One-query attention of every head over the cache rows [lo, pos], the keys of a head
 // split over `nsplit` CTAs.  A unit is (head, split); the CTA leaves the unnormalised
 // partial (D outputs, running maximum, sum) in sp.att_part for the o_proj phase to fold.
-// The first batch of K and V rows is in flight before the wait for the QKV phase; the
-// newest row, which that phase wrote, is read again afterwards.
+//
+// This phase is also the consumer of the q/k/v projection: it sums that projection's K
+// parts for its own query head and KV head, rounds to bf16 and applies RoPE to q and k
+// (rows i and i + D/2 rotate together, cos at even and sin at odd columns of the angle
+// row), and one CTA per KV head stores the new k and v rows into the caches.  The first
+// batch of older K and V rows is in flight before the wait for the projection.
 template <int D>
-__device__ __forceinline__ bool attention_phase(const StepParams& sp, const __nv_bfloat16* Kc,
-                                                const __nv_bfloat16* Vc, int pos, StepShared& sh,
-                                                float (*sm_o)[D], unsigned int& epoch) {
-  constexpr int LPK = D / 8, KPW = 32 / LPK, TS = KPW * kStepWarps, UNR = 4;
-  constexpr int PS = D + 4;
+__device__ __forceinline__ bool attention_phase(const StepParams& sp, __nv_bfloat16* Kc, __nv_bfloat16* Vc,
+                                                int pos, StepShared& sh, float (*sm_o)[D],
+                                                unsigned int& epoch) {
+  constexpr int LPK = D / 8, KPW = 32 / LPK, TS = KPW * kStepWarps, UNR = 8;
+  constexpr int PS = D + 4, HALF = D / 2;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int dsel = lane % LPK, kslot = warp * KPW + lane / LPK;
   const int ns = sp.nsplit, units = sp.H * ns, group = sp.H / sp.G;
@@ -327,13 +578,14 @@ __device__ __forceinline__ bool attention_phase(const StepParams& sp, const __nv
   const int lo = (sp.window >= 0) ? max(0, kv_valid - 1 - sp.window) : 0;
   const int per = (kv_valid - lo + ns - 1) / ns;
   const size_t row = (size_t)sp.G * D;   // elements between cache rows
+  const int rows_qkv = (sp.H + 2 * sp.G) * D;
 
   int unit = blockIdx.x;
-  int h = 0, k_begin = 0, k_end = 0;
+  int h = 0, split = 0, k_begin = 0, k_end = 0;
   const __nv_bfloat16 *Kb = Kc, *Vb = Vc;
   auto place = [&](int u) {
     h = u / ns;
-    const int split = u - h * ns;
+    split = u - h * ns;
     k_begin = lo + split * per;
     k_end = min(kv_valid, k_begin + per);
     Kb = Kc + (size_t)(h / group) * D + dsel * 8;
@@ -353,29 +605,72 @@ __device__ __forceinline__ bool attention_phase(const StepParams& sp, const __nv
   if (unit < units) {
     place(unit);
     early = k_begin < k_end;
-    if (early) load_batch(k_begin);
+    if (early) load_batch(k_begin);   // the newest row is not in the cache yet: replaced below
+  }
+  // the RoPE row of this position
+  float cs = 1.f, sn = 0.f;
+  if (tid < 2 * HALF) {
+    const int i = tid < HALF ? tid : tid - HALF;
+    const __nv_bfloat16* ang = sp.angles + (size_t)pos * D;
+    cs = __bfloat162float(ang[2 * i]);
+    sn = __bfloat162float(ang[2 * i + 1]);
   }
 
   if (!grid_wait(sp.barrier, epoch, sp.status, &sh.abort)) return false;
+  step_stamp(sp, epoch, 0);
+  step_stamp(sp, epoch, 1);
 
   for (; unit < units; unit += gridDim.x) {
     if (!early) place(unit);
-    float q[8], o[8], m = -INFINITY, l = 0.f;
-    unpack8(__ldcg(reinterpret_cast<const uint4*>(sp.q + (size_t)h * D + dsel * 8)), q);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { q[j] *= sp.scale_log2; o[j] = 0.f; }
-    if (early) {
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int k = k_begin + u * TS + kslot;
-        if (k == kv_valid - 1) {
-          kraw[u] = __ldcg(reinterpret_cast<const uint4*>(Kb + (size_t)k * row));
-          vraw[u] = __ldcg(reinterpret_cast<const uint4*>(Vb + (size_t)k * row));
+    // ---- q, and the new k and v rows of this head's KV head, from the projection's parts ----
+    {
+      const int kh = h / group;
+      auto part_sum = [&](int r) {
+        float s = 0.f;
+        for (int p = 0; p < sp.kp_qkv; ++p) s += __ldcg(sp.part_qkv + (size_t)p * rows_qkv + r);
+        return round_bf16(s);
+      };
+      if (tid < 2 * HALF) {
+        // threads [0, HALF): q pairs; [HALF, 2 HALF): k pairs
+        const bool is_k = tid >= HALF;
+        const int i = is_k ? tid - HALF : tid;
+        const int base = is_k ? (sp.H + kh) * D : h * D;
+        const float x1 = part_sum(base + i), x2 = part_sum(base + i + HALF);
+        const float y1 = round_bf16(__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn)));
+        const float y2 = round_bf16(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
+        if (is_k) {
+          sh.knew[i] = __float2bfloat16_rn(y1);
+          sh.knew[i + HALF] = __float2bfloat16_rn(y2);
+        } else {
+          sh.q[i] = y1 * sp.scale_log2;
+          sh.q[i + HALF] = y2 * sp.scale_log2;
         }
       }
+      if (tid >= kStepThreads - D) {
+        const int i = tid - (kStepThreads - D);
+        sh.vnew[i] = __float2bfloat16_rn(part_sum((sp.H + sp.G + kh) * D + i));
+      }
+      __syncthreads();
+      if (h == kh * group && split == 0 && tid < 2 * LPK) {
+        // one CTA per KV head stores the new rows for the steps to come
+        const int i = tid % LPK;
+        __nv_bfloat16* dst = (tid < LPK ? Kc : Vc) + (size_t)pos * row + (size_t)kh * D + i * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>((tid < LPK ? sh.knew : sh.vnew) + i * 8);
+      }
     }
+    float q[8], o[8], m = -INFINITY, l = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { q[j] = sh.q[dsel * 8 + j]; o[j] = 0.f; }
     for (int kb = k_begin; kb < k_end; kb += TS * UNR) {
       if (!(early && kb == k_begin)) load_batch(kb);
+      // the newest row comes from this step's projection
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        if (kb + u * TS + kslot == kv_valid - 1) {
+          kraw[u] = *reinterpret_cast<const uint4*>(sh.knew + dsel * 8);
+          vraw[u] = *reinterpret_cast<const uint4*>(sh.vnew + dsel * 8);
+        }
+      }
       float s[UNR];
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
@@ -451,19 +746,42 @@ __device__ __forceinline__ bool attention_phase(const StepParams& sp, const __nv
     }
     __syncthreads();
   }
+  step_stamp(sp, epoch, 2);
   grid_arrive(sp.barrier);
   ++epoch;
   return true;
 }
 
 template <int D>
-__global__ void __launch_bounds__(kStepThreads, 2) decode_step_kernel(const StepParams sp) {
-  extern __shared__ uint4 xs[];
+__global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const StepParams sp) {
+  extern __shared__ __align__(128) unsigned char smem[];
   __shared__ StepShared sh;
-  __shared__ float sm_o[kStepWarps][D];
-  const int tid = threadIdx.x;
-  if (tid == 0) sh.abort = 0;
+  __shared__ __align__(16) float sm_o[kStepWarps][D];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned char* xs_bytes = smem + kStepRingBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStepBarsOff);
+  for (int i = tid; i < sp.L * 9; i += kStepThreads)
+    reinterpret_cast<const void**>(layer_table())[i] = reinterpret_cast<const void* const*>(sp.layers)[i];
+  if (tid == 0) {
+    sh.abort = 0;
+    for (int i = 0; i < kStepWarps * kSlots; ++i) step_mbar_init(bars + i, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   __syncthreads();
+
+  // ---- start the weight stream: the first kSlots items of this warp's sequence ----
+  Stream st;
+  st.slots = smem_u32(smem) + (uint32_t)(warp * kSlots * kSlotBytes);
+  st.bars = bars + warp * kSlots;
+  st.policy = step_evict_first_policy();
+  st.NW = gridDim.x * kStepWarps;
+  st.gw = warp * gridDim.x + blockIdx.x;   // neighbouring units go to different SMs
+  cursor_start(st.con, sp, st.gw, st.NW);
+  st.iss = st.con;
+  for (int i = 0; i < kSlots && !st.iss.done; ++i) {
+    ring_issue(st, lane);
+    cursor_advance(st.iss, sp, st.gw, st.NW);
+  }
 
   // (token, position) were left by the previous step or by the host
   int token = sp.values[0], pos = sp.values[1];
@@ -471,124 +789,120 @@ __global__ void __launch_bounds__(kStepThreads, 2) decode_step_kernel(const Step
   pos = max(0, min(pos, sp.S - 1));
   unsigned int epoch = 0;
   unsigned long long best = 0ull;
-  const int QD = sp.H * D, rows_qkv = (sp.H + 2 * sp.G) * D;
+  bool ok = true;
+  const __nv_bfloat16* x0 = sp.embed + (size_t)token * sp.E;   // layer 0's residual stream
 
-  for (int l = 0; l < sp.L; ++l) {
-    const StepLayer& ly = sp.layers[l];
-    const __nv_bfloat16* x_in = (l == 0) ? sp.embed + (size_t)token * sp.E : sp.xa;
+  // One loop over the step's phases with one call site per kind of phase keeps the code of
+  // the whole step small enough for the instruction cache.
+  const int phases = 5 * sp.L + 1;
+#pragma unroll 1
+  for (int p = 0; p < phases && ok; ++p) {
+    const int l = p / 5, j = p - 5 * l;
+    const StepLayer& ly = layer_table()[l < sp.L ? l : 0];
+    if (l < sp.L && j == 1) {
+      ok = attention_phase<D>(sp, ly.k, ly.v, pos, sh, sm_o, epoch);
+      continue;
+    }
     PhaseArgs a = {};
-    a.A = ly.wqkv; a.x = x_in; a.norm_w = ly.ln1; a.y = sp.q; a.rows = rows_qkv; a.K = sp.E;
-    a.plan = sp.qkv; a.stage = ST_VECTOR; a.k_cache = ly.k; a.v_cache = ly.v; a.pos = pos;
-    if (!gemv_phase<PH_QKV, true>(sp, a, xs, sh, epoch, best)) return;
-
-    if (!attention_phase<D>(sp, ly.k, ly.v, pos, sh, sm_o, epoch)) return;
-
-    a = PhaseArgs{};
-    a.A = ly.wo; a.residual = x_in; a.y = sp.xb; a.rows = sp.E; a.K = QD;
-    a.plan = sp.o; a.stage = ST_ATTENTION;
-    if (!gemv_phase<PH_PLAIN, true>(sp, a, xs, sh, epoch, best)) return;
-
-    a = PhaseArgs{};
-    a.A = ly.wg; a.A2 = ly.wu; a.x = sp.xb; a.norm_w = ly.ln2; a.y = sp.act; a.rows = sp.F; a.K = sp.E;
-    a.plan = sp.swiglu; a.stage = ST_VECTOR;
-    if (!gemv_phase<PH_SWIGLU, true>(sp, a, xs, sh, epoch, best)) return;
-
-    a = PhaseArgs{};
-    a.A = ly.wd; a.x = sp.act; a.residual = sp.xb; a.y = sp.xa; a.rows = sp.E; a.K = sp.F;
-    a.plan = sp.down; a.stage = ST_VECTOR;
-    if (!gemv_phase<PH_PLAIN, true>(sp, a, xs, sh, epoch, best)) return;
+    int pid;
+    if (l >= sp.L || j == 0) {
+      // the residual stream after the layer before (or the embedding row), then the final
+      // norm and the head, or this layer's first norm and q/k/v
+      if (l == 0) {
+        a.stage = ST_VECTOR; a.x = x0;
+      } else {
+        a.stage = ST_PARTIAL; a.parts = sp.part_d; a.nparts = sp.kp_d; a.residual = sp.xb; a.keep = sp.xa;
+      }
+      a.K = sp.E;
+      if (l >= sp.L) { a.mode = PH_HEAD; pid = 4 * sp.L; a.norm_w = sp.final_norm; a.y = sp.logits; }
+      else { a.mode = PH_PART; pid = 4 * l; a.norm_w = ly.ln1; }
+    } else if (j == 2) {      // attention fold, o_proj
+      a.mode = PH_PART; pid = 4 * l + 1; a.stage = ST_ATTENTION; a.K = sp.H * D;
+    } else if (j == 3) {      // residual, RMSNorm, gate/up, SiLU, product
+      a.mode = PH_SWIGLU; pid = 4 * l + 2; a.stage = ST_PARTIAL; a.K = sp.E;
+      a.parts = sp.part_o; a.nparts = sp.kp_o; a.residual = l == 0 ? x0 : sp.xa; a.keep = sp.xb;
+      a.norm_w = ly.ln2; a.y = sp.act;
+    } else {                  // down_proj
+      a.mode = PH_PART; pid = 4 * l + 3; a.stage = ST_VECTOR; a.x = sp.act; a.K = sp.F;
+    }
+    ok = weight_phase(sp, pid, a, st, xs_bytes, sh, epoch, best);
   }
-  {
-    PhaseArgs a = {};
-    a.A = sp.head; a.x = sp.xa; a.norm_w = sp.final_norm; a.y = sp.logits; a.rows = sp.V; a.K = sp.E;
-    a.plan = sp.headp; a.stage = ST_VECTOR; a.track_best = 1;
-    // gemv_phase arrives once the CTA's rows are stored; its maximum has to be published
-    // first, so the head phase is followed by one more barrier for the keys.
-    if (!gemv_phase<PH_PLAIN, true>(sp, a, xs, sh, epoch, best)) return;
+  if (!ok || sh.abort) {
+    // the step is abandoned: let this warp's copies in flight land before the CTA leaves
+    const unsigned long long t0 = step_ns();
+    for (int idx = st.con.idx; idx < st.iss.idx; ++idx) {
+      uint64_t* bar = st.bars + idx % kSlots;
+      const uint32_t parity = (uint32_t)(idx / kSlots) & 1u;
+      while (!step_mbar_try_wait(bar, parity) && step_ns() - t0 < kStepWaitNs) {}
+    }
+    return;
   }
   // ---- greedy draw: CTA maxima, then CTA 0 folds them ----
-  {
-    const int lane = tid & 31, warp = tid >> 5;
 #pragma unroll
-    for (int off = 16; off; off >>= 1) best = step_max(best, __shfl_xor_sync(0xffffffffu, best, off));
-    if (lane == 0) sh.best[warp] = best;
-    __syncthreads();
-    if (tid == 0) {
-      unsigned long long b = 0ull;
-      for (int w = 0; w < kStepWarps; ++w) b = step_max(b, sh.best[w]);
-      sp.best[blockIdx.x] = b;
-    }
-    grid_arrive(sp.barrier);
-    ++epoch;
-    if (blockIdx.x != 0) return;
-    if (!grid_wait(sp.barrier, epoch, sp.status, &sh.abort)) return;
+  for (int off = 16; off; off >>= 1) best = step_max(best, __shfl_xor_sync(0xffffffffu, best, off));
+  if (lane == 0) sh.best[warp] = best;
+  __syncthreads();
+  if (tid == 0) {
     unsigned long long b = 0ull;
-    for (int i = tid; i < (int)gridDim.x; i += kStepThreads) b = step_max(b, __ldcg(sp.best + i));
+    for (int w = 0; w < kStepWarps; ++w) b = step_max(b, sh.best[w]);
+    sp.best[blockIdx.x] = b;
+  }
+  grid_arrive(sp.barrier);
+  ++epoch;
+  if (blockIdx.x != 0) return;
+  if (!grid_wait(sp.barrier, epoch, sp.status, &sh.abort)) return;
+  unsigned long long b = 0ull;
+  for (int i = tid; i < (int)gridDim.x; i += kStepThreads) b = step_max(b, __ldcg(sp.best + i));
 #pragma unroll
-    for (int off = 16; off; off >>= 1) b = step_max(b, __shfl_xor_sync(0xffffffffu, b, off));
-    if (lane == 0) sh.best[warp] = b;
-    __syncthreads();
-    if (tid == 0) {
-      b = 0ull;
-      for (int w = 0; w < kStepWarps; ++w) b = step_max(b, sh.best[w]);
-      const int drawn = (int)(~(uint32_t)(b & 0xffffffffull));
-      sp.drawn[pos] = drawn;
-      sp.values[0] = drawn;
-      sp.values[1] = pos + 1;
-    }
+  for (int off = 16; off; off >>= 1) b = step_max(b, __shfl_xor_sync(0xffffffffu, b, off));
+  if (lane == 0) sh.best[warp] = b;
+  __syncthreads();
+  if (tid == 0) {
+    b = 0ull;
+    for (int w = 0; w < kStepWarps; ++w) b = step_max(b, sh.best[w]);
+    const int drawn = (int)(~(uint32_t)(b & 0xffffffffull));
+    sp.drawn[pos] = drawn;
+    sp.values[0] = drawn;
+    sp.values[1] = pos + 1;
   }
 }
 
-// Pick the K split and the CTA count of one GEMV phase on a grid of `slots` CTAs.
-static PhasePlan plan_phase(int npairs, int K, int slots) {
-  const int nch = K >> 3;
-  constexpr int kStep = 32 * kItem;
-  int best_ks = 1;
-  double best_score = -1.0;
-  for (int ks = 1; ks <= kStepWarps; ks *= 2) {
-    if (ks > 1 && nch / ks < kStep) break;
-    const long long cta_iters = ((long long)npairs * ks + kStepWarps - 1) / kStepWarps;
-    const long long waves = (cta_iters + slots - 1) / slots;
-    const double eff = (double)cta_iters / (double)(waves * slots);
-    const double score = cta_iters >= slots ? eff : 0.9 * (double)cta_iters / slots;
-    if (score > best_score + 0.02) { best_score = score; best_ks = ks; }
-  }
-  const int groups = kStepWarps / best_ks;
-  const long long cta_iters = (npairs + groups - 1) / groups;
-  const long long waves = (cta_iters + slots - 1) / slots;
-  int ctas = (int)((cta_iters + waves - 1) / waves);
-  ctas = ctas < 1 ? 1 : (ctas > slots ? slots : ctas);
-  return PhasePlan{best_ks, ctas};
+// K parts of a narrow projection: the smallest power of two that gives the grid's warps a
+// unit each, while a part keeps whole 32-column blocks.
+static int pick_parts(int rows, int K, int warps) {
+  int p = 1;
+  while (p < kStepMaxParts && (rows / kItemRows) * p * 5 < warps * 4 && K % (64 * p) == 0) p *= 2;
+  return p;
 }
 
 template <int D>
-static int launch_step(StepParams& sp, size_t smem, cudaStream_t stream) {
+static int launch_step(StepParams& sp, cudaStream_t stream) {
   static int grid = 0;
   if (grid == 0) {
-    if (cudaFuncSetAttribute(decode_step_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(decode_step_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kStepSmem) != cudaSuccess)
       return IRON_ERR_LAUNCH;
     int per_sm = 0, dev = 0, sms = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<D>, kStepThreads, 64 * 1024) !=
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<D>, kStepThreads, kStepSmem) !=
             cudaSuccess ||
         cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       return IRON_ERR_LAUNCH;
-    if (per_sm < 1) return IRON_ERR_LAUNCH;
-    grid = (per_sm > 2 ? 2 : per_sm) * sms;
+    if (per_sm < 1 || sms < 1) return IRON_ERR_LAUNCH;
+    grid = sms > 512 ? 512 : sms;
   }
-  if (smem > 64 * 1024) return IRON_ERR_SHAPE;
-  const int rows_qkv = (sp.H + 2 * sp.G) * sp.D;
-  sp.qkv = plan_phase(rows_qkv / 2, sp.E, grid);
-  sp.o = plan_phase((sp.E + 1) / 2, sp.H * sp.D, grid);
-  sp.swiglu = plan_phase(sp.F, sp.E, grid);
-  sp.down = plan_phase((sp.E + 1) / 2, sp.F, grid);
-  sp.headp = plan_phase((sp.V + 1) / 2, sp.E, grid);
+  const int warps = grid * kStepWarps;
+  sp.kp_qkv = pick_parts((sp.H + 2 * sp.G) * sp.D, sp.E, warps);
+  sp.kp_o = pick_parts(sp.E, sp.H * sp.D, warps);
+  sp.kp_d = pick_parts(sp.E, sp.F, warps);
+  // keys of a head go to as many CTAs as the grid has per head
+  int ns = grid / sp.H;
+  sp.nsplit = ns < 1 ? 1 : (ns > 16 ? 16 : ns);
   if (cudaMemsetAsync(sp.barrier, 0, sizeof(unsigned int), stream) != cudaSuccess) return IRON_ERR_LAUNCH;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kStepThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
+  cfg.dynamicSmemBytes = kStepSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;   // every CTA resident: the barrier cannot starve
@@ -599,28 +913,47 @@ static int launch_step(StepParams& sp, size_t smem, cudaStream_t stream) {
   return IRON_OK;
 }
 
+// Workspace layout (bytes): barrier word at 0, status word at 128, one key per CTA at 256,
+// then the attention partials, the trace and the three projections' f32 partial sums.
+struct StepWorkspace {
+  size_t best, att, trace, part_qkv, part_o, part_d, total;
+};
+static StepWorkspace step_workspace(int E, int H, int G, int D) {
+  StepWorkspace w;
+  w.best = 256;
+  w.att = w.best + 512 * sizeof(unsigned long long);
+  w.trace = w.att + (size_t)H * 16 * (D + 4) * sizeof(float);
+  w.part_qkv = w.trace + 1024 * sizeof(unsigned long long);
+  w.part_o = w.part_qkv + (size_t)kStepMaxParts * (H + 2 * G) * D * sizeof(float);
+  w.part_d = w.part_o + (size_t)kStepMaxParts * E * sizeof(float);
+  w.total = w.part_d + (size_t)kStepMaxParts * E * sizeof(float);
+  return w;
+}
+
 }  // namespace iron
 
 using namespace iron;
 
-extern "C" size_t iron_decode_step_workspace_bytes(int H, int D) {
-  // barrier word, status word, one key per CTA (at most 2 x 256 SMs), attention partials
-  return 256 + 512 * sizeof(unsigned long long) + (size_t)H * 16 * (D + 4) * sizeof(float);
+extern "C" size_t iron_decode_step_workspace_bytes(int E, int H, int G, int D) {
+  if (E <= 0 || H <= 0 || G <= 0 || D <= 0) return 0;
+  return step_workspace(E, H, G, D).total;
 }
 
 extern "C" int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E, int F, int H, int G,
                                      int D, int V, int S, const void* embed, const void* head,
                                      const void* final_norm, const void* angles, float eps,
-                                     float scale, int window, int kv_len_hint, int* values,
-                                     int* drawn, void* xa, void* xb, void* q, void* act, void* logits,
-                                     void* workspace, iron_stream_t stream) {
+                                     float scale, int window, int* values, int* drawn, void* xa,
+                                     void* xb, void* act, void* logits, void* workspace,
+                                     iron_stream_t stream) {
   if (L <= 0 || E <= 0 || F <= 0 || H <= 0 || G <= 0 || V <= 0 || S <= 0 || H % G) return IRON_ERR_SHAPE;
   if (D != 64 && D != 128) return IRON_ERR_SHAPE;
-  if ((E & 15) || (F & 15) || ((H * D) & 15)) return IRON_ERR_SHAPE;
-  const void* must32[] = {embed, head, xa, xb, q, act, logits, workspace};
-  for (const void* p : must32)
-    if (!p || (reinterpret_cast<uintptr_t>(p) & 31u)) return IRON_ERR_ALIGN;
-  if (!layer_ptrs || !final_norm || !angles || !values || !drawn) return IRON_ERR_SHAPE;
+  if (L > kStepMaxLayers) return IRON_ERR_SHAPE;
+  if ((E & 31) || (F & 31) || (V & 7)) return IRON_ERR_SHAPE;
+  if (E > kStepMaxK || F > kStepMaxK || H * D > kStepMaxK) return IRON_ERR_SHAPE;
+  const void* must16[] = {embed, head, xa, xb, act, logits, workspace, final_norm, angles};
+  for (const void* p : must16)
+    if (!p || (reinterpret_cast<uintptr_t>(p) & 15u)) return IRON_ERR_ALIGN;
+  if (!layer_ptrs || !values || !drawn) return IRON_ERR_SHAPE;
   StepParams sp = {};
   sp.layers = reinterpret_cast<const StepLayer*>(layer_ptrs);
   sp.L = L; sp.E = E; sp.F = F; sp.H = H; sp.G = G; sp.D = D; sp.V = V; sp.S = S;
@@ -628,19 +961,17 @@ extern "C" int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E
   sp.final_norm = (const __nv_bfloat16*)final_norm; sp.angles = (const __nv_bfloat16*)angles;
   sp.eps = eps; sp.scale_log2 = scale * 1.4426950408889634f; sp.window = window;
   sp.values = values; sp.drawn = drawn;
-  sp.xa = (__nv_bfloat16*)xa; sp.xb = (__nv_bfloat16*)xb; sp.q = (__nv_bfloat16*)q;
+  sp.xa = (__nv_bfloat16*)xa; sp.xb = (__nv_bfloat16*)xb;
   sp.act = (__nv_bfloat16*)act; sp.logits = (__nv_bfloat16*)logits;
+  const StepWorkspace w = step_workspace(E, H, G, D);
   char* ws = static_cast<char*>(workspace);
   sp.barrier = reinterpret_cast<unsigned int*>(ws);
   sp.status = reinterpret_cast<int*>(ws + 128);
-  sp.best = reinterpret_cast<unsigned long long*>(ws + 256);
-  sp.att_part = reinterpret_cast<float*>(ws + 256 + 512 * sizeof(unsigned long long));
-  // keys of a head go to as many CTAs as the grid has per head, while each keeps a batch
-  int ns = (2 * kSMs) / H;
-  const int keys = kv_len_hint > 0 ? kv_len_hint : S;
-  while (ns > 1 && keys / ns < 64) --ns;
-  sp.nsplit = ns < 1 ? 1 : (ns > 16 ? 16 : ns);
-  const int kmax = E > F ? E : F;
-  const size_t smem = (size_t)(kmax > H * D ? kmax : H * D) * 2;
-  return D == 64 ? launch_step<64>(sp, smem, (cudaStream_t)stream) : launch_step<128>(sp, smem, (cudaStream_t)stream);
+  sp.best = reinterpret_cast<unsigned long long*>(ws + w.best);
+  sp.att_part = reinterpret_cast<float*>(ws + w.att);
+  sp.trace = reinterpret_cast<unsigned long long*>(ws + w.trace);
+  sp.part_qkv = reinterpret_cast<float*>(ws + w.part_qkv);
+  sp.part_o = reinterpret_cast<float*>(ws + w.part_o);
+  sp.part_d = reinterpret_cast<float*>(ws + w.part_d);
+  return D == 64 ? launch_step<64>(sp, (cudaStream_t)stream) : launch_step<128>(sp, (cudaStream_t)stream);
 }

@@ -307,9 +307,9 @@ def prefetch_hint(*tensors) -> None:
     call("iron_prefetch_hint", lo, hi - lo)
 
 
-def decode_step_workspace(H: int, D: int, device) -> torch.Tensor:
+def decode_step_workspace(E: int, H: int, G: int, D: int, device) -> torch.Tensor:
     """Zeroed workspace of the one-kernel decode step (barrier, status word, partials)."""
-    n = _lib.load().iron_decode_step_workspace_bytes(H, D)
+    n = _lib.load().iron_decode_step_workspace_bytes(E, H, G, D)
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
@@ -323,13 +323,13 @@ def decode_step_table(layers, device) -> torch.Tensor:
 
 
 def decode_step(table, *, L, E, F, H, G, D, V, S, embed, head, final_norm, angles, eps, scale,
-                window, kv_len_hint, values, drawn, xa, xb, q, act, logits, workspace):
+                window, values, drawn, xa, xb, act, logits, workspace):
     """One greedy decode step in one cooperative launch (token and position in ``values``)."""
-    _bf16(embed, head, final_norm, angles, xa, xb, q, act, logits)
+    _bf16(embed, head, final_norm, angles, xa, xb, act, logits)
     call("iron_decode_step_bf16", _ptr(table), L, E, F, H, G, D, V, S, _ptr(embed), _ptr(head),
          _ptr(final_norm), _ptr(angles), float(eps), float(scale), -1 if window is None else int(window),
-         int(kv_len_hint), _ptr(values), _ptr(drawn), _ptr(xa), _ptr(xb), _ptr(q), _ptr(act),
-         _ptr(logits), _ptr(workspace), _stream())
+         _ptr(values), _ptr(drawn), _ptr(xa), _ptr(xb), _ptr(act), _ptr(logits), _ptr(workspace),
+         _stream())
 
 
 def decode_step_status(workspace: torch.Tensor) -> int:

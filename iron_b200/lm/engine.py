@@ -98,11 +98,12 @@ class LlamaEngine:
         # which launches carry an L2 prefetch hint (bit 0: QKV -> o_proj weights, bit 1:
         # attention -> gate/up, bit 2: gate/up -> down, bit 3: down -> next layer's QKV)
         self.prefetch_hints = int(os.environ.get("IRON_PREFETCH_HINTS", "0"))
-        # One sequence on one GPU decodes in one persistent kernel per step; batches and
-        # tensor-parallel shards take the separate launches.  IRON_DECODE_STEP=0 forces the
-        # separate launches (the two paths are compared by the tests).
-        self.fused_step = (batch == 1 and tp_size == 1 and D in (64, 128)
-                           and os.environ.get("IRON_DECODE_STEP", "1") != "0")
+        # One sequence on one GPU can decode in one persistent kernel per step
+        # (IRON_DECODE_STEP=1); batches and tensor-parallel shards always take the separate
+        # launches.  The two paths are compared by the tests.
+        self.fused_step = (batch == 1 and tp_size == 1 and D in (64, 128) and L <= 64
+                           and E % 32 == 0 and F % 32 == 0 and V % 8 == 0 and max(E, F, H * D) <= 8192
+                           and os.environ.get("IRON_DECODE_STEP", "0") == "1")
 
         # ---- plan the arena: residents first, then the decode step's transients ----
         plan = ArenaPlan()
@@ -180,7 +181,7 @@ class LlamaEngine:
         self._load(weights)
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
-        self.step_ws = K.decode_step_workspace(H, D, self.device)
+        self.step_ws = K.decode_step_workspace(E, H, G, D, self.device)
         self.step_table = K.decode_step_table(
             [dict(l, k=l["k"][0], v=l["v"][0]) for l in self.layers], self.device)
         self._graph: torch.cuda.CUDAGraph | None = None
@@ -250,8 +251,8 @@ class LlamaEngine:
                           D=D, V=c.vocab_size, S=c.max_seq_len, embed=self.embed, head=self.head,
                           final_norm=self.norm, angles=self.angles, eps=c.eps,
                           scale=c.attention_scale or 1.0 / math.sqrt(D), window=c.window,
-                          kv_len_hint=self.kv_len_hint, values=self.values, drawn=self.drawn[0],
-                          xa=self.x0[0], xb=self.x1[0], q=self.q[0], act=self.act[0],
+                          values=self.values, drawn=self.drawn[0],
+                          xa=self.x0[0], xb=self.x1[0], act=self.act[0],
                           logits=self.logits_buf[0], workspace=self.step_ws)
             return
         E2 = c.hidden_size * 2
