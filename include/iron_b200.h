@@ -301,11 +301,13 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
  * as the separate entry points above (dot products in another summation order), in one
  * cooperative launch, one CTA per SM, whose phases are separated by a bounded grid barrier.
  * Every warp streams its share of the weights of ALL phases through a private
- * shared-memory ring filled by bulk asynchronous copies and consumes them on the tensor
- * cores, so the weight stream does not stop between projections.  Batch 1, one GPU.
+ * shared-memory ring filled by tiled TMA copies, so the weight stream does not stop
+ * between projections.  Batch 1, one GPU.
  *   layer_ptrs : DEVICE array of L x 9 pointers per layer, in this order (16-byte aligned):
  *                ln1 (E), wqkv ((H+2G)*D x E), wo (E x H*D), ln2 (E), wg (F x E),
  *                wu (F x E), wd (E x F), k cache (S x G x D), v cache (S x G x D)
+ *   maps       : DEVICE copy (64-byte aligned) of the tensor maps
+ *                iron_decode_step_encode_maps wrote for the same pointers
  *   values     : device int32[2] = (token, position); left as (drawn token, position + 1)
  *   drawn      : device int32[S]; drawn[position] receives the token
  *   xa, xb (E), act (F), logits (V): bf16 transients, 16-byte aligned; on return xa holds
@@ -316,10 +318,18 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
  *                zeroes it, and a step launched while it is set returns early.
  * D is 64 or 128; E, F and H*D are multiples of 32 and at most 8192; V is a multiple of 8;
  * L is at most 64.  The launch is cooperative (every CTA resident); it may be captured in
- * a CUDA graph. */
+ * a CUDA graph.
+ *
+ * iron_decode_step_encode_maps runs on the host and launches nothing: it describes every
+ * weight matrix to the TMA engine.  h_layer_ptrs is a HOST array with the same L x 9 device
+ * pointers as layer_ptrs; h_maps_out is a HOST buffer of iron_decode_step_maps_bytes(L)
+ * bytes that the caller then copies to device memory. */
 size_t iron_decode_step_workspace_bytes(int E, int H, int G, int D);
-int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E, int F, int H, int G, int D,
-                          int V, int S, const void* embed, const void* head,
+size_t iron_decode_step_maps_bytes(int L);
+int iron_decode_step_encode_maps(const void* const* h_layer_ptrs, int L, int E, int F, int H, int G,
+                                 int D, int V, const void* head, void* h_maps_out);
+int iron_decode_step_bf16(const void* const* layer_ptrs, const void* maps, int L, int E, int F,
+                          int H, int G, int D, int V, int S, const void* embed, const void* head,
                           const void* final_norm, const void* angles, float eps, float scale,
                           int window, int* values, int* drawn, void* xa, void* xb, void* act,
                           void* logits, void* workspace, iron_stream_t stream);

@@ -61,9 +61,11 @@ SIGNATURES: dict[str, tuple] = {
     "iron_argmax_noalloc_max_n": (_I, []),
     "iron_argmax_bf16_noalloc": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "iron_decode_step_workspace_bytes": (_Z, [_I, _I, _I, _I]),
+    "iron_decode_step_maps_bytes": (_Z, [_I]),
+    "iron_decode_step_encode_maps": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "iron_decode_step_bf16": (
         _I,
-        [_P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+        [_P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     ),
     "iron_mha_decode_splits": (_I, [_I, _I, _I]),
     "iron_mha_decode_bf16": (

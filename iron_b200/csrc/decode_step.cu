@@ -12,11 +12,11 @@
 //     columns of 8 consecutive weight rows -- form ONE static sequence over all phases of
 //     the step, so the copies for the next phase are issued, and land, while the CTA is
 //     still waiting for the previous phase to finish everywhere.
-//   * An item is consumed on the tensor cores: the 8 weight rows are the B operand of
-//     mma.sync m16n8k16 (ldmatrix straight from the slot), the activation vector,
-//     replicated over the 16 rows of A, comes from shared memory in fragment order.  A 4 KB
-//     item costs ~50 instructions instead of the ~400 of a SIMT dot product, so the
-//     arithmetic catches up with the prefetched data at several times the HBM rate.
+//   * An item (8 rows x 256 columns, 4 KB) arrives by ONE tiled TMA copy
+//     (cp.async.bulk.tensor.2d through a tensor map of the weight matrix; two copies of
+//     4 rows for the gate/up pair).  A lane multiplies its 8 columns of the staged
+//     activation vector into all 8 rows with packed two-wide f32 FMAs, so the vector is
+//     unpacked once per item and an item costs ~120 instructions per lane.
 //   * The narrow projections (q/k/v, o_proj, down_proj) have too few 8-row groups to
 //     occupy the grid, so their reduction dimension is split too: a unit is (row group,
 //     K part), its result an f32 partial in global memory, and the *consumer* of the
@@ -39,17 +39,17 @@
 
 namespace iron {
 
-constexpr int kStepWarps = 8;
+constexpr int kStepWarps = 16;
 constexpr int kStepThreads = kStepWarps * 32;
 constexpr int kItemRows = 8;                        // weight rows of one item
-constexpr int kItemCols = 512;                      // columns of one item
-constexpr int kRowPitch = kItemCols * 2 + 16;       // bytes between rows in a slot: ldmatrix
-                                                    // reads 8 rows at once without conflicts
-constexpr int kSlotBytes = kItemRows * kRowPitch;
-constexpr int kSlots = 3;                           // slots in a warp's ring
+constexpr int kItemCols = 256;                      // columns of one item: 8 per lane
+constexpr int kRowPitch = kItemCols * 2;            // bytes between rows in a slot
+constexpr int kSlotBytes = kItemRows * kRowPitch;   // 4 KB
+constexpr int kSlots = 3;                           // slots in a warp's ring (192 KB per CTA)
 constexpr int kStepMaxK = 8192;                     // longest reduction (activation staging)
 constexpr int kStepMaxParts = 8;                    // K parts of a narrow projection
 constexpr int kStepMaxLayers = 64;                  // rows of the layer table in shared memory
+constexpr int kMapsPerLayer = 5;                    // tensor maps: wqkv, wo, wg, wu, wd
 constexpr unsigned long long kStepWaitNs = 2000000000ull;  // 2 s
 constexpr size_t kStepRingBytes = (size_t)kStepWarps * kSlots * kSlotBytes;
 constexpr size_t kStepBarsOff = kStepRingBytes + (size_t)kStepMaxK * 2;
@@ -63,6 +63,7 @@ struct StepLayer {
 
 struct StepParams {
   const StepLayer* layers;  // device array of L entries
+  const CUtensorMap* maps;  // device array: 5 per layer (wqkv, wo, wg, wu, wd), then the head
   int L, E, F, H, G, D, V, S;
   const __nv_bfloat16 *embed, *head, *final_norm, *angles;
   float eps, scale_log2;
@@ -124,28 +125,20 @@ __device__ __forceinline__ uint64_t step_evict_first_policy() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
-// `bytes` (a multiple of 16) from global to this CTA's shared memory; completion is counted
-// on `bar`.  The weights are read once per step: first in line for eviction from L2.
-__device__ __forceinline__ void step_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar,
-                                               uint64_t policy) {
+// One box of a tensor map (rows x 256 columns from column x, row y) to this CTA's shared
+// memory; completion is counted on `bar`.  The weights are read once per step: first in
+// line for eviction from L2.  Columns and rows past the matrix arrive as zeros.
+__device__ __forceinline__ void step_tensor_load(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
-__device__ __forceinline__ void step_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
-                                                 uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-// d += a (16x16, rows g and g+8 hold the same vector) * b (16x8)
-__device__ __forceinline__ void step_mma(float (&d)[4], uint32_t a_lo, uint32_t a_hi, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %4, %5, %5}, {%6, %7}, "
-      "{%0, %1, %2, %3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a_lo), "r"(a_hi), "r"(b0), "r"(b1));
+// (lo, hi) of a word holding two bf16, as f32
+__device__ __forceinline__ float2 step_pair(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 
 // ---- grid barrier, split into arrive and wait ----------------------------------------
@@ -205,15 +198,15 @@ struct StepShared {
 // phase streams no weights and has no id.  A phase is cut into units that go round the
 // grid's warps; a unit is cut into items of 8 rows x 256 columns.
 //   PH_PART   a unit is (8-row group, K part); the result is an f32 partial per row.
-//   PH_SWIGLU a unit is an 8-row group of the gate matrix followed by the same rows of the
-//             up matrix, over all of K; the result is bf16 silu(gate) * up.
+//   PH_SWIGLU a unit is 4 rows of the gate matrix and the same 4 rows of the up matrix
+//             (slot rows 0-3 and 4-7), over all of K; the result is bf16 silu(gate) * up.
 //   PH_HEAD   a unit is an 8-row group over all of K; the result is a bf16 logit per row.
 enum { PH_PART = 0, PH_SWIGLU = 1, PH_HEAD = 2 };
 
 struct Phase {
-  const __nv_bfloat16 *A, *A2;
-  float* part;       // PH_PART: (parts, rows)
-  int mode, units, K, rows, kshift, part_cols, chunks, nitems, first;
+  const CUtensorMap *map_a, *map_b;   // map_b: the up matrix of PH_SWIGLU
+  float* part;                        // PH_PART: (parts, rows)
+  int mode, units, K, rows, kshift, part_cols, nitems, first;
 };
 
 __device__ __forceinline__ Phase load_phase(const StepParams& sp, int pid, int gw, int NW) {
@@ -221,48 +214,43 @@ __device__ __forceinline__ Phase load_phase(const StepParams& sp, int pid, int g
   const int rows_qkv = (sp.H + 2 * sp.G) * sp.D;
   const unsigned int u_qkv = (unsigned int)(rows_qkv >> 3) * (unsigned int)sp.kp_qkv;
   const unsigned int u_o = (unsigned int)(sp.E >> 3) * (unsigned int)sp.kp_o;
-  const unsigned int u_sw = (unsigned int)(sp.F >> 3);
+  const unsigned int u_sw = (unsigned int)(sp.F >> 2);
   const unsigned int u_d = (unsigned int)(sp.E >> 3) * (unsigned int)sp.kp_d;
   const int layer = pid >> 2, j = pid & 3;
   unsigned int before = (unsigned int)layer * (u_qkv + u_o + u_sw + u_d);   // units of every earlier phase
   int parts = 1;
-  ph.A2 = nullptr; ph.part = nullptr;
+  ph.map_b = nullptr; ph.part = nullptr;
   if (layer >= sp.L) {
-    ph.A = sp.head; ph.mode = PH_HEAD; ph.rows = sp.V; ph.K = sp.E;
+    ph.map_a = sp.maps + kMapsPerLayer * sp.L; ph.mode = PH_HEAD; ph.rows = sp.V; ph.K = sp.E;
   } else {
-    const StepLayer& ly = layer_table()[layer];
-    if (j == 0) { ph.A = ly.wqkv; ph.mode = PH_PART; ph.rows = rows_qkv; ph.K = sp.E; parts = sp.kp_qkv; ph.part = sp.part_qkv; }
-    else if (j == 1) { ph.A = ly.wo; ph.mode = PH_PART; ph.rows = sp.E; ph.K = sp.H * sp.D; parts = sp.kp_o; ph.part = sp.part_o; before += u_qkv; }
-    else if (j == 2) { ph.A = ly.wg; ph.A2 = ly.wu; ph.mode = PH_SWIGLU; ph.rows = sp.F; ph.K = sp.E; before += u_qkv + u_o; }
-    else { ph.A = ly.wd; ph.mode = PH_PART; ph.rows = sp.E; ph.K = sp.F; parts = sp.kp_d; ph.part = sp.part_d; before += u_qkv + u_o + u_sw; }
+    const CUtensorMap* m = sp.maps + kMapsPerLayer * layer;
+    if (j == 0) { ph.map_a = m; ph.mode = PH_PART; ph.rows = rows_qkv; ph.K = sp.E; parts = sp.kp_qkv; ph.part = sp.part_qkv; }
+    else if (j == 1) { ph.map_a = m + 1; ph.mode = PH_PART; ph.rows = sp.E; ph.K = sp.H * sp.D; parts = sp.kp_o; ph.part = sp.part_o; before += u_qkv; }
+    else if (j == 2) { ph.map_a = m + 2; ph.map_b = m + 3; ph.mode = PH_SWIGLU; ph.rows = sp.F; ph.K = sp.E; before += u_qkv + u_o; }
+    else { ph.map_a = m + 4; ph.mode = PH_PART; ph.rows = sp.E; ph.K = sp.F; parts = sp.kp_d; ph.part = sp.part_d; before += u_qkv + u_o + u_sw; }
   }
   ph.kshift = 31 - __clz(parts);
-  ph.units = (ph.rows >> 3) << ph.kshift;
+  ph.units = ph.mode == PH_SWIGLU ? (ph.rows >> 2) : ((ph.rows >> 3) << ph.kshift);
   ph.part_cols = (((ph.K >> ph.kshift) + 31) >> 5) << 5;
-  ph.chunks = (ph.part_cols + kItemCols - 1) / kItemCols;
-  ph.nitems = ph.mode == PH_SWIGLU ? 2 * ph.chunks : ph.chunks;
+  ph.nitems = (ph.part_cols + kItemCols - 1) / kItemCols;
   // units go round the grid's warps, each phase starting where the one before stopped
   const int rot = (int)(before % (unsigned int)NW);
   ph.first = gw - rot + (gw < rot ? NW : 0);
   return ph;
 }
 
-// Where an item's weights are and what it covers.
+// What an item covers: `group` counts 8-row groups (4-row groups of both matrices for
+// PH_SWIGLU), the columns are [col0, col0 + ncols).
 struct ItemGeom {
-  const __nv_bfloat16* src;   // first of the 8 row segments
   int group, kpart, col0, ncols;
-  bool second;                // PH_SWIGLU: the up-matrix half of the unit
 };
 __device__ __forceinline__ ItemGeom item_geom(const Phase& ph, int unit, int item) {
   ItemGeom g;
   g.group = unit >> ph.kshift;
   g.kpart = unit - (g.group << ph.kshift);
-  g.second = ph.mode == PH_SWIGLU && item >= ph.chunks;
-  const int it = g.second ? item - ph.chunks : item;
-  g.col0 = g.kpart * ph.part_cols + it * kItemCols;
+  g.col0 = g.kpart * ph.part_cols + item * kItemCols;
   const int end = min(ph.K, (g.kpart + 1) * ph.part_cols);
   g.ncols = max(0, min(kItemCols, end - g.col0));
-  g.src = (g.second ? ph.A2 : ph.A) + (size_t)g.group * kItemRows * ph.K + g.col0;
   return g;
 }
 
@@ -305,17 +293,20 @@ struct Stream {
   int gw, NW;        // this warp's index in the grid, warps in the grid
 };
 
-// The warp starts the copies of the item at `st.iss` into the slot its index maps to:
-// eight row segments, one per lane.
-__device__ __forceinline__ void ring_issue(const Stream& st, int lane) {
+// Lane 0 starts the copy of the item at `st.iss` into the slot its index maps to.  A box
+// always counts its full size on the mbarrier, zero fill included.
+__device__ __forceinline__ void ring_issue(const Stream& st) {
   const Cursor& c = st.iss;
   const ItemGeom g = item_geom(c.ph, c.unit, c.item);
   const int s = c.idx % kSlots;
-  if (lane == 0) step_mbar_expect_tx(st.bars + s, (uint32_t)(kItemRows * g.ncols * 2));
-  __syncwarp();
-  if (lane < kItemRows && g.ncols > 0)
-    step_bulk_load(st.slots + s * kSlotBytes + lane * kRowPitch, g.src + (size_t)lane * c.ph.K,
-                   (uint32_t)g.ncols * 2u, st.bars + s, st.policy);
+  const uint32_t dst = st.slots + s * kSlotBytes;
+  step_mbar_expect_tx(st.bars + s, kSlotBytes);
+  if (c.ph.mode == PH_SWIGLU) {
+    step_tensor_load(dst, c.ph.map_a, g.col0, g.group * 4, st.bars + s, st.policy);
+    step_tensor_load(dst + 4 * kRowPitch, c.ph.map_b, g.col0, g.group * 4, st.bars + s, st.policy);
+  } else {
+    step_tensor_load(dst, c.ph.map_a, g.col0, g.group * kItemRows, st.bars + s, st.policy);
+  }
 }
 
 // Every lane waits for the item with index `idx` to have landed; false when out of time.
@@ -332,15 +323,6 @@ __device__ __forceinline__ bool ring_wait(const Stream& st, int idx, int* status
       return false;
     }
   }
-}
-
-// The staged activation vector lives in shared memory in mma fragment order: within each
-// block of 32 columns (16 words of two bf16) word 4c + t sits at position 4t + c, so that
-// one 16-byte load gives lane t its A operands for two k16 steps.
-__device__ __forceinline__ void store_x8(uint32_t* xs_words, int chunk, const uint4& v) {
-  // `chunk` counts groups of 8 columns: block chunk/4, c = chunk%4, words t = 0..3
-  uint32_t* p = xs_words + (chunk >> 2) * 16 + (chunk & 3);
-  p[0] = v.x; p[4] = v.y; p[8] = v.z; p[12] = v.w;
 }
 
 enum { ST_VECTOR = 0, ST_PARTIAL = 1, ST_ATTENTION = 2 };
@@ -364,12 +346,12 @@ struct PhaseArgs {
 // Whatever does not depend on the phase before (norm weights, the residual vector, which
 // is at least two phases old) is fetched ahead of the wait.
 __device__ __forceinline__ bool weight_phase(const StepParams& sp, int pid, const PhaseArgs& a, Stream& st,
-                                             unsigned char* xs_bytes, StepShared& sh, unsigned int& epoch,
-                                             unsigned long long& best) {
+                                             const unsigned char* ring_bytes, unsigned char* xs_bytes,
+                                             StepShared& sh, unsigned int& epoch, unsigned long long& best) {
   constexpr int kIter = (kStepMaxK / 8 + kStepThreads - 1) / kStepThreads;
   const int tid = threadIdx.x, lane = tid & 31;
   const int K = a.K, nch = K >> 3;
-  uint32_t* xs_words = reinterpret_cast<uint32_t*>(xs_bytes);
+  uint4* xs = reinterpret_cast<uint4*>(xs_bytes);
 
   uint4 wreg[kIter], rreg[kIter];
 #pragma unroll
@@ -446,7 +428,7 @@ __device__ __forceinline__ bool weight_phase(const StepParams& sp, int pid, cons
 #pragma unroll
     for (int k = 0; k < kIter; ++k) {
       const int i = tid + k * kStepThreads;
-      if (i < nch) store_x8(xs_words, i, xreg[k]);
+      if (i < nch) xs[i] = xreg[k];
     }
   } else {
     // the attention phase left (D outputs, maximum, sum) per head and key split: fold them
@@ -476,79 +458,91 @@ __device__ __forceinline__ bool weight_phase(const StepParams& sp, int pid, cons
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = L > 0.f ? acc[j] / L : 0.f;
-      store_x8(xs_words, i, pack8(acc));
+      xs[i] = pack8(acc);
     }
   }
   __syncthreads();
   step_stamp(sp, epoch, 1);
 
-  // ---- this warp's items of the phase, on the tensor cores ----
-  float acc[4][4];
+  // ---- this warp's items of the phase ----
+  // A lane owns columns 8 * lane .. + 8 of the item; acc[r] holds the (even, odd) column
+  // sums of row r as one packed pair.
+  float2 acc[kItemRows];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) { acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f; }
-  float gate0 = 0.f, gate1 = 0.f;
-  int dbgn = 0;
-  const uint32_t xs_addr = smem_u32(xs_bytes) + (lane & 3) * 16;
+  for (int r = 0; r < kItemRows; ++r) acc[r] = make_float2(0.f, 0.f);
   while (!st.con.done && st.con.pid == pid) {
     const Cursor& c = st.con;
-    const bool dbg = blockIdx.x == 0 && tid == 0 && epoch >= 37u && epoch <= 39u;
-    unsigned long long* dt = sp.trace + 700 + (epoch - 37u) * 64 + (dbgn < 12 ? dbgn : 12) * 5;
-    if (dbg) dt[0] = step_ns();
     if (!ring_wait(st, c.idx, sp.status, &sh.abort)) break;
-    if (dbg) dt[1] = step_ns();
     const ItemGeom g = item_geom(c.ph, c.unit, c.item);
-    const uint32_t w_addr = st.slots + (c.idx % kSlots) * kSlotBytes + (lane & 7) * kRowPitch + (lane >> 3) * 16;
-    const uint32_t x_addr = xs_addr + (g.col0 >> 5) * 64;
-    const int nb = g.ncols >> 5;
+    if (lane * 8 < g.ncols) {
+      const uint4* w = reinterpret_cast<const uint4*>(ring_bytes + (size_t)(c.idx % kSlots) * kSlotBytes) + lane;
+      const uint4 xv = xs[(g.col0 >> 3) + lane];
+      const float2 x0 = step_pair(xv.x), x1 = step_pair(xv.y), x2 = step_pair(xv.z), x3 = step_pair(xv.w);
 #pragma unroll
-    for (int b = 0; b < kItemCols / 32; ++b) {
-      if (b < nb) {
-        uint32_t r0, r1, r2, r3;
-        step_ldmatrix_x4(w_addr + b * 64, r0, r1, r2, r3);
-        uint4 xa;
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w)
-                     : "r"(x_addr + b * 64));
-        step_mma(acc[(2 * b) & 3], xa.x, xa.y, r0, r1);
-        step_mma(acc[(2 * b + 1) & 3], xa.z, xa.w, r2, r3);
+      for (int r = 0; r < kItemRows; ++r) {
+        const uint4 wv = w[r * (kRowPitch / 16)];
+        acc[r] = __ffma2_rn(step_pair(wv.x), x0, acc[r]);
+        acc[r] = __ffma2_rn(step_pair(wv.y), x1, acc[r]);
+        acc[r] = __ffma2_rn(step_pair(wv.z), x2, acc[r]);
+        acc[r] = __ffma2_rn(step_pair(wv.w), x3, acc[r]);
       }
     }
-    // the slot is free: start the copies of the item kSlots ahead in the sequence
+    // the slot is free: start the copy of the item kSlots ahead in the sequence
     __syncwarp();
-    if (dbg) dt[2] = step_ns() + (unsigned long long)(acc[0][0] == 123.f);
     if (!st.iss.done) {
-      ring_issue(st, lane);
-      if (dbg) dt[4] = step_ns();
+      if (lane == 0) ring_issue(st);
       cursor_advance(st.iss, sp, st.gw, st.NW);
     }
-    if (dbg) dt[3] = step_ns();
-    const bool half_done = c.ph.mode == PH_SWIGLU && c.item == c.ph.chunks - 1;
-    if (half_done || c.item == c.ph.nitems - 1) {
-      // every lane (g, t) holds rows 2t and 2t + 1 of the group
-      const float v0 = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
-      const float v1 = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
+    if (c.item == c.ph.nitems - 1) {
+      // Sum over the lanes and transpose in one pass: each exchange halves the rows a lane
+      // still carries, so 8 rows x 32 lanes take 9 shuffles; lane L ends with row L / 4.
+      float v[kItemRows];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) { acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f; }
-      const int row = g.group * kItemRows + 2 * (lane & 3);
-      if (half_done) {
-        gate0 = v0; gate1 = v1;
-      } else if (lane < 4) {
+      for (int r = 0; r < kItemRows; ++r) { v[r] = acc[r].x + acc[r].y; acc[r] = make_float2(0.f, 0.f); }
+      float w4[4], w2[2], tot;
+      {
+        const bool up = lane & 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float send = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
+          w4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+      }
+      {
+        const bool up = lane & 8;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float send = up ? w4[i] : w4[i + 2], keep = up ? w4[i + 2] : w4[i];
+          w2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+      }
+      {
+        const bool up = lane & 4;
+        const float send = up ? w2[0] : w2[1], keep = up ? w2[1] : w2[0];
+        tot = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+      }
+      tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+      tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+      const int r = lane >> 2;
+      if (c.ph.mode == PH_SWIGLU) {
+        // rows 0-3 are gate rows (lanes 0-15), rows 4-7 the matching up rows (lanes 16-31)
+        const float upv = __shfl_xor_sync(0xffffffffu, tot, 16);
+        if (lane < 16 && (lane & 3) == 0) {
+          const float act = round_bf16(silu_f32(round_bf16(tot)));
+          a.y[g.group * 4 + r] = __float2bfloat16_rn(__fmul_rn(act, round_bf16(upv)));
+        }
+      } else if ((lane & 3) == 0) {
+        const int row = g.group * kItemRows + r;
         if (c.ph.mode == PH_PART) {
-          *reinterpret_cast<float2*>(c.ph.part + (size_t)g.kpart * c.ph.rows + row) = make_float2(v0, v1);
-        } else if (c.ph.mode == PH_HEAD) {
-          const float l0 = round_bf16(v0), l1 = round_bf16(v1);
-          *reinterpret_cast<__nv_bfloat162*>(a.y + row) =
-              __halves2bfloat162(__float2bfloat16_rn(l0), __float2bfloat16_rn(l1));
-          best = step_max(best, step_max(step_key(l0, row), step_key(l1, row + 1)));
+          c.ph.part[(size_t)g.kpart * c.ph.rows + row] = tot;
         } else {
-          const float a0 = round_bf16(silu_f32(round_bf16(gate0))), a1 = round_bf16(silu_f32(round_bf16(gate1)));
-          *reinterpret_cast<__nv_bfloat162*>(a.y + row) = __halves2bfloat162(
-              __float2bfloat16_rn(__fmul_rn(a0, round_bf16(v0))), __float2bfloat16_rn(__fmul_rn(a1, round_bf16(v1))));
+          const float lg = round_bf16(tot);
+          a.y[row] = __float2bfloat16_rn(lg);
+          best = step_max(best, step_key(lg, row));
         }
       }
     }
     cursor_advance(st.con, sp, st.gw, st.NW);
-    if (dbg) { ++dbgn; }
   }
   step_stamp(sp, epoch, 2);
   grid_arrive(sp.barrier);
@@ -569,7 +563,7 @@ template <int D>
 __device__ __forceinline__ bool attention_phase(const StepParams& sp, __nv_bfloat16* Kc, __nv_bfloat16* Vc,
                                                 int pos, StepShared& sh, float (*sm_o)[D],
                                                 unsigned int& epoch) {
-  constexpr int LPK = D / 8, KPW = 32 / LPK, TS = KPW * kStepWarps, UNR = 8;
+  constexpr int LPK = D / 8, KPW = 32 / LPK, TS = KPW * kStepWarps, UNR = 4;
   constexpr int PS = D + 4, HALF = D / 2;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int dsel = lane % LPK, kslot = warp * KPW + lane / LPK;
@@ -779,7 +773,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const Step
   cursor_start(st.con, sp, st.gw, st.NW);
   st.iss = st.con;
   for (int i = 0; i < kSlots && !st.iss.done; ++i) {
-    ring_issue(st, lane);
+    if (lane == 0) ring_issue(st);
     cursor_advance(st.iss, sp, st.gw, st.NW);
   }
 
@@ -825,7 +819,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const Step
     } else {                  // down_proj
       a.mode = PH_PART; pid = 4 * l + 3; a.stage = ST_VECTOR; a.x = sp.act; a.K = sp.F;
     }
-    ok = weight_phase(sp, pid, a, st, xs_bytes, sh, epoch, best);
+    ok = weight_phase(sp, pid, a, st, smem + (size_t)warp * kSlots * kSlotBytes, xs_bytes, sh, epoch, best);
   }
   if (!ok || sh.abort) {
     // the step is abandoned: let this warp's copies in flight land before the CTA leaves
@@ -871,8 +865,36 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const Step
 // unit each, while a part keeps whole 32-column blocks.
 static int pick_parts(int rows, int K, int warps) {
   int p = 1;
-  while (p < kStepMaxParts && (rows / kItemRows) * p * 5 < warps * 4 && K % (64 * p) == 0) p *= 2;
+  while (p < kStepMaxParts && (rows / kItemRows) * p * 5 < warps * 4 && K % (2 * p * kItemCols) == 0) p *= 2;
   return p;
+}
+
+// ---- tensor maps of the weight matrices (host) ----------------------------------------
+typedef CUresult (*StepEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static StepEncodeFn step_encode_fn() {
+  static StepEncodeFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      return reinterpret_cast<StepEncodeFn>(sym);
+    return static_cast<StepEncodeFn>(nullptr);
+  }();
+  return fn;
+}
+// A (rows, K) row-major bf16 matrix, read in boxes of `box_rows` rows x 256 columns.
+static bool step_make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  StepEncodeFn fn = step_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kItemCols, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int D>
@@ -939,7 +961,34 @@ extern "C" size_t iron_decode_step_workspace_bytes(int E, int H, int G, int D) {
   return step_workspace(E, H, G, D).total;
 }
 
-extern "C" int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E, int F, int H, int G,
+extern "C" size_t iron_decode_step_maps_bytes(int L) {
+  return L > 0 ? (size_t)(kMapsPerLayer * L + 1) * sizeof(CUtensorMap) : 0;
+}
+
+extern "C" int iron_decode_step_encode_maps(const void* const* h_layer_ptrs, int L, int E, int F, int H, int G,
+                                            int D, int V, const void* head, void* h_maps_out) {
+  if (!h_layer_ptrs || !h_maps_out || !head) return IRON_ERR_SHAPE;
+  if (L <= 0 || L > kStepMaxLayers || E <= 0 || F <= 0 || H <= 0 || G <= 0 || D <= 0 || V <= 0) return IRON_ERR_SHAPE;
+  if ((E & 31) || (F & 31) || ((H * D) & 31)) return IRON_ERR_SHAPE;
+  CUtensorMap* out = static_cast<CUtensorMap*>(h_maps_out);
+  for (int l = 0; l < L; ++l) {
+    const void* const* p = h_layer_ptrs + 9 * l;   // ln1, wqkv, wo, ln2, wg, wu, wd, k, v
+    for (int i = 0; i < 9; ++i)
+      if (!p[i] || (reinterpret_cast<uintptr_t>(p[i]) & 15u)) return IRON_ERR_ALIGN;
+    CUtensorMap* m = out + kMapsPerLayer * l;
+    if (!step_make_map(m + 0, p[1], (H + 2 * G) * D, E, kItemRows) ||
+        !step_make_map(m + 1, p[2], E, H * D, kItemRows) ||
+        !step_make_map(m + 2, p[4], F, E, 4) ||
+        !step_make_map(m + 3, p[5], F, E, 4) ||
+        !step_make_map(m + 4, p[6], E, F, kItemRows))
+      return IRON_ERR_LAUNCH;
+  }
+  if (reinterpret_cast<uintptr_t>(head) & 15u) return IRON_ERR_ALIGN;
+  if (!step_make_map(out + kMapsPerLayer * L, head, V, E, kItemRows)) return IRON_ERR_LAUNCH;
+  return IRON_OK;
+}
+
+extern "C" int iron_decode_step_bf16(const void* const* layer_ptrs, const void* maps, int L, int E, int F, int H, int G,
                                      int D, int V, int S, const void* embed, const void* head,
                                      const void* final_norm, const void* angles, float eps,
                                      float scale, int window, int* values, int* drawn, void* xa,
@@ -948,14 +997,16 @@ extern "C" int iron_decode_step_bf16(const void* const* layer_ptrs, int L, int E
   if (L <= 0 || E <= 0 || F <= 0 || H <= 0 || G <= 0 || V <= 0 || S <= 0 || H % G) return IRON_ERR_SHAPE;
   if (D != 64 && D != 128) return IRON_ERR_SHAPE;
   if (L > kStepMaxLayers) return IRON_ERR_SHAPE;
-  if ((E & 31) || (F & 31) || (V & 7)) return IRON_ERR_SHAPE;
+  if ((E & 31) || (F & 31) || ((H * D) & 31) || (V & 7) || (F & 3)) return IRON_ERR_SHAPE;
   if (E > kStepMaxK || F > kStepMaxK || H * D > kStepMaxK) return IRON_ERR_SHAPE;
   const void* must16[] = {embed, head, xa, xb, act, logits, workspace, final_norm, angles};
   for (const void* p : must16)
     if (!p || (reinterpret_cast<uintptr_t>(p) & 15u)) return IRON_ERR_ALIGN;
-  if (!layer_ptrs || !values || !drawn) return IRON_ERR_SHAPE;
+  if (!layer_ptrs || !maps || !values || !drawn) return IRON_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(maps) & 63u) return IRON_ERR_ALIGN;
   StepParams sp = {};
   sp.layers = reinterpret_cast<const StepLayer*>(layer_ptrs);
+  sp.maps = static_cast<const CUtensorMap*>(maps);
   sp.L = L; sp.E = E; sp.F = F; sp.H = H; sp.G = G; sp.D = D; sp.V = V; sp.S = S;
   sp.embed = (const __nv_bfloat16*)embed; sp.head = (const __nv_bfloat16*)head;
   sp.final_norm = (const __nv_bfloat16*)final_norm; sp.angles = (const __nv_bfloat16*)angles;

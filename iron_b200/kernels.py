@@ -322,11 +322,24 @@ def decode_step_table(layers, device) -> torch.Tensor:
     return torch.tensor(rows, dtype=torch.int64).to(device)
 
 
-def decode_step(table, *, L, E, F, H, G, D, V, S, embed, head, final_norm, angles, eps, scale,
+def decode_step_maps(table: torch.Tensor, *, E, F, H, G, D, V, head) -> torch.Tensor:
+    """The device copy of the TMA tensor maps of every weight matrix ``table`` points to."""
+    import numpy as np
+
+    host = np.ascontiguousarray(table.cpu().numpy())
+    L = host.shape[0]
+    n = _lib.load().iron_decode_step_maps_bytes(L)
+    out = np.zeros(n, dtype=np.uint8)
+    call("iron_decode_step_encode_maps", host.ctypes.data, L, E, F, H, G, D, V, _ptr(head), out.ctypes.data)
+    # cudaMalloc'ed storage is 256-byte aligned: the maps need 64
+    return torch.from_numpy(out).to(table.device)
+
+
+def decode_step(table, maps, *, L, E, F, H, G, D, V, S, embed, head, final_norm, angles, eps, scale,
                 window, values, drawn, xa, xb, act, logits, workspace):
     """One greedy decode step in one cooperative launch (token and position in ``values``)."""
     _bf16(embed, head, final_norm, angles, xa, xb, act, logits)
-    call("iron_decode_step_bf16", _ptr(table), L, E, F, H, G, D, V, S, _ptr(embed), _ptr(head),
+    call("iron_decode_step_bf16", _ptr(table), _ptr(maps), L, E, F, H, G, D, V, S, _ptr(embed), _ptr(head),
          _ptr(final_norm), _ptr(angles), float(eps), float(scale), -1 if window is None else int(window),
          _ptr(values), _ptr(drawn), _ptr(xa), _ptr(xb), _ptr(act), _ptr(logits), _ptr(workspace),
          _stream())

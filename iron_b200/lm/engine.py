@@ -184,6 +184,9 @@ class LlamaEngine:
         self.step_ws = K.decode_step_workspace(E, H, G, D, self.device)
         self.step_table = K.decode_step_table(
             [dict(l, k=l["k"][0], v=l["v"][0]) for l in self.layers], self.device)
+        self.step_maps = None
+        if self.fused_step:
+            self.step_maps = K.decode_step_maps(self.step_table, E=E, F=F, H=H, G=G, D=D, V=V, head=self.head)
         self._graph: torch.cuda.CUDAGraph | None = None
         # Per-call values are staged in a ring of pinned slots: a slot is rewritten only
         # after the copy that read it has completed, so calls can be queued without a
@@ -247,7 +250,7 @@ class LlamaEngine:
         H, G, D = self.H, self.G, c.head_dim
         d_token, d_pos = self.values[0:1], self.values[1:2]
         if self.fused_step:
-            K.decode_step(self.step_table, L=c.num_hidden_layers, E=c.hidden_size, F=self.F, H=H, G=G,
+            K.decode_step(self.step_table, self.step_maps, L=c.num_hidden_layers, E=c.hidden_size, F=self.F, H=H, G=G,
                           D=D, V=c.vocab_size, S=c.max_seq_len, embed=self.embed, head=self.head,
                           final_norm=self.norm, angles=self.angles, eps=c.eps,
                           scale=c.attention_scale or 1.0 / math.sqrt(D), window=c.window,
