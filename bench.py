@@ -182,7 +182,10 @@ def time_dominant_kernel(engine, peak_gbs: float, peak_kind: str) -> dict:
             "achieved": round(achieved, 1), "peak": peak_gbs, "peak_kind": peak_kind,
             "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
             "bytes_per_launch": bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 2),
-            "traffic": None}
+            # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel on these
+            # shapes, from one ncu capture (mean of two launches)
+            "traffic": 67_510_000 if (c.intermediate_size, c.hidden_size) == (8192, 2048) else None,
+            "traffic_from": "profiles/gemv_swiglu_llama1b_ncu.md"}
 
 
 def cpu_baseline(tokens: int = 2) -> dict:
@@ -307,6 +310,87 @@ def run_tp(args, rank: int, world: int, device) -> None:
         "all_reduces_per_step": 56 if world > 1 else 0}))
 
 
+def run_batch(args, rank: int, world: int, device) -> None:
+    """Llama-3.2-1B architecture, 64 independent sequences decoded in lockstep after a
+    2048-token context each, the batch split over the ranks with no collective (every rank
+    holds the full weights and 64 / world sequences)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from iron_b200.lm.engine import LlamaEngine, batch_shard
+
+    total = 64
+    mine = batch_shard(total, rank, world)
+    config = build_config()
+    weights = device_weights(config, 3001, device)
+    engine = LlamaEngine(config, weights, device=device, batch=len(mine), kv_len_hint=CONTEXT + args.steps)
+    del weights
+    for b, seq in enumerate(mine):
+        engine.prefill(np.random.default_rng(3100 + seq).integers(0, config.vocab_size, CONTEXT), 0, seq=b)
+    first = engine.drawn[:, CONTEXT - 1].cpu().numpy()       # the token each prompt drew
+    engine.capture()
+    warm = max(args.warmup, 3)
+    positions = [CONTEXT] * len(mine)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    engine.set_batch(first, positions)
+    for _ in range(warm):
+        engine.step()
+    engine.set_batch(first, positions)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            engine.step()
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+    # host-facing: every step's tokens go in from pinned host memory and come back
+    toks = list(first)
+    for i in range(warm):
+        toks = engine.decode_batch(toks, [CONTEXT + i] * len(mine))
+    barrier()
+    toks = list(first)
+    start.record()
+    for i in range(args.steps):
+        toks = engine.decode_batch(toks, [CONTEXT + i] * len(mine))
+    stop.record()
+    barrier()
+    ms_e2e = start.elapsed_time(stop)
+    t = torch.tensor([ms, ms_e2e], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = t.tolist()
+    if rank != 0:
+        return
+    peak, kind = measured_peaks()
+    kv = (CONTEXT + args.steps // 2) * 32768 * len(mine)
+    step_bytes = engine.weight_bytes_per_token + kv
+    gbs = step_bytes / (ms / args.steps / 1e3) / 1e9
+    print(json.dumps({
+        "metric": "llama-3.2-1b-arch decode throughput (64 sequences, greedy, context 2048+)",
+        "value": round(total * args.steps / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "configs[2] batch 64: Llama-3.2-1B architecture, 64 independent sequences after a "
+                               "2048-token prompt each, split over the ranks with no collective",
+                   "sequences_per_gpu": len(mine), "context": CONTEXT,
+                   "l2": "every step streams 2.47 GB of weights and 67 MB of KV cache per sequence"},
+        "e2e": {"value": round(total * args.steps / (ms_e2e / 1e3), 1), "unit": UNIT,
+                "h2d_bytes_per_step": 8 * len(mine), "d2h_bytes_per_step": 4 * len(mine),
+                "ms_per_step": round(ms_e2e / args.steps, 4)},
+        "gpu_launches": engine.launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+        "per_rank_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": round(gbs, 1),
+                              "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": round(gbs / peak, 4)}}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,7 +398,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="llama1b", choices=["llama1b", "llama3b-tp"],
+    ap.add_argument("--workload", default="llama1b", choices=["llama1b", "llama3b-tp", "llama1b-batch64"],
                     help="llama1b: the headline decode, one replica per GPU; llama3b-tp: the 3B "
                          "architecture tensor-parallel over --gpus ranks at context 4096")
     args = ap.parse_args()
@@ -344,6 +428,11 @@ def main() -> None:
 
     from iron_b200.lm.engine import LlamaEngine
 
+    if args.workload == "llama1b-batch64":
+        run_batch(args, rank, world, device)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "llama3b-tp":
         run_tp(args, rank, world, device)
         # the captured graphs hold NCCL work: leave without tearing the group down under them

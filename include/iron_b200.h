@@ -293,6 +293,27 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
                           iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * Batched decode: every row of the batch is another sequence at its own position with its
+ * own KV cache -- the reference runs such sequences one Session at a time
+ * (iron/lm/session.py:138-144); the per-row arithmetic is that of iron/lm/blocks.py:642-644
+ * (RoPE), :483-486 (cache write) and iron/operators/sample.py:148 (greedy draw).
+ *
+ * iron_rope_kv_scatter_bf16: qkv is (rows, (H + 2G) * D) with row pitch `pitch` (elements).
+ * Row r is rotated with angle row d_positions[r]; q goes to q_out (rows, H, D) dense, k and v
+ * into row d_positions[r] of the caches of sequence r, which start kv_batch_stride elements
+ * apart (each (S, G, D)).  Positions are clamped to [0, S - 1].
+ *
+ * iron_argmax_rows_bf16: logits is (rows, n) with row pitch `pitch`; for every row the first
+ * index of the maximum goes to drawn[r * S + positions[r]] and tokens[r], and positions[r]
+ * advances by one. */
+int iron_rope_kv_scatter_bf16(const void* qkv, long long pitch, const void* angles, void* q_out,
+                              void* k_cache, void* v_cache, long long kv_batch_stride, int rows,
+                              const int* d_positions, int H, int G, int D, int S,
+                              iron_stream_t stream);
+int iron_argmax_rows_bf16(const void* logits, long long pitch, int rows, int n, int* tokens,
+                          int* positions, int* drawn, int S, iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * One whole greedy decode step as one persistent kernel -- replaces the decode version the
  * reference records per call, iron/lm/causal.py:248-287 (embedding gather, per layer
  * iron/lm/blocks.py:438-470: RMSNorm, q/k/v GEMV, RoPE, cache write, packed attention,

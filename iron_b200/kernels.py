@@ -348,3 +348,22 @@ def decode_step(table, maps, *, L, E, F, H, G, D, V, S, embed, head, final_norm,
 def decode_step_status(workspace: torch.Tensor) -> int:
     """The step kernel's status word (0, or IRON_ERR_TIMEOUT after a barrier wait gave up)."""
     return int(workspace[128:132].view(torch.int32).item())
+
+
+def rope_kv_scatter(qkv, angles, q_out, k_cache, v_cache, positions, *, H, G, D):
+    """Per-sequence RoPE and cache write of a batched decode step.
+
+    ``qkv`` (rows, (H + 2G) * D); ``positions`` int32 (rows,) on the device; ``k_cache`` and
+    ``v_cache`` (rows, S, G, D); ``q_out`` (rows, H, D) dense."""
+    _bf16(qkv, angles, q_out, k_cache, v_cache)
+    rows, S = qkv.shape[0], k_cache.shape[1]
+    call("iron_rope_kv_scatter_bf16", _ptr(qkv), qkv.stride(0), _ptr(angles), _ptr(q_out), _ptr(k_cache),
+         _ptr(v_cache), k_cache.stride(0), rows, _ptr(positions), H, G, D, S, _stream())
+
+
+def argmax_rows(logits, tokens, positions, drawn):
+    """Greedy draw per row; ``drawn`` (rows, S) int32, ``tokens`` and ``positions`` int32 (rows,)."""
+    _bf16(logits)
+    rows, n = logits.shape
+    call("iron_argmax_rows_bf16", _ptr(logits), logits.stride(0), rows, n, _ptr(tokens), _ptr(positions),
+         _ptr(drawn), drawn.shape[1], _stream())

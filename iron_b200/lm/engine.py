@@ -122,9 +122,11 @@ class LlamaEngine:
             res(f"l{i}.wg", (F, E)); res(f"l{i}.wu", (F, E)); res(f"l{i}.wd", (E, F))
             res(f"l{i}.k", (batch, S, G, D)); res(f"l{i}.v", (batch, S, G, D))
         res("values", (16,), 4); res("drawn", (batch, S), 4)
+        # used by every version (decode step, prompt chunk, batched step): resident too
+        res("x0", (batch, E)); res("logits", (batch, V)); res("b.values", (2, max(batch, 8)), 4)
         residents = {n: n for n in sizes}
-        trans = {"x0": (batch, E), "x1": (batch, E), "q": (batch, H * D), "att": (batch, H * D),
-                 "act": (batch, F), "logits": (batch, V), "part": (batch, E)}
+        trans = {"x1": (batch, E), "q": (batch, H * D), "att": (batch, H * D),
+                 "act": (batch, F), "part": (batch, E)}
         for n, shape in trans.items():
             sizes[n] = int(np.prod(shape)) * 2
         # the decode step touches every transient in each layer: all live together
@@ -149,6 +151,18 @@ class LlamaEngine:
         psteps.append(["p.x", "p.y", "p.part"])
         psteps[4].append("p.part")
         spans.update(plan.place_version(psteps, psizes, {n: n for n in residents}))
+        # The batched decode step (one row per sequence): the prompt chunk's recipe on
+        # `batch` rows, with a dense q for the packed attention.
+        if batch > 1:
+            btrans = {"b.x": (batch, E), "b.h": (batch, E), "b.y": (batch, E), "b.qkv": (batch, QKV),
+                      "b.q": (batch, H * D), "b.att": (batch, H * D), "b.gate": (batch, F), "b.up": (batch, F)}
+            bsizes = {n: sizes[n] for n in residents}
+            for n, shape in btrans.items():
+                bsizes[n] = int(np.prod(shape)) * 2
+            bsteps = [["b.x"], ["b.x", "b.h"], ["b.h", "b.qkv"], ["b.qkv", "b.q"], ["b.q", "b.att"],
+                      ["b.att", "b.x", "b.y"], ["b.y", "b.h"], ["b.h", "b.gate"], ["b.h", "b.up"],
+                      ["b.gate", "b.up"], ["b.gate", "b.y", "b.x"], ["b.x", "b.y"]]
+            spans.update(plan.place_version(bsteps, bsizes, {n: n for n in residents}))
         self.plan = plan
         self.arena = torch.empty(plan.size, dtype=torch.uint8, device=self.device)
         self.arena.zero_()
@@ -177,6 +191,13 @@ class LlamaEngine:
         self.p_qkv, self.p_att = view("p.qkv", (C, QKV)), view("p.att", (C, H * D))
         self.p_gate, self.p_up = view("p.gate", (C, F)), view("p.up", (C, F))
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        bv = view("b.values", (2, max(batch, 8)), torch.int32)
+        self.b_tokens, self.b_pos = bv[0, :batch], bv[1, :batch]   # per-sequence (token, position)
+        if batch > 1:
+            self.b_x, self.b_h, self.b_y = view("b.x", (batch, E)), view("b.h", (batch, E)), view("b.y", (batch, E))
+            self.b_qkv, self.b_q = view("b.qkv", (batch, QKV)), view("b.q", (batch, H, D))
+            self.b_att = view("b.att", (batch, H, D))
+            self.b_gate, self.b_up = view("b.gate", (batch, F)), view("b.up", (batch, F))
 
         self._load(weights)
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
@@ -229,7 +250,9 @@ class LlamaEngine:
     @property
     def launches_per_step(self) -> int:
         """Kernels one decode step launches: one persistent kernel, or gather, five per
-        layer, head, draw."""
+        layer, head, draw; a batched step takes gather, ten per layer, norm, head, draw."""
+        if self.batch > 1:
+            return 1 + 10 * self.c.num_hidden_layers + 3
         if self.fused_step:
             return 1
         return 1 + 5 * self.c.num_hidden_layers + 2
@@ -243,9 +266,37 @@ class LlamaEngine:
         layer = ((Q + 2 * KV) * E + E * Q + 3 * F * E) * 2
         return c.num_hidden_layers * layer // self.tp_size + V * E * 2
 
+    def _batch_launches(self) -> None:
+        """Launch one decode step of every sequence of the batch: row b reads
+        (b_tokens[b], b_pos[b]) and leaves (drawn token, position + 1) there.  The
+        projections are skinny GEMMs on the tensor cores (the weights cross HBM once for the
+        whole batch); RoPE, the cache writes, the attention and the draw are per sequence."""
+        c = self.c
+        H, G, D, E, V = self.H, self.G, c.head_dim, c.hidden_size, c.vocab_size
+        n = self.batch
+        x, h, y = self.b_x, self.b_h, self.b_y
+        K.copy_rows(self.embed, x, ids=self.b_tokens, nrows=n, row_bytes=E * 2, src_rows=V)
+        for l in self.layers:
+            K.rms_norm(x, l["ln1"], h, eps=c.eps)
+            K.gemm(h, l["wqkv"], self.b_qkv, b_col_maj=True, status=self.status)
+            K.rope_kv_scatter(self.b_qkv, self.angles, self.b_q, l["k"], l["v"], self.b_pos, H=H, G=G, D=D)
+            K.mha_decode(self.b_q, l["k"], l["v"], self.b_att, d_kv_valid=self.b_pos, per_batch=True,
+                         kv_valid_add=1, window=c.window, scale=c.attention_scale)
+            K.gemm(self.b_att.view(n, H * D), l["wo"], y, b_col_maj=True, residual=x, status=self.status)
+            K.rms_norm(y, l["ln2"], h, eps=c.eps)
+            K.gemm(h, l["wg"], self.b_gate, b_col_maj=True, status=self.status)
+            K.gemm(h, l["wu"], self.b_up, b_col_maj=True, status=self.status)
+            K.elementwise("silu_mul", self.b_gate, self.b_up, self.b_gate)
+            K.gemm(self.b_gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
+        K.rms_norm(x, self.norm, h, eps=c.eps)
+        K.gemm(h, self.head, self.logits_buf, b_col_maj=True, status=self.status)
+        K.argmax_rows(self.logits_buf, self.b_tokens, self.b_pos, self.drawn)
+
     def _decode_launches(self) -> None:
         """Launch one decode step on the current stream, reading (token, position) from
         the device values buffer and leaving (drawn token, position + 1) there."""
+        if self.batch > 1:
+            return self._batch_launches()
         c = self.c
         H, G, D = self.H, self.G, c.head_dim
         d_token, d_pos = self.values[0:1], self.values[1:2]
@@ -396,21 +447,25 @@ class LlamaEngine:
             return
         # the warm-up and the capture run a step at position 0: keep what they overwrite
         saved = self.values.clone()
+        saved_b = (self.b_tokens.clone(), self.b_pos.clone())
         rows = [(l["k"][:, 0].clone(), l["v"][:, 0].clone()) for l in self.layers]
         drawn0 = self.drawn[:, 0].clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):  # warm up outside capture: lazy module loading
             self.set_call(0, 0)
+            self.b_tokens.zero_(); self.b_pos.zero_()
             self._decode_launches()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         self.set_call(0, 0)
+        self.b_tokens.zero_(); self.b_pos.zero_()
         with torch.cuda.graph(g):
             self._decode_launches()
         self._graph = g
         self.values.copy_(saved)
+        self.b_tokens.copy_(saved_b[0]); self.b_pos.copy_(saved_b[1])
         for l, (k0, v0) in zip(self.layers, rows):
             l["k"][:, 0].copy_(k0); l["v"][:, 0].copy_(v0)
         self.drawn[:, 0].copy_(drawn0)
@@ -456,6 +511,47 @@ class LlamaEngine:
             raise RuntimeError("a GEMM pipeline wait gave up (IRON_ERR_TIMEOUT)")
         if K.decode_step_status(self.step_ws) != 0:
             raise RuntimeError("the decode step's grid barrier gave up (IRON_ERR_TIMEOUT)")
+
+    # ------------------------------------------------------------------ batched decode
+    def set_batch(self, tokens, positions) -> None:
+        """Write every sequence's (token, position) for the next batched step."""
+        tokens = np.asarray(tokens, dtype=np.int64).reshape(-1)
+        positions = np.asarray(positions, dtype=np.int64).reshape(-1)
+        if len(tokens) != self.batch or len(positions) != self.batch:
+            raise ValueError(f"a batched step takes {self.batch} tokens and positions")
+        if positions.min() < 0 or positions.max() >= self.c.max_seq_len:
+            raise IndexError(f"a position is outside the {self.c.max_seq_len}-row caches")
+        if tokens.min() < 0 or tokens.max() >= self.c.vocab_size:
+            raise IndexError(f"a token is outside the {self.c.vocab_size}-row vocabulary")
+        host = torch.from_numpy(np.stack([tokens, positions]).astype(np.int32)).pin_memory()
+        self.b_tokens.copy_(host[0], non_blocking=True)
+        self.b_pos.copy_(host[1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the pinned staging buffer is released here
+
+    def decode_batch(self, tokens, positions) -> list[int]:
+        """One decode step of every sequence from the host: tokens in, drawn tokens out."""
+        self.set_batch(tokens, positions)
+        self.step()
+        out = self.b_tokens.cpu().tolist()
+        self.check()
+        return out
+
+    def generate_batch(self, tokens, positions, steps: int) -> np.ndarray:
+        """``steps`` greedy tokens per sequence, the loop carried on the device; (batch, steps)."""
+        positions = np.asarray(positions).reshape(-1)
+        if positions.max() + steps > self.c.max_seq_len:
+            raise IndexError("the run would pass the end of the caches")
+        self.set_batch(tokens, positions)
+        self.capture()
+        for _ in range(steps):
+            self._graph.replay()
+        drawn = self.drawn.cpu().numpy()
+        self.check()
+        return np.stack([drawn[b, p : p + steps] for b, p in enumerate(positions)])
+
+    def logits_batch(self) -> np.ndarray:
+        """The last batched step's logits, (batch, vocab) float32 on the host."""
+        return self.logits_buf.float().cpu().numpy()
 
     def logits(self) -> np.ndarray:
         """The last step's logits as float32 on the host."""
