@@ -15,10 +15,19 @@
 // Every wait on an mbarrier is bounded by a wall-clock limit; a wait that gives up sets
 // an abort flag that unwinds all three roles, the producer drains its in-flight copies,
 // tensor memory is freed, and the host finds IRON_ERR_TIMEOUT in the status word.
-// No cluster launch and no multicast: every CTA loads its own operands.
+// No multicast: every CTA loads its own operands.
+//
+// Skinny problems (a decode batch: few rows, so few output tiles) are split along K over
+// a thread-block cluster of 2 or 4 CTAs instead: every CTA of a cluster accumulates one
+// slice of K for the same tile, the others ship their f32 accumulators into the leader's
+// shared memory over distributed shared memory, and after one cluster barrier the leader
+// adds them in rank order and runs the output stage.  The result does not depend on timing.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace iron {
 
@@ -135,14 +144,18 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, bool b_n_major) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-template <int BN>
+constexpr int kMaxSplit = 4;   // CTAs of a cluster that share one tile along K
+
+template <int BN, bool SPLIT = false>
 struct GemmCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = SPLIT ? 4 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  // the leader's landing area for the other CTAs' accumulators
+  static constexpr int kStagingBytes = SPLIT ? (kMaxSplit - 1) * BM * BN * 4 : 0;
   static constexpr int kBarBytes = 256;
-  static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kSmem = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ float epilogue_apply(int mode, float c) {
@@ -156,14 +169,15 @@ __device__ __forceinline__ float epilogue_apply(int mode, float c) {
   }
 }
 
-template <int BN>
+template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, SPLIT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  float* staging = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
   uint64_t* full = bars;                         // [kStages]
   uint64_t* empty = bars + Cfg::kStages;         // [kStages]
   uint64_t* acc_full = bars + 2 * Cfg::kStages;  // [2]
@@ -200,6 +214,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int n_tiles = (p.N + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
+  // Which tiles and which K blocks this CTA takes: every tile and all of K, or -- split --
+  // the cluster's one tile and this rank's slice of K.
+  int t_first = blockIdx.x, t_step = gridDim.x, k_lo = 0, k_hi = num_kb;
+  unsigned int crank = 0, csize = 1;
+  if constexpr (SPLIT) {
+    cg::cluster_group cl = cg::this_cluster();
+    crank = cl.block_rank();
+    csize = cl.num_blocks();
+    t_first = blockIdx.x / csize;
+    t_step = total > 0 ? total : 1;
+    const int per = (num_kb + (int)csize - 1) / (int)csize;
+    k_lo = min(num_kb, (int)crank * per);
+    k_hi = min(num_kb, k_lo + per);
+  }
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -208,9 +236,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int t = t_first; t < total && ok; t += t_step) {
         const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = k_lo; kb < k_hi; ++kb) {
           if (!mbar_wait(empty + s, phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* a_dst = smem + s * Cfg::kStageBytes;
           uint8_t* b_dst = a_dst + Cfg::kABytes;
@@ -247,13 +275,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      for (int t = t_first; t < total && ok; t += t_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = k_lo; kb < k_hi; ++kb) {
           if (!mbar_wait(full + s, phase, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
@@ -266,7 +294,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // one K step is 16 rows of 128 bytes.
             const uint64_t b_desc = p.b_n_major ? make_desc(b_addr + k * UK * 128, 64 * BK * 2, 1024)
                                                 : make_desc(b_addr + k * UK * 2, 16, 1024);
-            tcgen05_mma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+            tcgen05_mma_bf16(d_tmem, a_desc, b_desc, idesc, kb != k_lo || k != 0);
           }
           tcgen05_commit(empty + s);  // the stage is free once these MMAs have read it
           if (++s == Cfg::kStages) { s = 0; phase ^= 1; }
@@ -274,12 +302,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (ok) tcgen05_commit(acc_full + acc);
       }
     }
-  } else {
-    // ---------------- epilogue (warps 2..5) ----------------
+  }
+  // ---------------- epilogue (warps 2..5) ----------------
+  // `ship`: this CTA's accumulator goes to the cluster leader's staging area as it is;
+  // `gather`: the other ranks' accumulators are added to this one before the output stage.
+  auto drain = [&](bool ship, bool gather) {
     const int group = warp & 3;  // the TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (int t = t_first; t < total && ok; t += t_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
@@ -297,6 +328,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if constexpr (SPLIT) {
+          const size_t mine = ((size_t)(group * 32 + lane)) * BN + c * 32;
+          if (ship) {
+            float* dst = cg::this_cluster().map_shared_rank(staging, 0) + (size_t)(crank - 1) * BM * BN + mine;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            continue;
+          }
+          if (gather) {
+            for (unsigned int rk = 1; rk < csize; ++rk) {
+              const float4* src = reinterpret_cast<const float4*>(staging + (size_t)(rk - 1) * BM * BN + mine);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 f = src[q];
+                v[4 * q] += f.x; v[4 * q + 1] += f.y; v[4 * q + 2] += f.z; v[4 * q + 3] += f.w;
+              }
+            }
+          }
+        }
         if (!p.out_f32) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = epilogue_apply(p.epilogue, round_bf16(v[j]));
@@ -350,6 +401,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tcgen05_fence_before();
       mbar_arrive(acc_empty + acc);
     }
+  };
+  if constexpr (!SPLIT) {
+    if (warp >= 2) drain(false, false);
+  } else {
+    if (warp >= 2 && crank != 0) drain(true, false);
+    cg::this_cluster().sync();   // every rank's accumulator is in the leader's staging area
+    if (warp >= 2 && crank == 0) drain(false, true);
   }
 
   pdl_launch();
@@ -400,8 +458,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmem) != cudaSuccess)
       return IRON_ERR_LAUNCH;
     configured = true;
   }
@@ -413,7 +471,37 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
-  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN>, ma, mb, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, false>, ma, mb, p) == cudaSuccess ? IRON_OK
+                                                                                        : IRON_ERR_LAUNCH;
+}
+
+// One tile per cluster of `splits` CTAs, each taking a slice of K.
+static int launch_gemm_split(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles,
+                             int splits, cudaStream_t stream) {
+  using Cfg = GemmCfg<64, true>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmem) != cudaSuccess)
+      return IRON_ERR_LAUNCH;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * splits);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1 + pdl_attr_count();
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<64, true>, ma, mb, p) == cudaSuccess ? IRON_OK
+                                                                                        : IRON_ERR_LAUNCH;
 }
 
 }  // namespace iron
@@ -456,6 +544,14 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   p.status = d_status;
   const int max_rows = d_valid_rows ? M : valid_rows;
   cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 64) {
+    // few tiles (a decode batch): split K over a cluster so that more SMs stream the weights
+    const int tiles = ((max_rows + BM - 1) / BM) * ((N + 63) / 64);
+    const int num_kb = (valid_k + BK - 1) / BK;
+    int splits = 1;
+    while (splits < kMaxSplit && tiles * splits * 2 <= kSMs && num_kb / (splits * 2) >= 4) splits *= 2;
+    if (splits > 1 && tiles >= 1) return launch_gemm_split(ma, mb, p, tiles, splits, s);
+  }
   if (bn == 256) return launch_gemm<256>(ma, mb, p, max_rows, s);
   if (bn == 128) return launch_gemm<128>(ma, mb, p, max_rows, s);
   return launch_gemm<64>(ma, mb, p, max_rows, s);
