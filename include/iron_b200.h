@@ -293,6 +293,26 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
                           iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * Tensor-parallel all-reduce of a small bf16 vector through peer memory, fused with the
+ * residual add that follows it -- the exchange step after the row-parallel o_proj and
+ * down_proj when a decoder is sharded over GPUs (the reference is single-device; its
+ * residual add is iron/lm/blocks.py:386-391):
+ *   y = bf16( bf16( sum over ranks of part_r ) + residual ),  partials added in rank order.
+ * Every rank owns one buffer of iron_tp_buffer_bytes(world, slot_elems) bytes that all
+ * ranks can address (peer-mapped, zeroed once); h_peer_buffers is a HOST array with the
+ * `world` device addresses of those buffers as THIS rank sees them, own buffer included.
+ * d_seq is a device counter private to the rank, zeroed once; every call advances it, and
+ * all ranks must make the same sequence of calls.  One launch per rank: it stores its
+ * partial into every rank's buffer, raises a flag there, waits (at most 2 s) for every
+ * rank's flag in its own buffer and reduces.  A wait that gives up writes IRON_ERR_TIMEOUT
+ * to *d_status and the kernel finishes with the data it has.  n % 8 == 0, n <= slot_elems,
+ * world <= 8. */
+size_t iron_tp_buffer_bytes(int world, int slot_elems);
+int iron_tp_allreduce_bf16(const void* part, const void* residual, void* y, int n, int slot_elems,
+                           const void* const* h_peer_buffers, int rank, int world,
+                           unsigned int* d_seq, int* d_status, iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * Batched decode: every row of the batch is another sequence at its own position with its
  * own KV cache -- the reference runs such sequences one Session at a time
  * (iron/lm/session.py:138-144); the per-row arithmetic is that of iron/lm/blocks.py:642-644

@@ -367,3 +367,18 @@ def argmax_rows(logits, tokens, positions, drawn):
     rows, n = logits.shape
     call("iron_argmax_rows_bf16", _ptr(logits), logits.stride(0), rows, n, _ptr(tokens), _ptr(positions),
          _ptr(drawn), drawn.shape[1], _stream())
+
+
+def tp_buffer_bytes(world: int, slot_elems: int) -> int:
+    return _lib.load().iron_tp_buffer_bytes(world, slot_elems)
+
+
+def tp_allreduce(part, y, *, residual=None, peer_buffers, slot_elems, rank, world, seq, status=None):
+    """Sum ``part`` over the tensor-parallel ranks through peer memory, add ``residual``.
+
+    ``peer_buffers``: a ctypes array of ``world`` device addresses (every rank's exchange
+    buffer as this rank maps it); ``seq``: this rank's device sequence counter."""
+    _bf16(part, y)
+    call("iron_tp_allreduce_bf16", _ptr(part), _ptr(residual), _ptr(y), part.numel(), slot_elems,
+         peer_buffers, rank, world, _ptr(seq), _ptr(status), _stream())
+    return y

@@ -200,6 +200,7 @@ class LlamaEngine:
             self.b_gate, self.b_up = view("b.gate", (batch, F)), view("b.up", (batch, F))
 
         self._load(weights)
+        self._peer_exchange_setup()
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
         self.step_ws = K.decode_step_workspace(E, H, G, D, self.device)
@@ -245,6 +246,43 @@ class LlamaEngine:
         import torch.distributed as dist
 
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.tp_group)
+
+    def _peer_exchange_setup(self) -> None:
+        """Map one small exchange buffer per rank into every rank's address space
+        (torch symmetric memory over NVLink peer access), for the decode step's fused
+        all-reduce + residual add.  IRON_TP_PEER=0 keeps the NCCL all-reduce."""
+        self.peer_buffers = None
+        if self.tp_size == 1 or os.environ.get("IRON_TP_PEER", "1") == "0":
+            return
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        # plain peer loads and stores only: no multicast object is bound to the buffer
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        E = self.c.hidden_size
+        nbytes = K.tp_buffer_bytes(self.tp_size, E)
+        group = self.tp_group if self.tp_group is not None else dist.group.WORLD
+        self._peer_mem = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self._peer_mem.zero_()
+        self._peer_handle = symm.rendezvous(self._peer_mem, group)
+        ptrs = [int(q) for q in self._peer_handle.buffer_ptrs]
+        self.peer_buffers = (ctypes.c_void_p * self.tp_size)(*ptrs)
+        self.peer_seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)   # every rank's buffer is zeroed before anyone stores into it
+
+    def _reduce_add(self, part: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> None:
+        """out = residual + (sum of ``part`` over the ranks): one kernel over peer memory
+        for a decode step's vector, NCCL and an add otherwise."""
+        if self.peer_buffers is not None and part.numel() == self.c.hidden_size:
+            K.tp_allreduce(part, out, residual=residual, peer_buffers=self.peer_buffers,
+                           slot_elems=self.c.hidden_size, rank=self.tp_rank, world=self.tp_size,
+                           seq=self.peer_seq, status=self.status)
+        else:
+            self._all_reduce(part)
+            K.elementwise("add", residual, part, out)
 
     # ------------------------------------------------------------------ decode step
     @property
@@ -337,12 +375,10 @@ class LlamaEngine:
                 continue
             if tp:   # partial sums meet in an all-reduce before each residual add
                 K.gemv(l["wo"], self.att[0].view(-1), part)
-                self._all_reduce(part)
-                K.elementwise("add", x, part, y)
+                self._reduce_add(part, x, y)
                 K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
                 K.gemv(l["wd"], self.act[0], part)
-                self._all_reduce(part)
-                K.elementwise("add", y, part, x)
+                self._reduce_add(part, y, x)
                 continue
             K.gemv(l["wo"], self.att[0].view(-1), y, residual=x)
             K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)

@@ -1,4 +1,6 @@
-"""Tensor-parallel decode and prefill on two GPUs against the single-GPU engine (NCCL).
+"""Tensor-parallel decode and prefill on two GPUs against the single-GPU engine, with the
+decode step's exchange through peer memory (one fused all-reduce + residual kernel per
+rank) and through NCCL.
 
 The ranks are child processes.  A rank that fails reports its traceback through the queue
 and leaves at once (between steps, nothing of its own in flight); the parent then ends the
@@ -45,13 +47,15 @@ def _work(rank: int, size: int, out):
         want_drawn = one.complete(prompt, 5)
         want.append(one.logits())
         err = max(float(np.abs(a - b).max() / np.abs(b).max()) for a, b in zip(logits, want))
+        tp.check()
         out.put(("ok", rank, (err, drawn, want_drawn)))
     else:
         out.put(("ok", rank, None))
 
 
-def _rank(rank: int, size: int, port: int, out):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def _rank(rank: int, size: int, port: int, out, peer: str):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      IRON_TP_PEER=peer, TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     try:
         _work(rank, size, out)
     except BaseException:  # noqa: BLE001 -- report and leave; the parent ends the peer
@@ -62,7 +66,8 @@ def _rank(rank: int, size: int, port: int, out):
         os._exit(0)   # no collective teardown: the peer may already be gone
 
 
-def test_two_way_tensor_parallel_matches_one_gpu():
+@pytest.mark.parametrize("peer", ["1", "0"], ids=["peer-memory exchange", "nccl exchange"])
+def test_two_way_tensor_parallel_matches_one_gpu(peer):
     import queue
 
     import torch
@@ -73,7 +78,7 @@ def test_two_way_tensor_parallel_matches_one_gpu():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, out), daemon=True) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, out, peer), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
     results = {}
