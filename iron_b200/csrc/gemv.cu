@@ -212,6 +212,305 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same GEMV family with the weights streamed by the TMA engine.
+//
+// One CTA per SM, 16 warps.  Every warp owns a ring of three 4 KB shared-memory slots; lane 0
+// fills a slot with two bulk copies (cp.async.bulk + mbarrier complete_tx: 2 KB of each row
+// of a pair, or 4 KB of one row) and re-arms it as soon as the warp has read it, so about
+// 190 KB per SM are in flight or parked at any time without holding them in registers.  The
+// first three items of every warp are issued before the programmatic-dependency wait:
+// the weights do not depend on the previous kernel, so this kernel's stream starts while
+// that one drains.  A pure read stream through this path runs at ~8 TB/s on a B200, above
+// what register-buffered loads reach; it is used for the large matrices of a decode step.
+//   RING_PAIR   rows (2p, 2p+1)                        RING_SWIGLU  gate row m, up row m
+//   RING_QKV    rows (i, i + D/2) of one head          RING_ROW     one row, 2048 columns per item
+// Every mbarrier wait is bounded by a wall-clock limit; a wait that gives up leaves the
+// kernel early (the rows of that warp are not written) -- there is no status word in this
+// entry point's signature, so the limit is generous (2 s) and only a lost copy reaches it.
+enum { RING_PAIR = 0, RING_SWIGLU = 1, RING_QKV = 2, RING_ROW = 3 };
+constexpr int kRingWarps = 16;
+constexpr int kRingThreads = kRingWarps * 32;
+constexpr int kRingChunk = 1024;                 // columns of one segment
+constexpr int kRingChunk16 = kRingChunk / 8;
+constexpr int kRingSlotBytes = 2 * kRingChunk * 2;
+constexpr int kRingSlots = 3;
+constexpr int kRingMaxK = 8192;
+constexpr size_t kRingBytes = (size_t)kRingWarps * kRingSlots * kRingSlotBytes;
+constexpr unsigned long long kRingWaitNs = 2000000000ull;
+
+__device__ __forceinline__ void ring_mbar_init(uint64_t* bar) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void ring_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ring_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void ring_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar,
+                                               uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ unsigned long long ring_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// The two segments of item `chunk` of unit `unit`: rows, first column and length of each.
+template <int MODE>
+__device__ __forceinline__ void ring_item(const GemvParams& p, int unit, int chunk, int& ra, int& rb,
+                                          const __nv_bfloat16*& src_a, const __nv_bfloat16*& src_b, int& col_a,
+                                          int& n_a, int& col_b, int& n_b) {
+  const int K = p.K;
+  const __nv_bfloat16* B = p.A;
+  if (MODE == RING_PAIR) { ra = 2 * unit; rb = ra + 1; }
+  else if (MODE == RING_SWIGLU) { ra = rb = unit; B = p.A2; }
+  else if (MODE == RING_QKV) {
+    const int half = p.D >> 1, head = unit / half;
+    ra = head * p.D + (unit - head * half); rb = ra + half;
+  } else { ra = rb = unit; }
+  if (MODE == RING_ROW) {
+    col_a = chunk * 2 * kRingChunk; col_b = col_a + kRingChunk;
+    n_a = min(kRingChunk, K - col_a);
+    n_b = max(0, min(kRingChunk, K - col_b));
+  } else {
+    col_a = col_b = chunk * kRingChunk;
+    n_a = min(kRingChunk, K - col_a);
+    n_b = (MODE == RING_PAIR && rb >= p.rows) ? 0 : n_a;
+  }
+  src_a = p.A + (size_t)ra * K + col_a;
+  src_b = B + (size_t)(n_b ? rb : ra) * K + col_b;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvParams p, const int active_warps) {
+  extern __shared__ __align__(128) unsigned char ring_smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = p.K, nch = K >> 3;
+  uint4* xs = reinterpret_cast<uint4*>(ring_smem + kRingBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring_smem + kRingBytes + (size_t)kRingMaxK * 2);
+  float* red = reinterpret_cast<float*>(bars + kRingWarps * kRingSlots);
+  if (tid == 0) {
+    for (int i = 0; i < kRingWarps * kRingSlots; ++i) ring_mbar_init(bars + i);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch();
+
+  // ---- this warp's units: round-robin over the active warps of the grid ----
+  int units;
+  if (MODE == RING_PAIR) units = (p.rows + 1) >> 1;
+  else if (MODE == RING_QKV) units = p.rows >> 1;
+  else units = p.rows;
+  const int span = MODE == RING_ROW ? 2 * kRingChunk : kRingChunk;
+  const int nchunks = (K + span - 1) / span;
+  const int NW = gridDim.x * active_warps;
+  const bool working = warp < active_warps;
+  unsigned char* slots = ring_smem + (size_t)warp * kRingSlots * kRingSlotBytes;
+  uint64_t* my_bars = bars + warp * kRingSlots;
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+
+  int i_unit = working ? warp * gridDim.x + blockIdx.x : units, i_chunk = 0, i_idx = 0;   // issue cursor
+  auto issue_next = [&]() {
+    if (i_unit >= units) return;
+    if (lane == 0) {
+      int ra, rb, col_a, n_a, col_b, n_b;
+      const __nv_bfloat16 *src_a, *src_b;
+      ring_item<MODE>(p, i_unit, i_chunk, ra, rb, src_a, src_b, col_a, n_a, col_b, n_b);
+      const int s = i_idx % kRingSlots;
+      unsigned char* dst = slots + (size_t)s * kRingSlotBytes;
+      ring_expect_tx(my_bars + s, 2u * (uint32_t)(n_a + n_b));
+      ring_bulk_load(dst, src_a, 2u * (uint32_t)n_a, my_bars + s, policy);
+      if (n_b > 0) ring_bulk_load(dst + kRingChunk * 2, src_b, 2u * (uint32_t)n_b, my_bars + s, policy);
+    }
+    ++i_idx;
+    if (++i_chunk == nchunks) { i_chunk = 0; i_unit += NW; }
+  };
+  for (int i = 0; i < kRingSlots; ++i) issue_next();
+
+  // The activation vector is the previous kernel's output: wait for it now.
+  pdl_wait();
+  {
+    const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+    float ss = 0.f;
+    for (int i = tid; i < nch; i += kRingThreads) {
+      const uint4 v = ld_cached(xg + i);
+      xs[i] = v;
+      if (p.norm_mode) {
+        float f[8];
+        unpack8(v, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+    }
+    if (p.norm_mode) {
+      const float tot = block_sum(ss, red);
+      const float inv = 1.0f / sqrtf(tot / (float)K + p.eps);
+      const uint4* wg = reinterpret_cast<const uint4*>(p.norm_w);
+      for (int i = tid; i < nch; i += kRingThreads) {
+        float f[8];
+        unpack8(xs[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv);
+        if (p.norm_mode == 2) {
+          float w[8];
+          unpack8(ld_cached(wg + i), w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = f[j] * w[j];
+        }
+        xs[i] = pack8(f);
+      }
+    }
+    __syncthreads();
+  }
+
+  float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+  int c_idx = 0;
+  bool lost = false;
+  for (int unit = working ? warp * gridDim.x + blockIdx.x : units; unit < units && !lost; unit += NW) {
+    for (int chunk = 0; chunk < nchunks; ++chunk, ++c_idx) {
+      uint64_t* bar = my_bars + c_idx % kRingSlots;
+      const uint32_t parity = (uint32_t)(c_idx / kRingSlots) & 1u;
+      if (!ring_try_wait(bar, parity)) {
+        const unsigned long long t0 = ring_ns();
+        for (uint32_t it = 1; !ring_try_wait(bar, parity); ++it)
+          if ((it & 63u) == 0 && ring_ns() - t0 > kRingWaitNs) { lost = true; break; }
+        if (lost) break;
+      }
+      int ra, rb, col_a, n_a, col_b, n_b;
+      const __nv_bfloat16 *src_a, *src_b;
+      ring_item<MODE>(p, unit, chunk, ra, rb, src_a, src_b, col_a, n_a, col_b, n_b);
+      const uint4* wa = reinterpret_cast<const uint4*>(slots + (size_t)(c_idx % kRingSlots) * kRingSlotBytes);
+      const uint4* wb = wa + kRingChunk16;
+      const uint4* xv = xs + (col_a >> 3);
+      if (MODE == RING_ROW) {
+        const int n16a = n_a >> 3, n16b = n_b >> 3;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = lane + 32 * u;
+          if (i < n16a) pa[u] = dot8(wa[i], xv[i], pa[u]);
+          if (i < n16b) pb[u] = dot8(wb[i], xv[kRingChunk16 + i], pb[u]);
+        }
+      } else {
+        const int n16 = n_a >> 3;
+        const bool both = n_b > 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = lane + 32 * u;
+          if (i < n16) {
+            const uint4 x = xv[i];
+            pa[u] = dot8(wa[i], x, pa[u]);
+            if (both) pb[u] = dot8(wb[i], x, pb[u]);
+          }
+        }
+      }
+      __syncwarp();     // the slot is free: start the item kRingSlots ahead
+      issue_next();
+      if (chunk != nchunks - 1) continue;
+      float acc0 = (pa[0] + pa[1]) + (pa[2] + pa[3]);
+      float acc1 = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+      if (MODE == RING_ROW) acc0 += acc1;
+      acc0 = warp_sum(acc0);
+      if (MODE != RING_ROW) acc1 = warp_sum(acc1);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { pa[u] = 0.f; pb[u] = 0.f; }
+      if (lane != 0) continue;
+      if (MODE == RING_ROW || MODE == RING_PAIR) {
+        float v0 = round_bf16(acc0), v1 = round_bf16(acc1);
+        if (p.residual) {
+          v0 = __fadd_rn(v0, __bfloat162float(p.residual[ra]));
+          if (MODE == RING_PAIR && rb < p.rows) v1 = __fadd_rn(v1, __bfloat162float(p.residual[rb]));
+        }
+        p.y[ra] = __float2bfloat16_rn(v0);
+        if (MODE == RING_PAIR && rb < p.rows) p.y[rb] = __float2bfloat16_rn(v1);
+      } else if (MODE == RING_SWIGLU) {
+        const float gate = round_bf16(acc0), up = round_bf16(acc1);
+        const float act = round_bf16(silu_f32(gate));
+        p.y[ra] = __float2bfloat16_rn(__fmul_rn(act, up));
+      } else {
+        const int half = p.D >> 1;
+        const int pos = p.d_position ? *p.d_position : p.position;
+        const int head = ra / p.D, i = ra - head * p.D;
+        float x1 = round_bf16(acc0), x2 = round_bf16(acc1);
+        if (head < p.H + p.G) {
+          const __nv_bfloat16* ang = p.angles + (size_t)pos * p.D;
+          const float c = __bfloat162float(ang[2 * i]), s = __bfloat162float(ang[2 * i + 1]);
+          const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+          const float y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+          x1 = y1; x2 = y2;
+        }
+        __nv_bfloat16* dst;
+        if (head < p.H) dst = p.y + (size_t)head * p.D;
+        else if (head < p.H + p.G) dst = p.k_cache + ((size_t)pos * p.G + (head - p.H)) * p.D;
+        else dst = p.v_cache + ((size_t)pos * p.G + (head - p.H - p.G)) * p.D;
+        dst[i] = __float2bfloat16_rn(x1);
+        dst[i + half] = __float2bfloat16_rn(x2);
+      }
+    }
+  }
+  // copies this warp started and did not consume (only after a lost wait): let them land
+  if (lost) {
+    const unsigned long long t0 = ring_ns();
+    for (int idx = c_idx; idx < i_idx; ++idx) {
+      uint64_t* bar = my_bars + idx % kRingSlots;
+      while (!ring_try_wait(bar, (uint32_t)(idx / kRingSlots) & 1u) && ring_ns() - t0 < kRingWaitNs) {}
+    }
+  }
+}
+
+// Which shapes go to the TMA-fed kernel (IRON_GEMV_RING, a bit mask; -1 = unset).
+static int ring_policy() {
+  static const int v = [] {
+    const char* e = getenv("IRON_GEMV_RING");
+    return e ? atoi(e) : -1;
+  }();
+  return v;
+}
+
+template <int MODE>
+static int launch_ring(const GemvParams& p, int units, cudaStream_t stream) {
+  static bool configured = false;
+  constexpr size_t smem = kRingBytes + (size_t)kRingMaxK * 2 + kRingWarps * kRingSlots * 8 + 32 * sizeof(float);
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemv_ring_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return IRON_ERR_LAUNCH;
+    configured = true;
+  }
+  // as many warps per CTA as split the units most evenly over the grid
+  int best_w = kRingWarps;
+  double best_eff = -1.0;
+  for (int w = kRingWarps; w >= 8; --w) {
+    const long long nw = (long long)kSMs * w;
+    const long long rounds = (units + nw - 1) / nw;
+    const double eff = (double)units / (double)(rounds * nw);
+    if (eff > best_eff + 1e-3) { best_eff = eff; best_w = w; }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kSMs, 1, 1);
+  cfg.blockDim = dim3(kRingThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  if (cudaLaunchKernelEx(&cfg, gemv_ring_kernel<MODE>, p, best_w) != cudaSuccess) return IRON_ERR_LAUNCH;
+  return IRON_OK;
+}
+
 template <int MODE, bool WIDE>
 static int launch_gemv_w(GemvParams& p, int npairs, int batches, cudaStream_t stream) {
   static bool configured = false;
@@ -269,6 +568,22 @@ static bool aligned32(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 
 
 template <int MODE>
 static int launch_gemv(GemvParams& p, int npairs, int batches, cudaStream_t stream) {
+  // Which shapes stream through the TMA-fed kernel: IRON_GEMV_RING is a bit mask (1 gate/up,
+  // 2 large plain matrices, 4 q/k/v, 8 small plain matrices); unset = none.  Alone, the
+  // TMA-fed gate/up kernel is faster (12.5 us against 14.4 us at 8192 x 2048 twice), but its
+  // CTAs fill an SM, so the next kernel of a decode step cannot start under its tail and the
+  // step as a whole is 1-3 % slower: the register-streamed kernels stay the default.
+  const int policy = ring_policy();
+  const int mask = policy >= 0 ? policy : 0;
+  const long long bytes = (long long)p.rows * p.K * 2 * (MODE == GEMV_SWIGLU ? 2 : 1);
+  if (mask && batches == 1 && p.repeat == 1 && p.K <= kRingMaxK) {
+    if (MODE == GEMV_SWIGLU && (mask & 1)) return launch_ring<RING_SWIGLU>(p, p.rows, stream);
+    if (MODE == GEMV_QKV && (mask & 4)) return launch_ring<RING_QKV>(p, p.rows >> 1, stream);
+    if (MODE == GEMV_PLAIN && (mask & (bytes >= (24ll << 20) ? 2 : 8))) {
+      if (npairs < kSMs * kRingWarps) return launch_ring<RING_ROW>(p, p.rows, stream);
+      return launch_ring<RING_PAIR>(p, npairs, stream);
+    }
+  }
   const bool wide = (p.K % 16 == 0) && aligned32(p.A) && (MODE != GEMV_SWIGLU || aligned32(p.A2));
   return wide ? launch_gemv_w<MODE, true>(p, npairs, batches, stream)
               : launch_gemv_w<MODE, false>(p, npairs, batches, stream);
