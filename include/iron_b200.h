@@ -212,6 +212,17 @@ int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
                    const int* d_valid_rows, int valid_k, int epilogue, const void* residual,
                    int out_f32, int* d_status, iron_stream_t stream);
 
+/* Gate/up projection with SwiGLU for a block of rows -- the chain ProjectionGEMM,
+ * ProjectionGEMM, SiLU, ElementwiseMul that `GatedMLP.body` records for a prompt chunk
+ * (iron/lm/blocks.py:697-699) in one pass over both weight matrices:
+ *   C[m, n] = bf16( bf16(silu(bf16(A[m,:] . Wg[n,:]))) * bf16(A[m,:] . Wu[n,:]) ).
+ * A is (M, K) with pitch lda, Wg and Wu are (N, K) with pitch ldb (checkpoint layout), C is
+ * (M, N) with pitch ldc.  One tensor-memory accumulator holds 128 columns of both products,
+ * so gate and up never travel through HBM.  valid_rows / d_valid_rows as in iron_gemm_bf16. */
+int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* C, int M, int N,
+                          int K, int lda, int ldb, int ldc, int valid_rows,
+                          const int* d_valid_rows, int* d_status, iron_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * Mamba2.
  */

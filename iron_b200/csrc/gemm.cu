@@ -50,6 +50,7 @@ struct GemmParams {
   int out_f32;
   int c_transposed;     // C is (N, M)
   int b_n_major;        // B is (K, N) row-major
+  int dual;             // two (N, K) weight matrices: C = bf16(silu(bf16(A W1^T))) * bf16(A W2^T)
   int* status;          // optional device word: receives IRON_ERR_TIMEOUT
 };
 
@@ -172,7 +173,7 @@ __device__ __forceinline__ float epilogue_apply(int mode, float c) {
 template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
   using Cfg = GemmCfg<BN, SPLIT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -194,6 +195,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b2) : "memory");
   }
   if (warp == 1) {  // the MMA warp owns tensor memory: all 512 columns (one CTA per SM)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
@@ -211,7 +213,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   int valid = p.d_valid ? min(*p.d_valid, p.M) : p.valid;
   valid = max(valid, 0);
   const int m_tiles = (valid + BM - 1) / BM;
-  const int n_tiles = (p.N + BN - 1) / BN;
+  // Output columns per tile: in the gated form one accumulator holds BN/2 columns of the
+  // first product and the matching BN/2 columns of the second.
+  const int BNO = p.dual ? BN / 2 : BN;
+  const int n_tiles = (p.N + BNO - 1) / BNO;
   const int total = m_tiles * n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
   // Which tiles and which K blocks this CTA takes: every tile and all of K, or -- split --
@@ -237,14 +242,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int issued = 0;
       bool ok = true;
       for (int t = t_first; t < total && ok; t += t_step) {
-        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BNO;
         for (int kb = k_lo; kb < k_hi; ++kb) {
           if (!mbar_wait(empty + s, phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* a_dst = smem + s * Cfg::kStageBytes;
           uint8_t* b_dst = a_dst + Cfg::kABytes;
           mbar_expect_tx(full + s, Cfg::kStageBytes);
           tma_load_2d(a_dst, &map_a, kb * BK, m0, full + s);
-          if (!p.b_n_major) {
+          if (p.dual) {
+            tma_load_2d(b_dst, &map_b, kb * BK, n0, full + s);
+            tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b2, kb * BK, n0, full + s);
+          } else if (!p.b_n_major) {
             tma_load_2d(b_dst, &map_b, kb * BK, n0, full + s);
           } else {
 #pragma unroll
@@ -313,21 +321,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int t = t_first; t < total && ok; t += t_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BNO;
       if (!mbar_wait(acc_full + acc, acc_phase, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
       const int row = m0 + group * 32 + lane;
       const bool row_live = row < valid;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < BNO / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (!row_live || col0 >= p.N) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.dual) {
+          // the second product's columns sit BN/2 further in the accumulator
+          tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * BN + BN / 2 + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = __fmul_rn(round_bf16(silu_f32(round_bf16(v[j]))), round_bf16(__uint_as_float(r[j])));
+        }
+        if (!row_live || col0 >= p.N) continue;
         if constexpr (SPLIT) {
           const size_t mine = ((size_t)(group * 32 + lane)) * BN + c * 32;
           if (ship) {
@@ -453,8 +469,8 @@ static bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_
 }
 
 template <int BN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_rows,
-                       cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const GemmParams& p,
+                       int max_rows, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   if (!configured) {
@@ -463,7 +479,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
       return IRON_ERR_LAUNCH;
     configured = true;
   }
-  const int tiles = ((max_rows + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int bno = p.dual ? BN / 2 : BN;
+  const int tiles = ((max_rows + BM - 1) / BM) * ((p.N + bno - 1) / bno);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles < kSMs ? (tiles < 1 ? 1 : tiles) : kSMs);
   cfg.blockDim = dim3(kGemmThreads);
@@ -471,8 +488,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
-  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, false>, ma, mb, p) == cudaSuccess ? IRON_OK
-                                                                                        : IRON_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, false>, ma, mb, mb2, p) == cudaSuccess ? IRON_OK
+                                                                                             : IRON_ERR_LAUNCH;
 }
 
 // One tile per cluster of `splits` CTAs, each taking a slice of K.
@@ -500,8 +517,8 @@ static int launch_gemm_split(const CUtensorMap& ma, const CUtensorMap& mb, const
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1 + pdl_attr_count();
-  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<64, true>, ma, mb, p) == cudaSuccess ? IRON_OK
-                                                                                        : IRON_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<64, true>, ma, mb, mb, p) == cudaSuccess ? IRON_OK
+                                                                                            : IRON_ERR_LAUNCH;
 }
 
 }  // namespace iron
@@ -552,7 +569,38 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     while (splits < kMaxSplit && tiles * splits * 2 <= kSMs && num_kb / (splits * 2) >= 4) splits *= 2;
     if (splits > 1 && tiles >= 1) return launch_gemm_split(ma, mb, p, tiles, splits, s);
   }
-  if (bn == 256) return launch_gemm<256>(ma, mb, p, max_rows, s);
-  if (bn == 128) return launch_gemm<128>(ma, mb, p, max_rows, s);
-  return launch_gemm<64>(ma, mb, p, max_rows, s);
+  if (bn == 256) return launch_gemm<256>(ma, mb, mb, p, max_rows, s);
+  if (bn == 128) return launch_gemm<128>(ma, mb, mb, p, max_rows, s);
+  return launch_gemm<64>(ma, mb, mb, p, max_rows, s);
+}
+
+extern "C" int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* C, int M, int N, int K,
+                                     int lda, int ldb, int ldc, int valid_rows, const int* d_valid_rows,
+                                     int* d_status, iron_stream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > M) return IRON_ERR_SHAPE;
+  if (!aligned16(A) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(C)) return IRON_ERR_ALIGN;
+  if ((lda & 7) || (ldb & 7)) return IRON_ERR_ALIGN;
+  if (lda < K || ldb < K || ldc < N) return IRON_ERR_SHAPE;
+  if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
+  // One 128 x BN accumulator = BN/2 output columns: the gate half and the up half.  The
+  // widest tile that still gives at least half a wave of CTAs.
+  const int max_rows = d_valid_rows ? M : valid_rows;
+  const int m_tiles = (max_rows + BM - 1) / BM;
+  int bn = 256;
+  if ((long long)m_tiles * ((N + 127) / 128) < kSMs / 2) bn = 128;
+  if (bn == 128 && (long long)m_tiles * ((N + 63) / 64) < kSMs / 2) bn = 64;
+  CUtensorMap ma, mg, mu;
+  if (!make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM) ||
+      !make_map(&mg, Wg, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, bn / 2) ||
+      !make_map(&mu, Wu, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, bn / 2))
+    return IRON_ERR_LAUNCH;
+  GemmParams p = {};
+  p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.valid = valid_rows; p.d_valid = d_valid_rows;
+  p.epilogue = EPI_NONE; p.dual = 1; p.status = d_status;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256>(ma, mg, mu, p, max_rows, s);
+  if (bn == 128) return launch_gemm<128>(ma, mg, mu, p, max_rows, s);
+  return launch_gemm<64>(ma, mg, mu, p, max_rows, s);
 }

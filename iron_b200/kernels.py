@@ -199,6 +199,22 @@ def gemm(A, B, out=None, *, b_col_maj=False, c_col_maj=False, valid=None, d_vali
     return out
 
 
+def gemm_swiglu(A, Wg, Wu, out=None, *, valid=None, d_valid=None, status=None):
+    """``bf16(silu(bf16(A @ Wg.T))) * bf16(A @ Wu.T)`` in one tensor-core pass.
+
+    ``A`` (M, K); ``Wg`` and ``Wu`` (N, K) as a checkpoint stores them; the result is (M, N)."""
+    _bf16(A, Wg, Wu)
+    M, Kd = A.shape
+    N = Wg.shape[0]
+    if Wg.shape != Wu.shape or Wg.shape[1] != Kd:
+        raise ValueError(f"gemm_swiglu: A {tuple(A.shape)}, Wg {tuple(Wg.shape)}, Wu {tuple(Wu.shape)} do not chain")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    call("iron_gemm_swiglu_bf16", _ptr(A), _ptr(Wg), _ptr(Wu), _ptr(out), M, N, Kd, A.stride(0), Wg.stride(0),
+         out.stride(0), M if valid is None else int(valid), _ptr(d_valid), _ptr(status), _stream())
+    return out
+
+
 def mha_prefill(Q, K, V, out=None, *, q_tokens=None, d_q_tokens=None, kv_tokens=None,
                 d_kv_tokens=None, kv_tokens_add=0, causal=True, window=None, scale=None,
                 heads_interleaved=True, kv_interleaved=True, q_row_stride=None):

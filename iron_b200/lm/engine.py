@@ -288,9 +288,9 @@ class LlamaEngine:
     @property
     def launches_per_step(self) -> int:
         """Kernels one decode step launches: one persistent kernel, or gather, five per
-        layer, head, draw; a batched step takes gather, ten per layer, norm, head, draw."""
+        layer, head, draw; a batched step takes gather, eight per layer, norm, head, draw."""
         if self.batch > 1:
-            return 1 + 10 * self.c.num_hidden_layers + 3
+            return 1 + 8 * self.c.num_hidden_layers + 3
         if self.fused_step:
             return 1
         return 1 + 5 * self.c.num_hidden_layers + 2
@@ -322,9 +322,7 @@ class LlamaEngine:
                          kv_valid_add=1, window=c.window, scale=c.attention_scale)
             K.gemm(self.b_att.view(n, H * D), l["wo"], y, b_col_maj=True, residual=x, status=self.status)
             K.rms_norm(y, l["ln2"], h, eps=c.eps)
-            K.gemm(h, l["wg"], self.b_gate, b_col_maj=True, status=self.status)
-            K.gemm(h, l["wu"], self.b_up, b_col_maj=True, status=self.status)
-            K.elementwise("silu_mul", self.b_gate, self.b_up, self.b_gate)
+            K.gemm_swiglu(h, l["wg"], l["wu"], self.b_gate, status=self.status)
             K.gemm(self.b_gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
         K.rms_norm(x, self.norm, h, eps=c.eps)
         K.gemm(h, self.head, self.logits_buf, b_col_maj=True, status=self.status)
@@ -390,8 +388,8 @@ class LlamaEngine:
     # ------------------------------------------------------------------ prompt chunk
     @property
     def launches_per_chunk(self) -> int:
-        """Kernels one prompt chunk launches: gather, eleven per layer, row pick, head, draw."""
-        return 1 + 11 * self.c.num_hidden_layers + 3
+        """Kernels one prompt chunk launches: gather, nine per layer, row pick, head, draw."""
+        return 1 + 9 * self.c.num_hidden_layers + 3
 
     def prefill_chunk(self, tokens, start: int, seq: int = 0) -> None:
         """Run one prompt chunk (at most ``prefill_chunk`` tokens) at positions ``start...``.
@@ -434,9 +432,7 @@ class LlamaEngine:
             else:
                 K.gemm(att, l["wo"], y, b_col_maj=True, residual=x, status=self.status)
             K.rms_norm(y, l["ln2"], h, eps=c.eps)
-            K.gemm(h, l["wg"], gate, b_col_maj=True, status=self.status)
-            K.gemm(h, l["wu"], up, b_col_maj=True, status=self.status)
-            K.elementwise("silu_mul", gate, up, gate)
+            K.gemm_swiglu(h, l["wg"], l["wu"], gate, status=self.status)
             if tp:
                 K.gemm(gate, l["wd"], part, b_col_maj=True, status=self.status)
                 self._all_reduce(part)

@@ -116,3 +116,35 @@ def test_no_pipeline_wait_gave_up(K):
     K.gemm(to_torch(A), to_torch(W), b_col_maj=True, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (2048, 8192, 2048), (64, 8192, 2048), (200, 328, 136), (7, 2048, 512)])
+def test_gated_two_weight_form_matches_the_chain_of_references(K, M, N, Kd):
+    """gate GEMM, up GEMM, SiLU, product -- each rounded as the separate operators round."""
+    rng = np.random.default_rng(1010)
+    A = normal(rng, (M, Kd), 1.0)
+    Wg = normal(rng, (N, Kd), 1 / np.sqrt(Kd))
+    Wu = normal(rng, (N, Kd), 1 / np.sqrt(Kd))
+    gate, up = ops.gemm(A, Wg, b_col_maj=True), ops.gemm(A, Wu, b_col_maj=True)
+    want = ops.mul(ops.silu(gate), up)
+    got = to_numpy(K.gemm_swiglu(to_torch(A), to_torch(Wg), to_torch(Wu)))
+    assert got.shape == (M, N)
+    # A one-ulp flip of gate or of up (f32 sums in another order) moves the product by one
+    # of its own ulps, 2^-8 relative: all but a few in a million elements are inside the
+    # north-star bound (1e-2 relative / 2e-2 absolute), and none is further than two ulps.
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    scale = np.abs(want.astype(np.float64))
+    inside = (err <= 1e-2 * scale) | (err <= 2e-2)
+    assert inside.mean() >= 1 - 1e-5, f"{M}x{N}x{Kd}: {int((~inside).sum())} of {inside.size} outside the bound"
+    assert (err <= 2 ** -6 * scale + 2e-2).all()
+    # and it is what the three separate launches give: bit for bit where both walk K in the
+    # same order, a rounding flip here and there where the skinny separate GEMMs split K
+    g = K.gemm(to_torch(A), to_torch(Wg), b_col_maj=True)
+    u = K.gemm(to_torch(A), to_torch(Wu), b_col_maj=True)
+    chain = to_numpy(K.elementwise("silu_mul", g, u))
+    same = got.view(np.uint16) == chain.view(np.uint16)
+    if M >= 128:
+        assert same.all()
+    else:
+        d = np.abs(got.astype(np.float64) - chain.astype(np.float64))
+        assert same.mean() >= 0.99 and (d <= 2 ** -6 * np.abs(chain.astype(np.float64)) + 2e-2).all()
