@@ -60,6 +60,14 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x on the special-function unit, one instruction (no denormal rescue: a probability
+// below 2^-126 is zero either way once it is rounded to bf16).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows are D bf16 wide.
 template <int D>
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -90,7 +98,7 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int head = blockIdx.y, b = blockIdx.z;
+  const int head = blockIdx.x, b = blockIdx.z;
   const int kvh = head / (p.H / p.G);
 
   pdl_wait();
@@ -103,8 +111,9 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
   const bool masked = p.causal || p.window >= 0;
   const int offset = masked ? kv_tokens - q_tokens : 0;  // position of query row 0
 
-  // heavy (late) query blocks first: their key ranges are the longest
-  const int qb = gridDim.x - 1 - blockIdx.x;
+  // Heavy (late) query blocks first, for every head, before any light one: the heads are
+  // the fast grid dimension, so the tail of the launch is made of the shortest key ranges.
+  const int qb = gridDim.y - 1 - blockIdx.y;
   const int m0 = qb * kBlockM;
   __nv_bfloat16* Ob = p.O + (long long)b * p.o_batch_stride + (long long)head * p.o_head_stride;
 
@@ -205,7 +214,7 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float mn = fmaxf(m_run[r], mx[r]);
       msafe[r] = (mn == -INFINITY) ? 0.f : mn;
-      corr[r] = exp2f(m_run[r] - msafe[r]);  // m_run = -inf gives 0
+      corr[r] = ex2(m_run[r] - msafe[r]);  // m_run = -inf gives 0
       m_run[r] = mn;
       l_run[r] *= corr[r];
     }
@@ -213,8 +222,8 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
     float ls[2] = {0.f, 0.f};
 #pragma unroll
     for (int nt = 0; nt < kBlockN / 8; ++nt) {
-      const float p0 = exp2f(s[nt][0] - msafe[0]), p1 = exp2f(s[nt][1] - msafe[0]);
-      const float p2 = exp2f(s[nt][2] - msafe[1]), p3 = exp2f(s[nt][3] - msafe[1]);
+      const float p0 = ex2(s[nt][0] - msafe[0]), p1 = ex2(s[nt][1] - msafe[0]);
+      const float p2 = ex2(s[nt][2] - msafe[1]), p3 = ex2(s[nt][3] - msafe[1]);
       ls[0] += p0 + p1;
       ls[1] += p2 + p3;
       pf[nt >> 1][(nt & 1) * 2] = pack_bf16x2(p0, p1);
@@ -274,7 +283,7 @@ static int launch_prefill(const PrefillParams& p, int batch, cudaStream_t stream
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.q_rows + kBlockM - 1) / kBlockM, p.H, batch);
+  cfg.gridDim = dim3(p.H, (p.q_rows + kBlockM - 1) / kBlockM, batch);
   cfg.blockDim = dim3(kPfThreads);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
