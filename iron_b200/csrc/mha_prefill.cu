@@ -89,12 +89,15 @@ __device__ __forceinline__ void load_tile(uint32_t smem_tile, const __nv_bfloat1
   }
 }
 
-template <int D>
+// MT: 16-row query tiles per warp.  With MT = 2 a CTA covers 128 query rows and every K and V
+// fragment read from shared memory feeds two MMAs.
+template <int D, int MT>
 __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillParams p) {
   extern __shared__ __align__(128) uint8_t pf_smem[];
   constexpr int kTile = kBlockN * D * 2;
+  constexpr int kRowsM = kBlockM * MT;          // query rows of a CTA
   const uint32_t sQ = smem_u32(pf_smem);
-  const uint32_t sK = sQ + kTile, sV = sK + 2 * kTile;
+  const uint32_t sK = sQ + MT * kTile, sV = sK + 2 * kTile;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -114,12 +117,12 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
   // Heavy (late) query blocks first, for every head, before any light one: the heads are
   // the fast grid dimension, so the tail of the launch is made of the shortest key ranges.
   const int qb = gridDim.y - 1 - blockIdx.y;
-  const int m0 = qb * kBlockM;
+  const int m0 = qb * kRowsM;
   __nv_bfloat16* Ob = p.O + (long long)b * p.o_batch_stride + (long long)head * p.o_head_stride;
 
   if (m0 >= q_tokens || offset < 0 || kv_tokens == 0) {
     // nothing to attend from: the block's rows are zeros
-    for (int idx = tid; idx < kBlockM * (D / 8); idx += kPfThreads) {
+    for (int idx = tid; idx < kRowsM * (D / 8); idx += kPfThreads) {
       const int r = idx / (D / 8), c = idx % (D / 8);
       if (m0 + r < p.q_rows)
         *reinterpret_cast<uint4*>(Ob + (long long)(m0 + r) * p.o_row_stride + c * 8) = make_uint4(0, 0, 0, 0);
@@ -133,20 +136,27 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
 
   // key blocks this query block can see
   int j_lo = 0, j_hi = (kv_tokens + kBlockN - 1) / kBlockN;
-  if (p.causal) j_hi = min(j_hi, (offset + min(m0 + kBlockM, q_tokens) - 1) / kBlockN + 1);
-  else if (p.window >= 0) j_hi = min(j_hi, (offset + min(m0 + kBlockM, q_tokens) - 1 + p.window) / kBlockN + 1);
+  if (p.causal) j_hi = min(j_hi, (offset + min(m0 + kRowsM, q_tokens) - 1) / kBlockN + 1);
+  else if (p.window >= 0) j_hi = min(j_hi, (offset + min(m0 + kRowsM, q_tokens) - 1 + p.window) / kBlockN + 1);
   if (p.window >= 0) j_lo = max(0, (offset + m0 - p.window) / kBlockN);
 
-  load_tile<D>(sQ, Qb, p.q_row_stride, m0, q_tokens, tid);
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) load_tile<D>(sQ + mt * kTile, Qb, p.q_row_stride, m0 + mt * kBlockM, q_tokens, tid);
   load_tile<D>(sK, Kb, p.kv_row_stride, j_lo * kBlockN, kv_tokens, tid);
   load_tile<D>(sV, Vb, p.kv_row_stride, j_lo * kBlockN, kv_tokens, tid);
   cp_async_commit();
 
-  uint32_t qf[D / 16][4];
-  float o[D / 8][4];
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // query tile mt of this warp: rows m0 + mt * 64 + warp * 16 ..+ 16
+  uint32_t qf[MT][D / 16][4];
+  float o[MT][D / 8][4];
+  float m_run[MT][2], l_run[MT][2];
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  for (int mt = 0; mt < MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f; }
+  }
 
   for (int j = j_lo; j < j_hi; ++j) {
     const int buf = (j - j_lo) & 1;
@@ -160,16 +170,29 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
 
     if (j == j_lo) {
 #pragma unroll
-      for (int kt = 0; kt < D / 16; ++kt) {
-        const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldmatrix_x4(sQ + swz<D>(row, kt * 2 + (lane >> 4)), qf[kt][0], qf[kt][1], qf[kt][2], qf[kt][3]);
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int kt = 0; kt < D / 16; ++kt) {
+          const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4(sQ + mt * kTile + swz<D>(row, kt * 2 + (lane >> 4)), qf[mt][kt][0], qf[mt][kt][1],
+                      qf[mt][kt][2], qf[mt][kt][3]);
+        }
       }
     }
-
-    // ---- S = Q K^T (16 x 64 per warp) ----
-    float s[kBlockN / 8][4];
+    const int key0 = j * kBlockN;
+    // a query tile whose rows all sit above this key block has nothing to do here (causal)
+    bool dead[MT];
 #pragma unroll
-    for (int nt = 0; nt < kBlockN / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+    for (int mt = 0; mt < MT; ++mt)
+      dead[mt] = p.causal && key0 > offset + m0 + mt * kBlockM + warp * 16 + 15;
+
+    // ---- S = Q K^T (16 x 64 per query tile) ----
+    float s[MT][kBlockN / 8][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int nt = 0; nt < kBlockN / 8; ++nt) { s[mt][nt][0] = s[mt][nt][1] = s[mt][nt][2] = s[mt][nt][3] = 0.f; }
+    }
     const uint32_t kt_base = sK + buf * kTile;
 #pragma unroll
     for (int kt = 0; kt < D / 16; ++kt) {
@@ -178,63 +201,70 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
         uint32_t b0, b1, b2, b3;
         const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
         ldmatrix_x4(kt_base + swz<D>(row, kt * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
-        mma_bf16(s[2 * np], qf[kt], b0, b1);
-        mma_bf16(s[2 * np + 1], qf[kt], b2, b3);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          if (dead[mt]) continue;
+          mma_bf16(s[mt][2 * np], qf[mt][kt], b0, b1);
+          mma_bf16(s[mt][2 * np + 1], qf[mt][kt], b2, b3);
+        }
       }
     }
 
     // ---- scale, mask, online softmax ----
-    const int row_a = m0 + warp * 16 + g;  // this thread's rows: row_a and row_a + 8
-    const int key0 = j * kBlockN;
-    const bool partial = (key0 + kBlockN > kv_tokens) || p.window >= 0 ||
-                         (p.causal && key0 + kBlockN - 1 > offset + m0 + warp * 16);
-    float mx[2] = {-INFINITY, -INFINITY};
+    uint32_t pf[MT][kBlockN / 16][4];
 #pragma unroll
-    for (int nt = 0; nt < kBlockN / 8; ++nt) {
+    for (int mt = 0; mt < MT; ++mt) {
+      if (dead[mt]) continue;
+      const int row_a = m0 + mt * kBlockM + warp * 16 + g;  // this thread's rows: row_a and row_a + 8
+      const bool partial = (key0 + kBlockN > kv_tokens) || p.window >= 0 ||
+                           (p.causal && key0 + kBlockN - 1 > offset + m0 + mt * kBlockM + warp * 16);
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s[nt][e] * p.scale_log2;
-        if (partial) {
-          const int key = key0 + nt * 8 + 2 * t + (e & 1);
-          const int pos = offset + row_a + (e >> 1) * 8;
-          bool ok = key < kv_tokens;
-          if (p.causal) ok = ok && key <= pos;
-          else if (p.window >= 0) ok = ok && key <= pos + p.window;
-          if (p.window >= 0) ok = ok && key >= pos - p.window;
-          if (!ok) v = -INFINITY;
+      for (int nt = 0; nt < kBlockN / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[mt][nt][e] * p.scale_log2;
+          if (partial) {
+            const int key = key0 + nt * 8 + 2 * t + (e & 1);
+            const int pos = offset + row_a + (e >> 1) * 8;
+            bool ok = key < kv_tokens;
+            if (p.causal) ok = ok && key <= pos;
+            else if (p.window >= 0) ok = ok && key <= pos + p.window;
+            if (p.window >= 0) ok = ok && key >= pos - p.window;
+            if (!ok) v = -INFINITY;
+          }
+          s[mt][nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
-        s[nt][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
-    }
-    float corr[2], msafe[2];
+      float corr[2], msafe[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float mn = fmaxf(m_run[r], mx[r]);
-      msafe[r] = (mn == -INFINITY) ? 0.f : mn;
-      corr[r] = ex2(m_run[r] - msafe[r]);  // m_run = -inf gives 0
-      m_run[r] = mn;
-      l_run[r] *= corr[r];
-    }
-    uint32_t pf[kBlockN / 16][4];
-    float ls[2] = {0.f, 0.f};
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float mn = fmaxf(m_run[mt][r], mx[r]);
+        msafe[r] = (mn == -INFINITY) ? 0.f : mn;
+        corr[r] = ex2(m_run[mt][r] - msafe[r]);  // m_run = -inf gives 0
+        m_run[mt][r] = mn;
+        l_run[mt][r] *= corr[r];
+      }
+      float ls[2] = {0.f, 0.f};
 #pragma unroll
-    for (int nt = 0; nt < kBlockN / 8; ++nt) {
-      const float p0 = ex2(s[nt][0] - msafe[0]), p1 = ex2(s[nt][1] - msafe[0]);
-      const float p2 = ex2(s[nt][2] - msafe[1]), p3 = ex2(s[nt][3] - msafe[1]);
-      ls[0] += p0 + p1;
-      ls[1] += p2 + p3;
-      pf[nt >> 1][(nt & 1) * 2] = pack_bf16x2(p0, p1);
-      pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
-    }
-    l_run[0] += ls[0];
-    l_run[1] += ls[1];
+      for (int nt = 0; nt < kBlockN / 8; ++nt) {
+        const float p0 = ex2(s[mt][nt][0] - msafe[0]), p1 = ex2(s[mt][nt][1] - msafe[0]);
+        const float p2 = ex2(s[mt][nt][2] - msafe[1]), p3 = ex2(s[mt][nt][3] - msafe[1]);
+        ls[0] += p0 + p1;
+        ls[1] += p2 + p3;
+        pf[mt][nt >> 1][(nt & 1) * 2] = pack_bf16x2(p0, p1);
+        pf[mt][nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+      }
+      l_run[mt][0] += ls[0];
+      l_run[mt][1] += ls[1];
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) {
-      o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
-      o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+      for (int dt = 0; dt < D / 8; ++dt) {
+        o[mt][dt][0] *= corr[0]; o[mt][dt][1] *= corr[0];
+        o[mt][dt][2] *= corr[1]; o[mt][dt][3] *= corr[1];
+      }
     }
 
     // ---- O += P V ----
@@ -246,8 +276,12 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
         uint32_t b0, b1, b2, b3;
         const int row = kt2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         ldmatrix_x4_trans(vt_base + swz<D>(row, dp * 2 + (lane >> 4)), b0, b1, b2, b3);
-        mma_bf16(o[2 * dp], pf[kt2], b0, b1);
-        mma_bf16(o[2 * dp + 1], pf[kt2], b2, b3);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          if (dead[mt]) continue;
+          mma_bf16(o[mt][2 * dp], pf[mt][kt2], b0, b1);
+          mma_bf16(o[mt][2 * dp + 1], pf[mt][kt2], b2, b3);
+        }
       }
     }
     __syncthreads();  // the other buffer is overwritten by the next iteration's prefetch
@@ -256,40 +290,43 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
 
   // ---- normalise and store; rows past the bound are zeros ----
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-  }
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = m0 + warp * 16 + g + r * 8;
-    if (row >= p.q_rows) continue;
-    const bool live = row < q_tokens;
-    const float inv = (live && l_run[r] > 0.f) ? 1.0f / l_run[r] : 0.f;
-    __nv_bfloat16* dst = Ob + (long long)row * p.o_row_stride;
+    for (int r = 0; r < 2; ++r) {
+      float l = l_run[mt][r];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int row = m0 + mt * kBlockM + warp * 16 + g + r * 8;
+      if (row >= p.q_rows) continue;
+      const bool live = row < q_tokens;
+      const float inv = (live && l > 0.f) ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = Ob + (long long)row * p.o_row_stride;
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt)
-      *reinterpret_cast<uint32_t*>(dst + dt * 8 + 2 * t) = pack_bf16x2(o[dt][2 * r] * inv, o[dt][2 * r + 1] * inv);
+      for (int dt = 0; dt < D / 8; ++dt)
+        *reinterpret_cast<uint32_t*>(dst + dt * 8 + 2 * t) =
+            pack_bf16x2(o[mt][dt][2 * r] * inv, o[mt][dt][2 * r + 1] * inv);
+    }
   }
 }
 
-template <int D>
+template <int D, int MT>
 static int launch_prefill(const PrefillParams& p, int batch, cudaStream_t stream) {
-  constexpr int kSmem = 5 * kBlockN * D * 2;
+  constexpr int kSmem = (MT + 4) * kBlockN * D * 2;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(mha_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(mha_prefill_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+        cudaSuccess)
       return IRON_ERR_LAUNCH;
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.H, (p.q_rows + kBlockM - 1) / kBlockM, batch);
+  cfg.gridDim = dim3(p.H, (p.q_rows + kBlockM * MT - 1) / (kBlockM * MT), batch);
   cfg.blockDim = dim3(kPfThreads);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
-  return cudaLaunchKernelEx(&cfg, mha_prefill_kernel<D>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, mha_prefill_kernel<D, MT>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
 }  // namespace iron
@@ -326,6 +363,8 @@ extern "C" int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V
   p.causal = causal; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
-  if (D == 64) return launch_prefill<64>(p, batch, s);
-  return launch_prefill<128>(p, batch, s);
+  // One 16-row query tile per warp: two (128 query rows per CTA, every K/V fragment feeding
+  // two MMAs) measured slower at 2048 x 2048 -- 249 registers leave 8 warps per SM.
+  if (D == 64) return launch_prefill<64, 1>(p, batch, s);
+  return launch_prefill<128, 1>(p, batch, s);
 }
