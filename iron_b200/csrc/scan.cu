@@ -41,7 +41,7 @@ __device__ __forceinline__ float softplus_f32(float v) {
 
 template <int N>
 __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const ScanParams p) {
-  constexpr int NH = N / 2;        // states per thread
+  constexpr int NQ = N / 16;       // float4 groups of states per thread and row (a quarter of N)
   constexpr int CB = N / 8;        // 16-byte chunks per B (or C) row
   constexpr int kBC = (kTB * CB + kScanThreads - 1) / kScanThreads;  // chunks per thread per block
   __shared__ __align__(16) float sB[2][kTB][N];
@@ -50,13 +50,16 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
   __shared__ float2 sDt[2][kTB];   // (step, exp(step * A))
   __shared__ __align__(16) __nv_bfloat16 sY[kTB][kPT];
 
-  const int tid = threadIdx.x, p_local = tid >> 1, half = tid & 1;
+  // A thread owns two state rows (2 rp, 2 rp + 1) and every fourth float4 group of N:
+  // B and C, which all rows of a head share, are read from shared memory once for both
+  // rows, and the four threads of a row pair read one contiguous 64 bytes (no bank conflict).
+  const int tid = threadIdx.x, rp = tid >> 2, q = tid & 3;
   const int ptiles = (p.P + kPT - 1) / kPT;
   const int h = blockIdx.x / ptiles, p0 = (blockIdx.x - h * ptiles) * kPT;
   const int b = blockIdx.y;
   const int grp = h / (p.H / p.G);
   const int pcount = min(kPT, p.P - p0);
-  const bool row_live = p_local < pcount;
+  const bool live_a = 2 * rp < pcount, live_b = 2 * rp + 1 < pcount;
   const int inner = p.H * p.P;
 
   pdl_wait();
@@ -69,14 +72,23 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
   const __nv_bfloat16* dtp = p.dt + (size_t)b * p.dt_batch;
   __nv_bfloat16* yb = p.y + (size_t)b * p.y_batch;
 
-  float2 s[NH / 2];
-  if (row_live && p.state) {
-    const float* src = p.state + (size_t)b * p.state_batch + ((size_t)h * p.P + p0 + p_local) * N + half * NH;
+  float2 sa[2 * NQ], sb[2 * NQ];   // group j of this thread: states (4 j + q) * 4 .. + 4
 #pragma unroll
-    for (int i = 0; i < NH / 2; ++i) s[i] = *reinterpret_cast<const float2*>(src + 2 * i);
-  } else {
+  for (int i = 0; i < 2 * NQ; ++i) { sa[i] = make_float2(0.f, 0.f); sb[i] = make_float2(0.f, 0.f); }
+  if (p.state) {
+    const float* src = p.state + (size_t)b * p.state_batch + ((size_t)h * p.P + p0 + 2 * rp) * N;
 #pragma unroll
-    for (int i = 0; i < NH / 2; ++i) s[i] = make_float2(0.f, 0.f);
+    for (int j = 0; j < NQ; ++j) {
+      const int n0 = (4 * j + q) * 4;
+      if (live_a) {
+        const float4 v = *reinterpret_cast<const float4*>(src + n0);
+        sa[2 * j] = make_float2(v.x, v.y); sa[2 * j + 1] = make_float2(v.z, v.w);
+      }
+      if (live_b) {
+        const float4 v = *reinterpret_cast<const float4*>(src + N + n0);
+        sb[2 * j] = make_float2(v.x, v.y); sb[2 * j + 1] = make_float2(v.z, v.w);
+      }
+    }
   }
 
   // registers holding the next block's raw rows while the current block computes
@@ -148,30 +160,46 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
     if (more) fetch(t0 + kTB);
     const int steps = min(kTB, valid - t0);  // <= 0 past the bound: rows of zeros
     for (int tt = 0; tt < kTB; ++tt) {
-      float yv = 0.f;
+      float ya = 0.f, yb2 = 0.f;
       if (tt < steps) {
         const float2 sd = sDt[buf][tt];
-        const float xv = sX[buf][tt][p_local];
-        const float xdt = sd.x * xv;
-        const float2 dA2 = make_float2(sd.y, sd.y), xdt2 = make_float2(xdt, xdt);
-        float2 acc = make_float2(0.f, 0.f);
-        const float4* Bp = reinterpret_cast<const float4*>(&sB[buf][tt][half * NH]);
-        const float4* Cp = reinterpret_cast<const float4*>(&sC[buf][tt][half * NH]);
+        const float2 xv = *reinterpret_cast<const float2*>(&sX[buf][tt][2 * rp]);
+        const float2 dA2 = make_float2(sd.y, sd.y);
+        const float2 xa2 = make_float2(sd.x * xv.x, sd.x * xv.x), xb2 = make_float2(sd.x * xv.y, sd.x * xv.y);
+        float2 acc_a0 = make_float2(0.f, 0.f), acc_a1 = acc_a0, acc_b0 = acc_a0, acc_b1 = acc_a0;
+        const float4* Bp = reinterpret_cast<const float4*>(&sB[buf][tt][0]) + q;
+        const float4* Cp = reinterpret_cast<const float4*>(&sC[buf][tt][0]) + q;
 #pragma unroll
-        for (int i = 0; i < NH / 4; ++i) {
-          const float4 bv = Bp[i], cv = Cp[i];
-          s[2 * i] = __ffma2_rn(dA2, s[2 * i], __fmul2_rn(xdt2, make_float2(bv.x, bv.y)));
-          s[2 * i + 1] = __ffma2_rn(dA2, s[2 * i + 1], __fmul2_rn(xdt2, make_float2(bv.z, bv.w)));
-          acc = __ffma2_rn(s[2 * i], make_float2(cv.x, cv.y), acc);
-          acc = __ffma2_rn(s[2 * i + 1], make_float2(cv.z, cv.w), acc);
+        for (int j = 0; j < NQ; ++j) {
+          const float4 bv = Bp[4 * j], cv = Cp[4 * j];
+          const float2 b0 = make_float2(bv.x, bv.y), b1 = make_float2(bv.z, bv.w);
+          const float2 c0 = make_float2(cv.x, cv.y), c1 = make_float2(cv.z, cv.w);
+          sa[2 * j] = __ffma2_rn(dA2, sa[2 * j], __fmul2_rn(xa2, b0));
+          sa[2 * j + 1] = __ffma2_rn(dA2, sa[2 * j + 1], __fmul2_rn(xa2, b1));
+          sb[2 * j] = __ffma2_rn(dA2, sb[2 * j], __fmul2_rn(xb2, b0));
+          sb[2 * j + 1] = __ffma2_rn(dA2, sb[2 * j + 1], __fmul2_rn(xb2, b1));
+          acc_a0 = __ffma2_rn(sa[2 * j], c0, acc_a0);
+          acc_a1 = __ffma2_rn(sa[2 * j + 1], c1, acc_a1);
+          acc_b0 = __ffma2_rn(sb[2 * j], c0, acc_b0);
+          acc_b1 = __ffma2_rn(sb[2 * j + 1], c1, acc_b1);
         }
-        yv = acc.x + acc.y;
-        yv += __shfl_xor_sync(0xffffffffu, yv, 1);
-        yv = fmaf(Dh, xv, yv);
+        ya = (acc_a0.x + acc_a0.y) + (acc_a1.x + acc_a1.y);
+        yb2 = (acc_b0.x + acc_b0.y) + (acc_b1.x + acc_b1.y);
+        ya += __shfl_xor_sync(0xffffffffu, ya, 1);
+        yb2 += __shfl_xor_sync(0xffffffffu, yb2, 1);
+        ya += __shfl_xor_sync(0xffffffffu, ya, 2);
+        yb2 += __shfl_xor_sync(0xffffffffu, yb2, 2);
+        ya = fmaf(Dh, xv.x, ya);
+        yb2 = fmaf(Dh, xv.y, yb2);
       } else {
-        (void)__shfl_xor_sync(0xffffffffu, yv, 1);
+        (void)__shfl_xor_sync(0xffffffffu, ya, 1);
+        (void)__shfl_xor_sync(0xffffffffu, yb2, 1);
+        (void)__shfl_xor_sync(0xffffffffu, ya, 2);
+        (void)__shfl_xor_sync(0xffffffffu, yb2, 2);
       }
-      if (half == 0) sY[tt][p_local] = __float2bfloat16_rn(yv);
+      if (q == 0)
+        *reinterpret_cast<__nv_bfloat162*>(&sY[tt][2 * rp]) =
+            __halves2bfloat162(__float2bfloat16_rn(ya), __float2bfloat16_rn(yb2));
     }
     __syncthreads();
     // y tile out: 16 rows x up to 64 columns
@@ -190,10 +218,15 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
     __syncthreads();
   }
 
-  if (row_live && p.final_state) {
-    float* dst = p.final_state + (size_t)b * p.state_batch + ((size_t)h * p.P + p0 + p_local) * N + half * NH;
+  if (p.final_state) {
+    float* dst = p.final_state + (size_t)b * p.state_batch + ((size_t)h * p.P + p0 + 2 * rp) * N;
 #pragma unroll
-    for (int i = 0; i < NH / 2; ++i) *reinterpret_cast<float2*>(dst + 2 * i) = s[i];
+    for (int j = 0; j < NQ; ++j) {
+      const int n0 = (4 * j + q) * 4;
+      if (live_a) *reinterpret_cast<float4*>(dst + n0) = make_float4(sa[2 * j].x, sa[2 * j].y, sa[2 * j + 1].x, sa[2 * j + 1].y);
+      if (live_b)
+        *reinterpret_cast<float4*>(dst + N + n0) = make_float4(sb[2 * j].x, sb[2 * j].y, sb[2 * j + 1].x, sb[2 * j + 1].y);
+    }
   }
 }
 
@@ -247,35 +280,48 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
   };
 #pragma unroll
   for (int k = 0; k < K - 1; ++k) input_row(r_lo - (K - 1) + k, win[k]);
-  for (int r = r_lo; r < r_hi; ++r) {
-    input_row(r, win[K - 1]);
-    float out[8];
-    if (r < valid) {
+  // Eight rows at a time: their loads are issued together, then the eight outputs follow.
+  constexpr int kRows = 8;
+  for (int r0 = r_lo; r0 < r_hi; r0 += kRows) {
+    uint4 raw[kRows];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float acc;
-        if (p.decode_order) {
-          acc = round_bf16(__fmul_rn(win[K - 1][j], w[K - 1][j]));
-#pragma unroll
-          for (int k = 0; k < K - 1; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
-        } else {
-          acc = round_bf16(__fmul_rn(win[0][j], w[0][j]));
-#pragma unroll
-          for (int k = 1; k < K; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
-        }
-        if (p.bias) acc = round_bf16(__fadd_rn(acc, bias[j]));
-        if (p.silu) acc = silu_f32(acc);
-        out[j] = acc;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) out[j] = 0.f;
+    for (int u = 0; u < kRows; ++u) {
+      const int r = r0 + u;
+      raw[u] = (r < r_hi && r < valid) ? ld_cached(x + (size_t)r * p.C) : make_uint4(0, 0, 0, 0);
     }
-    *reinterpret_cast<uint4*>(y + (size_t)r * p.C) = pack8(out);
 #pragma unroll
-    for (int k = 0; k < K - 1; ++k)
+    for (int u = 0; u < kRows; ++u) {
+      const int r = r0 + u;
+      if (r >= r_hi) break;
+      unpack8(raw[u], win[K - 1]);
+      float out[8];
+      if (r < valid) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+        for (int j = 0; j < 8; ++j) {
+          float acc;
+          if (p.decode_order) {
+            acc = round_bf16(__fmul_rn(win[K - 1][j], w[K - 1][j]));
+#pragma unroll
+            for (int k = 0; k < K - 1; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
+          } else {
+            acc = round_bf16(__fmul_rn(win[0][j], w[0][j]));
+#pragma unroll
+            for (int k = 1; k < K; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
+          }
+          if (p.bias) acc = round_bf16(__fadd_rn(acc, bias[j]));
+          if (p.silu) acc = silu_f32(acc);
+          out[j] = acc;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out[j] = 0.f;
+      }
+      *reinterpret_cast<uint4*>(y + (size_t)r * p.C) = pack8(out);
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+    }
   }
   // the K-1 rows ending the valid run become the next call's history
   if (p.new_history && blockIdx.y == 0) {
@@ -358,9 +404,9 @@ extern "C" int iron_causal_conv1d_bf16(const void* x, const void* taps, const vo
   // rows are cut into segments so a long prompt fills the machine; each segment re-reads
   // the K-1 rows before it
   const int cgroups = (channels / 8 + 127) / 128;
-  int segs = (2 * kSMs) / (cgroups * batch);
+  int segs = (16 * kSMs + cgroups * batch - 1) / (cgroups * batch);
   segs = segs < 1 ? 1 : segs;
-  const int max_segs = (rows + 63) / 64;
+  const int max_segs = (rows + 31) / 32;
   if (segs > max_segs) segs = max_segs;
   const dim3 grid(cgroups, segs, batch), block(128);
   cudaStream_t s = (cudaStream_t)stream;
