@@ -17,6 +17,8 @@
 // programmatic-dependency wait and the newest row is re-read after it.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -267,6 +269,12 @@ static int launch_decode(const DecodeParams& p, int B, cudaStream_t stream) {
                                                                               : IRON_ERR_LAUNCH;
 }
 
+// the tensor-core kernel for batches that fill the machine (mha_decode_tc.cu)
+int mha_decode_tc(const void* Q, const void* K, const void* V, void* O, int batch, int H, int G, int D, int kv_max,
+                  long long kv_batch_stride, long long kv_seq_stride, long long kv_head_stride, int kv_valid,
+                  const int* d_kv_valid, int d_kv_valid_stride, int kv_valid_add, int window, float scale,
+                  cudaStream_t stream);
+
 static int decode_gq(int group) { return group >= 5 ? 8 : (group >= 3 ? 4 : (group == 2 ? 2 : 1)); }
 
 }  // namespace iron
@@ -296,6 +304,19 @@ extern "C" int iron_mha_decode_bf16(const void* Q, const void* K, const void* V,
   if ((kv_batch_stride & 7) || (kv_seq_stride & 7) || (kv_head_stride & 7)) return IRON_ERR_ALIGN;
   if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return IRON_ERR_ALIGN;
   const int group = H / G;
+  // A batch that fills the machine on its own (one CTA per sequence and KV head) goes to the
+  // tensor-core kernel: the group's query heads are the rows of one MMA tile.
+  // IRON_MHA_DECODE_TC=0 keeps the SIMT kernel.
+  static const bool use_tc = [] {
+    const char* e = getenv("IRON_MHA_DECODE_TC");
+    return !(e && e[0] == '0');
+  }();
+  if (use_tc && group > 1 && (long long)batch * G >= 2 * kSMs) {
+    const int rc = mha_decode_tc(Q, K, V, O, batch, H, G, D, kv_max, kv_batch_stride, kv_seq_stride,
+                                 kv_head_stride, kv_valid, d_kv_valid, d_kv_valid_stride, kv_valid_add, window,
+                                 scale, (cudaStream_t)stream);
+    if (rc != IRON_ERR_UNSUPPORTED) return rc;
+  }
   // Query heads that share a KV head run in one CTA only when the grid already fills the
   // machine; a single sequence gives every query head a CTA of its own (the re-read keys
   // hit in L2) so that the per-key work spreads over all SMs.

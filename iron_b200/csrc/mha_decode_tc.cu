@@ -1,0 +1,290 @@
+// One-query attention for a *batch* of sequences on the warp tensor cores.
+//
+// When the batch alone fills the machine (batch x KV heads >= two CTAs per SM) the SIMT
+// decode kernel is bound by instruction issue: every key costs a dot product and an
+// accumulation per query head.  Here the query heads that share a KV head are the rows of
+// one 16-row MMA tile, so K and V are read once for the whole group and the arithmetic runs
+// as mma.sync m16n8k16:
+//   one CTA = one (sequence, KV head); 4 warps; keys stream through shared memory in
+//   64-row tiles (cp.async, double buffered, XOR-swizzled 16-byte chunks); within a tile
+//   each warp takes 16 keys: S = Q K^T (2 key tiles x D/16 steps), online softmax in the
+//   exp2 domain, O += P V (D/8 column tiles); the four warps' (max, sum, O) are merged
+//   through shared memory at the end.
+// Rows of the tile beyond the group are zero queries whose results are dropped.
+#include "common.cuh"
+
+namespace iron {
+
+struct DecodeTcParams {
+  const __nv_bfloat16* Q;   // (B, H, D)
+  const __nv_bfloat16* K;
+  const __nv_bfloat16* V;
+  __nv_bfloat16* O;         // (B, H, D)
+  long long kv_batch_stride, kv_seq_stride, kv_head_stride;  // elements
+  int H, G, group;
+  int kv_valid;
+  const int* d_kv_valid;
+  int d_kv_valid_stride;
+  int kv_valid_add;
+  int kv_max;
+  int window;               // < 0: none
+  float scale_log2;
+};
+
+constexpr int kDtThreads = 128;
+constexpr int kDtKeys = 64;   // keys per shared-memory tile
+
+__device__ __forceinline__ void dt_cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void dt_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void dt_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void dt_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void dt_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                     uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void dt_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float dt_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t dt_pack(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows are D bf16 wide.
+template <int D>
+__device__ __forceinline__ uint32_t dt_swz(int row, int chunk) {
+  return (uint32_t)(row * (D * 2) + ((((chunk & 7) ^ (row & 7)) | (chunk & ~7)) << 4));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kDtThreads) mha_decode_tc_kernel(const DecodeTcParams p) {
+  extern __shared__ __align__(128) uint8_t dt_smem[];
+  constexpr int kTile = kDtKeys * D * 2;
+  constexpr int kChunks = D / 8;
+  const uint32_t sQ = smem_u32(dt_smem);            // 16 rows x D
+  const uint32_t sK = sQ + 16 * D * 2, sV = sK + 2 * kTile;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+
+  pdl_wait();
+  pdl_launch();
+
+  int kv_valid = p.kv_valid;
+  if (p.d_kv_valid) kv_valid = p.d_kv_valid[b * p.d_kv_valid_stride] + p.kv_valid_add;
+  kv_valid = max(0, min(kv_valid, p.kv_max));
+  const int lo = (p.window >= 0) ? max(0, kv_valid - 1 - p.window) : 0;
+  const int j_lo = lo / kDtKeys, j_hi = (kv_valid + kDtKeys - 1) / kDtKeys;
+
+  const __nv_bfloat16* Qb = p.Q + ((size_t)b * p.H + (size_t)kvh * p.group) * D;
+  const __nv_bfloat16* Kb = p.K + (size_t)b * p.kv_batch_stride + (size_t)kvh * p.kv_head_stride;
+  const __nv_bfloat16* Vb = p.V + (size_t)b * p.kv_batch_stride + (size_t)kvh * p.kv_head_stride;
+
+  auto load_kv = [&](uint32_t tile, const __nv_bfloat16* base, int row0) {
+#pragma unroll
+    for (int i = 0; i < (kDtKeys * kChunks) / kDtThreads; ++i) {
+      const int idx = tid + i * kDtThreads;
+      const int r = idx / kChunks, c = idx % kChunks;
+      const bool live = row0 + r < kv_valid;
+      dt_cp_async16(tile + dt_swz<D>(r, c), base + (size_t)(live ? row0 + r : 0) * p.kv_seq_stride + c * 8, live);
+    }
+  };
+  // the query heads of this KV head are rows 0 .. group-1 of the tile; the rest are zeros
+  for (int idx = tid; idx < 16 * kChunks; idx += kDtThreads) {
+    const int r = idx / kChunks, c = idx % kChunks;
+    const bool live = r < p.group;
+    dt_cp_async16(sQ + dt_swz<D>(r, c), Qb + (size_t)(live ? r : 0) * D + c * 8, live);
+  }
+  if (j_lo < j_hi) {
+    load_kv(sK, Kb, j_lo * kDtKeys);
+    load_kv(sV, Vb, j_lo * kDtKeys);
+  }
+  dt_commit();
+
+  uint32_t qf[D / 16][4];
+  float o[D / 8][4];
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+  for (int j = j_lo; j < j_hi; ++j) {
+    const int buf = (j - j_lo) & 1;
+    if (j + 1 < j_hi) {
+      load_kv(sK + (buf ^ 1) * kTile, Kb, (j + 1) * kDtKeys);
+      load_kv(sV + (buf ^ 1) * kTile, Vb, (j + 1) * kDtKeys);
+    }
+    dt_commit();
+    dt_wait<1>();
+    __syncthreads();
+    if (j == j_lo) {
+#pragma unroll
+      for (int kt = 0; kt < D / 16; ++kt) {
+        const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+        dt_ldmatrix_x4(sQ + dt_swz<D>(row, kt * 2 + (lane >> 4)), qf[kt][0], qf[kt][1], qf[kt][2], qf[kt][3]);
+      }
+    }
+    // ---- S = Q K^T for this warp's 16 keys of the tile ----
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+    const uint32_t kt_base = sK + buf * kTile;
+#pragma unroll
+    for (int kt = 0; kt < D / 16; ++kt) {
+      uint32_t b0, b1, b2, b3;
+      const int row = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+      dt_ldmatrix_x4(kt_base + dt_swz<D>(row, kt * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+      dt_mma(s[0], qf[kt], b0, b1);
+      dt_mma(s[1], qf[kt], b2, b3);
+    }
+    // ---- mask, online softmax (rows g and g + 8 of the tile) ----
+    const int key0 = j * kDtKeys + warp * 16;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + nt * 8 + 2 * t + (e & 1);
+        float v = s[nt][e] * p.scale_log2;
+        if (key >= kv_valid || key < lo) v = -INFINITY;
+        s[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float mn = fmaxf(m_run[r], mx[r]);
+      msafe[r] = (mn == -INFINITY) ? 0.f : mn;
+      corr[r] = dt_ex2(m_run[r] - msafe[r]);
+      m_run[r] = mn;
+      l_run[r] *= corr[r];
+    }
+    uint32_t pf[4];
+    {
+      const float p00 = dt_ex2(s[0][0] - msafe[0]), p01 = dt_ex2(s[0][1] - msafe[0]);
+      const float p02 = dt_ex2(s[0][2] - msafe[1]), p03 = dt_ex2(s[0][3] - msafe[1]);
+      const float p10 = dt_ex2(s[1][0] - msafe[0]), p11 = dt_ex2(s[1][1] - msafe[0]);
+      const float p12 = dt_ex2(s[1][2] - msafe[1]), p13 = dt_ex2(s[1][3] - msafe[1]);
+      l_run[0] += (p00 + p01) + (p10 + p11);
+      l_run[1] += (p02 + p03) + (p12 + p13);
+      pf[0] = dt_pack(p00, p01); pf[1] = dt_pack(p02, p03);
+      pf[2] = dt_pack(p10, p11); pf[3] = dt_pack(p12, p13);
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+      o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+    }
+    // ---- O += P V over this warp's 16 keys ----
+    const uint32_t vt_base = sV + buf * kTile;
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b0, b1, b2, b3;
+      const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      dt_ldmatrix_x4_trans(vt_base + dt_swz<D>(row, dp * 2 + (lane >> 4)), b0, b1, b2, b3);
+      dt_mma(o[2 * dp], pf, b0, b1);
+      dt_mma(o[2 * dp + 1], pf, b2, b3);
+    }
+    __syncthreads();  // the other buffer is overwritten by the next iteration's prefetch
+  }
+  dt_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps (each saw a quarter of the keys) ----
+  // per warp: 16 rows x (D outputs, max, sum) in f32, over the tiles' shared memory
+  float* part = reinterpret_cast<float*>(dt_smem);
+  constexpr int kRow = D + 2;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = g + r * 8;
+    float* dst = part + ((size_t)warp * 16 + row) * kRow;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      dst[dt * 8 + 2 * t] = o[dt][2 * r];
+      dst[dt * 8 + 2 * t + 1] = o[dt][2 * r + 1];
+    }
+    if (t == 0) { dst[D] = m_run[r]; dst[D + 1] = l; }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < p.group * D; idx += kDtThreads) {
+    const int row = idx / D, d = idx - row * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, part[((size_t)w * 16 + row) * kRow + D]);
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = part + ((size_t)w * 16 + row) * kRow;
+      const float c = (src[D] == -INFINITY) ? 0.f : dt_ex2(src[D] - M);
+      acc = fmaf(src[d], c, acc);
+      L = fmaf(src[D + 1], c, L);
+    }
+    p.O[((size_t)b * p.H + (size_t)kvh * p.group + row) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+template <int D>
+static int launch_decode_tc(const DecodeTcParams& p, int batch, cudaStream_t stream) {
+  // Q tile + double-buffered K and V tiles; the merge reuses the same bytes
+  constexpr int kTiles = 16 * D * 2 + 4 * kDtKeys * D * 2;
+  constexpr int kMerge = 4 * 16 * (D + 2) * 4;
+  constexpr int kSmem = kTiles > kMerge ? kTiles : kMerge;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(mha_decode_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+        cudaSuccess)
+      return IRON_ERR_LAUNCH;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.G, batch, 1);
+  cfg.blockDim = dim3(kDtThreads);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  return cudaLaunchKernelEx(&cfg, mha_decode_tc_kernel<D>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+}
+
+// Called by iron_mha_decode_bf16 for batches that fill the machine; the arguments are that
+// entry point's, already validated.  Returns IRON_ERR_UNSUPPORTED when the shape is not
+// this kernel's (the caller then takes the SIMT kernel).
+int mha_decode_tc(const void* Q, const void* K, const void* V, void* O, int batch, int H, int G, int D, int kv_max,
+                  long long kv_batch_stride, long long kv_seq_stride, long long kv_head_stride, int kv_valid,
+                  const int* d_kv_valid, int d_kv_valid_stride, int kv_valid_add, int window, float scale,
+                  cudaStream_t stream) {
+  const int group = H / G;
+  if (group > 16 || (D != 64 && D != 128)) return IRON_ERR_UNSUPPORTED;
+  DecodeTcParams p = {};
+  p.Q = (const __nv_bfloat16*)Q; p.K = (const __nv_bfloat16*)K; p.V = (const __nv_bfloat16*)V;
+  p.O = (__nv_bfloat16*)O;
+  p.kv_batch_stride = kv_batch_stride; p.kv_seq_stride = kv_seq_stride; p.kv_head_stride = kv_head_stride;
+  p.H = H; p.G = G; p.group = group;
+  p.kv_valid = kv_valid; p.d_kv_valid = d_kv_valid; p.d_kv_valid_stride = d_kv_valid_stride;
+  p.kv_valid_add = kv_valid_add; p.kv_max = kv_max; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  return D == 64 ? launch_decode_tc<64>(p, batch, stream) : launch_decode_tc<128>(p, batch, stream);
+}
+
+}  // namespace iron

@@ -273,6 +273,32 @@ def test_mha_decode_batched_with_per_sequence_lengths_on_device(K):
         assert_verdict(got[b : b + 1], want, MHA_TOL, what=f"sequence {b}")
 
 
+@pytest.mark.parametrize("B,H,G,D,S,window", [
+    (40, 32, 8, 64, 300, None),     # 320 (sequence, KV head) pairs: the tensor-core kernel
+    (64, 24, 8, 128, 200, None),    # 128-wide heads, groups of 3
+    (300, 5, 1, 64, 130, 40),       # groups of 5, one KV head, a sliding window
+    (38, 32, 8, 64, 129, None),
+])
+def test_mha_decode_large_batches_on_the_tensor_cores(K, B, H, G, D, S, window):
+    """A batch that fills the machine takes the MMA kernel: every sequence has its own
+    length (empty, one key, tile boundaries, full)."""
+    rng = np.random.default_rng(12)
+    q = normal(rng, (B, H, D))
+    k, v = normal(rng, (B, S, G, D)), normal(rng, (B, S, G, D))
+    pos = rng.integers(0, S, B).astype(np.int32)
+    pos[:6] = [0, 63, 64, 127, 128, S - 1]
+    got = to_numpy(K.mha_decode(to_torch(q), to_torch(k), to_torch(v), d_kv_valid=to_torch(pos),
+                                per_batch=True, kv_valid_add=1, window=window))
+    for b in list(range(8)) + [B // 2, B - 1]:
+        want = ops.mha(q[b : b + 1], k[b], v[b], num_heads=H, num_kv_heads=G, window=window,
+                       heads_interleaved=True, kv_interleaved=True, q_tokens=1, kv_tokens=int(pos[b]) + 1)
+        assert_verdict(got[b : b + 1], want, MHA_TOL, what=f"sequence {b} of {B}")
+        assert_north_star(got[b : b + 1], want, f"sequence {b} of {B}")
+    # a sequence with no keys at all gives zeros
+    zero = to_numpy(K.mha_decode(to_torch(q), to_torch(k), to_torch(v), kv_valid=0))
+    assert not zero.any()
+
+
 def test_mha_decode_non_interleaved_cache_layout(K):
     rng = np.random.default_rng(10)
     H, G, D, S = 8, 2, 64, 512
