@@ -152,11 +152,13 @@ struct GemmCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = SPLIT ? 4 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
-  // the leader's landing area for the other CTAs' accumulators
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  // The leader's landing area for the other CTAs' accumulators lies over the pipeline
+  // stages: nothing is shipped before every CTA of the cluster has finished its main loop.
   static constexpr int kStagingBytes = SPLIT ? (kMaxSplit - 1) * BM * BN * 4 : 0;
+  static_assert(kStagingBytes <= kStages * kStageBytes, "the staging area must fit in the stages");
   static constexpr int kBarBytes = 256;
-  static constexpr int kSmem = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ float epilogue_apply(int mode, float c) {
@@ -177,8 +179,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   using Cfg = GemmCfg<BN, SPLIT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* staging = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
+  float* staging = reinterpret_cast<float*>(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
   uint64_t* full = bars;                         // [kStages]
   uint64_t* empty = bars + Cfg::kStages;         // [kStages]
   uint64_t* acc_full = bars + 2 * Cfg::kStages;  // [2]
@@ -421,6 +423,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if constexpr (!SPLIT) {
     if (warp >= 2) drain(false, false);
   } else {
+    // every CTA's main loop is over (its copies have landed and its MMAs have read them)
+    // before anything is written over the leader's stages
+    if (warp >= 2 && t_first < total) mbar_wait(acc_full, 0, abort_flag);
+    cg::this_cluster().sync();
     if (warp >= 2 && crank != 0) drain(true, false);
     cg::this_cluster().sync();   // every rank's accumulator is in the leader's staging area
     if (warp >= 2 && crank == 0) drain(false, true);
