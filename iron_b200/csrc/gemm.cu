@@ -152,7 +152,10 @@ struct GemmCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  // The split (skinny) form keeps its footprint to half an SM -- four stages, one 64-column
+  // accumulator -- so that the next kernel of a chain can start under it.
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = SPLIT ? 64 : 512;
   // The leader's landing area for the other CTAs' accumulators lies over the pipeline
   // stages: nothing is shipped before every CTA of the cluster has finished its main loop.
   static constexpr int kStagingBytes = SPLIT ? (kMaxSplit - 1) * BM * BN * 4 : 0;
@@ -199,8 +202,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b2) : "memory");
   }
-  if (warp == 1) {  // the MMA warp owns tensor memory: all 512 columns (one CTA per SM)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+  if (warp == 1) {  // the MMA warp owns tensor memory (all 512 columns unless split)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(Cfg::kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -209,32 +213,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // A and (for b_n_major) B are inputs the previous kernel may have produced.
-  pdl_wait();
-
-  int valid = p.d_valid ? min(*p.d_valid, p.M) : p.valid;
-  valid = max(valid, 0);
-  const int m_tiles = (valid + BM - 1) / BM;
+  // Which tiles and which K blocks this CTA takes: every tile and all of K, or -- split --
+  // the cluster's one tile and this rank's slice of K.
+  int valid = 0, m_tiles = 0, n_tiles = 0, total = 0, t_first = blockIdx.x, t_step = gridDim.x, k_lo = 0, k_hi = 0;
+  unsigned int crank = 0, csize = 1;
   // Output columns per tile: in the gated form one accumulator holds BN/2 columns of the
   // first product and the matching BN/2 columns of the second.
   const int BNO = p.dual ? BN / 2 : BN;
-  const int n_tiles = (p.N + BNO - 1) / BNO;
-  const int total = m_tiles * n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
-  // Which tiles and which K blocks this CTA takes: every tile and all of K, or -- split --
-  // the cluster's one tile and this rank's slice of K.
-  int t_first = blockIdx.x, t_step = gridDim.x, k_lo = 0, k_hi = num_kb;
-  unsigned int crank = 0, csize = 1;
-  if constexpr (SPLIT) {
-    cg::cluster_group cl = cg::this_cluster();
-    crank = cl.block_rank();
-    csize = cl.num_blocks();
-    t_first = blockIdx.x / csize;
-    t_step = total > 0 ? total : 1;
-    const int per = (num_kb + (int)csize - 1) / (int)csize;
-    k_lo = min(num_kb, (int)crank * per);
-    k_hi = min(num_kb, k_lo + per);
+  auto setup = [&](int rows) {
+    valid = max(rows, 0);
+    m_tiles = (valid + BM - 1) / BM;
+    n_tiles = (p.N + BNO - 1) / BNO;
+    total = m_tiles * n_tiles;
+    k_hi = num_kb;
+    if constexpr (SPLIT) {
+      cg::cluster_group cl = cg::this_cluster();
+      crank = cl.block_rank();
+      csize = cl.num_blocks();
+      t_first = blockIdx.x / csize;
+      t_step = total > 0 ? total : 1;
+      const int per = (num_kb + (int)csize - 1) / (int)csize;
+      k_lo = min(num_kb, (int)crank * per);
+      k_hi = min(num_kb, k_lo + per);
+    }
+  };
+  // The dependents of this kernel may start their own prologue (and weight loads) now.
+  pdl_launch();
+  // Split form with the row count known at launch: the weight tiles do not depend on the
+  // kernel before, so the first stages' B copies go out ahead of the dependency wait.
+  const bool early = SPLIT && p.d_valid == nullptr && !p.b_n_major;
+  int pre = 0;
+  if (early) {
+    setup(p.valid);
+    if (warp == 0 && lane == 0 && t_first < total) {
+      const int n0 = (t_first / m_tiles) * BNO;
+      for (int kb = k_lo; kb < k_hi && pre < Cfg::kStages; ++kb, ++pre) {
+        mbar_expect_tx(full + pre, Cfg::kStageBytes);
+        tma_load_2d(smem + pre * Cfg::kStageBytes + Cfg::kABytes, &map_b, kb * BK, n0, full + pre);
+      }
+    }
   }
+  // A and (for b_n_major) B are inputs the previous kernel may have produced.
+  pdl_wait();
+  if (!early) setup(p.d_valid ? min(*p.d_valid, p.M) : p.valid);
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -249,6 +271,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (!mbar_wait(empty + s, phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* a_dst = smem + s * Cfg::kStageBytes;
           uint8_t* b_dst = a_dst + Cfg::kABytes;
+          if (issued < pre) {   // this stage's B tile is already on its way
+            tma_load_2d(a_dst, &map_a, kb * BK, m0, full + s);
+            ++issued;
+            if (++s == Cfg::kStages) { s = 0; phase ^= 1; }
+            continue;
+          }
           mbar_expect_tx(full + s, Cfg::kStageBytes);
           tma_load_2d(a_dst, &map_a, kb * BK, m0, full + s);
           if (p.dual) {
@@ -432,13 +460,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp >= 2 && crank == 0) drain(false, true);
   }
 
-  pdl_launch();
   tcgen05_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = IRON_ERR_TIMEOUT;
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
+                 : "memory");
   }
 }
 
