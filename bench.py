@@ -24,6 +24,8 @@ import subprocess
 import sys
 import threading
 import time
+
+import numpy as np
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
@@ -398,6 +400,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-step-trace", action="store_true",
+                    help="with IRON_DECODE_STEP=1: print the one-kernel step's per-phase timeline and exit")
     ap.add_argument("--workload", default="llama1b", choices=["llama1b", "llama3b-tp", "llama1b-batch64"],
                     help="llama1b: the headline decode, one replica per GPU; llama3b-tp: the 3B "
                          "architecture tensor-parallel over --gpus ranks at context 4096")
@@ -446,6 +450,27 @@ def main() -> None:
     tokens = prompt_tokens(3002 + rank)
     prefill = time_prefill(engine, tokens)
     engine.capture()
+    if args.decode_step_trace:
+        engine.set_call(1, CONTEXT)
+        for _ in range(max(args.steps, 1)):
+            engine.step()
+        torch.cuda.synchronize()
+        t = engine.step_trace()
+        L = config.num_hidden_layers
+        names = ["qkv", "attention", "o_proj", "gate_up", "down_proj"]
+        out = {}
+        for j, name in enumerate(names):
+            rows = [5 * l + j for l in range(L)]
+            wait = [t[p, 0] - (t[p - 1, 2] if p else t[p, 0]) for p in rows]
+            out[name] = {"wait_us": round(float(np.mean(wait)) / 1e3, 2),
+                         "stage_us": round(float(np.mean([t[p, 1] - t[p, 0] for p in rows])) / 1e3, 2),
+                         "items_us": round(float(np.mean([t[p, 2] - t[p, 1] for p in rows])) / 1e3, 2)}
+        p = 5 * L
+        out["head"] = {"wait_us": round((t[p, 0] - t[p - 1, 2]) / 1e3, 2), "stage_us": round((t[p, 1] - t[p, 0]) / 1e3, 2),
+                       "items_us": round((t[p, 2] - t[p, 1]) / 1e3, 2)}
+        out["step_us"] = round((t[p, 2] - t[0, 0]) / 1e3, 1)
+        print(json.dumps({"decode_step_trace": out}))
+        return
     warm = max(args.warmup, 3)
 
     def barrier():

@@ -537,6 +537,18 @@ class LlamaEngine:
             raise RuntimeError("the decode step's grid barrier gave up (IRON_ERR_TIMEOUT)")
         return int(self._h_token[0])
 
+    def step_trace(self) -> np.ndarray:
+        """CTA 0's timestamps of the last one-kernel decode step, nanoseconds: one row per
+        phase (five per layer -- q/k/v, attention, o_proj, gate/up, down_proj -- then the
+        head), columns (barrier wait over, staging done, own weight items done)."""
+        if not self.fused_step:
+            raise RuntimeError("the phase trace belongs to the one-kernel decode step (IRON_DECODE_STEP=1)")
+        c = self.c
+        off = 256 + 512 * 8 + self.H * 16 * (c.head_dim + 4) * 4
+        n = 5 * c.num_hidden_layers + 1
+        raw = self.step_ws[off : off + 3 * n * 8].view(torch.int64).cpu().numpy()
+        return raw.reshape(n, 3).astype(np.int64)
+
     def check(self) -> None:
         """Raise if a kernel's bounded wait gave up since the last check (reads two words)."""
         if int(self.status.item()) != 0:
