@@ -180,7 +180,7 @@ def time_dominant_kernel(engine, peak_gbs: float, peak_kind: str) -> dict:
     per_launch_s = start.elapsed_time(stop) / 1e3 / (reps * len(engine.layers))
     bytes_per_launch = 2 * c.intermediate_size * c.hidden_size * 2
     achieved = bytes_per_launch / per_launch_s / 1e9
-    return {"bound": "hbm", "kernel": "gemv_kernel<SWIGLU> (gate/up GEMV + SiLU + mul)",
+    return {"bound": "hbm", "kernel": "gemv_ring_kernel<SWIGLU> (gate/up GEMV + SiLU + mul, TMA-fed)",
             "achieved": round(achieved, 1), "peak": peak_gbs, "peak_kind": peak_kind,
             "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
             "bytes_per_launch": bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 2),

@@ -215,21 +215,24 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
 // ---------------------------------------------------------------------------------------
 // The same GEMV family with the weights streamed by the TMA engine.
 //
-// One CTA per SM, 16 warps.  Every warp owns a ring of three 4 KB shared-memory slots; lane 0
+// Two CTAs per SM, 8 warps each.  Every warp owns a ring of three 4 KB shared-memory slots; lane 0
 // fills a slot with two bulk copies (cp.async.bulk + mbarrier complete_tx: 2 KB of each row
 // of a pair, or 4 KB of one row) and re-arms it as soon as the warp has read it, so about
 // 190 KB per SM are in flight or parked at any time without holding them in registers.  The
 // first three items of every warp are issued before the programmatic-dependency wait:
 // the weights do not depend on the previous kernel, so this kernel's stream starts while
 // that one drains.  A pure read stream through this path runs at ~8 TB/s on a B200, above
-// what register-buffered loads reach; it is used for the large matrices of a decode step.
+// what register-buffered loads reach; it is used for the large matrices of a decode step
+// (gate/up, down_proj, the head).  A CTA takes half an SM so that, as with the
+// register-streamed kernels, the next kernel of the chain can start under this one's tail.
 //   RING_PAIR   rows (2p, 2p+1)                        RING_SWIGLU  gate row m, up row m
 //   RING_QKV    rows (i, i + D/2) of one head          RING_ROW     one row, 2048 columns per item
 // Every mbarrier wait is bounded by a wall-clock limit; a wait that gives up leaves the
 // kernel early (the rows of that warp are not written) -- there is no status word in this
 // entry point's signature, so the limit is generous (2 s) and only a lost copy reaches it.
 enum { RING_PAIR = 0, RING_SWIGLU = 1, RING_QKV = 2, RING_ROW = 3 };
-constexpr int kRingWarps = 16;
+constexpr int kRingWarps = 8;                   // two CTAs per SM, each with half of the SM's rings
+constexpr int kRingCtasPerSm = 2;
 constexpr int kRingThreads = kRingWarps * 32;
 constexpr int kRingChunk = 1024;                 // columns of one segment
 constexpr int kRingChunk16 = kRingChunk / 8;
@@ -296,7 +299,7 @@ __device__ __forceinline__ void ring_item(const GemvParams& p, int unit, int chu
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvParams p, const int active_warps) {
+__global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel(const GemvParams p, const int active_warps) {
   extern __shared__ __align__(128) unsigned char ring_smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K, nch = K >> 3;
@@ -494,14 +497,14 @@ static int launch_ring(const GemvParams& p, int units, cudaStream_t stream) {
   // as many warps per CTA as split the units most evenly over the grid
   int best_w = kRingWarps;
   double best_eff = -1.0;
-  for (int w = kRingWarps; w >= 8; --w) {
-    const long long nw = (long long)kSMs * w;
+  for (int w = kRingWarps; w >= kRingWarps / 2; --w) {
+    const long long nw = (long long)kRingCtasPerSm * kSMs * w;
     const long long rounds = (units + nw - 1) / nw;
     const double eff = (double)units / (double)(rounds * nw);
     if (eff > best_eff + 1e-3) { best_eff = eff; best_w = w; }
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(kSMs, 1, 1);
+  cfg.gridDim = dim3(kRingCtasPerSm * kSMs, 1, 1);
   cfg.blockDim = dim3(kRingThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -569,18 +572,17 @@ static bool aligned32(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 
 template <int MODE>
 static int launch_gemv(GemvParams& p, int npairs, int batches, cudaStream_t stream) {
   // Which shapes stream through the TMA-fed kernel: IRON_GEMV_RING is a bit mask (1 gate/up,
-  // 2 large plain matrices, 4 q/k/v, 8 small plain matrices); unset = none.  Alone, the
-  // TMA-fed gate/up kernel is faster (12.5 us against 14.4 us at 8192 x 2048 twice), but its
-  // CTAs fill an SM, so the next kernel of a decode step cannot start under its tail and the
-  // step as a whole is 1-3 % slower: the register-streamed kernels stay the default.
+  // 2 large plain matrices, 4 q/k/v, 8 small plain matrices); unset = 3.  Measured on the
+  // Llama-3.2-1B decode step: gate/up 12.3 us against 14.5 us register-streamed; the whole
+  // step 695 us with mask 3, 710 us with 0, 704 us with 15 (the small matrices gain nothing).
   const int policy = ring_policy();
-  const int mask = policy >= 0 ? policy : 0;
+  const int mask = policy >= 0 ? policy : 3;
   const long long bytes = (long long)p.rows * p.K * 2 * (MODE == GEMV_SWIGLU ? 2 : 1);
   if (mask && batches == 1 && p.repeat == 1 && p.K <= kRingMaxK) {
     if (MODE == GEMV_SWIGLU && (mask & 1)) return launch_ring<RING_SWIGLU>(p, p.rows, stream);
     if (MODE == GEMV_QKV && (mask & 4)) return launch_ring<RING_QKV>(p, p.rows >> 1, stream);
     if (MODE == GEMV_PLAIN && (mask & (bytes >= (24ll << 20) ? 2 : 8))) {
-      if (npairs < kSMs * kRingWarps) return launch_ring<RING_ROW>(p, p.rows, stream);
+      if (npairs < kRingCtasPerSm * kSMs * kRingWarps) return launch_ring<RING_ROW>(p, p.rows, stream);
       return launch_ring<RING_PAIR>(p, npairs, stream);
     }
   }
