@@ -186,7 +186,7 @@ def time_dominant_kernel(engine, peak_gbs: float, peak_kind: str) -> dict:
             "bytes_per_launch": bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 2),
             # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel on these
             # shapes, from one ncu capture (mean of two launches)
-            "traffic": 67_510_000 if (c.intermediate_size, c.hidden_size) == (8192, 2048) else None,
+            "traffic": 67_480_000 if (c.intermediate_size, c.hidden_size) == (8192, 2048) else None,
             "traffic_from": "profiles/gemv_swiglu_llama1b_ncu.md"}
 
 
