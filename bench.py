@@ -322,7 +322,7 @@ def run_batch(args, rank: int, world: int, device) -> None:
 
     from iron_b200.lm.engine import LlamaEngine, batch_shard
 
-    total = 64
+    total = args.sequences
     mine = batch_shard(total, rank, world)
     config = build_config()
     weights = device_weights(config, 3001, device)
@@ -376,11 +376,11 @@ def run_batch(args, rank: int, world: int, device) -> None:
     step_bytes = engine.weight_bytes_per_token + kv
     gbs = step_bytes / (ms / args.steps / 1e3) / 1e9
     print(json.dumps({
-        "metric": "llama-3.2-1b-arch decode throughput (64 sequences, greedy, context 2048+)",
+        "metric": f"llama-3.2-1b-arch decode throughput ({total} sequences, greedy, context 2048+)",
         "value": round(total * args.steps / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "configs[2] batch 64: Llama-3.2-1B architecture, 64 independent sequences after a "
+        "config": {"workload": f"configs[2] batch {total}: Llama-3.2-1B architecture, {total} independent sequences after a "
                                "2048-token prompt each, split over the ranks with no collective",
                    "sequences_per_gpu": len(mine), "context": CONTEXT,
                    "l2": "every step streams 2.47 GB of weights and 67 MB of KV cache per sequence"},
@@ -400,6 +400,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sequences", type=int, default=64,
+                    help="llama1b-batch64: sequences in the whole job (split over the ranks)")
     ap.add_argument("--decode-step-trace", action="store_true",
                     help="with IRON_DECODE_STEP=1: print the one-kernel step's per-phase timeline and exit")
     ap.add_argument("--workload", default="llama1b", choices=["llama1b", "llama3b-tp", "llama1b-batch64"],

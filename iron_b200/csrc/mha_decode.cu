@@ -304,14 +304,14 @@ extern "C" int iron_mha_decode_bf16(const void* Q, const void* K, const void* V,
   if ((kv_batch_stride & 7) || (kv_seq_stride & 7) || (kv_head_stride & 7)) return IRON_ERR_ALIGN;
   if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return IRON_ERR_ALIGN;
   const int group = H / G;
-  // A batch that fills the machine on its own (one CTA per sequence and KV head) goes to the
-  // tensor-core kernel: the group's query heads are the rows of one MMA tile.
+  // A batch of a few sequences or more (one CTA per sequence and KV head, at least 32)
+  // goes to the tensor-core kernel: the group's query heads are the rows of one MMA tile.
   // IRON_MHA_DECODE_TC=0 keeps the SIMT kernel.
   static const bool use_tc = [] {
     const char* e = getenv("IRON_MHA_DECODE_TC");
     return !(e && e[0] == '0');
   }();
-  if (use_tc && group > 1 && (long long)batch * G >= 2 * kSMs) {
+  if (use_tc && group > 1 && (long long)batch * G >= 32) {
     const int rc = mha_decode_tc(Q, K, V, O, batch, H, G, D, kv_max, kv_batch_stride, kv_seq_stride,
                                  kv_head_stride, kv_valid, d_kv_valid, d_kv_valid_stride, kv_valid_add, window,
                                  scale, (cudaStream_t)stream);
