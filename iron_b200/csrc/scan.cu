@@ -252,6 +252,29 @@ struct ConvParams {
 };
 
 // One thread per 8 channels, marching down the rows with the last K-1 inputs in registers.
+//
+// The recorded chain rounds every product and every sum to bf16.  A bf16 x bf16 product is
+// exact in f32, and the f32 sum of two bf16 values is either exact or differs from the larger
+// operand by less than 2^-16 of it, so "f32 operation, then round to bf16" is the correctly
+// rounded bf16 operation: the chain runs on packed bf16x2 multiplies and adds (mul.rn.bf16x2,
+// add.rn.bf16x2), two channels per instruction, bit for bit the same.
+__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint4 bmul8(const uint4& a, const uint4& b) {
+  return make_uint4(bmul2(a.x, b.x), bmul2(a.y, b.y), bmul2(a.z, b.z), bmul2(a.w, b.w));
+}
+__device__ __forceinline__ uint4 badd8(const uint4& a, const uint4& b) {
+  return make_uint4(badd2(a.x, b.x), badd2(a.y, b.y), badd2(a.z, b.z), badd2(a.w, b.w));
+}
+
 template <int K>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
   pdl_wait();
@@ -268,23 +291,19 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
   const __nv_bfloat16* hist = p.history ? p.history + (size_t)b * p.hist_batch + c8 * 8 : nullptr;
   __nv_bfloat16* y = p.y + (size_t)b * p.y_batch + c8 * 8;
 
-  float w[K][8], win[K][8], bias[8];
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 w[K], win[K], bias = zero;
 #pragma unroll
-  for (int k = 0; k < K; ++k) unpack8(ld_cached(p.taps + (size_t)k * p.C + c8 * 8), w[k]);
-  if (p.bias) unpack8(ld_cached(p.bias + c8 * 8), bias);
+  for (int k = 0; k < K; ++k) w[k] = ld_cached(p.taps + (size_t)k * p.C + c8 * 8);
+  if (p.bias) bias = ld_cached(p.bias + c8 * 8);
   // row index r of the concatenation history ++ x is (r - (K-1)) of x
-  auto input_row = [&](int r, float* f) {
-    if (r >= 0) {
-      if (r < valid) unpack8(ld_cached(x + (size_t)r * p.C), f);
-      else { for (int j = 0; j < 8; ++j) f[j] = 0.f; }
-    } else if (hist) {
-      unpack8(ld_cached(hist + (size_t)(r + K - 1) * p.C), f);
-    } else {
-      for (int j = 0; j < 8; ++j) f[j] = 0.f;
-    }
+  auto input_row = [&](int r) -> uint4 {
+    if (r >= 0) return r < valid ? ld_cached(x + (size_t)r * p.C) : zero;
+    if (hist) return ld_cached(hist + (size_t)(r + K - 1) * p.C);
+    return zero;
   };
 #pragma unroll
-  for (int k = 0; k < K - 1; ++k) input_row(r_lo - (K - 1) + k, win[k]);
+  for (int k = 0; k < K - 1; ++k) win[k] = input_row(r_lo - (K - 1) + k);
   // Eight rows at a time: their loads are issued together, then the eight outputs follow.
   constexpr int kRows = 8;
   for (int r0 = r_lo; r0 < r_hi; r0 += kRows) {
@@ -292,40 +311,38 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
 #pragma unroll
     for (int u = 0; u < kRows; ++u) {
       const int r = r0 + u;
-      raw[u] = (r < r_hi && r < valid) ? ld_cached(x + (size_t)r * p.C) : make_uint4(0, 0, 0, 0);
+      raw[u] = (r < r_hi && r < valid) ? ld_cached(x + (size_t)r * p.C) : zero;
     }
 #pragma unroll
     for (int u = 0; u < kRows; ++u) {
       const int r = r0 + u;
       if (r >= r_hi) break;
-      unpack8(raw[u], win[K - 1]);
-      float out[8];
+      win[K - 1] = raw[u];
+      uint4 out = zero;
       if (r < valid) {
+        uint4 acc;
+        if (p.decode_order) {
+          acc = bmul8(win[K - 1], w[K - 1]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float acc;
-          if (p.decode_order) {
-            acc = round_bf16(__fmul_rn(win[K - 1][j], w[K - 1][j]));
+          for (int k = 0; k < K - 1; ++k) acc = badd8(acc, bmul8(win[k], w[k]));
+        } else {
+          acc = bmul8(win[0], w[0]);
 #pragma unroll
-            for (int k = 0; k < K - 1; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
-          } else {
-            acc = round_bf16(__fmul_rn(win[0][j], w[0][j]));
-#pragma unroll
-            for (int k = 1; k < K; ++k) acc = round_bf16(__fadd_rn(acc, round_bf16(__fmul_rn(win[k][j], w[k][j]))));
-          }
-          if (p.bias) acc = round_bf16(__fadd_rn(acc, bias[j]));
-          if (p.silu) acc = silu_f32(acc);
-          out[j] = acc;
+          for (int k = 1; k < K; ++k) acc = badd8(acc, bmul8(win[k], w[k]));
         }
-      } else {
+        if (p.bias) acc = badd8(acc, bias);
+        if (p.silu) {
+          float f[8];
+          unpack8(acc, f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) out[j] = 0.f;
+          for (int j = 0; j < 8; ++j) f[j] = silu_f32(f[j]);
+          acc = pack8(f);
+        }
+        out = acc;
       }
-      *reinterpret_cast<uint4*>(y + (size_t)r * p.C) = pack8(out);
+      *reinterpret_cast<uint4*>(y + (size_t)r * p.C) = out;
 #pragma unroll
-      for (int k = 0; k < K - 1; ++k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+      for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
     }
   }
   // the K-1 rows ending the valid run become the next call's history
@@ -333,11 +350,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
     __nv_bfloat16* nh = p.new_history + (size_t)b * p.hist_batch + c8 * 8;
     uint4 keep[K - 1];
 #pragma unroll
-    for (int k = 0; k < K - 1; ++k) {
-      float f[8];
-      input_row(valid - (K - 1) + k, f);
-      keep[k] = pack8(f);
-    }
+    for (int k = 0; k < K - 1; ++k) keep[k] = input_row(valid - (K - 1) + k);
 #pragma unroll
     for (int k = 0; k < K - 1; ++k) *reinterpret_cast<uint4*>(nh + (size_t)k * p.C) = keep[k];
   }
