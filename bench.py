@@ -153,6 +153,7 @@ def time_dominant_kernel(engine, peak_gbs: float, peak_kind: str) -> dict:
     import torch
 
     from iron_b200 import kernels as K
+    from iron_b200.tensor import capturing
 
     c = engine.c
     x, act = engine.x1[0], engine.act[0]
@@ -168,7 +169,7 @@ def time_dominant_kernel(engine, peak_gbs: float, peak_kind: str) -> dict:
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = 20
     g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
+    with capturing(g):
         sweep()
     g.replay()
     torch.cuda.synchronize()

@@ -143,10 +143,24 @@ enum {
   IRON_EW_ROW_ADD = 5,  /* y = a + b[col] */
   IRON_EW_ROW_MUL = 6,  /* y = a * b[col] */
   IRON_EW_SIGMOID = 7,  /* y = 1 / (1 + exp(-a)) */
-  IRON_EW_GELU_SIG = 8  /* y = a * sigmoid(1.702 a) */
+  IRON_EW_GELU_SIG = 8, /* y = a * sigmoid(1.702 a) */
+  IRON_EW_RELU = 9,     /* y = max(a, 0) */
+  IRON_EW_TANH = 10,    /* y = tanh(a) */
+  IRON_EW_GELU_TANH = 11, /* y = 0.5 a (1 + tanh(sqrt(2/pi) (a + 0.044715 a^3))) */
+  IRON_EW_GELU_ERF = 12 /* y = 0.5 a (1 + erf(a / sqrt 2)) */
 };
 int iron_elementwise_bf16(int op, const void* a, const void* b, void* y, long long n,
                           int cols, float scalar, iron_stream_t stream);
+
+/* Clamp -- iron/operators/clamp.py: y = min(max(x, low), high) with the bounds rounded to
+ * bf16 first (exact). */
+int iron_clamp_bf16(const void* x, void* y, long long n, float low, float high, iron_stream_t stream);
+
+/* LayerNorm -- iron/operators/layer_norm.py:10 on WeightedRowwise (beta 0): per row
+ * n = bf16((x - mean) / sqrt(var + eps)) with the biased variance, then y = bf16(n * weight)
+ * when weight is non-NULL.  x, y (rows, cols); cols % 8 == 0. */
+int iron_layernorm_bf16(const void* x, const void* weight, void* y, int rows, int cols, float eps,
+                        int valid_rows, const int* d_valid_rows, iron_stream_t stream);
 
 /* Copy / Gather -- iron/operators/copy.py:546 (`Copy`, reference :839-902) and :72
  * (`Gather`), exact.  Gathers `nrows` rows of `row_bytes` bytes (multiple of 16):

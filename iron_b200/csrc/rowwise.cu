@@ -47,6 +47,72 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
   }
 }
 
+// ---------------------------------------------------------------- LayerNorm
+// One CTA per row: mean, then the biased variance about it, then the two roundings.
+__global__ void __launch_bounds__(256) layernorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                        const __nv_bfloat16* __restrict__ w,
+                                                        __nv_bfloat16* __restrict__ y, int rows, int cols,
+                                                        float eps, int valid, const int* d_valid) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
+  if (d_valid) valid = min(*d_valid, rows);
+  const int nch = cols >> 3;
+  for (int r = blockIdx.x; r < valid; r += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * cols);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)r * cols);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < nch; i += blockDim.x) {
+      float f[8];
+      unpack8(ld_cached(xr + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += f[j];
+    }
+    const float mean = block_sum(sum, red) / (float)cols;
+    __syncthreads();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nch; i += blockDim.x) {
+      float f[8];
+      unpack8(ld_cached(xr + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float d = f[j] - mean; ss = fmaf(d, d, ss); }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)cols + eps);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nch; i += blockDim.x) {
+      float f[8];
+      unpack8(ld_cached(xr + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = round_bf16((f[j] - mean) * inv);
+      if (w) {
+        float g[8];
+        unpack8(ld_cached(reinterpret_cast<const uint4*>(w) + i), g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] * g[j];
+      }
+      yr[i] = pack8(f);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- clamp
+__global__ void __launch_bounds__(256) clamp_kernel(const __nv_bfloat16* __restrict__ a, __nv_bfloat16* __restrict__ y,
+                                                    long long n, float low, float high) {
+  pdl_wait();
+  pdl_launch();
+  const long long nvec = n >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float f[8];
+    unpack8(ld_cached(reinterpret_cast<const uint4*>(a) + i), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], low), high);
+    reinterpret_cast<uint4*>(y)[i] = pack8(f);
+  }
+  for (long long i = (nvec << 3) + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = __float2bfloat16_rn(fminf(fmaxf(__bfloat162float(a[i]), low), high));
+}
+
 // ---------------------------------------------------------------- RoPE
 // One thread per 8 output pairs.  two_halves: pair (i, i + cols/2); else (2i, 2i+1).
 __global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* __restrict__ x,
@@ -164,6 +230,10 @@ __device__ __forceinline__ float ew_apply(int op, float a, float b, float s) {
     case IRON_EW_SILU_MUL: return __fmul_rn(round_bf16(silu_f32(a)), b);
     case IRON_EW_SIGMOID: return 1.0f / (1.0f + expf(-a));
     case IRON_EW_GELU_SIG: return __fmul_rn(a, round_bf16(1.0f / (1.0f + expf(-__fmul_rn(1.702f, a)))));
+    case IRON_EW_RELU: return fmaxf(a, 0.f);
+    case IRON_EW_TANH: return tanhf(a);
+    case IRON_EW_GELU_TANH: return 0.5f * a * (1.0f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
+    case IRON_EW_GELU_ERF: return 0.5f * a * (1.0f + erff(a * 0.7071067811865476f));
   }
   return 0.f;
 }
@@ -362,6 +432,28 @@ extern "C" int iron_rmsnorm_bf16(const void* x, const void* weight, void* y, int
                     cols, eps, valid_rows, d_valid_rows);
 }
 
+extern "C" int iron_layernorm_bf16(const void* x, const void* weight, void* y, int rows, int cols, float eps,
+                                   int valid_rows, const int* d_valid_rows, iron_stream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7)) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > rows) return IRON_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(y) || (weight && !aligned16(weight))) return IRON_ERR_ALIGN;
+  if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
+  const int upper = d_valid_rows ? rows : valid_rows;
+  const int grid = upper < kSMs * 8 ? upper : kSMs * 8;
+  return launch_pdl(layernorm_kernel, dim3(grid), dim3(256), (cudaStream_t)stream, (const __nv_bfloat16*)x,
+                    (const __nv_bfloat16*)weight, (__nv_bfloat16*)y, rows, cols, eps, valid_rows, d_valid_rows);
+}
+
+extern "C" int iron_clamp_bf16(const void* x, void* y, long long n, float low, float high, iron_stream_t stream) {
+  if (n < 0 || !(low <= high)) return IRON_ERR_SHAPE;
+  if (n == 0) return IRON_OK;
+  if (!aligned16(x) || !aligned16(y)) return IRON_ERR_ALIGN;
+  // the bounds as bf16 values, as the reference passes them to its kernel
+  const float lo = __bfloat162float(__float2bfloat16_rn(low)), hi = __bfloat162float(__float2bfloat16_rn(high));
+  return launch_pdl(clamp_kernel, dim3(grid_for((n + 7) / 8, 256)), dim3(256), (cudaStream_t)stream,
+                    (const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, lo, hi);
+}
+
 extern "C" int iron_rope_bf16(const void* x, const void* angles, void* y, int rows, int cols,
                               int angle_rows, int two_halves, int angle_offset,
                               const int* d_angle_offset, int valid_rows, const int* d_valid_rows,
@@ -405,6 +497,10 @@ extern "C" int iron_elementwise_bf16(int op, const void* a, const void* b, void*
     IRON_EW_CASE(IRON_EW_ROW_MUL)
     IRON_EW_CASE(IRON_EW_SIGMOID)
     IRON_EW_CASE(IRON_EW_GELU_SIG)
+    IRON_EW_CASE(IRON_EW_RELU)
+    IRON_EW_CASE(IRON_EW_TANH)
+    IRON_EW_CASE(IRON_EW_GELU_TANH)
+    IRON_EW_CASE(IRON_EW_GELU_ERF)
   }
 #undef IRON_EW_CASE
   return IRON_ERR_UNSUPPORTED;

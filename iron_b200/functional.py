@@ -18,7 +18,9 @@ from .operators.copy import Copy
 from .operators.flm.gemm.design import Epilogue
 from .operators.flm.gemm.op import ProjectionGEMM
 from .operators.gemm import GEMM
+from .operators.gelu import GELU
 from .operators.gemv import GEMV
+from .operators.layer_norm import LayerNorm
 from .operators.rms_norm import RMSNorm
 from .operators.rope import RoPE
 from .operators.silu import SiLU
@@ -65,6 +67,24 @@ def rms_norm(x, normalized_shape, weight=None, eps: float | None = None) -> Hand
     rows = math.prod(shape) // shape[-1]
     y = RMSNorm.step(x.reshape(rows, shape[-1]), weight=weight, epsilon=eps)
     return y.reshape(shape)
+
+
+def layer_norm(x, normalized_shape, weight=None, bias=None, eps: float = 1e-5) -> Handle:
+    """``x`` minus its mean over its standard deviation along the last axis (``eps`` under the
+    root), times ``weight`` and plus ``bias`` when given (iron/functional.py:97-110)."""
+    _last_axis("layer_norm", x, normalized_shape)
+    shape = x.shape
+    rows = math.prod(shape) // shape[-1]
+    y = LayerNorm.step(x.reshape(rows, shape[-1]), weight=weight, epsilon=eps)
+    if bias is not None:
+        y = y + bias
+    return y.reshape(shape)
+
+
+def gelu(x, approximate: str = "none") -> Handle:
+    """GELU, exact by default; ``approximate="tanh"`` for the tanh form (iron/functional.py:118-124)."""
+    shape = x.shape
+    return GELU.step(x.reshape(math.prod(shape)), approximate=approximate).reshape(shape)
 
 
 def silu(x) -> Handle:

@@ -291,7 +291,7 @@ class CompiledGraph:
 
     def __call__(self, *arrays, **values):
         torch = self._torch
-        from ..tensor import numpy_to_torch
+        from ..tensor import capturing, numpy_to_torch
 
         rec = self.recording
         inputs, value_params = self.graph._parameters()
@@ -325,7 +325,7 @@ class CompiledGraph:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
+            with capturing(g, stream=side):
                 self._launch_all()
             torch.cuda.current_stream().wait_stream(side)
             self._cuda_graph = g   # capture records, it does not run: this call's results are the warm-up's

@@ -13,7 +13,8 @@ import torch
 from . import _lib
 from ._lib import call
 
-EW = dict(silu=0, add=1, mul=2, axpy=3, silu_mul=4, row_add=5, row_mul=6, sigmoid=7, gelu_sig=8)
+EW = dict(silu=0, add=1, mul=2, axpy=3, silu_mul=4, row_add=5, row_mul=6, sigmoid=7, gelu_sig=8,
+          relu=9, tanh=10, gelu_tanh=11, gelu_erf=12)
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -81,6 +82,27 @@ def rms_norm(x, weight=None, out=None, *, eps=1e-5, valid=None, d_valid=None):
         out = torch.empty_like(x)
     call("iron_rmsnorm_bf16", _ptr(x), _ptr(weight), _ptr(out), rows, cols, float(eps),
          rows if valid is None else valid, _ptr(d_valid), _stream())
+    return out
+
+
+def layer_norm(x, weight=None, out=None, *, eps=1e-5, valid=None, d_valid=None):
+    """Each row minus its mean over its standard deviation (biased), rounded, times ``weight``."""
+    _bf16(x, weight)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty_like(x)
+    call("iron_layernorm_bf16", _ptr(x), _ptr(weight), _ptr(out), rows, cols, float(eps),
+         rows if valid is None else valid, _ptr(d_valid), _stream())
+    return out
+
+
+def clamp(x, low, high, out=None):
+    """``x`` clamped to ``[low, high]``, the bounds rounded to bf16 (exact)."""
+    _bf16(x)
+    if out is None:
+        out = torch.empty_like(x)
+    call("iron_clamp_bf16", _ptr(x), _ptr(out), x.numel(), float(low), float(high), _stream())
     return out
 
 

@@ -31,6 +31,7 @@ import torch
 
 from .. import kernels as K
 from ..arena import ArenaPlan
+from ..tensor import capturing
 from .config import DecoderConfig
 
 BF16 = torch.bfloat16
@@ -493,7 +494,7 @@ class LlamaEngine:
         g = torch.cuda.CUDAGraph()
         self.set_call(0, 0)
         self.b_tokens.zero_(); self.b_pos.zero_()
-        with torch.cuda.graph(g):
+        with capturing(g):
             self._decode_launches()
         self._graph = g
         self.values.copy_(saved)

@@ -7,6 +7,9 @@ The reference's ``aie.utils.DEFAULT_TENSOR_CLASS`` (iron/common/testing.py:163-1
 
 from __future__ import annotations
 
+import contextlib
+import gc
+
 import numpy as np
 from ml_dtypes import bfloat16
 
@@ -17,6 +20,26 @@ def _torch():
     if not torch.cuda.is_available():
         raise RuntimeError("iron_b200 tensors live on a CUDA device; none is available")
     return torch
+
+
+@contextlib.contextmanager
+def capturing(graph, **kw):
+    """``torch.cuda.graph`` with the garbage collector held off.
+
+    A collection that runs while a stream is capturing may free an older ``CUDAGraph``; its
+    teardown is a call the capture does not allow and invalidates it.  So collect first,
+    then keep the collector off until the capture has ended.
+    """
+    torch = _torch()
+    was = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, **kw):
+            yield graph
+    finally:
+        if was:
+            gc.enable()
 
 
 def numpy_to_torch(a: np.ndarray, device="cuda"):

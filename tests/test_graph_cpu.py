@@ -81,6 +81,55 @@ def test_a_body_records_operator_steps_and_its_reference_runs_them():
     assert not g.cache.host.reshape(16, 64)[[0, 1, 2, 4]].astype(np.float32).any()
 
 
+class EncoderMLP(iron.Graph):
+    """The feed-forward half of an encoder layer: LayerNorm with bias, linear, GELU, linear, residual."""
+
+    def __init__(self, E, H, approximate="none"):
+        self.gamma, self.beta = iron.param(E), iron.param(E)
+        self.fc1, self.b1, self.fc2 = iron.param(H, E), iron.param(H), iron.param(E, H)
+        self.approximate = approximate
+
+    def body(self, x):
+        h = F.layer_norm(x, (x.shape[-1],), self.gamma, self.beta, 1e-5)
+        return x + F.linear(F.gelu(F.linear(h, self.fc1, self.b1), self.approximate), self.fc2)
+
+
+def loaded_encoder(approximate="none", rows=4, seed=1):
+    rng = np.random.default_rng(seed)
+    g = EncoderMLP(64, 128, approximate)
+    g.load_state_dict({"gamma": (1 + rng.standard_normal(64) / 10).astype(bfloat16),
+                       "beta": (rng.standard_normal(64) / 10).astype(bfloat16),
+                       "fc1": (rng.standard_normal((128, 64)) / 8).astype(bfloat16),
+                       "b1": (rng.standard_normal(128) / 10).astype(bfloat16),
+                       "fc2": (rng.standard_normal((64, 128)) / 11).astype(bfloat16)})
+    return g, rng.standard_normal((rows, 64)).astype(bfloat16)
+
+
+@pytest.mark.parametrize("approximate", ["none", "tanh"])
+def test_layer_norm_and_gelu_record_their_operators_and_follow_the_float64_formula(approximate):
+    import math
+
+    g, x = loaded_encoder(approximate)
+    rec = g.record(x=((4, 64), bfloat16))
+    names = [s.op.name for s in rec.steps]
+    assert names[0] == "LayerNorm" and "GELU" in names and names.count("ProjectionGEMM") == 2
+    y = g.reference(x)
+    y = y[0] if isinstance(y, tuple) else y
+    f = lambda a: np.asarray(a).astype(np.float64)
+    xf = f(x)
+    d = xf - xf.mean(-1, keepdims=True)
+    h = d / np.sqrt((d * d).mean(-1, keepdims=True) + 1e-5) * f(g.gamma) + f(g.beta)
+    u = h @ f(g.fc1).T + f(g.b1)
+    if approximate == "none":
+        a = 0.5 * u * (1 + np.vectorize(math.erf)(u / math.sqrt(2)))
+    else:
+        a = 0.5 * u * (1 + np.tanh(math.sqrt(2 / math.pi) * (u + 0.044715 * u ** 3)))
+    want = xf + a @ f(g.fc2).T
+    assert np.abs(f(y) - want).max() <= 6e-2     # a chain of bf16 roundings on values of a few units
+    with pytest.raises(ValueError, match="neither 'tanh' nor 'none'"):
+        loaded_encoder("fast")[0].record(x=((4, 64), bfloat16))
+
+
 def test_bad_calls_are_refused_before_anything_runs():
     g, x = loaded()
     with pytest.raises(IndexError):

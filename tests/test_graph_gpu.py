@@ -7,7 +7,7 @@ import pytest
 from ml_dtypes import bfloat16
 
 from oracle import model as M
-from tests.test_graph_cpu import FeedForward, loaded
+from tests.test_graph_cpu import FeedForward, loaded, loaded_encoder
 from tests.test_oracle_golden import assert_close
 
 pytestmark = pytest.mark.gpu
@@ -37,6 +37,18 @@ def test_a_compiled_graph_replays_with_new_per_call_values():
         version(x, position=16)
     with pytest.raises(TypeError):
         version(x)
+
+
+@pytest.mark.parametrize("approximate", ["none", "tanh"])
+def test_an_encoder_feed_forward_runs_layer_norm_and_gelu_on_the_device(approximate):
+    g, x = loaded_encoder(approximate)
+    ref, _ = loaded_encoder(approximate)
+    version = g.compile(x=((4, 64), bfloat16))
+    out = version(x)
+    y = out[0] if isinstance(out, tuple) else out
+    want = ref.reference(x)
+    want = want[0] if isinstance(want, tuple) else want
+    assert np.abs(y.numpy().astype(np.float32) - np.asarray(want).astype(np.float32)).max() <= 3e-2
 
 
 def test_llama_compiled_graphs_match_the_golden_logits_prompt_then_decode():
