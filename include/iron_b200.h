@@ -162,6 +162,14 @@ int iron_clamp_bf16(const void* x, void* y, long long n, float low, float high, 
 int iron_layernorm_bf16(const void* x, const void* weight, void* y, int rows, int cols, float eps,
                         int valid_rows, const int* d_valid_rows, iron_stream_t stream);
 
+/* Softmax -- iron/operators/softmax.py:77 (reference :523-545): per row, over the first
+ * `length` columns, y = softmax(v) with v = x (+ addend, f32), then soft_cap * tanh(v / soft_cap)
+ * when soft_cap > 0; f32 throughout, y (bf16) rounded once; columns >= length are zeros.
+ * x is bf16, or f32 when x_is_f32 != 0 (the operator's input_dtype).  d_length overrides
+ * length when non-NULL.  cols % 8 == 0.  The banded form (window, period) is not provided. */
+int iron_softmax_bf16(const void* x, int x_is_f32, const float* addend, void* y, int rows, int cols,
+                      int length, const int* d_length, float soft_cap, iron_stream_t stream);
+
 /* Copy / Gather -- iron/operators/copy.py:546 (`Copy`, reference :839-902) and :72
  * (`Gather`), exact.  Gathers `nrows` rows of `row_bytes` bytes (multiple of 16):
  *   dst[(dst_row0 + i) * dst_pitch ...] = src[row(i) * src_pitch ...]

@@ -56,6 +56,7 @@ SIGNATURES: dict[str, tuple] = {
     "iron_rope_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
     "iron_rope_kv_write_bf16": (_I, [_P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P, _P]),
     "iron_elementwise_bf16": (_I, [_I, _P, _P, _P, _L, _I, _F, _P]),
+    "iron_softmax_bf16": (_I, [_P, _I, _P, _P, _I, _I, _I, _P, _F, _P]),
     "iron_clamp_bf16": (_I, [_P, _P, _L, _F, _F, _P]),
     "iron_layernorm_bf16": (_I, [_P, _P, _P, _I, _I, _F, _I, _P, _P]),
     "iron_copy_rows": (_I, [_P, _P, _P, _I, _P, _L, _L, _L, _I, _I, _P, _I, _P, _P]),

@@ -14,6 +14,7 @@ import ml_dtypes
 
 from .graph.handle import Handle, State
 from .lm.config import Precision
+from .operators.causal_conv import CausalConv1d
 from .operators.copy import Copy
 from .operators.flm.gemm.design import Epilogue
 from .operators.flm.gemm.op import ProjectionGEMM
@@ -106,3 +107,19 @@ class ConvState:
     write: Handle
     window: State | None = None
     tail: State | None = None
+
+
+def causal_conv1d(x, taps, state: ConvState) -> Handle:
+    """``x`` ``(rows, channels)`` through a depth-wise causal filter of ``K`` taps.
+
+    Output row ``t`` is ``sum_k taps[k] * x[t - K + 1 + k]``; the ``K - 1`` rows before
+    ``x``'s first come from ``state.read`` and the ``K - 1`` rows ending this call go to
+    ``state.write`` (iron/functional.py:147-180).  ``x`` bounded per call (``x[:n]``) is a
+    prompt chunk; otherwise it is one row, a decode step.  The reference stages the rows in
+    ``state.window`` and ``state.tail``; one fused step needs neither, so both may be None.
+    """
+    decode = x.bound is None
+    if decode and x.shape[0] != 1:
+        raise ValueError(f"causal_conv1d(): x {tuple(x.shape)} is neither bounded per call nor one row")
+    y, _ = CausalConv1d.step(x, taps, state.read, new_history=state.write, decode=decode)
+    return y

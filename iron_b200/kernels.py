@@ -97,6 +97,21 @@ def layer_norm(x, weight=None, out=None, *, eps=1e-5, valid=None, d_valid=None):
     return out
 
 
+def softmax(x, out=None, *, addend=None, soft_cap=None, length=None, d_length=None):
+    """Softmax over the first ``length`` columns of each row of ``x`` (bf16 or float32), zeros past them."""
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"softmax input is bf16 or float32, not {x.dtype}")
+    if addend is not None and addend.dtype != torch.float32:
+        raise TypeError("the addend is float32")
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    call("iron_softmax_bf16", _ptr(x), int(x.dtype == torch.float32), _ptr(addend), _ptr(out), rows, cols,
+         cols if length is None else int(length), _ptr(d_length), float(soft_cap or 0.0), _stream())
+    return out
+
+
 def clamp(x, low, high, out=None):
     """``x`` clamped to ``[low, high]``, the bounds rounded to bf16 (exact)."""
     _bf16(x)

@@ -5,6 +5,7 @@ and Mamba2 paths and the element-wise and row-wise operators beside them.
 """
 
 from .axpy import AXPY
+from .causal_conv import CausalConv1d
 from .clamp import Clamp
 from .copy import Copy, Gather
 from .elementwise_add import ElementwiseAdd, RowwiseAdd
@@ -23,9 +24,11 @@ from .sample import Sample
 from .selective_scan import SelectiveScan
 from .sigmoid import Sigmoid
 from .silu import SiLU
+from .softmax import Softmax
 from .tanh import Tanh
 
 CATALOG = (GEMM, ProjectionGEMM, GEMV, RMSNorm, LayerNorm, RoPE, SiLU, Sigmoid, ReLU, Tanh, GELU, Clamp,
-           ElementwiseAdd, RowwiseAdd, ElementwiseMul, RowwiseMul, AXPY, MHA, Copy, Gather, SelectiveScan, Sample)
+           ElementwiseAdd, RowwiseAdd, ElementwiseMul, RowwiseMul, AXPY, MHA, Softmax, Copy, Gather,
+           SelectiveScan, CausalConv1d, Sample)
 
 __all__ = [c.__name__ for c in CATALOG] + ["CATALOG", "Epilogue"]

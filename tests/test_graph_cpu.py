@@ -130,6 +130,55 @@ def test_layer_norm_and_gelu_record_their_operators_and_follow_the_float64_formu
         loaded_encoder("fast")[0].record(x=((4, 64), bfloat16))
 
 
+class ShortConv(iron.Graph):
+    """A Mamba2 block's short conv: a prompt chunk of up to 8 rows, or one decode row."""
+
+    def __init__(self, C, K, decode):
+        self.taps = iron.param(K, C)
+        self.carry = iron.state((K - 1, C))
+        self.decode = decode
+
+    def body(self, x, *, rows: iron.Scratchpad[np.int32] = np.int32(1)):
+        state = F.ConvState(read=self.carry, write=self.carry)
+        return F.causal_conv1d(x if self.decode else x[:rows], self.taps, state)
+
+
+def conv_pair(C=64, K=4, seed=5):
+    rng = np.random.default_rng(seed)
+    taps = (rng.standard_normal((K, C)) / 2).astype(bfloat16)
+    chunk, step = ShortConv(C, K, False), ShortConv(C, K, True)
+    for g in (chunk, step):
+        g.load_state_dict({"taps": taps})
+    return chunk, step, taps, rng
+
+
+def test_causal_conv_carries_its_last_rows_from_a_prompt_chunk_into_decode_steps():
+    from oracle import ops
+
+    chunk, step, taps, rng = conv_pair()
+    assert [s.op.name for s in chunk.record(x=((8, 64), bfloat16)).steps] == ["CausalConv1d"]
+    x = rng.standard_normal((8, 64)).astype(bfloat16)
+    y = chunk.reference(x, rows=5)
+    y = y[0] if isinstance(y, tuple) else y
+    want, hist = ops.causal_conv1d(x[:5], taps, np.zeros((3, 64), bfloat16))
+    assert np.array_equal(np.asarray(y)[:5].view(np.uint16), want.view(np.uint16))
+    assert np.array_equal(chunk.carry.host.reshape(3, 64).view(np.uint16), np.asarray(hist).view(np.uint16))
+    # a second, shorter chunk than the carry keeps part of the old carry
+    y = chunk.reference(x, rows=2)
+    want, hist2 = ops.causal_conv1d(x[:2], taps, hist)
+    assert np.array_equal(chunk.carry.host.reshape(3, 64).view(np.uint16), np.asarray(hist2).view(np.uint16))
+    # the one-row form sums the newest tap first; in float32 both orders agree to a rounding
+    step.carry.host = np.array(chunk.carry.host)
+    row = rng.standard_normal((1, 64)).astype(bfloat16)
+    y1 = step.reference(row)
+    y1 = y1[0] if isinstance(y1, tuple) else y1
+    fwd, hist3 = ops.causal_conv1d(row, taps, hist2)
+    assert np.abs(np.asarray(y1).astype(np.float32) - fwd.astype(np.float32)).max() <= 2e-2
+    assert np.array_equal(step.carry.host.reshape(3, 64).view(np.uint16), np.asarray(hist3).view(np.uint16))
+    with pytest.raises(ValueError, match="neither bounded per call nor one row"):
+        step.record(x=((2, 64), bfloat16))
+
+
 def test_bad_calls_are_refused_before_anything_runs():
     g, x = loaded()
     with pytest.raises(IndexError):

@@ -7,7 +7,7 @@ import pytest
 from ml_dtypes import bfloat16
 
 from oracle import model as M
-from tests.test_graph_cpu import FeedForward, loaded, loaded_encoder
+from tests.test_graph_cpu import FeedForward, conv_pair, loaded, loaded_encoder
 from tests.test_oracle_golden import assert_close
 
 pytestmark = pytest.mark.gpu
@@ -49,6 +49,28 @@ def test_an_encoder_feed_forward_runs_layer_norm_and_gelu_on_the_device(approxim
     want = ref.reference(x)
     want = want[0] if isinstance(want, tuple) else want
     assert np.abs(y.numpy().astype(np.float32) - np.asarray(want).astype(np.float32)).max() <= 3e-2
+
+
+def test_causal_conv_graph_carries_rows_between_calls_bit_for_bit():
+    chunk, step, taps, rng = conv_pair()
+    ref_chunk, ref_step, _, _ = conv_pair()
+    bits = lambda a: np.ascontiguousarray(np.asarray(a)).view(np.uint16)
+    first = lambda out: out[0] if isinstance(out, tuple) else out
+    cv = chunk.compile(x=((8, 64), bfloat16))
+    x = rng.standard_normal((8, 64)).astype(bfloat16)
+    for rows in (5, 2, 8):
+        got = first(cv(x, rows=rows)).numpy()
+        want = np.asarray(first(ref_chunk.reference(x, rows=rows)))
+        assert np.array_equal(bits(got[:rows]), bits(want[:rows])) and not got[rows:].astype(np.float32).any()
+        assert np.array_equal(bits(cv.read(chunk.carry)), bits(ref_chunk.carry.host.reshape(3, 64)))
+        x = (x.astype(np.float32) * 0.5 - 0.25).astype(bfloat16)
+    sv = step.compile(x=((1, 64), bfloat16))
+    for _ in range(4):
+        row = rng.standard_normal((1, 64)).astype(bfloat16)
+        got = first(sv(row)).numpy()
+        want = np.asarray(first(ref_step.reference(row)))
+        assert np.array_equal(bits(got), bits(want))
+        assert np.array_equal(bits(sv.read(step.carry)), bits(ref_step.carry.host.reshape(3, 64)))
 
 
 def test_llama_compiled_graphs_match_the_golden_logits_prompt_then_decode():
