@@ -90,3 +90,11 @@ def __getattr__(name):
         globals()["Llama"] = cls
         return cls
     raise AttributeError(name)
+
+
+if __name__ == "__main__":
+    import sys
+
+    from ...lm.cli import main
+
+    sys.exit(main(_llama()))

@@ -81,7 +81,8 @@ class LlamaEngine:
     """
 
     def __init__(self, config: DecoderConfig, weights: dict, device="cuda", batch: int = 1,
-                 kv_len_hint: int | None = None, tp_rank: int = 0, tp_size: int = 1, tp_group=None):
+                 kv_len_hint: int | None = None, tp_rank: int = 0, tp_size: int = 1, tp_group=None,
+                 release=None):
         if not torch.cuda.is_available():
             raise RuntimeError("LlamaEngine needs a CUDA device: there is no CPU path")
         self.c, self.device, self.batch = config, torch.device(device), batch
@@ -200,7 +201,7 @@ class LlamaEngine:
             self.b_att = view("b.att", (batch, H, D))
             self.b_gate, self.b_up = view("b.gate", (batch, F)), view("b.up", (batch, F))
 
-        self._load(weights)
+        self._load(weights, release)
         self._peer_exchange_setup()
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
@@ -221,26 +222,68 @@ class LlamaEngine:
         self._h_status = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     # ------------------------------------------------------------------ weights
-    def _load(self, w: dict) -> None:
+    @classmethod
+    def from_checkpoint(cls, path, *, random_weights: int | None = None, max_seq_len: int | None = None,
+                        config_class=None, **kwargs) -> "LlamaEngine":
+        """The engine on a checkpoint directory (``config.json`` beside ``model.safetensors`` or
+        its shard index), as ``Model.from_checkpoint`` loads one (iron/lm/model.py:125-234).
+
+        ``random_weights`` draws weights at that seed in the checkpoint's shapes, reading only
+        its header; ``max_seq_len`` lowers the context served and refuses to raise it.
+        """
+        from pathlib import Path
+
+        from .checkpoint import Checkpoint, weights_file
+
+        if config_class is None:
+            from ..applications.llama.model import LlamaConfig as config_class
+        path = Path(path)
+        directory = path if path.is_dir() else path.parent
+        config = config_class.from_checkpoint(directory)
+        if max_seq_len is not None:
+            if max_seq_len > config.max_seq_len:
+                raise ValueError(f"max_seq_len {max_seq_len} is past the checkpoint's {config.max_seq_len}")
+            config = dataclasses.replace(config, max_seq_len=max_seq_len)
+        checkpoint = Checkpoint(weights_file(directory) if path.is_dir() else path)
+        weights = checkpoint.named("read" if random_weights is None else "random", seed=random_weights or 0)
+        engine = cls(config, weights, release=checkpoint.release if random_weights is None else None, **kwargs)
+        engine.checkpoint = checkpoint
+        return engine
+
+    def _load(self, w: dict, release=None) -> None:
+        """Every weight into its arena slice through the pinned staging ring; ``release`` drops
+        a mapped checkpoint's pages behind the copies."""
+        from .checkpoint import Uploader
+
         c = self.c
-        _as_device_bf16(w["model.embed_tokens.weight"], self.embed)
-        _as_device_bf16(w["model.norm.weight"], self.norm)
+        up = Uploader(self.device, release=release)
+
+        def put(a, out):
+            if isinstance(a, torch.Tensor):
+                _as_device_bf16(a, out)
+            else:
+                up.put(a, out)
+
+        put(w["model.embed_tokens.weight"], self.embed)
+        put(w["model.norm.weight"], self.norm)
         if not c.tie_word_embeddings:
-            _as_device_bf16(w["lm_head.weight"], self.head)
-        _as_device_bf16(c.angles().astype(np.float32), self.angles)
+            put(w["lm_head.weight"], self.head)
+        put(c.angles().astype(np.float32), self.angles)
         lay = shard_layout(c, self.tp_rank, self.tp_size)
         Q, KV = lay.heads * c.head_dim, lay.kv_heads * c.head_dim
         for i, l in enumerate(self.layers):
             p = f"model.layers.{i}"
-            _as_device_bf16(w[f"{p}.input_layernorm.weight"], l["ln1"])
-            _as_device_bf16(w[f"{p}.self_attn.q_proj.weight"][lay.q_rows], l["wqkv"][:Q])
-            _as_device_bf16(w[f"{p}.self_attn.k_proj.weight"][lay.kv_rows], l["wqkv"][Q : Q + KV])
-            _as_device_bf16(w[f"{p}.self_attn.v_proj.weight"][lay.kv_rows], l["wqkv"][Q + KV :])
-            _as_device_bf16(w[f"{p}.self_attn.o_proj.weight"][:, lay.q_rows], l["wo"])
-            _as_device_bf16(w[f"{p}.post_attention_layernorm.weight"], l["ln2"])
-            _as_device_bf16(w[f"{p}.mlp.gate_proj.weight"][lay.ffn_rows], l["wg"])
-            _as_device_bf16(w[f"{p}.mlp.up_proj.weight"][lay.ffn_rows], l["wu"])
-            _as_device_bf16(w[f"{p}.mlp.down_proj.weight"][:, lay.ffn_rows], l["wd"])
+            put(w[f"{p}.input_layernorm.weight"], l["ln1"])
+            put(w[f"{p}.self_attn.q_proj.weight"][lay.q_rows], l["wqkv"][:Q])
+            put(w[f"{p}.self_attn.k_proj.weight"][lay.kv_rows], l["wqkv"][Q : Q + KV])
+            put(w[f"{p}.self_attn.v_proj.weight"][lay.kv_rows], l["wqkv"][Q + KV :])
+            put(w[f"{p}.self_attn.o_proj.weight"][:, lay.q_rows], l["wo"])
+            put(w[f"{p}.post_attention_layernorm.weight"], l["ln2"])
+            put(w[f"{p}.mlp.gate_proj.weight"][lay.ffn_rows], l["wg"])
+            put(w[f"{p}.mlp.up_proj.weight"][lay.ffn_rows], l["wu"])
+            put(w[f"{p}.mlp.down_proj.weight"][:, lay.ffn_rows], l["wd"])
+        up.finish()
+        self.uploaded_bytes = up.bytes
 
     def _all_reduce(self, t: torch.Tensor) -> None:
         """Sum ``t`` over the tensor-parallel ranks in place (NCCL; stream-ordered, capturable)."""
@@ -467,6 +510,13 @@ class LlamaEngine:
         if n + steps > self.c.max_seq_len:
             raise IndexError("the run would pass the end of the caches")
         self.prefill(prompt)
+        return self.generate_from_prompt(n, steps)
+
+    def generate_from_prompt(self, n: int, steps: int) -> list[int]:
+        """After a prompt of ``n`` tokens has run: the token its last row drew, then ``steps - 1``
+        device-carried decode steps."""
+        if n + steps > self.c.max_seq_len:
+            raise IndexError("the run would pass the end of the caches")
         self.capture()
         for _ in range(steps - 1):
             self._graph.replay()
