@@ -23,6 +23,7 @@
 // shared memory over distributed shared memory, and after one cluster barrier the leader
 // adds them in rank order and runs the output stage.  The result does not depend on timing.
 #include <cooperative_groups.h>
+#include <cstdlib>
 #include <cuda.h>
 
 #include "common.cuh"
@@ -172,6 +173,60 @@ __device__ __forceinline__ float epilogue_apply(int mode, float c) {
     case EPI_SILU: return __fmul_rn(c, round_bf16(1.0f / (1.0f + expf(-c))));
     case EPI_SIGMOID: return 1.0f / (1.0f + expf(-c));
     default: return c;
+  }
+}
+
+// The output stage for 32 consecutive columns of one row: round, activation, residual,
+// store (bf16 or f32; C row-major or transposed).
+__device__ __forceinline__ void output_chunk(const GemmParams& p, float* v, int row, int col0) {
+  if (!p.out_f32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = epilogue_apply(p.epilogue, round_bf16(v[j]));
+  }
+  const bool full_chunk = col0 + 32 <= p.N;
+  if (!p.c_transposed) {
+    const size_t off = (size_t)row * p.ldc + col0;
+    if (p.residual) {
+      if (full_chunk) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float f[8];
+          unpack8(ld_cached(p.residual + off + q * 8), f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(round_bf16(v[q * 8 + j]), f[j]);
+        }
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+          v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(p.residual[off + j]));
+      }
+    }
+    if (p.out_f32) {
+      float* dst = reinterpret_cast<float*>(p.C) + off;
+      if (full_chunk && (p.ldc & 3) == 0) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+      }
+    } else {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+      if (full_chunk && (p.ldc & 7) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = pack8(v + q * 8);
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+  } else {
+    // C is (N, M): lanes hold consecutive rows, so each column is a coalesced run.
+    for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+      const size_t off = (size_t)(col0 + j) * p.ldc + row;
+      float x = v[j];
+      if (p.residual) x = __fadd_rn(round_bf16(x), __bfloat162float(p.residual[off]));
+      if (p.out_f32) reinterpret_cast<float*>(p.C)[off] = x;
+      else reinterpret_cast<__nv_bfloat16*>(p.C)[off] = __float2bfloat16_rn(x);
+    }
   }
 }
 
@@ -394,55 +449,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
-        if (!p.out_f32) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = epilogue_apply(p.epilogue, round_bf16(v[j]));
-        }
-        const bool full_chunk = col0 + 32 <= p.N;
-        if (!p.c_transposed) {
-          const size_t off = (size_t)row * p.ldc + col0;
-          if (p.residual) {
-            if (full_chunk) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float f[8];
-                unpack8(ld_cached(p.residual + off + q * 8), f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(round_bf16(v[q * 8 + j]), f[j]);
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-                v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(p.residual[off + j]));
-            }
-          }
-          if (p.out_f32) {
-            float* dst = reinterpret_cast<float*>(p.C) + off;
-            if (full_chunk && (p.ldc & 3) == 0) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
-            if (full_chunk && (p.ldc & 7) == 0) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = pack8(v + q * 8);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
-        } else {
-          // C is (N, M): lanes hold consecutive rows, so each column is a coalesced run.
-          for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-            const size_t off = (size_t)(col0 + j) * p.ldc + row;
-            float x = v[j];
-            if (p.residual) x = __fadd_rn(round_bf16(x), __bfloat162float(p.residual[off]));
-            if (p.out_f32) reinterpret_cast<float*>(p.C)[off] = x;
-            else reinterpret_cast<__nv_bfloat16*>(p.C)[off] = __float2bfloat16_rn(x);
-          }
-        }
+        output_chunk(p, v, row, col0);
       }
       tcgen05_fence_before();
       mbar_arrive(acc_empty + acc);
@@ -467,6 +474,231 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
                  : "memory");
+  }
+}
+
+
+// ---- the CTA-pair form ---------------------------------------------------------------
+// Two CTAs of a cluster, on two SMs, compute one 256 x 256 tile with tcgen05.mma
+// cta_group::2: each CTA stages its own 128 rows of A and its own half (128 of the 256
+// columns) of B, the leader's MMA warp issues one instruction that reads both CTAs'
+// shared memory, and each CTA's tensor memory receives the accumulator of its 128 rows.
+// Per SM and K block that is 32 KB of operands from L2 for the same math as the 48 KB of
+// the one-CTA form: the main loop is bound by L2 -> SM bandwidth, so this is what moves it.
+//
+// Protocol (every barrier wait bounded, as above):
+//   full[s]      in the leader; the leader's producer arms it with both CTAs' bytes and
+//                both producers' TMA copies complete on it (cta_group::2 lets a copy
+//                signal the peer's barrier).  No copy is multicast.
+//   empty[s]     in both CTAs; the leader's tcgen05.commit arrives on both.
+//   acc_full[a]  in both CTAs; the same.
+//   acc_empty[a] in the leader, 256 arrivals: both CTAs' epilogue threads.
+// In the gated form the leader stages the first weight matrix's rows and the peer the
+// second's, so accumulator columns 0..127 / 128..255 hold the two products as in the
+// one-CTA gated form.
+constexpr int kPairBN = 256;
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = BM * BK * 2;           // this CTA's 128 rows of A
+constexpr int kPairBBytes = (kPairBN / 2) * BK * 2;  // this CTA's 128 columns of B
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 256 + 1024;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar) {
+  // arrives on the barrier at this offset in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+  uint64_t* full = bars;                        // [kPairStages], used in the leader
+  uint64_t* empty = bars + kPairStages;         // [kPairStages]
+  uint64_t* acc_full = bars + 2 * kPairStages;  // [2]
+  uint64_t* acc_empty = acc_full + 2;           // [2], used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();   // 0: the leader
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 256); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b2) : "memory");
+  }
+  if (warp == 1) {  // each CTA's MMA warp takes part in the pair's allocation (all 512 columns)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers are initialised before either is signalled
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int BNO = p.dual ? kPairBN / 2 : kPairBN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  pdl_launch();
+  pdl_wait();
+  const int valid = max(p.d_valid ? min(*p.d_valid, p.M) : p.valid, 0);
+  const int m_tiles = (valid + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = (p.N + BNO - 1) / BNO;
+  const int total = m_tiles * n_tiles;
+
+  if (warp == 0) {
+    // ---------------- producer (one per CTA) ----------------
+    if (lane == 0) {
+      int s = 0, issued = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += pairs) {
+        const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM;
+        const int n0 = (t / m_tiles) * BNO;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty + s, phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * kPairStageBytes;
+          uint8_t* b_dst = a_dst + kPairABytes;
+          const uint32_t bar = map_to_rank(smem_u32(full + s), 0);
+          if (rank == 0) mbar_expect_tx(full + s, 2 * kPairStageBytes);
+          tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
+          if (p.dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
+          else tma_load_2d_pair(b_dst, &map_b, kb * BK, n0 + (int)rank * (kPairBN / 2), bar);
+          ++issued;
+          if (++s == kPairStages) { s = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Unwinding: this CTA's copies land in its own shared memory but complete on the
+        // leader's barrier, which the peer cannot poll: give them a millisecond, many
+        // times what a copy takes, before the CTA may leave.
+        if (issued > 0) {
+          const unsigned long long t0 = global_ns();
+          while (global_ns() - t0 < 1000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (the leader's) ----------------
+    if (lane == 0 && rank == 0) {
+      // M 256 across the pair (128 rows per CTA), N 256
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPairBN >> 3) << 17) |
+                             ((uint32_t)((2 * BM) >> 4) << 24);
+      int s = 0, it = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kPairBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full + s, phase, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * kPairStageBytes);
+          const uint32_t b_addr = a_addr + kPairABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t a_desc = make_desc(a_addr + k * UK * 2, 16, 1024);
+            const uint64_t b_desc = make_desc(b_addr + k * UK * 2, 16, 1024);
+            tcgen05_mma_bf16_pair(d_tmem, a_desc, b_desc, idesc, kb != 0 || k != 0);
+          }
+          tcgen05_commit_pair(empty + s);
+          if (++s == kPairStages) { s = 0; phase ^= 1; }
+        }
+        if (ok) tcgen05_commit_pair(acc_full + acc);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of each CTA: its own 128 rows) ----------------
+    const int group = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int t = pair; t < total && ok; t += pairs, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM, n0 = (t / m_tiles) * BNO;
+      if (!mbar_wait(acc_full + acc, acc_phase, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = m0 + group * 32 + lane;
+      const bool row_live = row < valid;
+#pragma unroll 1
+      for (int c = 0; c < BNO / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairBN + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.dual) {
+          tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairBN + kPairBN / 2 + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = __fmul_rn(round_bf16(silu_f32(round_bf16(v[j]))), round_bf16(__uint_as_float(r[j])));
+        }
+        if (!row_live || col0 >= p.N) continue;
+        output_chunk(p, v, row, col0);
+      }
+      tcgen05_fence_before();
+      mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + acc), 0));
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = IRON_ERR_TIMEOUT;
+  // neither CTA leaves, or frees the pair's tensor memory, while the other may still signal
+  // its barriers or read its shared memory
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
 }
 
@@ -555,6 +787,40 @@ static int launch_gemm_split(const CUtensorMap& ma, const CUtensorMap& mb, const
                                                                                             : IRON_ERR_LAUNCH;
 }
 
+// One 256 x 256 tile per CTA pair; pairs walk the tiles M-fastest.
+static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+                            const GemmParams& p, int max_rows, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
+        cudaSuccess)
+      return IRON_ERR_LAUNCH;
+    configured = true;
+  }
+  const int bno = p.dual ? kPairBN / 2 : kPairBN;
+  const int tiles = ((max_rows + 2 * BM - 1) / (2 * BM)) * ((p.N + bno - 1) / bno);
+  const int pairs = tiles < kSMs / 2 ? (tiles < 1 ? 1 : tiles) : kSMs / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kPairSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  return cudaLaunchKernelEx(&cfg, gemm_pair_kernel, ma, mb, mb2, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+}
+
+// The pair form takes K-major B (weights as stored) and problems with more than one
+// 128-row tile of A; IRON_GEMM_PAIR=0 keeps every problem on the one-CTA form.
+static bool pair_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("IRON_GEMM_PAIR");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
 }  // namespace iron
 
 using namespace iron;
@@ -603,6 +869,11 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     while (splits < kMaxSplit && tiles * splits * 2 <= kSMs && num_kb / (splits * 2) >= 4) splits *= 2;
     if (splits > 1 && tiles >= 1) return launch_gemm_split(ma, mb, p, tiles, splits, s);
   }
+  if (bn == 256 && b_col_maj && max_rows > BM && pair_enabled()) {
+    CUtensorMap mh;   // each CTA of a pair stages half of the tile's 256 rows of B
+    if (!make_map(&mh, B, (uint64_t)valid_k, (uint64_t)N, (uint64_t)ldb, BK, kPairBN / 2)) return IRON_ERR_LAUNCH;
+    return launch_gemm_pair(ma, mh, mh, p, max_rows, s);
+  }
   if (bn == 256) return launch_gemm<256>(ma, mb, mb, p, max_rows, s);
   if (bn == 128) return launch_gemm<128>(ma, mb, mb, p, max_rows, s);
   return launch_gemm<64>(ma, mb, mb, p, max_rows, s);
@@ -634,6 +905,7 @@ extern "C" int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* 
   p.valid = valid_rows; p.d_valid = d_valid_rows;
   p.epilogue = EPI_NONE; p.dual = 1; p.status = d_status;
   cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 256 && max_rows > BM && pair_enabled()) return launch_gemm_pair(ma, mg, mu, p, max_rows, s);
   if (bn == 256) return launch_gemm<256>(ma, mg, mu, p, max_rows, s);
   if (bn == 128) return launch_gemm<128>(ma, mg, mu, p, max_rows, s);
   return launch_gemm<64>(ma, mg, mu, p, max_rows, s);
