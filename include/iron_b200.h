@@ -325,6 +325,12 @@ int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, 
                           int kv_tokens_add, int causal, int window, float scale,
                           iron_stream_t stream);
 
+/* The device word that receives IRON_ERR_TIMEOUT when a bounded pipeline wait of the
+ * tensor-memory prompt attention gives up (NULL: none).  Applies to the launches that follow;
+ * set it once per process to a word the caller reads after synchronising.  No counterpart
+ * in the reference. */
+void iron_mha_prefill_status_word(int* d_status);
+
 /* ------------------------------------------------------------------------------------
  * Tensor-parallel all-reduce of a small bf16 vector through peer memory, fused with the
  * residual add that follows it -- the exchange step after the row-parallel o_proj and

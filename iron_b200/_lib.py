@@ -82,6 +82,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "iron_selective_scan_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "iron_causal_conv1d_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P]),
+    "iron_mha_prefill_status_word": (None, [_P]),
     "iron_mha_prefill_bf16": (
         _I,
         [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _I, _P, _I, _I, _I, _F, _P],

@@ -23,8 +23,12 @@ __device__ __forceinline__ float round_bf16(float x) {
 __device__ __forceinline__ uint16_t f2bf(float x) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
+// Two floats rounded to bf16 (to nearest even) in one conversion instruction: conversions run
+// on the special-function unit, so one per pair instead of one per value matters.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
   f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);

@@ -8,6 +8,8 @@
 // Key blocks wholly above the causal diagonal or below the window are skipped, so the
 // work follows the context.  Rows past the call's bound are written as zeros and keys
 // past its bound are masked, as the reference's bounded call does.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace iron {
@@ -329,9 +331,20 @@ static int launch_prefill(const PrefillParams& p, int batch, cudaStream_t stream
   return cudaLaunchKernelEx(&cfg, mha_prefill_kernel<D, MT>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
+// mha_prefill_tc.cu
+int mha_prefill_tc(const void* Q, const void* K, const void* V, void* O, int batch, int H, int G, int D,
+                   int q_rows, long long q_batch_stride, long long q_row_stride, long long q_head_stride,
+                   long long o_batch_stride, long long o_row_stride, long long o_head_stride,
+                   long long kv_batch_stride, long long kv_row_stride, long long kv_head_stride, int q_tokens,
+                   int kv_tokens, int causal, int window, float scale, int* d_status, cudaStream_t stream);
+
 }  // namespace iron
 
 using namespace iron;
+
+static int* g_prefill_status = nullptr;
+
+extern "C" void iron_mha_prefill_status_word(int* d_status) { g_prefill_status = d_status; }
 
 extern "C" int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, int batch, int H,
                                      int G, int D, int q_rows, int kv_rows, long long q_batch_stride,
@@ -363,6 +376,17 @@ extern "C" int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V
   p.causal = causal; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
+  // Bounds known on the host and at least a tile of queries: the tensor-memory kernel
+  // (IRON_MHA_PREFILL_TC=0 keeps the warp-MMA kernel).
+  if (!d_q_tokens && !d_kv_tokens && q_tokens >= 128) {
+    const char* e = getenv("IRON_MHA_PREFILL_TC");
+    if (!(e && e[0] == '0')) {
+      const int rc = mha_prefill_tc(Q, K, V, O, batch, H, G, D, q_rows, q_batch_stride, q_row_stride, q_head_stride,
+                                    o_batch_stride, o_row_stride, o_head_stride, kv_batch_stride, kv_row_stride,
+                                    kv_head_stride, q_tokens, kv_tokens, causal, window, scale, g_prefill_status, s);
+      if (rc != IRON_ERR_UNSUPPORTED) return rc;
+    }
+  }
   // One 16-row query tile per warp: two (128 query rows per CTA, every K/V fragment feeding
   // two MMAs) measured slower at 2048 x 2048 -- 249 registers leave 8 warps per SM.
   if (D == 64) return launch_prefill<64, 1>(p, batch, s);

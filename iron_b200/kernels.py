@@ -252,6 +252,19 @@ def gemm_swiglu(A, Wg, Wu, out=None, *, valid=None, d_valid=None, status=None):
     return out
 
 
+_PREFILL_STATUS: dict = {}
+
+
+def prefill_status(device=None):
+    """The device word the tensor-memory prompt attention reports a given-up wait in
+    (``IRON_ERR_TIMEOUT``); allocated once per device and handed to the library."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev not in _PREFILL_STATUS:
+        _PREFILL_STATUS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    _lib.load().iron_mha_prefill_status_word(_PREFILL_STATUS[dev].data_ptr())
+    return _PREFILL_STATUS[dev]
+
+
 def mha_prefill(Q, K, V, out=None, *, q_tokens=None, d_q_tokens=None, kv_tokens=None,
                 d_kv_tokens=None, kv_tokens_add=0, causal=True, window=None, scale=None,
                 heads_interleaved=True, kv_interleaved=True, q_row_stride=None):
@@ -261,6 +274,8 @@ def mha_prefill(Q, K, V, out=None, *, q_tokens=None, d_q_tokens=None, kv_tokens=
     when ``kv_interleaved`` else (G, rows, D); an optional leading batch axis on all.
     """
     _bf16(Q, K, V)
+    if Q.device not in _PREFILL_STATUS:
+        prefill_status(Q.device)
     if q_row_stride is not None:
         # Q is a strided view (rows, H, D) into a wider fused projection: rows are
         # `q_row_stride` elements apart and O is dense (rows, H, D).

@@ -498,6 +498,8 @@ class LlamaEngine:
         out = self.logits_buf[seq].float().cpu().numpy()
         if int(self.status.item()) != 0:
             raise RuntimeError("a GEMM pipeline wait gave up (IRON_ERR_TIMEOUT)")
+        if int(K.prefill_status(self.device).item()) != 0:
+            raise RuntimeError("a prompt-attention pipeline wait gave up (IRON_ERR_TIMEOUT)")
         return out
 
     def complete(self, prompt, steps: int) -> list[int]:
@@ -606,6 +608,8 @@ class LlamaEngine:
             raise RuntimeError("a GEMM pipeline wait gave up (IRON_ERR_TIMEOUT)")
         if K.decode_step_status(self.step_ws) != 0:
             raise RuntimeError("the decode step's grid barrier gave up (IRON_ERR_TIMEOUT)")
+        if int(K.prefill_status(self.device).item()) != 0:
+            raise RuntimeError("a prompt-attention pipeline wait gave up (IRON_ERR_TIMEOUT)")
 
     # ------------------------------------------------------------------ batched decode
     def set_batch(self, tokens, positions) -> None:
