@@ -53,6 +53,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // `hint_ns`, so a waiting warp does not take issue slots from the warps that compute.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   uint32_t hint_ns = 2000) {
+  if (mbar_try_wait(bar, parity)) return true;   // reading the timer costs more than a probe
   const unsigned long long t0 = global_ns();
   for (;;) {
     uint32_t ok;

@@ -69,6 +69,48 @@ def test_bounds_from_device_values_and_head_major_layout(K):
     assert not got[:, 100:].astype(np.float32).any()
 
 
+@pytest.mark.parametrize("H,G,D,qr,kr,qt,kt,causal,window", [c for c in CASES if (c[5] or c[3]) >= 128])
+def test_the_tensor_memory_kernel_and_the_warp_mma_kernel_agree(K, monkeypatch, H, G, D, qr, kr, qt, kt, causal, window):
+    """Calls with host-known bounds and at least 128 queries take the tcgen05 kernel; the same
+    call with it switched off takes the warp-MMA kernel.  Same arithmetic, other summation
+    order: the outputs agree to a bf16 rounding of values of order one."""
+    rng = np.random.default_rng(11)
+    q, k, v = (to_torch(normal(rng, s)) for s in ((qr, H, D), (kr, G, D), (kr, G, D)))
+    out = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("IRON_MHA_PREFILL_TC", mode)
+        out[mode] = to_numpy(K.mha_prefill(q, k, v, q_tokens=qt, kv_tokens=kt, causal=causal,
+                                           window=window)).astype(np.float32)
+    assert np.abs(out["1"] - out["0"]).max() <= 2 ** -6
+    assert int(K.prefill_status().item()) == 0
+
+
+def test_the_tensor_memory_kernel_on_batches_head_major_layouts_and_strided_queries(K):
+    import torch
+
+    rng = np.random.default_rng(5)
+    B, H, G, D, S = 3, 8, 4, 64, 384
+    q, k, v = normal(rng, (B, H, S, D)), normal(rng, (B, G, S, D)), normal(rng, (B, G, S, D))
+    got = to_numpy(K.mha_prefill(to_torch(q), to_torch(k), to_torch(v), q_tokens=300, kv_tokens=300,
+                                 heads_interleaved=False, kv_interleaved=False))
+    for b in range(B):
+        want = ops.mha(q[b], k[b], v[b], num_heads=H, num_kv_heads=G, q_tokens=300, kv_tokens=300)
+        assert_verdict(got[b], want, TIGHT, what=f"batch {b}")
+        assert not got[b][:, 300:].astype(np.float32).any()
+    # queries as a strided view of a fused q/k/v projection, the way the prompt path calls it
+    n, Hq, Gk = 256, 8, 2
+    qkv = normal(rng, (n, (Hq + 2 * Gk) * D))
+    kc, vc = normal(rng, (512, Gk, D)), normal(rng, (512, Gk, D))
+    t = to_torch(qkv)
+    got = to_numpy(K.mha_prefill(t.view(n, Hq + 2 * Gk, D)[:, :Hq], to_torch(kc), to_torch(vc),
+                                 torch.empty(n, Hq, D, dtype=torch.bfloat16, device="cuda"),
+                                 q_tokens=n, kv_tokens=400, q_row_stride=t.stride(0)))
+    want = ops.mha(qkv.reshape(n, Hq + 2 * Gk, D)[:, :Hq], kc, vc, num_heads=Hq, num_kv_heads=Gk,
+                   heads_interleaved=True, kv_interleaved=True, q_tokens=n, kv_tokens=400)
+    assert_verdict(got, want, TIGHT, what="strided queries over a cache")
+    assert int(K.prefill_status().item()) == 0
+
+
 def test_long_context_decode_accuracy_deep_in_the_cache(K):
     """iron/tests/operators/test_mha_long_context.py:45-62: one query at positions 1023 and
     32703 stays within 4 % of the output range."""
