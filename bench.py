@@ -394,6 +394,36 @@ def run_batch(args, rank: int, world: int, device) -> None:
                               "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": round(gbs / peak, 4)}}))
 
 
+def time_prompt_attention(device, n: int = CONTEXT, heads: int = 32, kv_heads: int = 8, head_dim: int = 64) -> None:
+    """CUDA-event time of the prompt-chunk attention kernel on its own: ``n`` queries over ``n``
+    keys, causal, random bf16 inputs (17.2 GFLOP at the defaults)."""
+    import torch
+
+    from iron_b200 import kernels as K
+
+    g = torch.Generator(device=device).manual_seed(7)
+    q = torch.randn(n, heads, head_dim, device=device, generator=g).to(torch.bfloat16)
+    k = torch.randn(n, kv_heads, head_dim, device=device, generator=g).to(torch.bfloat16)
+    v = torch.randn(n, kv_heads, head_dim, device=device, generator=g).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    for _ in range(3):
+        K.mha_prefill(q, k, v, o, q_tokens=n, kv_tokens=n)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    start.record()
+    for _ in range(reps):
+        K.mha_prefill(q, k, v, o, q_tokens=n, kv_tokens=n)
+    stop.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(stop) * 1e3 / reps
+    flops = 4 * heads * head_dim * n * (n + 1) // 2
+    print(json.dumps({"kernel": "prompt attention", "tokens": n, "heads": heads, "kv_heads": kv_heads,
+                      "head_dim": head_dim, "us_per_launch": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                      "tensor_memory_kernel": os.environ.get("IRON_MHA_PREFILL_TC", "1") != "0",
+                      "status": int(K.prefill_status(device).item())}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -405,6 +435,9 @@ def main() -> None:
                     help="llama1b-batch64: sequences in the whole job (split over the ranks)")
     ap.add_argument("--decode-step-trace", action="store_true",
                     help="with IRON_DECODE_STEP=1: print the one-kernel step's per-phase timeline and exit")
+    ap.add_argument("--prompt-attention", action="store_true",
+                    help="time the prompt-chunk attention kernel alone (2048 x 2048 causal, the 1B head "
+                         "shape; IRON_MHA_PREFILL_TC=0 for the warp-MMA kernel), print one JSON line and exit")
     ap.add_argument("--workload", default="llama1b", choices=["llama1b", "llama3b-tp", "llama1b-batch64"],
                     help="llama1b: the headline decode, one replica per GPU; llama3b-tp: the 3B "
                          "architecture tensor-parallel over --gpus ranks at context 4096")
@@ -435,6 +468,9 @@ def main() -> None:
 
     from iron_b200.lm.engine import LlamaEngine
 
+    if args.prompt_attention:
+        time_prompt_attention(device)
+        return
     if args.workload == "llama1b-batch64":
         run_batch(args, rank, world, device)
         if world > 1:
