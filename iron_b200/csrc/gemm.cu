@@ -538,7 +538,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (the leader's) ----------------
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
+      // The whole warp runs the loop and one elected lane issues (see elect_one); every lane
+      // probes the barriers, and the outcome is made uniform before anyone leaves the loop.
       // M 256 across the pair (128 rows per CTA), N 256
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPairBN >> 3) << 17) |
                              ((uint32_t)((2 * BM) >> 4) << 24);
@@ -548,24 +550,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       for (int t = pair; t < total && ok; t += pairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag));
+        if (!ok) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kPairBN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full + s, phase, abort_flag)) { ok = false; break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(full + s, phase, abort_flag));
+          if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * kPairStageBytes);
           const uint32_t b_addr = a_addr + kPairABytes;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t a_desc = make_desc(a_addr + k * UK * 2, 16, 1024);
-            const uint64_t b_desc = make_desc(b_addr + k * UK * 2, 16, 1024);
-            tcgen05_mma_bf16_pair(d_tmem, a_desc, b_desc, idesc, kb != 0 || k != 0);
+            for (int k = 0; k < BK / UK; ++k) {
+              const uint64_t a_desc = make_desc(a_addr + k * UK * 2, 16, 1024);
+              const uint64_t b_desc = make_desc(b_addr + k * UK * 2, 16, 1024);
+              tcgen05_mma_bf16_pair(d_tmem, a_desc, b_desc, idesc, kb != 0 || k != 0);
+            }
+            tcgen05_commit_pair(empty + s);
           }
-          tcgen05_commit_pair(empty + s);
+          __syncwarp();
           if (++s == kPairStages) { s = 0; phase ^= 1; }
         }
-        if (ok) tcgen05_commit_pair(acc_full + acc);
+        if (ok && elect_one()) tcgen05_commit_pair(acc_full + acc);
+        __syncwarp();
       }
     }
   } else {

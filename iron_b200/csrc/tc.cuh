@@ -69,6 +69,19 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
     if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
   }
 }
+// One lane of a converged warp.  A role written as "the whole warp runs the loop, one elected
+// lane issues" keeps addresses and descriptors warp-uniform, which the compiler can hold in
+// uniform registers; a role inside `if (lane == 0)` is divergent code and pays a register
+// move per operand of every tcgen05 instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
