@@ -372,6 +372,19 @@ int iron_rope_kv_scatter_bf16(const void* qkv, long long pitch, const void* angl
 int iron_argmax_rows_bf16(const void* logits, long long pitch, int rows, int n, int* tokens,
                           int* positions, int* drawn, int S, iron_stream_t stream);
 
+/* Temperature / top-k draw -- iron/operators/sample.py:106 with a non-zero draw row, the
+ * device side of iron/lm/generation.py:24-94 (`Sampler`).  The reference's arithmetic
+ * (`sample_ref`) lives in mlir-aie, outside its tree: the rule here is this library's own,
+ * stated in iron_b200/lm/generation.py, whose host Sampler it matches token for token.
+ * Per row r at position p = positions[r]: the draw row draws[(r * S + p) * 4 ..] holds the
+ * temperature's f32 bits, top_k (clamped to iron_sample_k_max()), and the low 32 / high 21
+ * bits of a 53-bit uniform; an all-zero row, temperature 0 or top_k 1 is the greedy draw.
+ * The token goes to drawn[r * S + p] and tokens[r]; positions[r] becomes p + 1 (the carry of
+ * iron_argmax_rows_bf16).  logits (rows, pitch >= n) bf16. */
+int iron_sample_k_max(void);
+int iron_sample_rows_bf16(const void* logits, long long pitch, int rows, int n, const int* draws,
+                          int* tokens, int* positions, int* drawn, int S, iron_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * One whole greedy decode step as one persistent kernel -- replaces the decode version the
  * reference records per call, iron/lm/causal.py:248-287 (embedding gather, per layer

@@ -429,6 +429,28 @@ def rope_kv_scatter(qkv, angles, q_out, k_cache, v_cache, positions, *, H, G, D)
          _ptr(v_cache), k_cache.stride(0), rows, _ptr(positions), H, G, D, S, _stream())
 
 
+def sample_k_max() -> int:
+    """The largest top-k the device draws."""
+    return _lib.load().iron_sample_k_max()
+
+
+def sample_rows(logits, draws, tokens, positions, drawn):
+    """Per row: the token its draw row (``draws[row, position]``: temperature bits, top_k, a
+    53-bit uniform) picks from ``logits[row]``; ``drawn[row, position]`` and ``tokens[row]``
+    receive it and ``positions[row]`` advances.  All-zero draw rows are greedy."""
+    _bf16(logits)
+    rows, n = (1, logits.shape[0]) if logits.dim() == 1 else logits.shape
+    pitch = logits.stride(0) if logits.dim() == 2 else n
+    S = drawn.shape[-1]
+    for t in (draws, tokens, positions, drawn):
+        if t.dtype != torch.int32:
+            raise TypeError("draws, tokens, positions and drawn are int32")
+    if draws.numel() != rows * S * 4:
+        raise ValueError(f"draws holds {draws.numel()} words, not {rows} x {S} x 4")
+    call("iron_sample_rows_bf16", _ptr(logits), pitch, rows, n, _ptr(draws), _ptr(tokens), _ptr(positions),
+         _ptr(drawn), S, _stream())
+
+
 def argmax_rows(logits, tokens, positions, drawn):
     """Greedy draw per row; ``drawn`` (rows, S) int32, ``tokens`` and ``positions`` int32 (rows,)."""
     _bf16(logits)

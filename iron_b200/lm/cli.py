@@ -5,17 +5,21 @@ the fused engine and samples from it, or checks it: ``--check-accuracy`` compare
 step's logits with the host reference's (every recorded operator's numpy ``reference()``),
 ``--check-determinism`` counts runs whose logits differ bitwise.  The flags are the
 reference's; the ones that choose an NPU packaging (``--full-elf``) have nothing to choose
-here and are not taken.  Draws are greedy: a non-zero ``--temperature`` is refused.
+here and are not taken.  ``--temperature`` / ``--top-k`` draw on the device by the rule of
+``iron_b200.lm.generation``; ``--compare-host`` repeats the run drawing on the host.
 """
 
 from __future__ import annotations
 
 import argparse
+import inspect
 import logging
 import time
 from pathlib import Path
 
 import numpy as np
+
+from .generation import Sampler
 
 #: Flags the command line and the test fixtures read alike (iron/lm/cli.py:19-42).
 FLAGS = (
@@ -81,6 +85,18 @@ def accuracy(engine, reference, tokens, steps: int):
     return results
 
 
+def host_draws(engine, tokens, steps: int, sampler) -> list[int]:
+    """The ``steps`` tokens drawn on the host from the engine's logits: the prompt, then each
+    drawn token fed back (iron/lm/generation.py:102-107 over an incremental model)."""
+    logits = engine.prefill(tokens)
+    out = []
+    for i in range(steps):
+        out.append(sampler(logits))
+        if i + 1 < steps:
+            logits = engine.feed([out[-1]], len(tokens) + i)
+    return out
+
+
 def determinism(engine, prompts, steps: int, rounds: int) -> int:
     """Run each prompt ``rounds`` times, alternating; count the runs whose logits differ
     bitwise from the prompt's first run."""
@@ -111,8 +127,12 @@ def main(model_class, args=None, out=print) -> int:
     parser.add_argument("--prompt-len", type=int, default=2048,
                         help="without --prompt, a third as many random tokens to prompt with (default: 2048)")
     parser.add_argument("--num-tokens", type=int, default=40, help="tokens to generate (default: 40)")
-    parser.add_argument("--temperature", type=float, default=0.0)
-    parser.add_argument("--top-k", type=int, default=0)
+    defaults = inspect.signature(Sampler).parameters
+    parser.add_argument("--temperature", type=float, default=defaults["temperature"].default)
+    parser.add_argument("--top-k", type=int, default=defaults["top_k"].default)
+    parser.add_argument("--compare-host", action="store_true",
+                        help="after drawing on the device, generate again drawing on the host from the same "
+                             "seed and count the tokens that differ")
     check = parser.add_mutually_exclusive_group()
     check.add_argument("--check-accuracy", action="store_true",
                        help="instead of sampling, compare each step's logits with the host reference's, "
@@ -123,8 +143,10 @@ def main(model_class, args=None, out=print) -> int:
     ns = parse_args(parser, args)
     if ns.check_determinism is not None and ns.check_determinism < 2:
         parser.error("--check-determinism compares rounds: give 2 or more")
-    if ns.temperature != 0.0 or ns.top_k not in (0, 1):
-        parser.error("draws are greedy here: --temperature 0 (the default) and no --top-k")
+    try:
+        Sampler(ns.temperature, ns.top_k).rows(0)
+    except ValueError as e:
+        parser.error(str(e))
     config_class = getattr(model_class, "config_class", None)
     try:
         engine = LlamaEngine.from_checkpoint(ns.path, random_weights=ns.random_weights,
@@ -158,6 +180,8 @@ def main(model_class, args=None, out=print) -> int:
     else:
         import torch
 
+        # draw rows for the positions this run draws at: the prompt's last row, then each new token's
+        engine.set_sampler(Sampler(ns.temperature, ns.top_k), start=len(tokens) - 1, count=ns.num_tokens)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         engine.prefill(tokens)
@@ -172,4 +196,8 @@ def main(model_class, args=None, out=print) -> int:
         out(f"\n[Prefill] Time to first token: {ttft:7.3f} s")
         if ns.num_tokens > 1:
             out(f"[Decode]  Tokens per second:   {(ns.num_tokens - 1) / decode_s:7.3f}")
+        if ns.compare_host:
+            host = host_draws(engine, tokens, ns.num_tokens, Sampler(ns.temperature, ns.top_k))
+            differ = sum(a != b for a, b in zip(drawn, host))
+            out(f"[Device] Tokens differing from the host loop: {differ}/{len(host)}")
     return 0

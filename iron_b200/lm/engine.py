@@ -205,6 +205,7 @@ class LlamaEngine:
         self._peer_exchange_setup()
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
+        self.draws = None   # (batch, S, 4) int32 draw rows once a sampler is set
         self.step_ws = K.decode_step_workspace(E, H, G, D, self.device)
         self.step_table = K.decode_step_table(
             [dict(l, k=l["k"][0], v=l["v"][0]) for l in self.layers], self.device)
@@ -370,7 +371,10 @@ class LlamaEngine:
             K.gemm(self.b_gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
         K.rms_norm(x, self.norm, h, eps=c.eps)
         K.gemm(h, self.head, self.logits_buf, b_col_maj=True, status=self.status)
-        K.argmax_rows(self.logits_buf, self.b_tokens, self.b_pos, self.drawn)
+        if self.draws is None:
+            K.argmax_rows(self.logits_buf, self.b_tokens, self.b_pos, self.drawn)
+        else:
+            K.sample_rows(self.logits_buf, self.draws, self.b_tokens, self.b_pos, self.drawn)
 
     def _decode_launches(self) -> None:
         """Launch one decode step on the current stream, reading (token, position) from
@@ -426,8 +430,37 @@ class LlamaEngine:
             K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
             K.gemv(l["wd"], self.act[0], x, residual=y)
         K.gemv(self.head, x, self.logits_buf[0], norm_weight=self.norm, eps=c.eps)
-        K.argmax(self.logits_buf[0], self.drawn[0], self.argmax_ws, d_out_index=d_pos,
-                 carry_token=d_token, carry_position=d_pos)
+        self._draw(0, d_token, d_pos)
+
+    def _draw(self, seq: int, d_token, d_pos) -> None:
+        """The draw after a head projection: greedy, or by the draw row of the position when a
+        sampler is set; writes drawn[seq][position] and carries (token, position + 1)."""
+        if self.draws is None:
+            K.argmax(self.logits_buf[seq], self.drawn[seq], self.argmax_ws, d_out_index=d_pos,
+                     carry_token=d_token, carry_position=d_pos)
+        else:
+            K.sample_rows(self.logits_buf[seq], self.draws[seq], d_token, d_pos, self.drawn[seq : seq + 1])
+
+    def set_sampler(self, sampler, start: int = 0, count: int | None = None, seq: int | None = None) -> None:
+        """Draw with ``sampler`` (an ``iron_b200.lm.generation.Sampler``) at positions
+        ``start .. start + count`` of sequence ``seq`` (every sequence when None, each taking
+        its own uniforms in turn): the device gets the uniforms the sampler's host draws would
+        use, one draw row per position (iron/lm/causal.py:340-347 keeps them in its ``draws``
+        state).  ``sampler`` None returns to the greedy draw.  Captured graphs are dropped."""
+        self._graph = None
+        if sampler is None:
+            self.draws = None
+            return
+        S = self.c.max_seq_len
+        count = S - start if count is None else count
+        if start < 0 or start + count > S:
+            raise IndexError(f"positions {start}..{start + count} leave the {S}-row caches")
+        if self.draws is None:
+            self.draws = torch.zeros((self.batch, S, 4), dtype=torch.int32, device=self.device)
+        self.fused_step = False   # the one-kernel step draws greedily
+        for b in (range(self.batch) if seq is None else (seq,)):
+            rows = torch.from_numpy(sampler.rows(count, K.sample_k_max()))
+            self.draws[b, start : start + count].copy_(rows)
 
     # ------------------------------------------------------------------ prompt chunk
     @property
@@ -487,8 +520,7 @@ class LlamaEngine:
         K.copy_rows(x, last, nrows=1, row_bytes=E * 2, src_row0=n - 1)
         K.gemv(self.head, last, self.logits_buf[seq], norm_weight=self.norm, eps=c.eps)
         self.set_call(0, start + n - 1)
-        K.argmax(self.logits_buf[seq], self.drawn[seq], self.argmax_ws, d_out_index=self.values[1:2],
-                 carry_token=self.values[0:1], carry_position=self.values[1:2])
+        self._draw(seq, self.values[0:1], self.values[1:2])
 
     def prefill(self, tokens, start: int = 0, seq: int = 0) -> np.ndarray:
         """Run a prompt of any length in chunks from ``start``; the logits after its last token."""

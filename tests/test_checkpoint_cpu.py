@@ -159,7 +159,8 @@ def test_the_command_line_refuses_what_it_cannot_do_before_loading(tmp_path, cap
     from iron_b200.lm.cli import main
 
     for argv, said in ((["x", "--check-determinism", "1"], "give 2 or more"),
-                       (["x", "--temperature", "0.7"], "draws are greedy"),
+                       (["x", "--top-k", "100"], "not one the device draws"),
+                       (["x", "--temperature", "-1"], "is negative"),
                        (["x", "--check-accuracy", "--check-determinism", "2"], "not allowed with")):
         with pytest.raises(SystemExit):
             main(Llama, argv)

@@ -45,7 +45,8 @@ def test_the_command_line_samples_and_checks_itself(directory, capsys):
     from iron_b200.lm.cli import main
 
     lines = []
-    assert main(Llama, [str(directory), "--prompt-len", "48", "--num-tokens", "6"], out=lines.append) == 0
+    assert main(Llama, [str(directory), "--prompt-len", "48", "--num-tokens", "6", "--temperature", "0"],
+                out=lines.append) == 0
     drawn = [int(t) for t in lines[0].split()]
     assert len(drawn) == 6 and all(0 <= t < 1024 for t in drawn)
     assert "[Prefill] Time to first token" in lines[1] and "[Decode]  Tokens per second" in lines[2]
@@ -54,6 +55,14 @@ def test_the_command_line_samples_and_checks_itself(directory, capsys):
     from iron_b200.lm.engine import LlamaEngine
 
     assert LlamaEngine.from_checkpoint(directory).complete(random_prompt(1024, 16), 6) == drawn
+
+    # temperature and top-k on the device, then the same draws on the host from the same seed
+    lines.clear()
+    main(Llama, [str(directory), "--prompt-len", "48", "--num-tokens", "12", "--temperature", "0.9", "--top-k", "40",
+                 "--compare-host"], out=lines.append)
+    sampled = [int(t) for t in lines[0].split()]
+    assert len(sampled) == 12 and sampled != drawn + sampled[6:]
+    assert lines[-1] == "[Device] Tokens differing from the host loop: 0/12"
 
     lines.clear()
     main(Llama, [str(directory), "--prompt-len", "24", "--num-tokens", "4", "--check-accuracy"], out=lines.append)
