@@ -411,12 +411,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // In the gated form the leader stages the first weight matrix's rows and the peer the
 // second's, so accumulator columns 0..127 / 128..255 hold the two products as in the
 // one-CTA gated form.
-constexpr int kPairBN = 256;
 constexpr int kPairStages = 6;
+constexpr int kPairAccStride = 256;                // tensor-memory columns between the two accumulators
 constexpr int kPairABytes = BM * BK * 2;           // this CTA's 128 rows of A
-constexpr int kPairBBytes = (kPairBN / 2) * BK * 2;  // this CTA's 128 columns of B
-constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
-constexpr int kPairSmem = kPairStages * kPairStageBytes + 256 + 1024;
+// PBN: columns of a pair's tile, 256 or 192 (the narrower tile when it saves a wave of tiles).
+template <int PBN>
+struct PairCfg {
+  static constexpr int kBBytes = (PBN / 2) * BK * 2;   // this CTA's half of the tile's columns of B
+  static constexpr int kStageBytes = kPairABytes + kBBytes;
+  static constexpr int kSmem = kPairStages * kStageBytes + 256 + 1024;
+};
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -457,9 +461,12 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+template <int PBN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
+  constexpr int kPairBN = PBN;
+  constexpr int kPairStageBytes = PairCfg<PBN>::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
@@ -553,7 +560,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         ok = __all_sync(0xffffffffu, mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag));
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kPairBN;
+        const uint32_t d_tmem = tmem_base + acc * kPairAccStride;
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = __all_sync(0xffffffffu, mbar_wait(full + s, phase, abort_flag));
           if (!ok) break;
@@ -592,14 +599,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll 1
       for (int c = 0; c < BNO / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairBN + c * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairAccStride + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (p.dual) {
-          tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairBN + kPairBN / 2 + c * 32, r);
+          tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairAccStride + kPairBN / 2 + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -711,11 +718,14 @@ static int launch_gemm_split(const CUtensorMap& ma, const CUtensorMap& mb, const
 }
 
 // One 256 x 256 tile per CTA pair; pairs walk the tiles M-fastest.
+template <int PBN>
 static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
                             const GemmParams& p, int max_rows, cudaStream_t stream) {
+  constexpr int kPairBN = PBN;
+  constexpr int kPairSmem = PairCfg<PBN>::kSmem;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
+    if (cudaFuncSetAttribute(gemm_pair_kernel<PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
         cudaSuccess)
       return IRON_ERR_LAUNCH;
     configured = true;
@@ -730,7 +740,7 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
-  return cudaLaunchKernelEx(&cfg, gemm_pair_kernel, ma, mb, mb2, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_pair_kernel<PBN>, ma, mb, mb2, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
 // The pair form takes K-major B (weights as stored) and problems with more than one
@@ -793,9 +803,15 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     if (splits > 1 && tiles >= 1) return launch_gemm_split(ma, mb, p, tiles, splits, s);
   }
   if (bn == 256 && b_col_maj && max_rows > BM && pair_enabled()) {
-    CUtensorMap mh;   // each CTA of a pair stages half of the tile's 256 rows of B
-    if (!make_map(&mh, B, (uint64_t)valid_k, (uint64_t)N, (uint64_t)ldb, BK, kPairBN / 2)) return IRON_ERR_LAUNCH;
-    return launch_gemm_pair(ma, mh, mh, p, max_rows, s);
+    // 192-column tiles when they finish in fewer, or shorter, waves over the 74 pairs
+    const long long mt2 = (max_rows + 2 * BM - 1) / (2 * BM);
+    auto cost = [&](int bn_) { return ((mt2 * ((N + bn_ - 1) / bn_) + kSMs / 2 - 1) / (kSMs / 2)) * bn_; };
+    // (the narrower tile re-reads A more often per flop: it must save more than a seventh)
+    const int pbn = cost(192) * 8 < cost(256) * 7 ? 192 : 256;
+    CUtensorMap mh;   // each CTA of a pair stages half of the tile's rows of B
+    if (!make_map(&mh, B, (uint64_t)valid_k, (uint64_t)N, (uint64_t)ldb, BK, pbn / 2)) return IRON_ERR_LAUNCH;
+    return pbn == 192 ? launch_gemm_pair<192>(ma, mh, mh, p, max_rows, s)
+                      : launch_gemm_pair<256>(ma, mh, mh, p, max_rows, s);
   }
   if (bn == 256) return launch_gemm<256>(ma, mb, mb, p, max_rows, s);
   if (bn == 128) return launch_gemm<128>(ma, mb, mb, p, max_rows, s);
@@ -828,7 +844,7 @@ extern "C" int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* 
   p.valid = valid_rows; p.d_valid = d_valid_rows;
   p.epilogue = EPI_NONE; p.dual = 1; p.status = d_status;
   cudaStream_t s = (cudaStream_t)stream;
-  if (bn == 256 && max_rows > BM && pair_enabled()) return launch_gemm_pair(ma, mg, mu, p, max_rows, s);
+  if (bn == 256 && max_rows > BM && pair_enabled()) return launch_gemm_pair<256>(ma, mg, mu, p, max_rows, s);
   if (bn == 256) return launch_gemm<256>(ma, mg, mu, p, max_rows, s);
   if (bn == 128) return launch_gemm<128>(ma, mg, mu, p, max_rows, s);
   return launch_gemm<64>(ma, mg, mu, p, max_rows, s);

@@ -32,6 +32,7 @@ CASES = [
     # M, N, K -- the reference's GEMM cases are multiples of 64; ragged ones added
     (128, 64, 64), (128, 256, 64), (256, 256, 256), (2048, 2048, 2048), (2048, 512, 2048),
     (384, 1536, 768), (200, 96, 136), (130, 520, 72), (64, 8192, 2048), (2048, 2048, 8192),
+    (2048, 3072, 512), (1500, 3000, 264),   # CTA pairs with 192-column tiles (fewer waves than 256), ragged too
 ]
 
 
