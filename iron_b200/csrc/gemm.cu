@@ -505,7 +505,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int BNO = p.dual ? kPairBN / 2 : kPairBN;
   const int num_kb = (p.K + BK - 1) / BK;
   pdl_launch();
-  pdl_wait();
+  // With the row count known at launch, the first tile's weight (B) copies do not depend on the
+  // kernel before: they go out ahead of the dependency wait, one per pipeline stage.
+  int pre = 0;
+  if (p.d_valid == nullptr && warp == 0 && lane == 0) {
+    const int v0 = max(p.valid, 0), mt = (v0 + 2 * BM - 1) / (2 * BM);
+    if (mt > 0 && pair < mt * ((p.N + BNO - 1) / BNO)) {
+      const int n0 = (pair / mt) * BNO;
+      for (int kb = 0; kb < num_kb && pre < kPairStages; ++kb, ++pre) {
+        uint8_t* b_dst = smem + pre * kPairStageBytes + kPairABytes;
+        const uint32_t bar = map_to_rank(smem_u32(full + pre), 0);
+        if (rank == 0) mbar_expect_tx(full + pre, 2 * kPairStageBytes);
+        if (p.dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
+        else tma_load_2d_pair(b_dst, &map_b, kb * BK, n0 + (int)rank * (kPairBN / 2), bar);
+      }
+    }
+  }
+  pdl_wait();   // A, and the residual, are the previous kernels' outputs
   const int valid = max(p.d_valid ? min(*p.d_valid, p.M) : p.valid, 0);
   const int m_tiles = (valid + 2 * BM - 1) / (2 * BM);
   const int n_tiles = (p.N + BNO - 1) / BNO;
@@ -514,7 +530,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 0) {
     // ---------------- producer (one per CTA) ----------------
     if (lane == 0) {
-      int s = 0, issued = 0;
+      int s = 0, issued = pre > 0 ? 1 : 0;
+      int early = pre;   // stages whose B copy is already on its way
       uint32_t phase = 0;
       bool ok = true;
       for (int t = pair; t < total && ok; t += pairs) {
@@ -525,6 +542,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint8_t* a_dst = smem + s * kPairStageBytes;
           uint8_t* b_dst = a_dst + kPairABytes;
           const uint32_t bar = map_to_rank(smem_u32(full + s), 0);
+          if (early > 0) {
+            --early;
+            tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
+            ++issued;
+            if (++s == kPairStages) { s = 0; phase ^= 1; }
+            continue;
+          }
           if (rank == 0) mbar_expect_tx(full + s, 2 * kPairStageBytes);
           tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
           if (p.dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
