@@ -210,9 +210,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   };
   // The dependents of this kernel may start their own prologue (and weight loads) now.
   pdl_launch();
-  // Split form with the row count known at launch: the weight tiles do not depend on the
-  // kernel before, so the first stages' B copies go out ahead of the dependency wait.
-  const bool early = SPLIT && p.d_valid == nullptr && !p.b_n_major;
+  // With the row count known at launch, the weight tiles do not depend on the kernel before:
+  // the first stages' B copies go out ahead of the dependency wait.
+  const bool early = p.d_valid == nullptr && !p.b_n_major;
   int pre = 0;
   if (early) {
     setup(p.valid);
@@ -220,7 +220,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int n0 = (t_first / m_tiles) * BNO;
       for (int kb = k_lo; kb < k_hi && pre < Cfg::kStages; ++kb, ++pre) {
         mbar_expect_tx(full + pre, Cfg::kStageBytes);
-        tma_load_2d(smem + pre * Cfg::kStageBytes + Cfg::kABytes, &map_b, kb * BK, n0, full + pre);
+        uint8_t* b_dst = smem + pre * Cfg::kStageBytes + Cfg::kABytes;
+        tma_load_2d(b_dst, &map_b, kb * BK, n0, full + pre);
+        if (p.dual) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b2, kb * BK, n0, full + pre);
       }
     }
   }
