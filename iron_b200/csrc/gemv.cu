@@ -389,9 +389,15 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
       uint64_t* bar = my_bars + c_idx % kRingSlots;
       const uint32_t parity = (uint32_t)(c_idx / kRingSlots) & 1u;
       if (!ring_try_wait(bar, parity)) {
-        const unsigned long long t0 = ring_ns();
-        for (uint32_t it = 1; !ring_try_wait(bar, parity); ++it)
-          if ((it & 63u) == 0 && ring_ns() - t0 > kRingWaitNs) { lost = true; break; }
+        // The timer costs a few hundred cycles to read: the wait probes many times between
+        // readings, so that a copy that lands is seen at once.
+        unsigned long long t0 = 0;
+        for (uint32_t it = 1; !ring_try_wait(bar, parity); ++it) {
+          if ((it & 255u) != 0) continue;
+          const unsigned long long now = ring_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > kRingWaitNs) { lost = true; break; }
+        }
         if (lost) break;
       }
       int ra, rb, col_a, n_a, col_b, n_b;

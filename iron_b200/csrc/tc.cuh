@@ -39,13 +39,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Wait for the phase of `parity` to complete; false when aborted or out of time.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
+  // The timer costs a few hundred cycles to read: many probes go between two readings, so
+  // that a phase that completes is seen at once.
+  unsigned long long t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0) {
+    if ((it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
     }
   }
 }
@@ -53,9 +56,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // `hint_ns`, so a waiting warp does not take issue slots from the warps that compute.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   uint32_t hint_ns = 2000) {
-  if (mbar_try_wait(bar, parity)) return true;   // reading the timer costs more than a probe
-  const unsigned long long t0 = global_ns();
-  for (;;) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  for (uint32_t it = 1;; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -65,8 +68,12 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
         : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     if (ok) return true;
-    if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    if ((it & 15u) == 0) {   // every sixteen naps: the timer costs a few hundred cycles to read
+      if (*abort_flag) return false;
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    }
   }
 }
 // One lane of a converged warp.  A role written as "the whole warp runs the loop, one elected

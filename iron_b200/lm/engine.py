@@ -220,6 +220,8 @@ class LlamaEngine:
         self._ring_done: list[torch.cuda.Event | None] = [None] * len(self._ring)
         self._ring_at = 0
         self._h_token = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._h_ids = torch.zeros(self.chunk, dtype=torch.int32).pin_memory()
+        self._h_ids_done: torch.cuda.Event | None = None
         self._h_status = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     # ------------------------------------------------------------------ weights
@@ -490,8 +492,13 @@ class LlamaEngine:
         H, G, D, E, F = self.H, self.G, c.head_dim, c.hidden_size, self.F
         tp = self.tp_size > 1
         part = self.p_part[:n]
-        ids_host = torch.from_numpy(tokens.astype(np.int32)).pin_memory()
-        self.p_ids[:n].copy_(ids_host, non_blocking=True)
+        # token ids go through one pinned buffer, reused once the copy that read it has run
+        if self._h_ids_done is not None:
+            self._h_ids_done.synchronize()
+        self._h_ids[:n].copy_(torch.from_numpy(tokens.astype(np.int32)))
+        self.p_ids[:n].copy_(self._h_ids[:n], non_blocking=True)
+        self._h_ids_done = torch.cuda.Event()
+        self._h_ids_done.record()
         x, h, y = self.p_x[:n], self.p_h[:n], self.p_y[:n]
         qkv, att, gate, up = self.p_qkv[:n], self.p_att[:n], self.p_gate[:n], self.p_up[:n]
         K.copy_rows(self.embed, x, ids=self.p_ids, nrows=n, row_bytes=E * 2, src_rows=c.vocab_size)
