@@ -5,7 +5,7 @@ per-call ``Expr`` when the body indexed by a per-call value), a shape, and an op
 per-call bound on its leading axis (``x[:n]``).  Indexing, slicing the leading axis,
 reshaping and arithmetic record nothing until an operator consumes the view; assignment
 into a view and arithmetic record steps on the active recorder.  This is the contract of
-``iron/common/graph/handle.py:95-602`` for the forms the decoder path uses (SURVEY of the
+``iron/common/graph/handle.py:95-602`` for the forms the decoder path uses (the
 body expressions: ``cache[position] = k``, ``cache[start:start+C][:rows] = x``,
 ``keys[:position+1]``, ``table[position]``, ``embed[ids]``, ``w[a:b]``, ``x[rows-1]``,
 reshapes carrying the leading bound, ``x + y``, ``x * w``, ``x - y``).

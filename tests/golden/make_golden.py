@@ -7,7 +7,7 @@ ids, iron/lm/golden.py:88-92): the toy ``SCALED`` Llama on ``filled("random", se
 weights, prompt ``default_rng(7).integers(0, 1024, 8)`` then six greedy steps, and the
 multi-chunk prompts of seeds 3 and 4 (iron/tests/support/llama_reference.py:134, :219-224).
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 """
 
 import sys
@@ -30,4 +30,6 @@ def main(reference: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])
