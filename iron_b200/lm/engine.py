@@ -220,6 +220,9 @@ class LlamaEngine:
         self._ring_done: list[torch.cuda.Event | None] = [None] * len(self._ring)
         self._ring_at = 0
         self._h_token = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._h_in = torch.zeros(16, dtype=torch.int32).pin_memory()   # the host loop's per-call values
+        self._h_in_np = self._h_in.numpy()
+        self._graph_host: torch.cuda.CUDAGraph | None = None
         self._h_ids = torch.zeros(self.chunk, dtype=torch.int32).pin_memory()
         self._h_ids_done: torch.cuda.Event | None = None
         self._h_status = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -588,6 +591,17 @@ class LlamaEngine:
         with capturing(g):
             self._decode_launches()
         self._graph = g
+        # The step a host loop drives: the per-call values in from pinned memory, the decode
+        # launches, the drawn token (and the one-kernel step's status) out to pinned memory,
+        # all nodes of one graph, so a call is one launch and one stream synchronisation.
+        gh = torch.cuda.CUDAGraph()
+        with capturing(gh):
+            self.values.copy_(self._h_in, non_blocking=True)
+            self._decode_launches()
+            self._h_token.copy_(self.values[0:1], non_blocking=True)
+            if self.fused_step:
+                self._h_status.copy_(self.step_ws[128:132].view(torch.int32), non_blocking=True)
+        self._graph_host = gh
         self.values.copy_(saved)
         self.b_tokens.copy_(saved_b[0]); self.b_pos.copy_(saved_b[1])
         for l, (k0, v0) in zip(self.layers, rows):
@@ -619,11 +633,13 @@ class LlamaEngine:
 
     def decode(self, token: int, position: int) -> int:
         """One decode step from the host: token in, drawn token out (both cross PCIe)."""
-        self.set_call(token, position)
-        self.step()
-        self._h_token.copy_(self.values[0:1], non_blocking=True)
-        if self.fused_step:
-            self._h_status.copy_(self.step_ws[128:132].view(torch.int32), non_blocking=True)
+        if not 0 <= position < self.c.max_seq_len:
+            raise IndexError(f"position {position} is outside the {self.c.max_seq_len}-row caches")
+        if not 0 <= token < self.c.vocab_size:
+            raise IndexError(f"token {token} is outside the {self.c.vocab_size}-row vocabulary")
+        self.capture()
+        self._h_in_np[0], self._h_in_np[1] = token, position
+        self._graph_host.replay()
         torch.cuda.current_stream().synchronize()
         if int(self._h_status[0]) != 0:
             raise RuntimeError("the decode step's grid barrier gave up (IRON_ERR_TIMEOUT)")
