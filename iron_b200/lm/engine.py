@@ -221,6 +221,10 @@ class LlamaEngine:
         self._ring_at = 0
         self._h_token = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._h_in = torch.zeros(16, dtype=torch.int32).pin_memory()   # the host loop's per-call values
+        self._h_b = torch.zeros((2, batch), dtype=torch.int32).pin_memory()
+        self._h_b_np = self._h_b.numpy()
+        self._h_b_out = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        self._h_b_out_np = self._h_b_out.numpy()
         self._h_in_np = self._h_in.numpy()
         self._graph_host: torch.cuda.CUDAGraph | None = None
         self._h_ids = torch.zeros(self.chunk, dtype=torch.int32).pin_memory()
@@ -453,6 +457,7 @@ class LlamaEngine:
         use, one draw row per position (iron/lm/causal.py:340-347 keeps them in its ``draws``
         state).  ``sampler`` None returns to the greedy draw.  Captured graphs are dropped."""
         self._graph = None
+        self._graph_host = None
         if sampler is None:
             self.draws = None
             return
@@ -591,23 +596,35 @@ class LlamaEngine:
         with capturing(g):
             self._decode_launches()
         self._graph = g
-        # The step a host loop drives: the per-call values in from pinned memory, the decode
-        # launches, the drawn token (and the one-kernel step's status) out to pinned memory,
-        # all nodes of one graph, so a call is one launch and one stream synchronisation.
-        gh = torch.cuda.CUDAGraph()
-        with capturing(gh):
-            self.values.copy_(self._h_in, non_blocking=True)
-            self._decode_launches()
-            self._h_token.copy_(self.values[0:1], non_blocking=True)
-            if self.fused_step:
-                self._h_status.copy_(self.step_ws[128:132].view(torch.int32), non_blocking=True)
-        self._graph_host = gh
         self.values.copy_(saved)
         self.b_tokens.copy_(saved_b[0]); self.b_pos.copy_(saved_b[1])
         for l, (k0, v0) in zip(self.layers, rows):
             l["k"][:, 0].copy_(k0); l["v"][:, 0].copy_(v0)
         self.drawn[:, 0].copy_(drawn0)
         torch.cuda.synchronize()
+
+    def _capture_host(self) -> None:
+        """The step a host loop drives, as one graph: the per-call values in from pinned
+        memory, the decode launches, the drawn tokens (and a status word) out to pinned memory,
+        so a call is one launch and one stream synchronisation.  Built on first use."""
+        self.capture()
+        if self._graph_host is not None:
+            return
+        gh = torch.cuda.CUDAGraph()
+        with capturing(gh):
+            if self.batch > 1:
+                self.b_tokens.copy_(self._h_b[0], non_blocking=True)
+                self.b_pos.copy_(self._h_b[1], non_blocking=True)
+                self._decode_launches()
+                self._h_b_out.copy_(self.b_tokens, non_blocking=True)
+                self._h_status.copy_(self.status.view(-1)[:1], non_blocking=True)
+            else:
+                self.values.copy_(self._h_in, non_blocking=True)
+                self._decode_launches()
+                self._h_token.copy_(self.values[0:1], non_blocking=True)
+                if self.fused_step:
+                    self._h_status.copy_(self.step_ws[128:132].view(torch.int32), non_blocking=True)
+        self._graph_host = gh
 
     def set_call(self, token: int, position: int) -> None:
         """Write the per-call values (one small pinned-host to device copy)."""
@@ -637,7 +654,7 @@ class LlamaEngine:
             raise IndexError(f"position {position} is outside the {self.c.max_seq_len}-row caches")
         if not 0 <= token < self.c.vocab_size:
             raise IndexError(f"token {token} is outside the {self.c.vocab_size}-row vocabulary")
-        self.capture()
+        self._capture_host()
         self._h_in_np[0], self._h_in_np[1] = token, position
         self._graph_host.replay()
         torch.cuda.current_stream().synchronize()
@@ -683,12 +700,25 @@ class LlamaEngine:
         torch.cuda.current_stream().synchronize()   # the pinned staging buffer is released here
 
     def decode_batch(self, tokens, positions) -> list[int]:
-        """One decode step of every sequence from the host: tokens in, drawn tokens out."""
-        self.set_batch(tokens, positions)
-        self.step()
-        out = self.b_tokens.cpu().tolist()
-        self.check()
-        return out
+        """One decode step of every sequence from the host: tokens in, drawn tokens out, the
+        copies being nodes of the step's graph (one launch and one synchronisation a call)."""
+        tokens = np.asarray(tokens, dtype=np.int64).reshape(-1)
+        positions = np.asarray(positions, dtype=np.int64).reshape(-1)
+        if len(tokens) != self.batch or len(positions) != self.batch:
+            raise ValueError(f"a batched step takes {self.batch} tokens and positions")
+        if positions.min() < 0 or positions.max() >= self.c.max_seq_len:
+            raise IndexError(f"a position is outside the {self.c.max_seq_len}-row caches")
+        if tokens.min() < 0 or tokens.max() >= self.c.vocab_size:
+            raise IndexError(f"a token is outside the {self.c.vocab_size}-row vocabulary")
+        if self.batch == 1:
+            return [self.decode(int(tokens[0]), int(positions[0]))]
+        self._capture_host()
+        self._h_b_np[0], self._h_b_np[1] = tokens, positions
+        self._graph_host.replay()
+        torch.cuda.current_stream().synchronize()
+        if int(self._h_status[0]) != 0:
+            raise RuntimeError("a GEMM pipeline wait gave up (IRON_ERR_TIMEOUT)")
+        return self._h_b_out_np.tolist()
 
     def generate_batch(self, tokens, positions, steps: int) -> np.ndarray:
         """``steps`` greedy tokens per sequence, the loop carried on the device; (batch, steps)."""
