@@ -267,7 +267,9 @@ def run_tp(args, rank: int, world: int, device) -> None:
     for name, dims in llama_shapes(shape).items():
         weights[name] = ((torch.randn(dims, generator=gen, device=device) * 0.02).to(torch.bfloat16)
                          if len(dims) >= 2 else torch.ones(dims, device=device, dtype=torch.bfloat16))
-    engine = LlamaEngine(config, weights, device=device, kv_len_hint=ctx + args.steps, tp_rank=rank, tp_size=world)
+    nb = max(1, args.tp_batch)
+    engine = LlamaEngine(config, weights, device=device, kv_len_hint=ctx + args.steps, tp_rank=rank, tp_size=world,
+                         batch=nb)
     del weights
     gen = torch.Generator(device=device).manual_seed(4002)
     for l in engine.layers:
@@ -275,11 +277,18 @@ def run_tp(args, rank: int, world: int, device) -> None:
             l[name][:, :ctx].copy_(torch.randn(l[name][:, :ctx].shape, generator=gen, device=device).to(torch.bfloat16))
     engine.capture()
     warm = max(args.warmup, 3)
-    engine.set_call(1, ctx)
+
+    def rewind():
+        if nb == 1:
+            engine.set_call(1, ctx)
+        else:
+            engine.set_batch([1 + b for b in range(nb)], [ctx] * nb)
+
+    rewind()
     for _ in range(warm):
         engine.step()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    engine.set_call(1, ctx)
+    rewind()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -297,14 +306,15 @@ def run_tp(args, rank: int, world: int, device) -> None:
     if rank != 0:
         return
     peak, kind = measured_peaks()
-    step_bytes = engine.weight_bytes_per_token + (ctx + args.steps // 2) * 2 * 28 * (8 // world) * 128 * 2
+    step_bytes = engine.weight_bytes_per_token + nb * (ctx + args.steps // 2) * 2 * 28 * (8 // world) * 128 * 2
     print(json.dumps({
-        "metric": "llama-3.2-3b-arch decode throughput (batch 1, context 4096, tensor parallel)",
-        "value": round(args.steps / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "metric": f"llama-3.2-3b-arch decode throughput (batch {nb}, context 4096, tensor parallel)",
+        "value": round(nb * args.steps / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "configs[3]: Llama-3.2-3B architecture decode, 4096-token KV cache N(0,1), "
-                               "batch 1, tensor parallel with NCCL all-reduce", "tp": world},
+                               f"batch {nb}, tensor parallel with one exchange after o_proj and down_proj",
+                   "tp": world, "batch": nb},
         "gpu_launches": (engine.launches_per_step + (4 * 28 if world > 1 else 0)) * args.steps,
         "per_rank_roofline": {"bound": "hbm", "bytes_per_step": step_bytes,
                               "achieved": round(step_bytes / (ms / args.steps / 1e3) / 1e9, 1),
@@ -435,6 +445,8 @@ def main() -> None:
                     help="llama1b-batch64: sequences in the whole job (split over the ranks)")
     ap.add_argument("--decode-step-trace", action="store_true",
                     help="with IRON_DECODE_STEP=1: print the one-kernel step's per-phase timeline and exit")
+    ap.add_argument("--tp-batch", type=int, default=1,
+                    help="llama3b-tp: sequences decoded in lockstep (1, 2, 4, ... 32)")
     ap.add_argument("--prompt-attention", action="store_true",
                     help="time the prompt-chunk attention kernel alone (2048 x 2048 causal, the 1B head "
                          "shape; IRON_MHA_PREFILL_TC=0 for the warp-MMA kernel), print one JSON line and exit")

@@ -157,13 +157,14 @@ class LlamaEngine:
         # `batch` rows, with a dense q for the packed attention.
         if batch > 1:
             btrans = {"b.x": (batch, E), "b.h": (batch, E), "b.y": (batch, E), "b.qkv": (batch, QKV),
-                      "b.q": (batch, H * D), "b.att": (batch, H * D), "b.gate": (batch, F), "b.up": (batch, F)}
+                      "b.q": (batch, H * D), "b.att": (batch, H * D), "b.gate": (batch, F), "b.up": (batch, F),
+                      "b.part": (batch, E)}
             bsizes = {n: sizes[n] for n in residents}
             for n, shape in btrans.items():
                 bsizes[n] = int(np.prod(shape)) * 2
             bsteps = [["b.x"], ["b.x", "b.h"], ["b.h", "b.qkv"], ["b.qkv", "b.q"], ["b.q", "b.att"],
-                      ["b.att", "b.x", "b.y"], ["b.y", "b.h"], ["b.h", "b.gate"], ["b.h", "b.up"],
-                      ["b.gate", "b.up"], ["b.gate", "b.y", "b.x"], ["b.x", "b.y"]]
+                      ["b.att", "b.x", "b.y", "b.part"], ["b.y", "b.h"], ["b.h", "b.gate"], ["b.h", "b.up"],
+                      ["b.gate", "b.up"], ["b.gate", "b.y", "b.x", "b.part"], ["b.x", "b.y"]]
             spans.update(plan.place_version(bsteps, bsizes, {n: n for n in residents}))
         self.plan = plan
         self.arena = torch.empty(plan.size, dtype=torch.uint8, device=self.device)
@@ -200,6 +201,7 @@ class LlamaEngine:
             self.b_qkv, self.b_q = view("b.qkv", (batch, QKV)), view("b.q", (batch, H, D))
             self.b_att = view("b.att", (batch, H, D))
             self.b_gate, self.b_up = view("b.gate", (batch, F)), view("b.up", (batch, F))
+            self.b_part = view("b.part", (batch, E))
 
         self._load(weights, release)
         self._peer_exchange_setup()
@@ -315,8 +317,10 @@ class LlamaEngine:
 
         # plain peer loads and stores only: no multicast object is bound to the buffer
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        E = self.c.hidden_size
-        nbytes = K.tp_buffer_bytes(self.tp_size, E)
+        # one slot holds a decode step's rows: the vector of one sequence, or a few sequences'
+        # (one CTA moves a slot: larger batches take NCCL)
+        self.peer_slot_elems = self.c.hidden_size * min(self.batch, 4)
+        nbytes = K.tp_buffer_bytes(self.tp_size, self.peer_slot_elems)
         group = self.tp_group if self.tp_group is not None else dist.group.WORLD
         self._peer_mem = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
         self._peer_mem.zero_()
@@ -330,9 +334,9 @@ class LlamaEngine:
     def _reduce_add(self, part: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> None:
         """out = residual + (sum of ``part`` over the ranks): one kernel over peer memory
         for a decode step's vector, NCCL and an add otherwise."""
-        if self.peer_buffers is not None and part.numel() == self.c.hidden_size:
+        if self.peer_buffers is not None and part.numel() <= self.peer_slot_elems and part.is_contiguous():
             K.tp_allreduce(part, out, residual=residual, peer_buffers=self.peer_buffers,
-                           slot_elems=self.c.hidden_size, rank=self.tp_rank, world=self.tp_size,
+                           slot_elems=self.peer_slot_elems, rank=self.tp_rank, world=self.tp_size,
                            seq=self.peer_seq, status=self.status)
         else:
             self._all_reduce(part)
@@ -367,6 +371,7 @@ class LlamaEngine:
         H, G, D, E, V = self.H, self.G, c.head_dim, c.hidden_size, c.vocab_size
         n = self.batch
         x, h, y = self.b_x, self.b_h, self.b_y
+        tp, part = self.tp_size > 1, self.b_part
         K.copy_rows(self.embed, x, ids=self.b_tokens, nrows=n, row_bytes=E * 2, src_rows=V)
         for l in self.layers:
             K.rms_norm(x, l["ln1"], h, eps=c.eps)
@@ -374,10 +379,18 @@ class LlamaEngine:
             K.rope_kv_scatter(self.b_qkv, self.angles, self.b_q, l["k"], l["v"], self.b_pos, H=H, G=G, D=D)
             K.mha_decode(self.b_q, l["k"], l["v"], self.b_att, d_kv_valid=self.b_pos, per_batch=True,
                          kv_valid_add=1, window=c.window, scale=c.attention_scale)
-            K.gemm(self.b_att.view(n, H * D), l["wo"], y, b_col_maj=True, residual=x, status=self.status)
+            if tp:   # row-parallel: this rank's partial sums meet the others', then the residual
+                K.gemm(self.b_att.view(n, H * D), l["wo"], part, b_col_maj=True, status=self.status)
+                self._reduce_add(part, x, y)
+            else:
+                K.gemm(self.b_att.view(n, H * D), l["wo"], y, b_col_maj=True, residual=x, status=self.status)
             K.rms_norm(y, l["ln2"], h, eps=c.eps)
             K.gemm_swiglu(h, l["wg"], l["wu"], self.b_gate, status=self.status)
-            K.gemm(self.b_gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
+            if tp:
+                K.gemm(self.b_gate, l["wd"], part, b_col_maj=True, status=self.status)
+                self._reduce_add(part, y, x)
+            else:
+                K.gemm(self.b_gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
         K.rms_norm(x, self.norm, h, eps=c.eps)
         K.gemm(h, self.head, self.logits_buf, b_col_maj=True, status=self.status)
         if self.draws is None:

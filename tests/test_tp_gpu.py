@@ -41,6 +41,25 @@ def _work(rank: int, size: int, out):
     drawn = tp.complete(prompt, 5)
     logits.append(tp.logits())
     torch.cuda.synchronize()
+    # a batch of sequences, tensor parallel: four prompts of different lengths, then three steps each
+    prompts = [np.random.default_rng(20 + b).integers(0, 1024, 5 + 3 * b) for b in range(4)]
+
+    def batched(engine):
+        firsts = []
+        for b, pr in enumerate(prompts):
+            engine.prefill(pr, seq=b)
+            firsts.append(int(engine.drawn[b, len(pr) - 1].item()))
+        return engine.generate_batch(firsts, [len(pr) for pr in prompts], 3).tolist(), engine.logits_batch()
+
+    tpb = LlamaEngine(toy_config(), weights, device=f"cuda:{rank}", kv_len_hint=64, batch=4, tp_rank=rank, tp_size=size)
+    b_drawn, b_logits = batched(tpb)
+    torch.cuda.synchronize()
+    if rank == 0:
+        oneb = LlamaEngine(toy_config(), weights, device="cuda:0", kv_len_hint=64, batch=4)
+        want_b_drawn, want_b_logits = batched(oneb)
+        assert b_drawn == want_b_drawn, (b_drawn, want_b_drawn)
+        assert float(np.abs(b_logits - want_b_logits).max() / np.abs(want_b_logits).max()) <= 0.02
+        tpb.check()
     if rank == 0:
         one = LlamaEngine(toy_config(), weights, device="cuda:0", kv_len_hint=64)
         want = [one.prefill(prompt)]
