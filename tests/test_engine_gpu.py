@@ -152,3 +152,33 @@ def test_prompt_rows_outside_the_caches_are_refused(case):
         engine.prefill_chunk([1, 5000], 0)
     with pytest.raises(ValueError):
         engine.prefill_chunk([], 0)
+
+
+def test_a_sliding_window_config_matches_the_host_graph_in_prompt_and_decode():
+    """``sliding_window`` in the config bounds every layer's attention (iron/lm/blocks.py:504-529):
+    the engine's prompt chunk (160 tokens: the tcgen05 attention with a window) and its decode
+    steps against the host path, every recorded operator's numpy reference."""
+    import dataclasses as dc
+
+    from iron_b200.applications.llama.model import Llama
+    from iron_b200.lm.engine import LlamaEngine
+
+    config = dc.replace(toy_config(), sliding_window=48)
+    assert config.window == 47
+    weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
+    prompt = np.random.default_rng(12).integers(0, 1024, 160)
+    engine = LlamaEngine(config, weights, kv_len_hint=200)
+    host = Llama(config, weights)
+    got = engine.prefill(prompt)
+    want = host.reference_logits(prompt, 0)
+    close_to_oracle(got, want, "windowed prompt")
+    # the window matters: the same prompt without it gives other logits
+    full = LlamaEngine(toy_config(), weights, kv_len_hint=200).prefill(prompt)
+    assert np.abs(full - got).max() > 0.05 * np.abs(got).max()
+    tokens = list(prompt)
+    for step in range(3):
+        nxt = int(np.argmax(want))
+        got = engine.feed([nxt], len(tokens))
+        want = host.reference_logits([nxt], len(tokens))
+        tokens.append(nxt)
+        close_to_oracle(got, want, f"windowed decode step {step}")
