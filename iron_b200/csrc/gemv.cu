@@ -43,7 +43,6 @@ struct GemvParams {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kUnroll = 2;         // 256-bit loads per row per work item (4 for 128-bit loads)
 
 template <int MODE>
 __device__ __forceinline__ void pair_rows(const GemvParams& p, const __nv_bfloat16* A, int pair, int half,

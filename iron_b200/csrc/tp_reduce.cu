@@ -50,11 +50,9 @@ __device__ __forceinline__ unsigned long long tp_ns() {
 }
 
 __global__ void __launch_bounds__(512) tp_allreduce_kernel(const TpParams p) {
-  __shared__ int s_abort;
   pdl_wait();
   pdl_launch();
   const int tid = threadIdx.x;
-  if (tid == 0) s_abort = 0;
   const unsigned int seq = *p.d_seq;
   const unsigned int par = seq & 1u;
   const int n8 = p.n >> 3;
@@ -80,7 +78,6 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const TpParams p) {
         if ((int)(tp_ld_acquire_sys(flag) - (seq + 1u)) >= 0) break;
         if ((it & 63u) == 0 && tp_ns() - t0 > kTpWaitNs) {
           if (p.status) *reinterpret_cast<volatile int*>(p.status) = IRON_ERR_TIMEOUT;
-          s_abort = 1;
           break;
         }
       }
