@@ -125,13 +125,17 @@ def time_prefill(engine, tokens, reps: int = 3) -> dict:
 
     c = engine.c
     engine.prefill(tokens)  # warm-up (module load, tensor-map encode paths)
-    times = []
+    times, device_ms = [], []
     for _ in range(reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
+        start.record()
         engine.prefill_chunk(tokens, 0)
+        stop.record()
         first = int(engine.values[0:1].cpu()[0])
         times.append(time.perf_counter() - t0)
+        device_ms.append(start.elapsed_time(stop))
     ttft = min(times)
     n = len(tokens)
     E, F, V = c.hidden_size, c.intermediate_size, c.vocab_size
@@ -141,7 +145,7 @@ def time_prefill(engine, tokens, reps: int = 3) -> dict:
     flops = linear + attn + 2 * V * E
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
-    return {"ttft_ms": round(ttft * 1e3, 3), "tokens": n, "first_token": first,
+    return {"ttft_ms": round(ttft * 1e3, 3), "device_ms": round(min(device_ms), 3), "tokens": n, "first_token": first,
             "tflops": round(flops / ttft / 1e12, 1), "peak_tflops": peak,
             "frac": round(flops / ttft / 1e12 / peak, 4),
             "launches": engine.launches_per_chunk}
