@@ -234,6 +234,19 @@ int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
                    const int* d_valid_rows, int valid_k, int epilogue, const void* residual,
                    int out_f32, int* d_status, iron_stream_t stream);
 
+/* The fused q/k/v projection of a prompt chunk with RoPE and the cache write in its output
+ * stage -- iron/lm/blocks.py:472-499 records a ProjectionGEMM, RoPE steps on q and k and the
+ * bounded cache copies; here rows [0, valid_rows) of A (M, K) times Wqkv ((H + 2G) D, K)^T,
+ * each output rounded to bf16, then per head: q rotated into qkv (rows ldc apart), k rotated
+ * into k_cache[start + row], v copied into v_cache[start + row] (caches (S, G, D)), with the
+ * angle row angle_start + row and the roundings of iron_rope_kv_write_bf16, bit for bit.
+ * Returns IRON_ERR_UNSUPPORTED for shapes the CTA-pair GEMM does not take (one row tile):
+ * the caller then runs iron_gemm_bf16 and iron_rope_kv_write_bf16.  D is 64 or 128. */
+int iron_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int M, int K, int lda, int ldb,
+                            int ldc, int valid_rows, const void* angles, void* k_cache, void* v_cache,
+                            int H, int G, int D, int start, int angle_start, int* d_status,
+                            iron_stream_t stream);
+
 /* Gate/up projection with SwiGLU for a block of rows -- the chain ProjectionGEMM,
  * ProjectionGEMM, SiLU, ElementwiseMul that `GatedMLP.body` records for a prompt chunk
  * (iron/lm/blocks.py:697-699) in one pass over both weight matrices:

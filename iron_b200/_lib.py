@@ -82,6 +82,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "iron_selective_scan_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "iron_causal_conv1d_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P]),
+    "iron_gemm_qkv_rope_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "iron_sample_k_max": (_I, []),
     "iron_sample_rows_bf16": (_I, [_P, _L, _I, _I, _P, _P, _P, _P, _I, _P]),
     "iron_mha_prefill_status_word": (None, [_P]),

@@ -53,6 +53,12 @@ struct GemmParams {
   int b_n_major;        // B is (K, N) row-major
   int dual;             // two (N, K) weight matrices: C = bf16(silu(bf16(A W1^T))) * bf16(A W2^T)
   int* status;          // optional device word: receives IRON_ERR_TIMEOUT
+  // The fused q/k/v projection of a prompt chunk (pair form only): RoPE in the output stage,
+  // q to C, k and v straight into the caches at row rope_start + row.
+  const __nv_bfloat16* rope_angles;
+  __nv_bfloat16* rope_k;
+  __nv_bfloat16* rope_v;
+  int rope_H, rope_G, rope_D, rope_start, rope_angle_start;
 };
 
 // Instruction descriptor for kind::f16: bf16 x bf16 -> f32, A K-major.
@@ -622,6 +628,61 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tcgen05_fence_after();
       const int row = m0 + group * 32 + lane;
       const bool row_live = row < valid;
+      if (p.rope_angles) {
+        // A tile holds whole heads (BNO % D == 0).  Per head and per run of 32 rotation pairs:
+        // element i and element i + D/2, rounded to bf16 as the projection's output is, then
+        // turned with the products and the sum each rounded once -- the arithmetic of the
+        // separate RoPE kernel -- and stored where that kernel stores them.
+        const int D = p.rope_D, half = D >> 1, H = p.rope_H, G = p.rope_G;
+        const uint32_t t_row = tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairAccStride;
+#pragma unroll 1
+        for (int hl = 0; hl < BNO / D; ++hl) {
+          const int hh = n0 / D + hl;
+          if (hh >= H + 2 * G) break;
+#pragma unroll 1
+          for (int s = 0; s < half / 32; ++s) {
+            uint32_t ra[32], rb[32];
+            tmem_ld32(t_row + hl * D + s * 32, ra);
+            tmem_ld32(t_row + hl * D + half + s * 32, rb);
+            tmem_ld_wait();
+            if (!row_live) continue;
+            float a[32], b[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              a[j] = round_bf16(__uint_as_float(ra[j]));
+              b[j] = round_bf16(__uint_as_float(rb[j]));
+            }
+            if (hh < H + G) {
+              const __nv_bfloat16* ar = p.rope_angles + (size_t)(p.rope_angle_start + row) * D + 2 * (s * 32);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float cs[16];
+                unpack8(ld_cached(ar + q * 16), cs);
+                unpack8(ld_cached(ar + q * 16 + 8), cs + 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float c = cs[2 * j], sn = cs[2 * j + 1];
+                  const float x = a[q * 8 + j], y = b[q * 8 + j];
+                  a[q * 8 + j] = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, sn));
+                  b[q * 8 + j] = __fadd_rn(__fmul_rn(y, c), __fmul_rn(x, sn));
+                }
+              }
+            }
+            __nv_bfloat16* dst;
+            if (hh < H) dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + (size_t)hh * D;
+            else if (hh < H + G) dst = p.rope_k + ((size_t)(p.rope_start + row) * G + (hh - H)) * D;
+            else dst = p.rope_v + ((size_t)(p.rope_start + row) * G + (hh - H - G)) * D;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              reinterpret_cast<uint4*>(dst + s * 32)[q] = pack8(a + q * 8);
+              reinterpret_cast<uint4*>(dst + half + s * 32)[q] = pack8(b + q * 8);
+            }
+          }
+        }
+        tcgen05_fence_before();
+        mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + acc), 0));
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BNO / 32; ++c) {
         uint32_t r[32];
@@ -842,6 +903,36 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (bn == 256) return launch_gemm<256>(ma, mb, mb, p, max_rows, s);
   if (bn == 128) return launch_gemm<128>(ma, mb, mb, p, max_rows, s);
   return launch_gemm<64>(ma, mb, mb, p, max_rows, s);
+}
+
+extern "C" int iron_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int M, int K, int lda, int ldb,
+                                       int ldc, int valid_rows, const void* angles, void* k_cache, void* v_cache,
+                                       int H, int G, int D, int start, int angle_start, int* d_status,
+                                       iron_stream_t stream) {
+  if (M <= 0 || K <= 0 || H <= 0 || G <= 0 || (D != 64 && D != 128)) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > M || start < 0 || angle_start < 0) return IRON_ERR_SHAPE;
+  const int N = (H + 2 * G) * D;
+  if (!aligned16(A) || !aligned16(Wqkv) || !aligned16(qkv) || !aligned16(angles) || !aligned16(k_cache) ||
+      !aligned16(v_cache))
+    return IRON_ERR_ALIGN;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7)) return IRON_ERR_ALIGN;
+  if (lda < K || ldb < K || ldc < N) return IRON_ERR_SHAPE;
+  // the pair form only, with tiles of whole heads; the caller runs the two kernels otherwise
+  if (valid_rows <= BM || !pair_enabled()) return IRON_ERR_UNSUPPORTED;
+  const long long mt2 = (valid_rows + 2 * BM - 1) / (2 * BM);
+  auto cost = [&](int bn_) { return ((mt2 * ((N + bn_ - 1) / bn_) + kSMs / 2 - 1) / (kSMs / 2)) * bn_; };
+  const int pbn = (D == 64 && cost(192) * 8 < cost(256) * 7) ? 192 : 256;
+  CUtensorMap ma, mh;
+  if (!make_map(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM) ||
+      !make_map(&mh, Wqkv, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, pbn / 2))
+    return IRON_ERR_LAUNCH;
+  GemmParams p = {};
+  p.C = qkv; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.valid = valid_rows; p.status = d_status;
+  p.rope_angles = (const __nv_bfloat16*)angles; p.rope_k = (__nv_bfloat16*)k_cache; p.rope_v = (__nv_bfloat16*)v_cache;
+  p.rope_H = H; p.rope_G = G; p.rope_D = D; p.rope_start = start; p.rope_angle_start = angle_start;
+  cudaStream_t s = (cudaStream_t)stream;
+  return pbn == 192 ? launch_gemm_pair<192>(ma, mh, mh, p, valid_rows, s)
+                    : launch_gemm_pair<256>(ma, mh, mh, p, valid_rows, s);
 }
 
 extern "C" int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* C, int M, int N, int K,

@@ -328,6 +328,22 @@ def rope_kv_write(qkv, angles, k_cache, v_cache, *, rows, H, G, D, start=0, angl
     return qkv
 
 
+def gemm_qkv_rope(x, wqkv, qkv, angles, k_cache, v_cache, *, H, G, D, start=0, angle_start=None, status=None) -> bool:
+    """The fused q/k/v projection of a prompt chunk: ``x @ wqkv.T`` with RoPE and the cache
+    write in the GEMM's output stage (q into ``qkv``, k and v into the caches at ``start``).
+    Returns False, having launched nothing, for shapes only the two separate kernels take."""
+    _bf16(x, wqkv, qkv, angles, k_cache, v_cache)
+    rc = _lib.load().iron_gemm_qkv_rope_bf16(
+        _ptr(x), _ptr(wqkv), _ptr(qkv), x.shape[0], x.shape[1], x.stride(0), wqkv.stride(0), qkv.stride(0),
+        x.shape[0], _ptr(angles), _ptr(k_cache), _ptr(v_cache), H, G, D, int(start),
+        int(start if angle_start is None else angle_start), _ptr(status), _stream())
+    if rc == -4:
+        return False
+    if rc != 0:
+        raise _lib.IronError("iron_gemm_qkv_rope_bf16", rc)
+    return True
+
+
 def selective_scan(xbc, dt, head, state=None, *, heads, head_dim, state_size, groups=1, valid=None,
                    d_valid=None, want_final=True):
     """Mamba2's recurrence; returns ``(y bf16, final f32)``.  A leading batch axis is optional."""

@@ -208,6 +208,8 @@ class LlamaEngine:
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
         self.draws = None   # (batch, S, 4) int32 draw rows once a sampler is set
+        self.fuse_rope = os.environ.get("IRON_PREFILL_FUSED_ROPE", "1") != "0"
+        self._chunk_launches: int | None = None
         self.step_ws = K.decode_step_workspace(E, H, G, D, self.device)
         self.step_table = K.decode_step_table(
             [dict(l, k=l["k"][0], v=l["v"][0]) for l in self.layers], self.device)
@@ -488,8 +490,14 @@ class LlamaEngine:
     # ------------------------------------------------------------------ prompt chunk
     @property
     def launches_per_chunk(self) -> int:
-        """Kernels one prompt chunk launches: gather, nine per layer, row pick, head, draw."""
-        return 1 + 9 * self.c.num_hidden_layers + 3
+        """Kernels the last prompt chunk launched (a full chunk's count before any ran): gather,
+        per layer two norms, the q/k/v projection (with RoPE and the cache write in its output
+        stage, or followed by the RoPE kernel), attention, o_proj, the gated gate/up GEMM and
+        down_proj, then row pick, head and draw; tensor-parallel chunks add two adds a layer."""
+        if self._chunk_launches is not None:
+            return self._chunk_launches
+        per_layer = 7 + (0 if self.fuse_rope else 1) + (2 if self.tp_size > 1 else 0)
+        return 1 + per_layer * self.c.num_hidden_layers + 3
 
     def prefill_chunk(self, tokens, start: int, seq: int = 0) -> None:
         """Run one prompt chunk (at most ``prefill_chunk`` tokens) at positions ``start...``.
@@ -523,10 +531,16 @@ class LlamaEngine:
         x, h, y = self.p_x[:n], self.p_h[:n], self.p_y[:n]
         qkv, att, gate, up = self.p_qkv[:n], self.p_att[:n], self.p_gate[:n], self.p_up[:n]
         K.copy_rows(self.embed, x, ids=self.p_ids, nrows=n, row_bytes=E * 2, src_rows=c.vocab_size)
+        launches = 4 + (7 + (2 if tp else 0)) * len(self.layers)
         for l in self.layers:
             K.rms_norm(x, l["ln1"], h, eps=c.eps)
-            K.gemm(h, l["wqkv"], qkv, b_col_maj=True, status=self.status)
-            K.rope_kv_write(qkv, self.angles, l["k"][seq], l["v"][seq], rows=n, H=H, G=G, D=D, start=start)
+            # one launch where the CTA-pair GEMM takes the shape (RoPE and the cache write in its
+            # output stage), the projection and the RoPE kernel otherwise
+            if not (self.fuse_rope and K.gemm_qkv_rope(h, l["wqkv"], qkv, self.angles, l["k"][seq], l["v"][seq],
+                                                       H=H, G=G, D=D, start=start, status=self.status)):
+                launches += 1
+                K.gemm(h, l["wqkv"], qkv, b_col_maj=True, status=self.status)
+                K.rope_kv_write(qkv, self.angles, l["k"][seq], l["v"][seq], rows=n, H=H, G=G, D=D, start=start)
             K.mha_prefill(qkv.view(n, H + 2 * G, D)[:, :H], l["k"][seq], l["v"][seq], att.view(n, H, D),
                           q_tokens=n, kv_tokens=start + n, window=c.window, scale=c.attention_scale,
                           q_row_stride=qkv.stride(0))
@@ -549,6 +563,7 @@ class LlamaEngine:
         K.gemv(self.head, last, self.logits_buf[seq], norm_weight=self.norm, eps=c.eps)
         self.set_call(0, start + n - 1)
         self._draw(seq, self.values[0:1], self.values[1:2])
+        self._chunk_launches = launches
 
     def prefill(self, tokens, start: int = 0, seq: int = 0) -> np.ndarray:
         """Run a prompt of any length in chunks from ``start``; the logits after its last token."""

@@ -149,3 +149,35 @@ def test_gated_two_weight_form_matches_the_chain_of_references(K, M, N, Kd):
     else:
         d = np.abs(got.astype(np.float64) - chain.astype(np.float64))
         assert same.mean() >= 0.99 and (d <= 2 ** -6 * np.abs(chain.astype(np.float64)) + 2e-2).all()
+
+
+@pytest.mark.parametrize("rows,H,G,D,Kd,start", [(512, 16, 4, 64, 512, 0), (300, 8, 2, 64, 264, 37),
+                                                 (256, 6, 2, 128, 256, 5), (2048, 32, 8, 64, 2048, 0)])
+def test_the_fused_qkv_projection_equals_the_projection_then_the_rope_kernel_bit_for_bit(K, rows, H, G, D, Kd, start):
+    import torch
+
+    from oracle.model import rope_angles
+
+    rng = np.random.default_rng(rows + D)
+    S = start + rows + 3
+    x = to_torch(normal(rng, (rows, Kd), 1.0))
+    w = to_torch(normal(rng, ((H + 2 * G) * D, Kd), 1 / np.sqrt(Kd)))
+    angles = to_torch(rope_angles(D, S, 500000.0).astype(np.float32)).to(torch.bfloat16)
+    N = (H + 2 * G) * D
+
+    def caches():
+        return (torch.full((S, G, D), 3.0, dtype=torch.bfloat16, device="cuda"),
+                torch.full((S, G, D), 3.0, dtype=torch.bfloat16, device="cuda"))
+
+    k0, v0 = caches()
+    qkv0 = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    K.gemm(x, w, qkv0, b_col_maj=True)
+    K.rope_kv_write(qkv0, angles, k0, v0, rows=rows, H=H, G=G, D=D, start=start)
+    k1, v1 = caches()
+    qkv1 = torch.zeros(rows, N, dtype=torch.bfloat16, device="cuda")
+    assert K.gemm_qkv_rope(x, w, qkv1, angles, k1, v1, H=H, G=G, D=D, start=start)
+    bits = lambda t: to_numpy(t).view(np.uint16)
+    assert np.array_equal(bits(qkv1[:, : H * D]), bits(qkv0[:, : H * D]))       # the rotated queries
+    assert np.array_equal(bits(k1), bits(k0)) and np.array_equal(bits(v1), bits(v0))   # rows outside stay 3.0
+    # one row tile is not the pair GEMM's: nothing is launched and the caller is told
+    assert not K.gemm_qkv_rope(x[:64], w, qkv1[:64], angles, k1, v1, H=H, G=G, D=D, start=start)
