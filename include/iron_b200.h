@@ -90,13 +90,18 @@ int iron_gemv_swiglu_bf16(const void* Wg, const void* Wu, const void* x, void* y
  * Wqkv is ((H + 2G) * D, K): q rows, then k rows, then v rows.  angles is the packed
  * RoPE table (positions, D) with cos at even and sin at odd columns
  * (iron/operators/rope.py:58); the row used is `position`.  q_out is (H, D);
- * k_cache and v_cache are (max_seq, G, D) and row `position` of each is written.
+ * k_cache and v_cache are (cache_rows, G, D) and row `position` of each is written;
+ * `angles` has at least cache_rows rows.  A position given on the device (d_position) is
+ * held inside 0 .. cache_rows - 1, so a replay past the end of the caches cannot write
+ * outside them; an immediate position outside that range is refused (IRON_ERR_SHAPE) --
+ * the reference refuses an out-of-range per-call index before any dispatch
+ * (iron/common/graph/compiled.py:972-1001).
  */
 int iron_decode_qkv_rope_bf16(const void* Wqkv, const void* x, int K, int norm_mode,
                               const void* norm_weight, float eps, const void* angles,
                               int position, const int* d_position, void* q_out,
                               void* k_cache, void* v_cache, int H, int G, int D,
-                              iron_stream_t stream);
+                              int cache_rows, iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Row-wise and element-wise kernels.
@@ -189,10 +194,13 @@ int iron_copy_rows(const void* src, void* dst, const int* ids, int nrows,
  * iron/lm/causal.py:340-347; when carry_token / carry_position are non-NULL the id is
  * also stored there and *carry_position is incremented afterwards, which is how a
  * captured decode loop carries (token, position + 1) to its next replay
- * (iron/lm/causal.py:348). */
+ * (iron/lm/causal.py:348).  out_rows > 0 is the length of token_out: an index outside
+ * 0 .. out_rows - 1 writes nothing and *carry_position stops growing at out_rows, so a
+ * loop replayed past the end of its caches stays inside its buffers; out_rows <= 0 means
+ * no bound. */
 size_t iron_argmax_workspace_bytes(int n);
 int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out_index,
-                     int* carry_token, int* carry_position, void* workspace,
+                     int out_rows, int* carry_token, int* carry_position, void* workspace,
                      iron_stream_t stream);
 
 /* The same greedy draw for callers that cannot give the library a workspace.  It has no

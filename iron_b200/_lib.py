@@ -45,7 +45,7 @@ SIGNATURES: dict[str, tuple] = {
     "iron_gemv_swiglu_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _F, _P]),
     "iron_decode_qkv_rope_bf16": (
         _I,
-        [_P, _P, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+        [_P, _P, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     ),
     "iron_gemm_bf16": (
         _I,
@@ -61,7 +61,7 @@ SIGNATURES: dict[str, tuple] = {
     "iron_layernorm_bf16": (_I, [_P, _P, _P, _I, _I, _F, _I, _P, _P]),
     "iron_copy_rows": (_I, [_P, _P, _P, _I, _P, _L, _L, _L, _I, _I, _P, _I, _P, _P]),
     "iron_argmax_workspace_bytes": (_Z, [_I]),
-    "iron_argmax_bf16": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
+    "iron_argmax_bf16": (_I, [_P, _I, _P, _P, _I, _P, _P, _P, _P]),
     "iron_argmax_noalloc_max_n": (_I, []),
     "iron_argmax_bf16_noalloc": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "iron_tp_buffer_bytes": (_Z, [_I, _I]),

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/iron_b200.h"
 
 namespace iron {
@@ -142,5 +144,26 @@ inline int check_launch() {
   return e == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The current device's ordinal when it is below 64, else -1.
+static inline int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  return dev;
+}
+
+// Something done once per device (a kernel's dynamic-shared-memory limit is a per-device
+// attribute): one bit per device ordinal, safe to race on from several host threads.
+struct DeviceOnce {
+  std::atomic<unsigned long long> bits{0};
+  bool done() const {
+    const int dev = current_device();
+    return dev >= 0 && ((bits.load(std::memory_order_acquire) >> dev) & 1ull);
+  }
+  void mark() {
+    const int dev = current_device();
+    if (dev >= 0) bits.fetch_or(1ull << dev, std::memory_order_release);
+  }
+};
 
 }  // namespace iron

@@ -108,7 +108,8 @@ __device__ __forceinline__ void output_chunk(const GemmParams& p, float* v, int 
   if (!p.c_transposed) {
     const size_t off = (size_t)row * p.ldc + col0;
     if (p.residual) {
-      if (full_chunk) {
+      // 16-byte loads need every row of the residual to start on an 8-element boundary
+      if (full_chunk && (p.ldc & 7) == 0) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           float f[8];
@@ -755,12 +756,12 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const GemmParams& p,
                        int max_rows, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmem) != cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   const int bno = p.dual ? BN / 2 : BN;
   const int tiles = ((max_rows + BM - 1) / BM) * ((p.N + bno - 1) / bno);
@@ -779,12 +780,12 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
 static int launch_gemm_split(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles,
                              int splits, cudaStream_t stream) {
   using Cfg = GemmCfg<64, true>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmem) != cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * splits);
@@ -810,12 +811,12 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
                             const GemmParams& p, int max_rows, cudaStream_t stream) {
   constexpr int kPairBN = PBN;
   constexpr int kPairSmem = PairCfg<PBN>::kSmem;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(gemm_pair_kernel<PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
         cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   const int bno = p.dual ? kPairBN / 2 : kPairBN;
   const int tiles = ((max_rows + 2 * BM - 1) / (2 * BM)) * ((p.N + bno - 1) / bno);
@@ -855,6 +856,8 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (out_f32 && epilogue != EPI_NONE) return IRON_ERR_UNSUPPORTED;
   // TMA: 16-byte aligned bases and row pitches
   if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return IRON_ERR_ALIGN;
+  // the residual shares C's pitch; its rows are read 16 bytes at a time when that pitch allows
+  if (residual && !aligned16(residual)) return IRON_ERR_ALIGN;
   if ((lda & 7) || (ldb & 7)) return IRON_ERR_ALIGN;
   if (lda < K || ldb < (b_col_maj ? K : N) || ldc < (c_col_maj ? M : N)) return IRON_ERR_SHAPE;
   if (valid_rows == 0 && !d_valid_rows) return IRON_OK;

@@ -38,6 +38,7 @@ struct GemvParams {
   __nv_bfloat16* v_cache;
   const int* d_position;
   int position, H, G, D;
+  int cache_rows;             // rows of the caches and of the angle table: the position is held below it
   PrefetchHint hint;          // weights a later kernel will stream (may be empty)
 };
 
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         const float act = round_bf16(silu_f32(gate));
         p.y[ra] = __float2bfloat16_rn(__fmul_rn(act, up));
       } else {
-        const int pos = p.d_position ? *p.d_position : p.position;
+        const int pos = min(max(p.d_position ? *p.d_position : p.position, 0), p.cache_rows - 1);
         const int head = ra / p.D, i = ra - head * p.D;
         float x1 = round_bf16(acc0), x2 = round_bf16(acc1);
         if (head < p.H + p.G) {
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
         p.y[ra] = __float2bfloat16_rn(__fmul_rn(act, up));
       } else {
         const int half = p.D >> 1;
-        const int pos = p.d_position ? *p.d_position : p.position;
+        const int pos = min(max(p.d_position ? *p.d_position : p.position, 0), p.cache_rows - 1);
         const int head = ra / p.D, i = ra - head * p.D;
         float x1 = round_bf16(acc0), x2 = round_bf16(acc1);
         if (head < p.H + p.G) {
@@ -491,13 +492,13 @@ static int ring_policy() {
 
 template <int MODE>
 static int launch_ring(const GemvParams& p, int units, cudaStream_t stream) {
-  static bool configured = false;
+  static DeviceOnce configured;   // the attribute is per device
   constexpr size_t smem = kRingBytes + (size_t)kRingMaxK * 2 + kRingWarps * kRingSlots * 8 + 32 * sizeof(float);
-  if (!configured) {
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(gemv_ring_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   // as many warps per CTA as split the units most evenly over the grid
   int best_w = kRingWarps;
@@ -521,13 +522,13 @@ static int launch_ring(const GemvParams& p, int units, cudaStream_t stream) {
 
 template <int MODE, bool WIDE>
 static int launch_gemv_w(GemvParams& p, int npairs, int batches, cudaStream_t stream) {
-  static bool configured = false;
+  static DeviceOnce configured;   // the attribute is per device
   constexpr int kMaxSmem = 100 * 1024;
-  if (!configured) {
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(gemv_kernel<MODE, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kMaxSmem) != cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   const int nch = p.K >> 3;
   constexpr int kStep = 32 * kItem;
@@ -643,14 +644,14 @@ extern "C" int iron_decode_qkv_rope_bf16(const void* Wqkv, const void* x, int K,
                                          const void* norm_weight, float eps, const void* angles,
                                          int position, const int* d_position, void* q_out,
                                          void* k_cache, void* v_cache, int H, int G, int D,
-                                         iron_stream_t stream) {
-  if (H <= 0 || G <= 0 || D <= 0 || (D & 15)) return IRON_ERR_SHAPE;
+                                         int cache_rows, iron_stream_t stream) {
+  if (H <= 0 || G <= 0 || D <= 0 || (D & 15) || cache_rows <= 0) return IRON_ERR_SHAPE;
   const int M = (H + 2 * G) * D;
   int rc = check_common(Wqkv, x, q_out, M, K);
   if (rc) return rc;
   if (!angles || !k_cache || !v_cache) return IRON_ERR_SHAPE;
   if (norm_mode < 0 || norm_mode > 2 || (norm_mode == 2 && !norm_weight)) return IRON_ERR_SHAPE;
-  if (!d_position && position < 0) return IRON_ERR_SHAPE;
+  if (!d_position && (position < 0 || position >= cache_rows)) return IRON_ERR_SHAPE;
   GemvParams p = {};
   p.A = (const __nv_bfloat16*)Wqkv; p.x = (const __nv_bfloat16*)x; p.y = (__nv_bfloat16*)q_out;
   p.norm_w = (const __nv_bfloat16*)norm_weight;
@@ -658,5 +659,6 @@ extern "C" int iron_decode_qkv_rope_bf16(const void* Wqkv, const void* x, int K,
   p.angles = (const __nv_bfloat16*)angles;
   p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
   p.d_position = d_position; p.position = position; p.H = H; p.G = G; p.D = D;
+  p.cache_rows = cache_rows;
   return launch_gemv<GEMV_QKV>(p, M / 2, 1, (cudaStream_t)stream);
 }

@@ -250,12 +250,12 @@ static int launch_decode_tc(const DecodeTcParams& p, int batch, cudaStream_t str
   constexpr int kTiles = 16 * D * 2 + 4 * kDtKeys * D * 2;
   constexpr int kMerge = 4 * 16 * (D + 2) * 4;
   constexpr int kSmem = kTiles > kMerge ? kTiles : kMerge;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(mha_decode_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
         cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.G, batch, 1);

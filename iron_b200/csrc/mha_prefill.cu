@@ -314,12 +314,12 @@ __global__ void __launch_bounds__(kPfThreads) mha_prefill_kernel(const PrefillPa
 template <int D, int MT>
 static int launch_prefill(const PrefillParams& p, int batch, cudaStream_t stream) {
   constexpr int kSmem = (MT + 4) * kBlockN * D * 2;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
     if (cudaFuncSetAttribute(mha_prefill_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
         cudaSuccess)
       return IRON_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.H, (p.q_rows + kBlockM * MT - 1) / (kBlockM * MT), batch);
@@ -342,9 +342,12 @@ int mha_prefill_tc(const void* Q, const void* K, const void* V, void* O, int bat
 
 using namespace iron;
 
-static int* g_prefill_status = nullptr;
+static int* g_prefill_status[64] = {};   // one status word per device
 
-extern "C" void iron_mha_prefill_status_word(int* d_status) { g_prefill_status = d_status; }
+extern "C" void iron_mha_prefill_status_word(int* d_status) {
+  const int dev = current_device();
+  if (dev >= 0) g_prefill_status[dev] = d_status;
+}
 
 extern "C" int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V, void* O, int batch, int H,
                                      int G, int D, int q_rows, int kv_rows, long long q_batch_stride,
@@ -383,7 +386,7 @@ extern "C" int iron_mha_prefill_bf16(const void* Q, const void* K, const void* V
     if (!(e && e[0] == '0')) {
       const int rc = mha_prefill_tc(Q, K, V, O, batch, H, G, D, q_rows, q_batch_stride, q_row_stride, q_head_stride,
                                     o_batch_stride, o_row_stride, o_head_stride, kv_batch_stride, kv_row_stride,
-                                    kv_head_stride, q_tokens, kv_tokens, causal, window, scale, g_prefill_status, s);
+                                    kv_head_stride, q_tokens, kv_tokens, causal, window, scale, current_device() >= 0 ? g_prefill_status[current_device()] : nullptr, s);
       if (rc != IRON_ERR_UNSUPPORTED) return rc;
     }
   }

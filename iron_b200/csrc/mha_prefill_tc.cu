@@ -572,15 +572,15 @@ template <int D>
 static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                              const PrefillTcParams& p, int batch, cudaStream_t stream) {
   using Cfg = TcCfg<D>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
     const cudaError_t e =
         cudaFuncSetAttribute(mha_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
     if (e != cudaSuccess) {
       if (getenv("IRON_DEBUG")) fprintf(stderr, "mha_prefill_tc<%d> smem %d: %s\n", D, Cfg::kSmem, cudaGetErrorString(e));
       return IRON_ERR_LAUNCH;
     }
-    configured = true;
+    configured.mark();
   }
   cudaLaunchConfig_t cfg = {};
   const int items = ((p.q_tokens + kTcM - 1) / kTcM) * p.H * batch;

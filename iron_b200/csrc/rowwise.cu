@@ -325,7 +325,7 @@ constexpr int kArgmaxBlocks = kSMs * 2;
 // workspace layout: [0] u32 arrival counter, [8 ..] u64 partial keys per block
 __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int n,
                                                      int* token_out, const int* d_out_index,
-                                                     int* carry_token, int* carry_position,
+                                                     int out_rows, int* carry_token, int* carry_position,
                                                      unsigned long long* workspace) {
   __shared__ unsigned long long sred[8];
   __shared__ bool last;
@@ -367,9 +367,12 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __rest
     if (threadIdx.x == 0) {
       for (int w = 1; w < 8; ++w) b = umax64(b, sred[w]);
       const int tok = (int)(~(uint32_t)(b & 0xffffffffull));
-      token_out[d_out_index ? *d_out_index : 0] = tok;
+      // out_rows > 0 bounds the row written and stops the carried position at out_rows: a
+      // replay past the end of the caches writes nothing outside them
+      const int at = d_out_index ? *d_out_index : 0;
+      if (out_rows <= 0 || (at >= 0 && at < out_rows)) token_out[at] = tok;
       if (carry_token) *carry_token = tok;
-      if (carry_position) *carry_position += 1;
+      if (carry_position && (out_rows <= 0 || *carry_position < out_rows)) *carry_position += 1;
       *counter = 0;  // leave the workspace ready for the next launch
     }
   }
@@ -528,14 +531,14 @@ extern "C" size_t iron_argmax_workspace_bytes(int n) {
 }
 
 extern "C" int iron_argmax_bf16(const void* logits, int n, int* token_out,
-                                const int* d_out_index, int* carry_token, int* carry_position,
-                                void* workspace, iron_stream_t stream) {
+                                const int* d_out_index, int out_rows, int* carry_token,
+                                int* carry_position, void* workspace, iron_stream_t stream) {
   if (n <= 0 || !token_out || !workspace) return IRON_ERR_SHAPE;
   if (!aligned16(logits) || (reinterpret_cast<uintptr_t>(workspace) & 7)) return IRON_ERR_ALIGN;
   int grid = (n / 8 + 255) / 256;
   grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
   return launch_pdl(argmax_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
-                    (const __nv_bfloat16*)logits, n, token_out, d_out_index, carry_token,
+                    (const __nv_bfloat16*)logits, n, token_out, d_out_index, out_rows, carry_token,
                     carry_position, (unsigned long long*)workspace);
 }
 
@@ -568,7 +571,7 @@ static __device__ __align__(256) unsigned long long g_argmax_scratch[1 + iron::k
 namespace {
 constexpr int kNoAllocMaxN = 1 << 22;  // logits per call this entry point accepts
 constexpr int kMaxDevices = 64;
-unsigned long long* g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+std::atomic<unsigned long long*> g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
 }  // namespace
 
 extern "C" int iron_argmax_noalloc_max_n(void) { return kNoAllocMaxN; }
@@ -580,19 +583,19 @@ extern "C" int iron_argmax_bf16_noalloc(const void* logits, int n, int* token_ou
   if (!aligned16(logits)) return IRON_ERR_ALIGN;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return IRON_ERR_LAUNCH;
-  if (!g_scratch_ptr[dev]) {
+  if (!g_scratch_ptr[dev].load(std::memory_order_acquire)) {
     // In host code `g_argmax_scratch` is only a stand-in for the symbol: its device address
     // has to be asked for, once per device, with that device current.
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_argmax_scratch) != cudaSuccess || !p) return IRON_ERR_LAUNCH;
-    g_scratch_ptr[dev] = static_cast<unsigned long long*>(p);
+    g_scratch_ptr[dev].store(static_cast<unsigned long long*>(p), std::memory_order_release);
   }
-  unsigned long long* scratch = g_scratch_ptr[dev];
+  unsigned long long* scratch = g_scratch_ptr[dev].load(std::memory_order_acquire);
   cudaStream_t s = (cudaStream_t)stream;
   // The array keeps whatever the last call left: the arrival counter must start at zero.
   if (cudaMemsetAsync(scratch, 0, sizeof(unsigned long long), s) != cudaSuccess) return IRON_ERR_LAUNCH;
   int grid = (n / 8 + 255) / 256;
   grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
   return launch_pdl(argmax_kernel, dim3(grid), dim3(256), s, (const __nv_bfloat16*)logits, n, token_out,
-                    d_out_index, carry_token, carry_position, scratch);
+                    d_out_index, 0, carry_token, carry_position, scratch);
 }

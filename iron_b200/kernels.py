@@ -70,7 +70,7 @@ def decode_qkv_rope(Wqkv, x, angles, k_cache, v_cache, q_out, *, H, G, D, positi
     mode = 2 if norm_weight is not None else (1 if norm else 0)
     call("iron_decode_qkv_rope_bf16", _ptr(Wqkv), _ptr(x), Wqkv.shape[1], mode, _ptr(norm_weight),
          float(eps), _ptr(angles), int(position), _ptr(d_position), _ptr(q_out), _ptr(k_cache),
-         _ptr(v_cache), H, G, D, _stream())
+         _ptr(v_cache), H, G, D, min(k_cache.shape[0], angles.shape[0]), _stream())
     return q_out
 
 
@@ -166,10 +166,11 @@ def argmax_workspace(device) -> torch.Tensor:
 
 def argmax(logits, token_out, workspace, *, d_out_index=None, carry_token=None,
            carry_position=None):
-    """Greedy draw: first index of the maximum, written to ``token_out[*d_out_index]``."""
+    """Greedy draw: first index of the maximum, written to ``token_out[*d_out_index]`` (an
+    index past ``token_out``'s end writes nothing and the carried position stops there)."""
     _bf16(logits)
     call("iron_argmax_bf16", _ptr(logits), logits.numel(), _ptr(token_out), _ptr(d_out_index),
-         _ptr(carry_token), _ptr(carry_position), _ptr(workspace), _stream())
+         token_out.numel(), _ptr(carry_token), _ptr(carry_position), _ptr(workspace), _stream())
     return token_out
 
 
@@ -229,6 +230,10 @@ def gemm(A, B, out=None, *, b_col_maj=False, c_col_maj=False, valid=None, d_vali
     if out is None:
         out = torch.empty((N, M) if c_col_maj else (M, N),
                           dtype=torch.float32 if out_f32 else torch.bfloat16, device=A.device)
+    if residual is not None and (tuple(residual.shape) != tuple(out.shape) or residual.stride() != out.stride()):
+        # the kernel walks the residual with the output's pitch
+        raise ValueError(f"gemm: residual {tuple(residual.shape)} (strides {residual.stride()}) is not laid out "
+                         f"as the output {tuple(out.shape)} (strides {out.stride()})")
     call("iron_gemm_bf16", _ptr(A), _ptr(B), _ptr(out), M, N, Kd, A.stride(0), B.stride(0),
          out.stride(0), int(b_col_maj), int(c_col_maj), M if valid is None else int(valid),
          _ptr(d_valid), Kd if valid_k is None else int(valid_k), EPILOGUES[epilogue],

@@ -83,10 +83,18 @@ class LlamaEngine:
     def __init__(self, config: DecoderConfig, weights: dict, device="cuda", batch: int = 1,
                  kv_len_hint: int | None = None, tp_rank: int = 0, tp_size: int = 1, tp_group=None,
                  release=None):
+        c = config
+        # what the fused kernels do not compute is refused, not skipped
+        if getattr(c, "attention_bias", False) or getattr(c, "mlp_bias", False):
+            raise ValueError("LlamaEngine: projections with biases run on the recorded graph (CausalLM), "
+                             "not on the fused engine")
+        if getattr(c, "hidden_act", "silu") != "silu":
+            raise ValueError(f"LlamaEngine: the gated MLP's activation is silu, not {c.hidden_act!r}")
+        if c.rope_theta is None or c.rope_width != c.head_dim:
+            raise ValueError("LlamaEngine: RoPE over the whole head (rope_width == head_dim) is the only form")
         if not torch.cuda.is_available():
             raise RuntimeError("LlamaEngine needs a CUDA device: there is no CPU path")
         self.c, self.device, self.batch = config, torch.device(device), batch
-        c = config
         E, V, L = c.hidden_size, c.vocab_size, c.num_hidden_layers
         D, S = c.head_dim, c.max_seq_len
         # Tensor parallelism: this rank holds heads [rank*H/t, ...) of q/k/v and o_proj's
@@ -106,6 +114,7 @@ class LlamaEngine:
         self.fused_step = (batch == 1 and tp_size == 1 and D in (64, 128) and L <= 64
                            and E % 32 == 0 and F % 32 == 0 and V % 8 == 0 and max(E, F, H * D) <= 8192
                            and os.environ.get("IRON_DECODE_STEP", "0") == "1")
+        self._fused_step_wanted = self.fused_step
 
         # ---- plan the arena: residents first, then the decode step's transients ----
         plan = ArenaPlan()
@@ -234,6 +243,9 @@ class LlamaEngine:
         self._h_ids = torch.zeros(self.chunk, dtype=torch.int32).pin_memory()
         self._h_ids_done: torch.cuda.Event | None = None
         self._h_status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        # the position the next replayed step runs at (the largest over a batch), mirrored on
+        # the host so that a replay past the end of the caches is refused before any launch
+        self._next_position = 0
 
     # ------------------------------------------------------------------ weights
     @classmethod
@@ -475,6 +487,7 @@ class LlamaEngine:
         self._graph_host = None
         if sampler is None:
             self.draws = None
+            self.fused_step = self._fused_step_wanted
             return
         S = self.c.max_seq_len
         count = S - start if count is None else count
@@ -563,6 +576,7 @@ class LlamaEngine:
         K.gemv(self.head, last, self.logits_buf[seq], norm_weight=self.norm, eps=c.eps)
         self.set_call(0, start + n - 1)
         self._draw(seq, self.values[0:1], self.values[1:2])
+        self._next_position = start + n
         self._chunk_launches = launches
 
     def prefill(self, tokens, start: int = 0, seq: int = 0) -> np.ndarray:
@@ -595,6 +609,8 @@ class LlamaEngine:
         if n + steps > self.c.max_seq_len:
             raise IndexError("the run would pass the end of the caches")
         self.capture()
+        self._next_position = n
+        self._advance(steps - 1)
         for _ in range(steps - 1):
             self._graph.replay()
         out = self.drawn[0, n - 1 : n - 1 + steps].cpu().tolist()
@@ -607,6 +623,8 @@ class LlamaEngine:
             return
         # the warm-up and the capture run a step at position 0: keep what they overwrite
         saved = self.values.clone()
+        saved_next = self._next_position
+        saved_logits = self.logits_buf.clone()   # the warm-up step overwrites the last call's logits
         saved_b = (self.b_tokens.clone(), self.b_pos.clone())
         rows = [(l["k"][:, 0].clone(), l["v"][:, 0].clone()) for l in self.layers]
         drawn0 = self.drawn[:, 0].clone()
@@ -629,6 +647,8 @@ class LlamaEngine:
         for l, (k0, v0) in zip(self.layers, rows):
             l["k"][:, 0].copy_(k0); l["v"][:, 0].copy_(v0)
         self.drawn[:, 0].copy_(drawn0)
+        self.logits_buf.copy_(saved_logits)
+        self._next_position = saved_next
         torch.cuda.synchronize()
 
     def _capture_host(self) -> None:
@@ -670,10 +690,20 @@ class LlamaEngine:
         done = torch.cuda.Event()
         done.record()
         self._ring_done[i] = done
+        self._next_position = int(position)
+
+    def _advance(self, steps: int = 1) -> None:
+        """Refuse ``steps`` more device-carried steps when they would leave the caches."""
+        if self._next_position + steps > self.c.max_seq_len:
+            raise IndexError(f"{steps} more step(s) from position {self._next_position} leave the "
+                             f"{self.c.max_seq_len}-row caches")
+        self._next_position += steps
 
     def step(self) -> None:
-        """Replay one decode step (stream-ordered; no host synchronisation)."""
+        """Replay one decode step (stream-ordered; no host synchronisation).  Raises
+        ``IndexError`` at the end of the caches, before anything is launched."""
         self.capture()
+        self._advance()
         self._graph.replay()
 
     def decode(self, token: int, position: int) -> int:
@@ -684,6 +714,7 @@ class LlamaEngine:
             raise IndexError(f"token {token} is outside the {self.c.vocab_size}-row vocabulary")
         self._capture_host()
         self._h_in_np[0], self._h_in_np[1] = token, position
+        self._next_position = position + 1
         self._graph_host.replay()
         torch.cuda.current_stream().synchronize()
         if int(self._h_status[0]) != 0:
@@ -726,6 +757,7 @@ class LlamaEngine:
         self.b_tokens.copy_(host[0], non_blocking=True)
         self.b_pos.copy_(host[1], non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the pinned staging buffer is released here
+        self._next_position = int(positions.max())
 
     def decode_batch(self, tokens, positions) -> list[int]:
         """One decode step of every sequence from the host: tokens in, drawn tokens out, the
@@ -742,6 +774,7 @@ class LlamaEngine:
             return [self.decode(int(tokens[0]), int(positions[0]))]
         self._capture_host()
         self._h_b_np[0], self._h_b_np[1] = tokens, positions
+        self._next_position = int(positions.max()) + 1
         self._graph_host.replay()
         torch.cuda.current_stream().synchronize()
         if int(self._h_status[0]) != 0:
@@ -755,6 +788,7 @@ class LlamaEngine:
             raise IndexError("the run would pass the end of the caches")
         self.set_batch(tokens, positions)
         self.capture()
+        self._advance(steps)
         for _ in range(steps):
             self._graph.replay()
         drawn = self.drawn.cpu().numpy()
@@ -775,6 +809,7 @@ class LlamaEngine:
             raise IndexError("the run would pass the end of the caches")
         self.set_call(token, position)
         self.capture()
+        self._advance(steps)
         for _ in range(steps):
             self._graph.replay()
         out = self.drawn[0, position : position + steps].cpu()

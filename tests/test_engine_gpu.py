@@ -182,3 +182,37 @@ def test_a_sliding_window_config_matches_the_host_graph_in_prompt_and_decode():
         want = host.reference_logits([nxt], len(tokens))
         tokens.append(nxt)
         close_to_oracle(got, want, f"windowed decode step {step}")
+
+
+def test_stepping_stops_at_the_end_of_the_caches():
+    """The carried loop is refused on the host at the last cache row, and the kernels hold a
+    device-carried position inside the caches even when replayed without the host's check."""
+    import torch
+
+    from iron_b200.lm.engine import LlamaEngine
+
+    config = dataclasses.replace(toy_config(), max_seq_len=16, prefill_chunk=16)
+    weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
+    engine = LlamaEngine(config, weights, kv_len_hint=16)
+    engine.set_call(3, 13)
+    engine.step(); engine.step(); engine.step()          # positions 13, 14, 15: the last row
+    with pytest.raises(IndexError):
+        engine.step()
+    with pytest.raises(IndexError):
+        engine.generate(3, 14, 3)
+    torch.cuda.synchronize()
+    assert int(engine.values[1].item()) == 16
+    # a raw replay past the end (what a caller holding the graph could do): nothing outside
+    # the caches and the drawn row changes, and the position stays at the end
+    before = engine.arena.clone()
+    engine._graph.replay()
+    torch.cuda.synchronize()
+    assert int(engine.values[1].item()) == 16
+    changed = (engine.arena != before).nonzero().flatten()
+    drawn_lo = engine.drawn.data_ptr() - engine.arena.data_ptr()
+    assert not ((changed >= drawn_lo) & (changed < drawn_lo + engine.drawn.numel() * 4)).any()
+    for l in engine.layers:   # only the last cache row may have been rewritten
+        for c in (l["k"], l["v"]):
+            lo = c.data_ptr() - engine.arena.data_ptr()
+            inside = changed[(changed >= lo) & (changed < lo + c.numel() * 2)]
+            assert ((inside - lo) // (c.shape[2] * c.shape[3] * 2) == 15).all()

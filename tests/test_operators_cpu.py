@@ -135,3 +135,26 @@ def test_tolerance_edges():
     ulps = Tolerance.bf16_ulps(1)
     one = np.array([1.0], np.float32)
     assert compare(one + 2 ** -7, one, ulps) and not compare(one + 2 ** -6, one, ulps)
+
+
+def test_host_refusals_come_before_any_launch():
+    """What the kernels cannot run is refused on the host: a residual that is not laid out as
+    the GEMM's output, and a decoder shape the fused engine has no kernels for."""
+    import dataclasses
+
+    import torch
+
+    from iron_b200 import kernels as K
+    from iron_b200.applications.llama.model import LlamaConfig
+    from iron_b200.lm.engine import LlamaEngine
+
+    A, W = torch.zeros(256, 64, dtype=torch.bfloat16), torch.zeros(100, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="residual"):
+        K.gemm(A, W, b_col_maj=True, residual=torch.zeros(256, 104, dtype=torch.bfloat16)[:, :100])
+    with pytest.raises(ValueError, match="residual"):
+        K.gemm(A, W, b_col_maj=True, residual=torch.zeros(100, 256, dtype=torch.bfloat16))
+    base = LlamaConfig(vocab_size=64, hidden_size=64, num_hidden_layers=1, num_attention_heads=1,
+                       num_key_value_heads=1, head_dim=64, intermediate_size=64, rope_theta=1e4, max_seq_len=8)
+    for change in (dict(attention_bias=True), dict(mlp_bias=True), dict(hidden_act="gelu")):
+        with pytest.raises(ValueError, match="LlamaEngine"):
+            LlamaEngine(dataclasses.replace(base, **change), {})

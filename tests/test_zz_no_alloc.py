@@ -35,8 +35,8 @@ def test_no_alloc_argmax_matches_the_workspace_entry_point_twice_in_a_row():
         index = torch.tensor([2], dtype=torch.int32, device="cuda")
         carry_a = torch.tensor([0, 7], dtype=torch.int32, device="cuda")
         carry_b = torch.tensor([0, 7], dtype=torch.int32, device="cuda")
-        rc = lib.iron_argmax_bf16(logits.data_ptr(), n, want.data_ptr(), index.data_ptr(), carry_a.data_ptr(),
-                                  carry_a[1:].data_ptr(), ws.data_ptr(), stream)
+        rc = lib.iron_argmax_bf16(logits.data_ptr(), n, want.data_ptr(), index.data_ptr(), want.numel(),
+                                  carry_a.data_ptr(), carry_a[1:].data_ptr(), ws.data_ptr(), stream)
         assert rc == 0
         rc = lib.iron_argmax_bf16_noalloc(logits.data_ptr(), n, got.data_ptr(), index.data_ptr(),
                                           carry_b.data_ptr(), carry_b[1:].data_ptr(), stream)

@@ -35,8 +35,8 @@ def assert_verdict(got, want, tolerance, bound=None, what=""):
     assert v, f"{what}: {v.detail}"
 
 
-def assert_north_star(got, want, what=""):
-    """The north-star bound for bf16 outputs: within 1e-2 relative or 2e-2 absolute."""
+def assert_bf16_bound(got, want, what=""):
+    """The bound every bf16 output is held to: within 1e-2 relative or 2e-2 absolute."""
     g = np.asarray(got).astype(np.float64)
     w = np.asarray(want).astype(np.float64)
     err = np.abs(g - w)
