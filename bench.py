@@ -97,19 +97,9 @@ def build_config():
 
 def device_weights(config, seed: int, device):
     """Random-init weights N(0, 0.02) (norms one), drawn on the device from ``seed``."""
-    import torch
+    from iron_b200.applications.llama.model import random_device_weights
 
-    from oracle.model import llama_shapes, LlamaShape
-
-    shape = LlamaShape(max_seq_len=config.max_seq_len)
-    gen = torch.Generator(device=device).manual_seed(seed)
-    out = {}
-    for name, dims in llama_shapes(shape).items():
-        if len(dims) >= 2:
-            out[name] = (torch.randn(dims, generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-        else:
-            out[name] = torch.ones(dims, device=device, dtype=torch.bfloat16)
-    return out
+    return random_device_weights(config, seed, device)
 
 
 def prompt_tokens(seed: int):
@@ -262,15 +252,7 @@ def run_tp(args, rank: int, world: int, device) -> None:
 
     ctx = 4096
     config = dataclasses.replace(LLAMA_3B, max_seq_len=ctx + 512)
-    gen = torch.Generator(device=device).manual_seed(4001)
-    from oracle.model import LlamaShape, llama_shapes
-
-    shape = LlamaShape(hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8,
-                       head_dim=128, intermediate_size=8192, max_seq_len=config.max_seq_len)
-    weights = {}
-    for name, dims in llama_shapes(shape).items():
-        weights[name] = ((torch.randn(dims, generator=gen, device=device) * 0.02).to(torch.bfloat16)
-                         if len(dims) >= 2 else torch.ones(dims, device=device, dtype=torch.bfloat16))
+    weights = device_weights(config, 4001, device)
     nb = max(1, args.tp_batch)
     engine = LlamaEngine(config, weights, device=device, kv_len_hint=ctx + args.steps, tp_rank=rank, tp_size=world,
                          batch=nb)

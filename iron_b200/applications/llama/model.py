@@ -72,6 +72,45 @@ LLAMA_3B = LlamaConfig(
 )
 
 
+def checkpoint_shapes(c: DecoderConfig) -> dict[str, tuple[int, ...]]:
+    """A Llama checkpoint's tensor names and shapes for ``c``, in the order the reference's
+    random fill draws them (iron/tests/support/llama_model.py:76-98); ``lm_head.weight`` only
+    when the head is not tied to the embedding."""
+    E, F, V = c.hidden_size, c.intermediate_size, c.vocab_size
+    Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+    out: dict[str, tuple[int, ...]] = {"model.embed_tokens.weight": (V, E), "model.norm.weight": (E,)}
+    for i in range(c.num_hidden_layers):
+        p = f"model.layers.{i}"
+        out[f"{p}.input_layernorm.weight"] = (E,)
+        out[f"{p}.self_attn.q_proj.weight"] = (Q, E)
+        out[f"{p}.self_attn.k_proj.weight"] = (KV, E)
+        out[f"{p}.self_attn.v_proj.weight"] = (KV, E)
+        out[f"{p}.self_attn.o_proj.weight"] = (E, Q)
+        out[f"{p}.post_attention_layernorm.weight"] = (E,)
+        out[f"{p}.mlp.gate_proj.weight"] = (F, E)
+        out[f"{p}.mlp.up_proj.weight"] = (F, E)
+        out[f"{p}.mlp.down_proj.weight"] = (E, F)
+    if not c.tie_word_embeddings:
+        out["lm_head.weight"] = (V, E)
+    return out
+
+
+def random_device_weights(c: DecoderConfig, seed: int, device, std: float = 0.02) -> dict:
+    """Random-init weights for ``c`` drawn on ``device``: matrices N(0, ``std``) in bf16, norm
+    weights one (the ``--random-weights`` mode of iron/lm/cli.py:83-208 with the benchmark's
+    deviation)."""
+    import torch
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    out = {}
+    for name, dims in checkpoint_shapes(c).items():
+        if len(dims) >= 2:
+            out[name] = (torch.randn(dims, generator=gen, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+        else:
+            out[name] = torch.ones(dims, device=device, dtype=torch.bfloat16)
+    return out
+
+
 def _llama():
     from ...lm.causal import CausalLM
 
