@@ -1,4 +1,5 @@
-"""CPU oracle for the model path: a numpy Llama decoder and the float32 transformers judge.
+"""CPU oracle for the model path: numpy decoders (Llama, biased Llama, Granite, the Granite 4.0-H
+hybrid with Mamba2 mixers) and the float32 transformers judge.
 
 TEST INFRASTRUCTURE ONLY (see ``oracle/ops.py``).
 
@@ -272,3 +273,272 @@ def hf_logits(model, tokens) -> np.ndarray:
     with torch.no_grad():
         out = model(torch.tensor([list(map(int, tokens))]), use_cache=False)
     return out.logits[0, -1].numpy()
+
+
+# ---------------------------------------------------------------------------------------
+# Granite, biased Llama and the Granite 4.0-H hybrid (Mamba2 mixers): the other toys the
+# reference records goldens for
+
+
+@dataclasses.dataclass(frozen=True)
+class DecoderShape(LlamaShape):
+    """``LlamaShape`` plus what the reference's other decoders read from their configs:
+    projection biases (iron/lm/config.py ``attention_bias``), Granite's four scalars
+    (iron/applications/granite/model.py:32-43) and the hybrid's Mamba2 mixer shape
+    (iron/applications/granite_hybrid/model.py:37-86).  ``rope_theta`` None is no RoPE."""
+
+    rope_theta: float | None = 500000.0
+    attention_bias: bool = False
+    attention_multiplier: float | None = None
+    residual_multiplier: float = 1.0
+    embedding_multiplier: float = 1.0
+    logits_scaling: float = 1.0
+    layer_types: tuple[str, ...] | None = None
+    shared_intermediate_size: int | None = None
+    mamba_n_heads: int = 0
+    mamba_d_head: int = 0
+    mamba_d_state: int = 0
+    mamba_n_groups: int = 1
+    mamba_d_conv: int = 4
+
+    def attends(self, i: int) -> bool:
+        return self.layer_types is None or self.layer_types[i] in ("attention", "full_attention")
+
+    @property
+    def d_inner(self) -> int:
+        return self.mamba_n_heads * self.mamba_d_head
+
+    @property
+    def conv_channels(self) -> int:
+        return self.d_inner + 2 * self.mamba_n_groups * self.mamba_d_state
+
+
+#: tests/applications/llama/reference/test.py:23-26: ``SMALL`` with a bias on q, k, v and o.
+BIASED = DecoderShape(
+    vocab_size=1024, hidden_size=512, num_hidden_layers=2, num_attention_heads=16,
+    num_key_value_heads=4, head_dim=64, intermediate_size=2048, max_seq_len=256,
+    prefill_chunk=256, attention_bias=True,
+)
+
+#: tests/applications/granite/reference/test.py:18-33.
+GRANITE_TOY = DecoderShape(
+    vocab_size=1024, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+    num_key_value_heads=2, head_dim=64, intermediate_size=1024, rope_theta=10000.0,
+    max_seq_len=256, prefill_chunk=256, eps=1e-6, tie_word_embeddings=False,
+    attention_multiplier=0.0625, residual_multiplier=0.22, embedding_multiplier=12.0,
+    logits_scaling=8.0,
+)
+
+#: tests/applications/granite_hybrid/reference/test.py:28-51: three Mamba2 layers of two
+#: groups, one attention layer without RoPE, the shared gated MLP, an untied head.
+HYBRID_TOY = DecoderShape(
+    vocab_size=1024, hidden_size=512, num_hidden_layers=4, num_attention_heads=8,
+    num_key_value_heads=2, head_dim=64, intermediate_size=256, rope_theta=None,
+    max_seq_len=256, prefill_chunk=64, eps=1e-6, tie_word_embeddings=False,
+    attention_multiplier=0.0625, residual_multiplier=0.22, embedding_multiplier=12.0,
+    logits_scaling=8.0, layer_types=("mamba", "attention", "mamba", "mamba"),
+    shared_intermediate_size=512, mamba_n_heads=16, mamba_d_head=64, mamba_d_state=64,
+    mamba_n_groups=2,
+)
+
+
+def decoder_shapes(c: DecoderShape) -> dict[str, tuple[int, ...]]:
+    """Checkpoint names and shapes in the reference's draw order: Llama's table, then the
+    biases (tests/applications/llama/reference/test.py:29-41) or the untied head
+    (tests/applications/granite/reference/test.py:41-43); the hybrid's own table
+    (tests/applications/granite_hybrid/reference/test.py:88-127)."""
+    E, V = c.hidden_size, c.vocab_size
+    Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+    if c.layer_types is None:
+        out = llama_shapes(c)
+        if c.attention_bias:
+            for i in range(c.num_hidden_layers):
+                a = f"model.layers.{i}.self_attn"
+                out |= {f"{a}.q_proj.bias": (Q,), f"{a}.k_proj.bias": (KV,), f"{a}.v_proj.bias": (KV,),
+                        f"{a}.o_proj.bias": (E,)}
+        if not c.tie_word_embeddings:
+            out |= {"lm_head.weight": (V, E)}
+        return out
+    S, H, N = c.shared_intermediate_size, c.mamba_n_heads, c.mamba_d_state
+    out = {"model.embed_tokens.weight": (V, E), "model.norm.weight": (E,), "lm_head.weight": (V, E)}
+    for i in range(c.num_hidden_layers):
+        p = f"model.layers.{i}"
+        out |= {f"{p}.input_layernorm.weight": (E,), f"{p}.post_attention_layernorm.weight": (E,),
+                f"{p}.shared_mlp.input_linear.weight": (2 * S, E),
+                f"{p}.shared_mlp.output_linear.weight": (E, S)}
+        if c.attends(i):
+            out |= {f"{p}.self_attn.q_proj.weight": (Q, E), f"{p}.self_attn.k_proj.weight": (KV, E),
+                    f"{p}.self_attn.v_proj.weight": (KV, E), f"{p}.self_attn.o_proj.weight": (E, Q)}
+        else:
+            m = f"{p}.mamba"
+            out |= {f"{m}.in_proj.weight": (c.d_inner + c.conv_channels + H, E),
+                    f"{m}.conv1d.weight": (c.conv_channels, 1, c.mamba_d_conv),
+                    f"{m}.conv1d.bias": (c.conv_channels,), f"{m}.dt_bias": (H,), f"{m}.A_log": (H,),
+                    f"{m}.D": (H,), f"{m}.norm.weight": (c.d_inner,), f"{m}.out_proj.weight": (E, c.d_inner)}
+    return out
+
+
+def hybrid_redraw(c: DecoderShape, weights: dict[str, np.ndarray]) -> dict[str, np.ndarray]:
+    """The hybrid toy's weights after the reference's own redraw, in place
+    (tests/applications/granite_hybrid/reference/test.py:62-71): decays and time steps as
+    Mamba2 initialises them, the convolution's bias ten times the shared draw's."""
+    rng = np.random.default_rng(0)
+    H = c.mamba_n_heads
+    for i in range(c.num_hidden_layers):
+        if c.attends(i):
+            continue
+        m = f"model.layers.{i}.mamba"
+        weights[f"{m}.A_log"][:] = np.log(rng.uniform(1, 16, H))
+        dt = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), H))
+        weights[f"{m}.dt_bias"][:] = dt + np.log(-np.expm1(-dt))
+        weights[f"{m}.conv1d.bias"][:] *= 10
+    return weights
+
+
+class NumpyDecoder:
+    """The reference's host graph for its other decoders, operator by operator in bf16:
+    Llama's layer with optional biases and Granite's scalars
+    (iron/applications/granite/model.py:46-93: attention scale, AXPY residuals, the embedding
+    row product, the logits' divisor folded into the final norm's weight), and the hybrid's
+    layer (iron/applications/granite_hybrid/model.py:87-176): a Mamba2 mixer or attention,
+    then the shared gated MLP.  The mixer's states -- the convolution's last ``K - 1`` rows
+    and the scan's float32 state -- carry from call to call as the reference's
+    ``Checkpoints`` do (iron/lm/causal.py:71-121)."""
+
+    def __init__(self, config: DecoderShape, weights: dict[str, np.ndarray]):
+        self.c, self.w = c, w = config, weights
+        self.angles = None if c.rope_theta is None else c.angles().astype(bfloat16)
+        G, D, L = c.num_key_value_heads, c.head_dim, c.num_hidden_layers
+        self.keys = [np.zeros((c.max_seq_len, G, D), bfloat16) for _ in range(L)]
+        self.values = [np.zeros((c.max_seq_len, G, D), bfloat16) for _ in range(L)]
+        K = c.mamba_d_conv
+        self.conv = [np.zeros((K - 1, c.conv_channels), bfloat16) for _ in range(L)]
+        self.ssm = [np.zeros((c.mamba_n_heads, c.mamba_d_head, c.mamba_d_state), np.float32) for _ in range(L)]
+        self.embed_scale = np.full(c.hidden_size, c.embedding_multiplier, bfloat16)
+        norm = np.asarray(w["model.norm.weight"])
+        # the reference divides in bf16 (iron/applications/granite/model.py:81-83)
+        self.final_norm = norm if c.logits_scaling == 1 else (norm / bfloat16(c.logits_scaling)).astype(bfloat16)
+        self.heads = {}
+        for i in range(L):
+            if not c.attends(i):
+                m = f"model.layers.{i}.mamba"
+                A = -np.exp(np.asarray(w[f"{m}.A_log"], np.float32))
+                self.heads[i] = np.stack([np.asarray(w[f"{m}.dt_bias"], np.float32), A,
+                                          np.asarray(w[f"{m}.D"], np.float32)], 1).astype(np.float32)
+
+    def _linear(self, x, W, bias=None):
+        y = (np.asarray(x, np.float32) @ np.asarray(W, np.float32).T).astype(bfloat16)
+        return y if bias is None else ops.add(y, np.broadcast_to(bias, y.shape))
+
+    def _residual(self, x, y):
+        r = self.c.residual_multiplier
+        return ops.add(x, y) if r == 1 else ops.axpy(y, x, r)
+
+    def _attention(self, i, h, start):
+        c, w = self.c, self.w
+        H, G, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        n, a = h.shape[0], f"model.layers.{i}.self_attn"
+        bias = (lambda p: w[f"{a}.{p}.bias"]) if c.attention_bias else (lambda p: None)
+        q = self._linear(h, w[f"{a}.q_proj.weight"], bias("q_proj")).reshape(n * H, D)
+        k = self._linear(h, w[f"{a}.k_proj.weight"], bias("k_proj")).reshape(n * G, D)
+        v = self._linear(h, w[f"{a}.v_proj.weight"], bias("v_proj")).reshape(n, G, D)
+        if self.angles is not None:
+            ang = self.angles[start : start + n]
+            q, k = ops.rope(q, ang), ops.rope(k, ang)
+        self.keys[i][start : start + n] = k.reshape(n, G, D)
+        self.values[i][start : start + n] = v
+        kv = start + n
+        o = ops.mha(q.reshape(n, H, D), self.keys[i][:kv], self.values[i][:kv], num_heads=H, num_kv_heads=G,
+                    heads_interleaved=True, kv_interleaved=True, scale=c.attention_multiplier).reshape(n, H * D)
+        return self._linear(o, w[f"{a}.o_proj.weight"], bias("o_proj"))
+
+    def _mamba(self, i, h):
+        c, w = self.c, self.w
+        m = f"model.layers.{i}.mamba"
+        d_inner, C = c.d_inner, c.conv_channels
+        W = w[f"{m}.in_proj.weight"]
+        gate, xbc, dt = (self._linear(h, part) for part in (W[:d_inner], W[d_inner : d_inner + C], W[d_inner + C :]))
+        taps = np.ascontiguousarray(np.asarray(w[f"{m}.conv1d.weight"]).reshape(C, c.mamba_d_conv).T)
+        conv, self.conv[i] = ops.causal_conv1d(xbc, taps, self.conv[i], w[f"{m}.conv1d.bias"])
+        xbc = ops.silu(conv)
+        y, self.ssm[i] = ops.selective_scan(xbc, dt, self.heads[i], self.ssm[i], heads=c.mamba_n_heads,
+                                            head_dim=c.mamba_d_head, state_size=c.mamba_d_state,
+                                            groups=c.mamba_n_groups)
+        y = ops.rms_norm(ops.mul(y, ops.silu(gate)), w[f"{m}.norm.weight"], c.eps)
+        return self._linear(y, w[f"{m}.out_proj.weight"])
+
+    def _mlp(self, i, h):
+        c, w, p = self.c, self.w, f"model.layers.{i}"
+        if c.layer_types is None:
+            gate = self._linear(h, w[f"{p}.mlp.gate_proj.weight"])
+            up = self._linear(h, w[f"{p}.mlp.up_proj.weight"])
+            return self._linear(ops.mul(ops.silu(gate), up), w[f"{p}.mlp.down_proj.weight"])
+        S, W = c.shared_intermediate_size, w[f"{p}.shared_mlp.input_linear.weight"]
+        gate, up = self._linear(h, W[:S]), self._linear(h, W[S:])
+        return self._linear(ops.mul(ops.silu(gate), up), w[f"{p}.shared_mlp.output_linear.weight"])
+
+    def forward(self, tokens, start: int):
+        """Run ``tokens`` at positions ``start...`` (in order: the mixers' states carry on);
+        logits of the last row, bf16."""
+        c, w = self.c, self.w
+        tokens = np.asarray(tokens).reshape(-1)
+        n = len(tokens)
+        x = ops.gather_rows(w["model.embed_tokens.weight"], tokens)
+        if c.embedding_multiplier != 1:
+            x = ops.mul(x, np.broadcast_to(self.embed_scale, x.shape))
+        for i in range(c.num_hidden_layers):
+            p = f"model.layers.{i}"
+            h = ops.rms_norm(x, w[f"{p}.input_layernorm.weight"], c.eps)
+            x = self._residual(x, self._attention(i, h, start) if c.attends(i) else self._mamba(i, h))
+            h = ops.rms_norm(x, w[f"{p}.post_attention_layernorm.weight"], c.eps)
+            x = self._residual(x, self._mlp(i, h))
+        last = ops.rms_norm(x[n - 1 : n], self.final_norm, c.eps)
+        head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
+        return self._linear(last, head).reshape(-1)
+
+    def logits(self, tokens):
+        """Logits after the last of ``tokens`` from empty states, in prompt chunks."""
+        tokens = np.asarray(tokens).reshape(-1)
+        C, out = self.c.prefill_chunk, None
+        for s in range(0, len(tokens), C):
+            out = self.forward(tokens[s : s + C], s)
+        return out
+
+
+def hf_decoder(model_type: str, c: DecoderShape, weights: dict[str, np.ndarray]):
+    """transformers' ``model_type`` ("llama", "granite", "granitemoehybrid") in float32 on
+    ``weights``, its config the fields ``c`` would write to a ``config.json``
+    (iron/lm/golden.py:193-224; the hybrid adds ``mamba_expand`` as
+    tests/applications/granite_hybrid/reference/test.py:83 does)."""
+    import tempfile
+
+    import torch
+    import transformers
+    from safetensors.torch import save_file
+
+    cfg = dict(vocab_size=c.vocab_size, hidden_size=c.hidden_size, num_hidden_layers=c.num_hidden_layers,
+               num_attention_heads=c.num_attention_heads, num_key_value_heads=c.num_key_value_heads,
+               head_dim=c.head_dim, intermediate_size=c.intermediate_size,
+               max_position_embeddings=c.max_seq_len, rms_norm_eps=c.eps, hidden_act="silu",
+               tie_word_embeddings=c.tie_word_embeddings, attention_bias=c.attention_bias, mlp_bias=False)
+    if c.rope_theta is not None:
+        cfg["rope_theta"] = c.rope_theta
+    if c.attention_multiplier is not None:
+        cfg |= dict(attention_multiplier=c.attention_multiplier, residual_multiplier=c.residual_multiplier,
+                    embedding_multiplier=c.embedding_multiplier, logits_scaling=c.logits_scaling)
+    if c.layer_types is not None:
+        cfg |= dict(layer_types=list(c.layer_types), position_embedding_type="nope",
+                    shared_intermediate_size=c.shared_intermediate_size, num_local_experts=0,
+                    num_experts_per_tok=2, mamba_n_heads=c.mamba_n_heads, mamba_d_head=c.mamba_d_head,
+                    mamba_d_state=c.mamba_d_state, mamba_n_groups=c.mamba_n_groups,
+                    mamba_d_conv=c.mamba_d_conv, mamba_expand=2, rope_theta=10000.0)
+    hf = transformers.AutoConfig.for_model(model_type, **cfg)
+    with tempfile.TemporaryDirectory() as directory:
+        hf.save_pretrained(directory)
+        save_file({k: torch.from_numpy(np.asarray(v).astype(np.float32)) for k, v in weights.items()},
+                  f"{directory}/model.safetensors")
+        model, info = transformers.AutoModelForCausalLM.from_pretrained(
+            directory, dtype=torch.float32, output_loading_info=True)
+    if info["missing_keys"] or info["unexpected_keys"]:
+        raise ValueError(f"weights lack {sorted(info['missing_keys'])} and hold {sorted(info['unexpected_keys'])}")
+    return model.eval()

@@ -174,3 +174,68 @@ def test_selective_scan_decays_and_reads_out():
     y1, mid = ops.selective_scan(xbc[:3], dt[:3], head, state, heads=H, head_dim=P, state_size=N)
     y2, final2 = ops.selective_scan(xbc[3:], dt[3:], head, mid, heads=H, head_dim=P, state_size=N)
     assert np.array_equal(y, np.concatenate([y1, y2])) and np.allclose(final, final2)
+
+
+# ---------------------------------------------------------------------------------------
+# The reference's other toy decoders: biased Llama, Granite, and the Granite 4.0-H hybrid,
+# whose golden is the one fixture that pins the selective scan and the causal convolution.
+
+OTHER_TOYS = {
+    # name: (shape, transformers model_type, prompt seed, fixture, float32 slack)
+    "biased": (M.BIASED, "llama", 1, "llama_biased.npz", 0.0),
+    "granite": (M.GRANITE_TOY, "granite", 0, "granite_toy.npz", 0.0),
+    # transformers' Mamba2 mixer off its fused kernels sums in an order that depends on the
+    # build: float32 rounding (2e-7 of logits up to 0.44) is all that separates the rows
+    "hybrid": (M.HYBRID_TOY, "granitemoehybrid", 2, "granite_hybrid_dense.npz", 1e-6),
+}
+
+
+@pytest.fixture(scope="module", params=sorted(OTHER_TOYS))
+def other(request):
+    c, model_type, seed, fixture, slack = OTHER_TOYS[request.param]
+    w = M.filled_random(M.decoder_shapes(c), 0)
+    if c.layer_types is not None:
+        w = M.hybrid_redraw(c, w)
+    with np.load(Path(__file__).parent / "golden" / fixture) as z:
+        rows = {k: z[k] for k in z.files}
+    return c, w, model_type, seed, rows, slack
+
+
+def test_float32_transformers_reproduces_the_other_toys_golden_rows(other):
+    c, w, model_type, seed, golden, slack = other
+    hf = M.hf_decoder(model_type, c, w)
+    prompt = np.random.default_rng(seed).integers(0, c.vocab_size, 8)
+    tokens, rows = greedy_rows(golden, prompt, 2)
+    for n, want in zip(range(len(prompt), len(tokens) + 1), rows):
+        got = M.hf_logits(hf, tokens[:n])
+        assert np.abs(got - want).max() <= slack, f"{n} tokens: max diff {np.abs(got - want).max()}"
+        assert got.argmax() == want.argmax()
+
+
+def test_the_numpy_decoder_of_the_other_toys_is_close_to_their_golden_rows(other):
+    """Prompt then six greedy steps, token by token from empty states, and a prompt of several
+    chunks followed by a decode step and a turn of thirty tokens (the mixers' convolution
+    history and scan state cross chunk boundaries): iron/tests/support/llama_reference.py:179-224."""
+    c, w, _, seed, golden, _ = other
+    prompt = np.random.default_rng(seed).integers(0, c.vocab_size, 8)
+    tokens, rows = greedy_rows(golden, prompt, 6)
+    model = M.NumpyDecoder(c, w)
+    assert_close(model.forward(prompt, 0), rows[0])
+    for step in range(6):
+        at = len(prompt) + step
+        assert_close(model.forward(tokens[at : at + 1], at), rows[step + 1], f"step {step}")
+    model = M.NumpyDecoder(c, w)
+    for i, t in enumerate(prompt):
+        got = model.forward([t], i)
+    assert_close(got, rows[0], "token by token")
+    C = c.prefill_chunk
+    long = np.random.default_rng(3).integers(0, c.vocab_size, C + 150)
+    want = golden[M.golden_key(long)]
+    model = M.NumpyDecoder(dataclasses.replace(c, max_seq_len=4 * C), w)
+    assert_close(model.logits(long), want, "several chunks")
+    long = np.append(long, want.argmax())
+    assert_close(model.forward(long[-1:], len(long) - 1), golden[M.golden_key(long)], "the step after")
+    turn = np.random.default_rng(4).integers(0, c.vocab_size, 30)
+    start = len(long)
+    long = np.append(long, turn)
+    assert_close(model.forward(turn, start), golden[M.golden_key(long)], "a turn of thirty tokens")
