@@ -65,6 +65,14 @@ def walk(node, path: str = "", seen=None):
             yield from walk(value, sub, seen)
 
 
+class MissingWeights(KeyError):
+    """``load_state_dict`` found no array for some of a graph's params."""
+
+    def __init__(self, graph: str, names: list[str]):
+        self.names = list(names)
+        super().__init__(f"{graph}: the weights lack {self.names}")
+
+
 class Graph:
     """Subclass it, define ``body``; see the module docstring."""
 
@@ -87,11 +95,31 @@ class Graph:
 
     # ---- weights ----
     def load_state_dict(self, tree: Mapping[str, np.ndarray], *, path: str = "") -> None:
-        """Bind every ``param`` this graph holds to ``tree``'s array at its attribute path."""
-        missing = []
-        for sub, value, owner, key in walk(self):
+        """Bind every ``param`` this graph holds to ``tree``'s array at its attribute path.
+
+        Module by module, as ``torch.nn.Module`` loads: a held graph loads its own attributes
+        through its own ``load_state_dict`` (``path`` its dotted prefix), so a subclass can
+        override it to derive what it computes with from what it just loaded
+        (iron/common/graph/compiled.py:430-470; iron/lm/causal.py:153-157 builds a
+        convolution's tap rows this way)."""
+        missing: list[str] = []
+        self._load_into(self, tree, path, missing, set())
+        if missing:
+            raise MissingWeights(self.name, missing)
+
+    @staticmethod
+    def _load_into(node, tree, path, missing, seen) -> None:
+        if isinstance(node, Graph):
+            items = [(k, v) for k, v in vars(node).items() if not k.startswith("_")]
+        elif isinstance(node, (list, tuple)):
+            items = [(str(i), v) for i, v in enumerate(node)]
+        elif isinstance(node, dict):
+            items = [(str(k), v) for k, v in node.items()]
+        else:
+            return
+        for key, value in items:
+            full = f"{path}.{key}" if path else key
             if isinstance(value, Param):
-                full = f"{path}.{sub}" if path else sub
                 if full in tree:
                     arr = np.ascontiguousarray(tree[full])
                     if tuple(arr.shape) != tuple(value.shape):
@@ -99,8 +127,16 @@ class Graph:
                     value.array, value.dtype = arr, arr.dtype
                 elif value.array is None:
                     missing.append(full)
-        if missing:
-            raise KeyError(f"{self.name}: the weights lack {missing}")
+            elif isinstance(value, Graph):
+                if id(value) in seen:
+                    continue
+                seen.add(id(value))
+                try:
+                    value.load_state_dict(tree, path=full)
+                except MissingWeights as e:   # one report for everything every module lacks
+                    missing.extend(e.names)
+            elif isinstance(value, (list, tuple, dict)):
+                Graph._load_into(value, tree, full, missing, seen)
 
     # ---- recording ----
     def _parameters(self):

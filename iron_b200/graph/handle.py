@@ -199,15 +199,12 @@ class Handle:
             if index.step not in (None, 1):
                 raise TypeError("strided slices are not views")
             start, stop = index.start, index.stop
-            if start is None and isinstance(stop, (Expr, int)) and not isinstance(stop, bool) and (
-                    isinstance(stop, Expr) or stop < n):
-                # x[:n]: a bound, not a smaller view
+            if start is None and isinstance(stop, Expr):
+                # x[:n] by a per-call value: a bound, not a smaller view (a static x[:8] is a slice)
                 if isinstance(stop, Expr) and not (stop.linear or stop.clamped):
                     raise TypeError("a bound is linear or clamped per call")
                 if self.bound is not None:
                     raise TypeError("the view is already bounded")
-                if isinstance(stop, int) and stop < 0:
-                    raise IndexError("negative bounds are not supported")
                 return dataclasses.replace(self, bound=stop, per=Fraction(1))
             start = 0 if start is None else start
             stop = n if stop is None else stop

@@ -118,6 +118,15 @@ class Recorder:
         given_in, given_out, fields = cls.call_operands(operands, kwargs)
         ins = {n: self._materialise(self.as_handle(v)) for n, v in given_in.items()}
         outs = {n: self.as_handle(v) for n, v in given_out.items()}
+        # An output given as a view at a per-call offset (a state's slot picked by the call's
+        # position) is computed into a transient and copied there: only Copy resolves a
+        # per-call offset on the device.
+        placed_later = []
+        for n, h in list(outs.items()):
+            if isinstance(h.offset, Expr):
+                tmp = self.transient(f"{cls.__name__}.{n}", h.shape, h.dtype)
+                placed_later.append((tmp, h))
+                outs[n] = tmp
         decl = cls.declaration
         per_call_given = {k: fields.pop(k) for k in list(fields) if k in decl.per_calls}
         shapes = {n: h.shape for n, h in ins.items()}
@@ -152,6 +161,8 @@ class Recorder:
             out_handles[b.name] = h
         step = Step(op, ins, out_handles, values, len(self.steps))
         self.steps.append(step)
+        for tmp, view in placed_later:
+            self._copy((tmp, view), {})
         results = [out_handles[b.name] for b in op.outputs]
         return results[0] if len(results) == 1 else tuple(results)
 

@@ -128,7 +128,7 @@ class Attention(Graph):
         linear = partial(Linear, bias=c.attention_bias, precision=c.precision)
         self.q_proj, self.k_proj, self.v_proj = linear(E, H * D), linear(E, G * D), linear(E, G * D)
         self.o_proj = Linear(H * D, E, bias=o_bias, precision=c.precision)
-        self.scaling: float | None = None
+        self.scaling: float | None = None   # the logits' scale; None is 1 / sqrt(head_dim)
 
     def body(self, x, cache: KVCache, call: Call, angles=None):
         n, H, G, D = x.shape[0], self.heads, self.groups, self.head_dim
@@ -165,7 +165,11 @@ class DecoderLayer(Graph):
         self.residual_multiplier = 1.0
 
     def body(self, x, call: Call):
-        angles = None if self.rope is None else call.ropes[self.rope]
-        x = residual_add(x, self.self_attn(self.input_layernorm(x), self.cache, call, angles),
-                         self.residual_multiplier)
+        x = residual_add(x, self.mix(self.input_layernorm(x), call), self.residual_multiplier)
         return residual_add(x, self.mlp(self.post_attention_layernorm(x)), self.residual_multiplier)
+
+    def mix(self, h, call: Call):
+        """Attend the normed rows ``h`` over the layer's cache (iron/lm/blocks.py:729-733); a
+        layer that mixes positions another way (a Mamba2 mixer) overrides it."""
+        angles = None if self.rope is None else call.ropes[self.rope]
+        return self.self_attn(h, self.cache, call, angles)

@@ -14,11 +14,73 @@ from __future__ import annotations
 import numpy as np
 from ml_dtypes import bfloat16
 
-from ..graph import Carried, Graph, Scratchpad, carry, state, walk
+import dataclasses
+
+from .. import functional as F
+from ..graph import Carried, Graph, Scratchpad, carry, param, state, walk
+from ..graph.handle import State
 from ..operators.copy import Copy
 from ..operators.sample import ROW_WORDS, Sample
 from .blocks import Call, DecoderLayer, Embedding, Linear, RMSNorm, Rope
 from .config import DecoderConfig
+
+
+@dataclasses.dataclass(frozen=True)
+class Checkpoints:
+    """A state carried from position to position, one slot per prompt-chunk boundary
+    (iron/lm/causal.py:71-121): slot ``k`` holds it after the first ``k * chunk`` positions
+    (or the positions run so far, for the chunk in progress); slot 0, never written, is the
+    state before the sequence.  A call reads the slot before its first position and writes
+    the slot after its last, so a sequence can restart at any chunk boundary."""
+
+    slots: State
+    chunk: int
+
+    @classmethod
+    def of(cls, shape, max_seq_len: int, chunk: int, dtype=bfloat16) -> "Checkpoints":
+        if chunk < 1 or chunk & (chunk - 1):
+            raise ValueError(f"Checkpoints: a {chunk}-position chunk is no power of two")
+        return cls(state(((max_seq_len - 1) // chunk + 2, *shape), dtype), chunk)
+
+    def at(self, call: Call):
+        """(the slot ``call`` reads, the slot it writes), inside a body."""
+        C = self.chunk
+        return self.slots[(call.start - 1) // C + 1], self.slots[call.position // C + 1]
+
+    def restart(self, held: int, ran: int) -> int:
+        """Where a call may start so that the positions from ``held`` on change, after ``ran``
+        ran: where the last call ended, else the chunk boundary before ``held``."""
+        return held if held == ran else held // self.chunk * self.chunk
+
+    def slot(self, position: int) -> int:
+        """The slot holding the state after the first ``position`` positions."""
+        return 0 if position == 0 else (position - 1) // self.chunk + 1
+
+
+class CausalConv1d(Graph):
+    """A depth-wise causal convolution of ``kernel`` taps over a call's rows
+    (iron/lm/causal.py:124-163): ``weight`` as torch stores it, ``(channels, 1, kernel)``,
+    an optional ``bias``, and the ``kernel - 1`` rows before a call as ``state``, a slot per
+    prompt-chunk boundary."""
+
+    def __init__(self, c, channels: int, kernel: int, bias: bool = False):
+        if c.prefill_chunk < kernel - 1:
+            raise ValueError(f"CausalConv1d: prefill_chunk {c.prefill_chunk} is smaller than "
+                             f"kernel - 1 ({kernel - 1})")
+        self.weight = param(channels, 1, kernel)
+        self.bias = param(channels) if bias else None
+        self.state = Checkpoints.of((kernel - 1, channels), c.max_seq_len, c.prefill_chunk)
+        self.taps = None
+
+    def load_state_dict(self, tree, *, path: str = "") -> None:
+        super().load_state_dict(tree, path=path)
+        C, _, K = self.weight.shape   # one row per tap
+        self.taps = param(np.ascontiguousarray(np.asarray(self.weight).reshape(C, K).T))
+
+    def body(self, x, call: Call):
+        read, write = self.state.at(call)
+        y = F.causal_conv1d(x, self.taps, F.ConvState(read, write))
+        return y if self.bias is None else y + self.bias
 
 
 class Decoder(Graph):
@@ -55,19 +117,27 @@ class CausalLM(Graph):
         prompt = ids is not None
         call = Call(prompt=prompt, start=start if prompt else position, rows=rows, position=position,
                     ids=ids[:rows] if prompt else token, token=token)
-        if prompt:
-            x = self.model.embed_tokens(call.ids)
-        else:
-            x = Copy.step(self.model.embed_tokens.weight[token]).reshape(1, c.hidden_size)
+        x = self.lookup(call.ids) if prompt else self.lookup(token).reshape(1, c.hidden_size)
         if self.rotary_emb is not None:
             call.ropes[self.rotary_emb] = self.rotary_emb.rows(call)
         for layer in self.model.layers:
             x = layer(x, call)
         if prompt:
             x = Copy.step(x[rows - 1]).reshape(1, c.hidden_size)   # the last row's logits alone
-        logits = self.lm_head(self.model.norm(x))
+        logits = self.head(x)
         drawn = Sample.step(logits.reshape(c.vocab_size), self.draws, self.drawn, at=position, vocab=c.vocab_size)
         return logits, carry(token=drawn[position], position=position + 1)
+
+    def lookup(self, ids):
+        """The embedding rows of ``ids`` (bounded as ``ids`` is), or of the decode step's token
+        (iron/lm/causal.py:262-268); a model that scales its embedding overrides it."""
+        if hasattr(ids, "shape") and len(ids.shape) == 1:
+            return self.model.embed_tokens(ids)
+        return Copy.step(self.model.embed_tokens.weight[ids])
+
+    def head(self, x):
+        """The final norm, then the output head (iron/lm/causal.py:253-255)."""
+        return self.lm_head(self.model.norm(x))
 
     # ---- running ----
     def shapes(self) -> list[dict]:

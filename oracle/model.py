@@ -459,7 +459,9 @@ class NumpyDecoder:
         W = w[f"{m}.in_proj.weight"]
         gate, xbc, dt = (self._linear(h, part) for part in (W[:d_inner], W[d_inner : d_inner + C], W[d_inner + C :]))
         taps = np.ascontiguousarray(np.asarray(w[f"{m}.conv1d.weight"]).reshape(C, c.mamba_d_conv).T)
-        conv, self.conv[i] = ops.causal_conv1d(xbc, taps, self.conv[i], w[f"{m}.conv1d.bias"])
+        # a call of one token is a decode step, which sums the taps in its own order
+        conv, self.conv[i] = ops.causal_conv1d(xbc, taps, self.conv[i], w[f"{m}.conv1d.bias"],
+                                               decode=h.shape[0] == 1)
         xbc = ops.silu(conv)
         y, self.ssm[i] = ops.selective_scan(xbc, dt, self.heads[i], self.ssm[i], heads=c.mamba_n_heads,
                                             head_dim=c.mamba_d_head, state_size=c.mamba_d_state,

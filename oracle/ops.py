@@ -237,21 +237,24 @@ def selective_scan(xbc, dt, head, state, *, heads, head_dim, state_size, groups=
     return y.astype(bfloat16), state
 
 
-def causal_conv1d(x, taps, history=None, bias=None):
+def causal_conv1d(x, taps, history=None, bias=None, decode=False):
     """Depth-wise causal filter -- iron/functional.py:147-180 (its recorded steps' references).
 
     ``y[t] = sum_k taps[k] * x[t - K + 1 + k]`` with the ``K - 1`` rows before ``x`` read
     from ``history`` (zeros if None).  The reference accumulates tap by tap in bf16:
-    ``y = x*taps[0]`` rounded, then ``y = y + bf16(x_k * taps[k])`` rounded, for k = 1..K-1
-    (the prompt-chunk order).  Returns ``(y, new_history)``.
+    a prompt chunk records ``y = x_0*taps[0]`` rounded, then ``y = y + bf16(x_k * taps[k])``
+    rounded, for k = 1..K-1 (:172-174); a decode step (one unbounded row, ``decode``) starts
+    from the newest row, ``y = x*taps[K-1]``, then adds the carried rows oldest first
+    (:165-167).  Returns ``(y, new_history)``.
     """
     x, taps = np.asarray(x), np.asarray(taps)
     K, C = taps.shape
     hist = np.zeros((K - 1, C), x.dtype) if history is None else np.asarray(history)
     full = np.concatenate([hist, x], axis=0)
     rows = x.shape[0]
-    y = mul(full[0:rows], taps[0])
-    for k in range(1, K):
+    order = [K - 1, *range(K - 1)] if decode else list(range(K))
+    y = mul(full[order[0] : order[0] + rows], taps[order[0]])
+    for k in order[1:]:
         y = add(y, mul(full[k : k + rows], taps[k]))
     if bias is not None:
         y = add(y, bias)
