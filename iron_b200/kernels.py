@@ -350,17 +350,21 @@ def gemm_qkv_rope(x, wqkv, qkv, angles, k_cache, v_cache, *, H, G, D, start=0, a
 
 
 def selective_scan(xbc, dt, head, state=None, *, heads, head_dim, state_size, groups=1, valid=None,
-                   d_valid=None, want_final=True):
-    """Mamba2's recurrence; returns ``(y bf16, final f32)``.  A leading batch axis is optional."""
-    _bf16(xbc, dt)
+                   d_valid=None, want_final=True, y=None, final=None):
+    """Mamba2's recurrence; returns ``(y bf16, final f32)``.  A leading batch axis is optional.
+    ``final`` may be ``state`` itself: a state is read whole before any of it is written."""
+    _bf16(xbc, dt, y)
     batched = xbc.dim() == 3
     B = xbc.shape[0] if batched else 1
     rows = xbc.shape[-2]
     inner = heads * head_dim
-    y = torch.empty((*xbc.shape[:-1], inner), dtype=torch.bfloat16, device=xbc.device)
+    if y is None:
+        y = torch.empty((*xbc.shape[:-1], inner), dtype=torch.bfloat16, device=xbc.device)
     shape = (B, heads, head_dim, state_size) if batched else (heads, head_dim, state_size)
-    final = torch.empty(shape, dtype=torch.float32, device=xbc.device) if want_final else None
-    if head.dtype != torch.float32 or (state is not None and state.dtype != torch.float32):
+    if final is None and want_final:
+        final = torch.empty(shape, dtype=torch.float32, device=xbc.device)
+    if head.dtype != torch.float32 or (state is not None and state.dtype != torch.float32) or (
+            final is not None and final.dtype != torch.float32):
         raise TypeError("head and state are float32")
     call("iron_selective_scan_bf16", _ptr(xbc), _ptr(dt), _ptr(head), _ptr(state), _ptr(y), _ptr(final),
          B, rows, heads, head_dim, state_size, groups, rows if valid is None else int(valid),

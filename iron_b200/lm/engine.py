@@ -345,6 +345,15 @@ class LlamaEngine:
         torch.cuda.synchronize()
         dist.barrier(group=group)   # every rank's buffer is zeroed before anyone stores into it
 
+    @property
+    def exchange_path(self) -> str:
+        """How a decode step's partial sums meet under tensor parallelism."""
+        if self.tp_size == 1:
+            return "none"
+        if self.peer_buffers is not None and self.c.hidden_size * self.batch <= self.peer_slot_elems:
+            return "peer-memory kernel (stores to every rank's slot, bounded flag wait, rank-ordered f32 sum)"
+        return "nccl all-reduce"
+
     def _reduce_add(self, part: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> None:
         """out = residual + (sum of ``part`` over the ranks): one kernel over peer memory
         for a decode step's vector, NCCL and an add otherwise."""

@@ -395,6 +395,31 @@ def hybrid_redraw(c: DecoderShape, weights: dict[str, np.ndarray]) -> dict[str, 
     return weights
 
 
+def mamba_mixer(h, w, prefix, conv_state, ssm_state, *, heads, head_dim, state_size, groups=1, kernel=4,
+                eps=1e-5):
+    """One Mamba2 mixer over the rows ``h`` of one sequence, operator by operator as
+    iron/applications/granite_hybrid/model.py:120-137 records it: three projections on row
+    slices of ``in_proj``, the causal convolution plus its bias, SiLU, the scan, the product
+    with SiLU of the gate, RMSNorm over ``d_inner``, ``out_proj``.  ``conv_state`` is the
+    ``kernel - 1`` rows before ``h``, ``ssm_state`` the scan's float32 state; returns
+    ``(out, conv_state, ssm_state)`` after the rows."""
+    lin = lambda x, W: (np.asarray(x, np.float32) @ np.asarray(W, np.float32).T).astype(bfloat16)
+    d_inner = heads * head_dim
+    C = d_inner + 2 * groups * state_size
+    W = w[prefix + "in_proj.weight"]
+    gate, xbc, dt = (lin(h, part) for part in (W[:d_inner], W[d_inner : d_inner + C], W[d_inner + C :]))
+    taps = np.ascontiguousarray(np.asarray(w[prefix + "conv1d.weight"]).reshape(C, kernel).T)
+    # a call of one row is a decode step, which sums the taps in its own order
+    conv, conv_state = ops.causal_conv1d(xbc, taps, conv_state, w[prefix + "conv1d.bias"], decode=h.shape[0] == 1)
+    A = -np.exp(np.asarray(w[prefix + "A_log"], np.float32))
+    head = np.stack([np.asarray(w[prefix + "dt_bias"], np.float32), A, np.asarray(w[prefix + "D"], np.float32)],
+                    1).astype(np.float32)
+    y, ssm_state = ops.selective_scan(ops.silu(conv), dt, head, ssm_state, heads=heads, head_dim=head_dim,
+                                      state_size=state_size, groups=groups)
+    y = ops.rms_norm(ops.mul(y, ops.silu(gate)), w[prefix + "norm.weight"], eps)
+    return lin(y, w[prefix + "out_proj.weight"]), conv_state, ssm_state
+
+
 class NumpyDecoder:
     """The reference's host graph for its other decoders, operator by operator in bf16:
     Llama's layer with optional biases and Granite's scalars
@@ -418,13 +443,6 @@ class NumpyDecoder:
         norm = np.asarray(w["model.norm.weight"])
         # the reference divides in bf16 (iron/applications/granite/model.py:81-83)
         self.final_norm = norm if c.logits_scaling == 1 else (norm / bfloat16(c.logits_scaling)).astype(bfloat16)
-        self.heads = {}
-        for i in range(L):
-            if not c.attends(i):
-                m = f"model.layers.{i}.mamba"
-                A = -np.exp(np.asarray(w[f"{m}.A_log"], np.float32))
-                self.heads[i] = np.stack([np.asarray(w[f"{m}.dt_bias"], np.float32), A,
-                                          np.asarray(w[f"{m}.D"], np.float32)], 1).astype(np.float32)
 
     def _linear(self, x, W, bias=None):
         y = (np.asarray(x, np.float32) @ np.asarray(W, np.float32).T).astype(bfloat16)
@@ -453,21 +471,12 @@ class NumpyDecoder:
         return self._linear(o, w[f"{a}.o_proj.weight"], bias("o_proj"))
 
     def _mamba(self, i, h):
-        c, w = self.c, self.w
-        m = f"model.layers.{i}.mamba"
-        d_inner, C = c.d_inner, c.conv_channels
-        W = w[f"{m}.in_proj.weight"]
-        gate, xbc, dt = (self._linear(h, part) for part in (W[:d_inner], W[d_inner : d_inner + C], W[d_inner + C :]))
-        taps = np.ascontiguousarray(np.asarray(w[f"{m}.conv1d.weight"]).reshape(C, c.mamba_d_conv).T)
-        # a call of one token is a decode step, which sums the taps in its own order
-        conv, self.conv[i] = ops.causal_conv1d(xbc, taps, self.conv[i], w[f"{m}.conv1d.bias"],
-                                               decode=h.shape[0] == 1)
-        xbc = ops.silu(conv)
-        y, self.ssm[i] = ops.selective_scan(xbc, dt, self.heads[i], self.ssm[i], heads=c.mamba_n_heads,
-                                            head_dim=c.mamba_d_head, state_size=c.mamba_d_state,
-                                            groups=c.mamba_n_groups)
-        y = ops.rms_norm(ops.mul(y, ops.silu(gate)), w[f"{m}.norm.weight"], c.eps)
-        return self._linear(y, w[f"{m}.out_proj.weight"])
+        c = self.c
+        out, self.conv[i], self.ssm[i] = mamba_mixer(
+            h, self.w, f"model.layers.{i}.mamba.", self.conv[i], self.ssm[i], heads=c.mamba_n_heads,
+            head_dim=c.mamba_d_head, state_size=c.mamba_d_state, groups=c.mamba_n_groups, kernel=c.mamba_d_conv,
+            eps=c.eps)
+        return out
 
     def _mlp(self, i, h):
         c, w, p = self.c, self.w, f"model.layers.{i}"

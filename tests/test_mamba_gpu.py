@@ -128,3 +128,84 @@ def want_plain(x, taps, hist, decode):
     for k in range(Kt - 1):
         want = ops.add(want, ops.mul(full[k : k + 1], taps[k]))
     return want
+
+
+def mixer_weights(E, H, P, N, G, Kc, seed):
+    """A mixer's checkpoint tensors: projections N(0, 1/sqrt(in)), taps N(0, 1/2), decays and
+    time steps as Mamba2 initialises them (A = -exp(U(0, 2.7)), softplus^-1 of dt in 1e-3..1e-1)."""
+    rng = np.random.default_rng(seed)
+    inner, C = H * P, H * P + 2 * G * N
+    dt = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), H))
+    return {
+        "in_proj.weight": normal(rng, (inner + C + H, E), 1 / np.sqrt(E)),
+        "conv1d.weight": normal(rng, (C, 1, Kc), 0.5),
+        "conv1d.bias": normal(rng, (C,), 0.1),
+        "dt_bias": (dt + np.log(-np.expm1(-dt))).astype(bfloat16),
+        "A_log": rng.uniform(0, 2.7, H).astype(bfloat16),
+        "D": np.ones(H, bfloat16),
+        "norm.weight": (1 + rng.standard_normal(inner) / 10).astype(bfloat16),
+        "out_proj.weight": normal(rng, (E, inner), 1 / np.sqrt(inner)),
+    }
+
+
+def assert_layer_close(got, want, what):
+    """The mixer's output is a 3072-term projection of normed rows: a one-ulp flip in the scan's
+    bf16 output moves it by an amount set by the output's scale, so the bound is 2 % of the
+    largest output (each kernel alone is held to its operator's tolerance above)."""
+    got, want = np.asarray(got, np.float32), np.asarray(want, np.float32)
+    err = np.abs(got - want).max()
+    assert err <= 0.02 * np.abs(want).max(), f"{what}: max error {err:.4g} against {np.abs(want).max():.4g}"
+
+
+def test_the_fused_mixer_matches_the_oracle_mixer_across_calls():
+    """Two sequences, a chunk of 200 rows, a chunk of 57 and three decode steps: the
+    convolution rows and scan states carry from call to call, per sequence."""
+    from iron_b200.lm.mamba import MambaMixer
+    from oracle import model as M
+
+    E, H, P, N, G, Kc = 256, 8, 64, 64, 2, 4
+    w = mixer_weights(E, H, P, N, G, Kc, 41)
+    mixer = MambaMixer(w, hidden_size=E, heads=H, head_dim=P, state_size=N, groups=G, kernel=Kc, eps=1e-6,
+                       batch=2, rows=256)
+    rng = np.random.default_rng(42)
+    C = H * P + 2 * G * N
+    states = [(np.zeros((Kc - 1, C), bfloat16), np.zeros((H, P, N), np.float32)) for _ in range(2)]
+    for rows in (200, 57, 1, 1, 1):
+        x = normal(rng, (2, rows, E))
+        got = to_numpy(mixer.forward(to_torch(x)))
+        for b in range(2):
+            want, conv, ssm = M.mamba_mixer(x[b], w, "", *states[b], heads=H, head_dim=P, state_size=N,
+                                            groups=G, kernel=Kc, eps=1e-6)
+            states[b] = (conv, ssm)
+            assert_layer_close(got[b], want, f"sequence {b}, {rows} rows")
+    mixer.check()
+
+
+def test_one_sequence_of_the_full_layer_shape_at_4096_rows(K):
+    """d_model 1536 -> d_inner 3072 (48 heads of 64), state 128, one group, 4096 rows: one batch
+    entry of the 8 x 4096 layer, the scan alone against the sequential oracle and the whole
+    mixer against the oracle mixer."""
+    from iron_b200.lm.mamba import MambaMixer
+    from oracle import model as M
+
+    E, H, P, N, G, Kc, rows = 1536, 48, 64, 128, 1, 4, 4096
+    rng = np.random.default_rng(5001)
+    xbc = normal(rng, (rows, H * P + 2 * N))
+    dt = (rng.standard_normal((rows, H), dtype=np.float32) - 4).astype(bfloat16)
+    head = np.stack([np.zeros(H), -np.exp(rng.uniform(0, 2.7, H)), np.ones(H)], 1).astype(np.float32)
+    want_y, want_s = ops.selective_scan(xbc, dt, head, np.zeros((H, P, N), np.float32), heads=H, head_dim=P,
+                                        state_size=N)
+    y, final = K.selective_scan(to_torch(xbc), to_torch(dt), to_torch(head), None, heads=H, head_dim=P,
+                                state_size=N)
+    assert_verdict(to_numpy(y), want_y, SCAN_TOL, what="scan, 4096 rows")
+    assert_verdict(to_numpy(final), want_s, Tolerance.relative(1e-4, atol=1e-5), what="final state")
+    w = mixer_weights(E, H, P, N, G, Kc, 43)
+    mixer = MambaMixer(w, hidden_size=E, heads=H, head_dim=P, state_size=N, groups=G, kernel=Kc, batch=1,
+                       rows=rows)
+    x = normal(rng, (1, rows, E))
+    got = to_numpy(mixer.forward(to_torch(x)))[0]
+    want, _, _ = M.mamba_mixer(x[0], w, "", np.zeros((Kc - 1, H * P + 2 * N), bfloat16),
+                               np.zeros((H, P, N), np.float32), heads=H, head_dim=P, state_size=N, groups=G,
+                               kernel=Kc)
+    assert_layer_close(got, want, "mixer, 4096 rows")
+    mixer.check()
