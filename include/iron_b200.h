@@ -195,9 +195,10 @@ int iron_copy_rows(const void* src, void* dst, const int* ids, int nrows,
  * also stored there and *carry_position is incremented afterwards, which is how a
  * captured decode loop carries (token, position + 1) to its next replay
  * (iron/lm/causal.py:348).  out_rows > 0 is the length of token_out: an index outside
- * 0 .. out_rows - 1 writes nothing and *carry_position stops growing at out_rows, so a
- * loop replayed past the end of its caches stays inside its buffers; out_rows <= 0 means
- * no bound. */
+ * 0 .. out_rows - 1 writes nothing, and when d_out_index and carry_position are the same
+ * word (the row written is the carried position, a decoder's loop) the position stops
+ * growing at out_rows, so a loop replayed past the end of its caches stays inside its
+ * buffers; out_rows <= 0 means no bound. */
 size_t iron_argmax_workspace_bytes(int n);
 int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out_index,
                      int out_rows, int* carry_token, int* carry_position, void* workspace,

@@ -367,12 +367,14 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __rest
     if (threadIdx.x == 0) {
       for (int w = 1; w < 8; ++w) b = umax64(b, sred[w]);
       const int tok = (int)(~(uint32_t)(b & 0xffffffffull));
-      // out_rows > 0 bounds the row written and stops the carried position at out_rows: a
-      // replay past the end of the caches writes nothing outside them
+      // out_rows > 0 bounds the row written; when the row written IS the carried position
+      // (a decoder's loop: d_out_index and carry_position are one word) the position stops
+      // growing at out_rows, so a replay past the end of the caches stays inside them
       const int at = d_out_index ? *d_out_index : 0;
       if (out_rows <= 0 || (at >= 0 && at < out_rows)) token_out[at] = tok;
       if (carry_token) *carry_token = tok;
-      if (carry_position && (out_rows <= 0 || *carry_position < out_rows)) *carry_position += 1;
+      const bool tied = out_rows > 0 && d_out_index == carry_position;
+      if (carry_position && (!tied || *carry_position < out_rows)) *carry_position += 1;
       *counter = 0;  // leave the workspace ready for the next launch
     }
   }
