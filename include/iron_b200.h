@@ -268,6 +268,37 @@ int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* C
                           const int* d_valid_rows, int* d_status, iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * One decode step's whole attention block of a layer -- input_layernorm, the q/k/v
+ * projections, RoPE, the two cache writes, one-query attention over the cache, o_proj and the
+ * residual add (iron/lm/blocks.py:627-648 `Attention.body`, :472-502 `KVCache.attend`,
+ * :723-728 `DecoderLayer.body`; operators iron/operators/rms_norm.py:10, gemv.py:79, rope.py:58,
+ * copy.py:546, mha.py:191, elementwise_add.py) -- in one launch:
+ *   y = bf16( x + bf16( Wo . att ) ),  att = MHA(RoPE(Wq.h), [cache; RoPE(Wk.h)], [cache; Wv.h]),
+ *   h = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * norm_weight),
+ * every intermediate rounded to bf16 where the separate operators round.  One thread-block
+ * cluster per KV group: its CTAs stage their rows of Wq/Wk/Wv, of the group's column block
+ * of Wo and their slice of the cached keys and values in shared memory before the previous
+ * kernel's result is needed, exchange q/k/v and the attention partials over distributed
+ * shared memory, and leave a float32 partial of y per group in `scratch`; the last cluster to
+ * arrive adds the partials in group order.  Wqkv ((H + 2G) * D, E) as iron_decode_qkv_rope_bf16
+ * takes it, Wo (E, H * D), x, norm_weight, y (E), angles (>= cache_rows, D), caches
+ * (cache_rows, G, D); row `position` (immediate or *d_position, held inside the caches) is
+ * written and keys 0 .. position attend (the last `window + 1` of them when window >= 0).
+ * scratch: iron_decode_attn_block_scratch_bytes(E, G) bytes, zeroed once by the caller
+ * (the kernel leaves its counter zero); it may be shared by launches that are ordered on
+ * one stream.  iron_decode_attn_block_supported() is the cluster size a shape runs with, 0
+ * when its rows do not fit one SM's shared memory (the entry point then returns
+ * IRON_ERR_UNSUPPORTED and the three separate kernels serve).  A copy that does not land
+ * within 2 s sets *d_status to IRON_ERR_TIMEOUT; nothing hangs. */
+size_t iron_decode_attn_block_scratch_bytes(int E, int G);
+int iron_decode_attn_block_supported(int E, int H, int G, int D);
+int iron_decode_attn_block_bf16(const void* Wqkv, const void* Wo, const void* x,
+                                const void* norm_weight, float eps, const void* angles,
+                                int position, const int* d_position, void* k_cache, void* v_cache,
+                                void* y, int E, int H, int G, int D, int cache_rows, int window,
+                                float scale, void* scratch, int* d_status, iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * Mamba2.
  */
 

@@ -47,6 +47,12 @@ SIGNATURES: dict[str, tuple] = {
         _I,
         [_P, _P, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     ),
+    "iron_decode_attn_block_scratch_bytes": (_Z, [_I, _I]),
+    "iron_decode_attn_block_supported": (_I, [_I, _I, _I, _I]),
+    "iron_decode_attn_block_bf16": (
+        _I,
+        [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
+    ),
     "iron_gemm_bf16": (
         _I,
         [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _I, _P, _P],

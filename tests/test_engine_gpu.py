@@ -39,19 +39,23 @@ def toy_config():
         rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 64))
 
 
-@pytest.fixture(scope="module", params=["one-kernel step", "separate launches"])
+@pytest.fixture(scope="module", params=["one-kernel step", "five launches a layer", "three launches a layer"])
 def case(request):
-    """The engine on both of its decode paths: the persistent one-kernel step and the
-    separate launches per projection (what batches and tensor-parallel shards take)."""
+    """The engine on each of its decode paths: the persistent one-kernel step, the separate
+    launches per projection (what batches and tensor-parallel shards take), and the default,
+    a layer's attention block as one launch."""
     from iron_b200.lm.engine import LlamaEngine
 
     mp = pytest.MonkeyPatch()
     mp.setenv("IRON_DECODE_STEP", "1" if request.param == "one-kernel step" else "0")
+    mp.setenv("IRON_ATTN_BLOCK", "1" if request.param == "three launches a layer" else "0")
     request.addfinalizer(mp.undo)
     weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
     with np.load(GOLDEN) as z:
         golden = {k: z[k] for k in z.files}
-    return LlamaEngine(toy_config(), weights, kv_len_hint=64), weights, golden
+    engine = LlamaEngine(toy_config(), weights, kv_len_hint=64)
+    assert engine.attn_block == (request.param == "three launches a layer")
+    return engine, weights, golden
 
 
 def test_decode_token_by_token_matches_the_golden_logits_and_the_oracle(case):
