@@ -268,33 +268,35 @@ int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* C
                           const int* d_valid_rows, int* d_status, iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
- * One decode step's whole attention block of a layer -- input_layernorm, the q/k/v
- * projections, RoPE, the two cache writes, one-query attention over the cache, o_proj and the
- * residual add (iron/lm/blocks.py:627-648 `Attention.body`, :472-502 `KVCache.attend`,
- * :723-728 `DecoderLayer.body`; operators iron/operators/rms_norm.py:10, gemv.py:79, rope.py:58,
- * copy.py:546, mha.py:191, elementwise_add.py) -- in one launch:
- *   y = bf16( x + bf16( Wo . att ) ),  att = MHA(RoPE(Wq.h), [cache; RoPE(Wk.h)], [cache; Wv.h]),
- *   h = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * norm_weight),
- * every intermediate rounded to bf16 where the separate operators round.  One thread-block
- * cluster per KV group: its CTAs stage their rows of Wq/Wk/Wv, of the group's column block
- * of Wo and their slice of the cached keys and values in shared memory before the previous
- * kernel's result is needed, exchange q/k/v and the attention partials over distributed
- * shared memory, and leave a float32 partial of y per group in `scratch`; the last cluster to
- * arrive adds the partials in group order.  Wqkv ((H + 2G) * D, E) as iron_decode_qkv_rope_bf16
- * takes it, Wo (E, H * D), x, norm_weight, y (E), angles (>= cache_rows, D), caches
- * (cache_rows, G, D); row `position` (immediate or *d_position, held inside the caches) is
- * written and keys 0 .. position attend (the last `window + 1` of them when window >= 0).
- * scratch: iron_decode_attn_block_scratch_bytes(E, G) bytes, zeroed once by the caller
- * (the kernel leaves its counter zero); it may be shared by launches that are ordered on
- * one stream.  iron_decode_attn_block_supported() is the cluster size a shape runs with, 0
- * when its rows do not fit one SM's shared memory (the entry point then returns
- * IRON_ERR_UNSUPPORTED and the three separate kernels serve).  A copy that does not land
- * within 2 s sets *d_status to IRON_ERR_TIMEOUT; nothing hangs. */
-size_t iron_decode_attn_block_scratch_bytes(int E, int G);
-int iron_decode_attn_block_supported(int E, int H, int G, int D);
-int iron_decode_attn_block_bf16(const void* Wqkv, const void* Wo, const void* x,
-                                const void* norm_weight, float eps, const void* angles,
-                                int position, const int* d_position, void* k_cache, void* v_cache,
+ * One decode step's attention, o_proj and residual add of a layer in one launch -- the
+ * reference's steps MHA (iron/operators/mha.py:191 as iron/lm/blocks.py:487-502 calls it: one
+ * query row per head over the cache rows 0 .. position, grouped heads, an optional window),
+ * the o_proj GEMV (iron/operators/gemv.py:79, iron/lm/blocks.py:646-648) and the residual add
+ * (iron/lm/blocks.py:723-728):
+ *   y = bf16( x + bf16( Wo . att ) ),   att = bf16( softmax(scale * q K^T) V ) per head.
+ * One thread-block cluster of eight CTAs per KV group: before the previous kernel's results
+ * are needed its CTAs stage their rows of the group's column block of Wo and their slice of
+ * the cached keys and values in shared memory; they exchange the attention partials over
+ * distributed shared memory and leave a float32 partial of y per group in `scratch`; for
+ * each eighth of the rows the last CTA to arrive adds the partials in group order.
+ * q (H, D) as iron_decode_qkv_rope_bf16 leaves it, Wo (E, H * D), x and y (E), the caches
+ * (cache_rows, G, D) with row `position` already written (immediate, or *d_position held
+ * inside the caches); keys 0 .. position attend (the last `window + 1` when window >= 0).
+ * scratch: iron_decode_attn_oproj_scratch_bytes(E, G) bytes, zeroed once by the caller (the
+ * kernel leaves its counters zero); launches ordered on one stream may share it.
+ * iron_decode_attn_oproj_supported() is the number of cache rows of a group one CTA holds at
+ * a time (longer contexts run in several passes), 0 when a CTA's rows of Wo do not fit one
+ * SM's shared memory or there are more groups than clusters the GPU holds at once (the entry
+ * point then returns IRON_ERR_UNSUPPORTED and the two separate kernels serve).  A copy that
+ * does not land within 2 s sets *d_status to IRON_ERR_TIMEOUT; nothing hangs.
+ * iron_decode_attn_oproj_trace is a diagnostic: a device buffer of 16 x (8 G) 64-bit words
+ * that later launches on the current device fill with each CTA's phase timestamps in
+ * nanoseconds (NULL turns it off again). */
+size_t iron_decode_attn_oproj_scratch_bytes(int E, int G);
+int iron_decode_attn_oproj_supported(int E, int H, int G, int D);
+void iron_decode_attn_oproj_trace(void* d_trace);
+int iron_decode_attn_oproj_bf16(const void* q, const void* Wo, const void* x, int position,
+                                const int* d_position, const void* k_cache, const void* v_cache,
                                 void* y, int E, int H, int G, int D, int cache_rows, int window,
                                 float scale, void* scratch, int* d_status, iron_stream_t stream);
 
@@ -311,7 +313,14 @@ int iron_decode_attn_block_bf16(const void* Wqkv, const void* Wo, const void* x,
  * state / final_state are (batch, H, P, N) f32 (state NULL = zeros, final_state NULL =
  * not wanted).  xbc (batch, rows, H*P + 2*G*N), dt (batch, rows, H), y (batch, rows, H*P),
  * all dense.  Rows >= valid_rows of y are zeros.  N is 16, 32, 64 or 128; P % 8 == 0.
- * The reference operator has no batch axis: batch > 1 is the independent-sequence axis. */
+ * The reference operator has no batch axis: batch > 1 is the independent-sequence axis.
+ * Calls of 32 rows or more with P = 64 and N of 64 or 128 run in the chunked form on the
+ * tensor cores (64-row chunks: scores C B^T, decay-masked scores times x, C times the
+ * carried state, the state update, as bf16 products with float32 accumulation and a float32
+ * state): the same function within the operator's tolerance (iron/operators/
+ * selective_scan.py:353-356), not bit for bit the step-by-step kernel.  iron_set_scan_chunked(0)
+ * (or IRON_SCAN_CHUNKED=0 in the environment) keeps every call step by step. */
+void iron_set_scan_chunked(int enabled);
 int iron_selective_scan_bf16(const void* xbc, const void* dt, const void* head,
                              const void* state, void* y, void* final_state, int batch,
                              int rows, int heads, int head_dim, int state_size, int groups,

@@ -47,11 +47,12 @@ SIGNATURES: dict[str, tuple] = {
         _I,
         [_P, _P, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     ),
-    "iron_decode_attn_block_scratch_bytes": (_Z, [_I, _I]),
-    "iron_decode_attn_block_supported": (_I, [_I, _I, _I, _I]),
-    "iron_decode_attn_block_bf16": (
+    "iron_decode_attn_oproj_scratch_bytes": (_Z, [_I, _I]),
+    "iron_decode_attn_oproj_supported": (_I, [_I, _I, _I, _I]),
+    "iron_decode_attn_oproj_trace": (None, [_P]),
+    "iron_decode_attn_oproj_bf16": (
         _I,
-        [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
+        [_P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     ),
     "iron_gemm_bf16": (
         _I,
@@ -86,6 +87,7 @@ SIGNATURES: dict[str, tuple] = {
         _I,
         [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _P, _I, _I, _I, _F, _I, _I, _P],
     ),
+    "iron_set_scan_chunked": (None, [_I]),
     "iron_selective_scan_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "iron_causal_conv1d_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P]),
     "iron_gemm_qkv_rope_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),

@@ -14,6 +14,7 @@
 // the call read from a history buffer, with the reference's operator chain roundings
 // (each product and each partial sum rounded to bf16), optional bias and SiLU fused.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace iron {
 
@@ -356,6 +357,345 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const ConvParams p) {
   }
 }
 
+
+// ---------------------------------------------------------------- chunked scan (tensor cores)
+// The same recurrence in the chunked ("state-space dual") form for prompt-length calls.  With
+// a_t = step_t * A (<= 0) and cum_t the running sum of a over a chunk of Q = 64 rows,
+//
+//   y_t     = sum_{j <= t} exp(cum_t - cum_j) step_j (C_t . B_j) x_j  +  exp(cum_t) C_t . S_prev  +  D x_t
+//   S_next  = exp(cum_Q) S_prev  +  sum_j exp(cum_Q - cum_j) step_j  x_j (x) B_j
+//
+// so a chunk is four small matrix products instead of 64 dependent steps: the scores
+// C B^T (Q x Q over the state axis), the decay-masked scores times X (Q x P), C times the
+// carried state (Q x P over the state axis) and the state update X_w^T B (P x N over the
+// chunk's rows).  All four run as bf16 mma.sync with float32 accumulation: x, B and C are
+// the call's own bf16 inputs (exact), the decay-masked scores, the weighted rows x_j w_j and
+// the carried state are rounded to bf16 once each as operands.  The decays are differences
+// of the float32 running sum (never a product of 64 factors) and every difference is <= 0,
+// so nothing overflows.  The state itself stays in float32 registers from chunk to chunk.
+// One CTA of four warps owns one (sequence, head): warp w owns rows 16 w .. 16 w + 15 of
+// every Q-row tile and rows 16 w .. of the (P x N) state; three CTAs share an SM, which is
+// what overlaps one CTA's loads with its neighbours' products.
+constexpr int kSsdQ = 64;       // rows per chunk
+constexpr int kSsdP = 64;       // head_dim this kernel takes
+constexpr int kSsdThreads = 128;
+
+template <int N>
+struct SsdSmem {
+  static constexpr int PX = kSsdP + 8, PN = N + 8, PQ = kSsdQ + 8;   // row pitches in elements
+  static constexpr size_t off_x = 0;
+  static constexpr size_t off_b = off_x + (size_t)kSsdQ * PX * 2;
+  static constexpr size_t off_c = off_b + (size_t)kSsdQ * PN * 2;
+  static constexpr size_t off_m = off_c + (size_t)kSsdQ * PN * 2;    // y tiles, then the weighted rows of x
+  static constexpr int PZ = kSsdP + 4;                              // floats
+  static constexpr size_t off_z = off_m + (size_t)kSsdQ * PQ * 2;    // C S_prev^T, float32
+  static constexpr size_t off_f = off_z + (size_t)kSsdQ * PZ * 4;    // cum, step, w, exp(cum): 4 x Q floats
+  static constexpr size_t total = off_f + 4 * kSsdQ * sizeof(float);
+};
+
+template <int N>
+__global__ void __launch_bounds__(kSsdThreads, 3) ssd_scan_kernel(const ScanParams p) {
+  using S = SsdSmem<N>;
+  constexpr int Q = kSsdQ, P = kSsdP, PX = S::PX, PN = S::PN, PQ = S::PQ, PZ = S::PZ;
+  extern __shared__ __align__(128) unsigned char ssd_smem[];
+  __nv_bfloat16* sX = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_x);
+  __nv_bfloat16* sB = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_b);
+  __nv_bfloat16* sC = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_c);
+  __nv_bfloat16* sM = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_m);
+  float* sZ = reinterpret_cast<float*>(ssd_smem + S::off_z);
+  float* s_cum = reinterpret_cast<float*>(ssd_smem + S::off_f);
+  float* s_step = s_cum + Q;
+  float* s_w = s_step + Q;
+  float* s_ecum = s_w + Q;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g4 = lane >> 2, t4 = lane & 3;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int grp = h / (p.H / p.G);
+  const int inner = p.H * P;
+  pdl_wait();
+  pdl_launch();
+  int valid = p.d_valid ? min(*p.d_valid, p.rows) : p.valid;
+  valid = max(valid, 0);
+  const float dt_bias = p.head[h * 3], A = p.head[h * 3 + 1], Dh = p.head[h * 3 + 2];
+  const __nv_bfloat16* xbc = p.xbc + (size_t)b * p.xbc_batch;
+  const __nv_bfloat16* dtp = p.dt + (size_t)b * p.dt_batch;
+  __nv_bfloat16* yb = p.y + (size_t)b * p.y_batch;
+
+  // the state: warp w holds rows 16 w + g4 and + 8, columns 8 i + 2 t4, + 1 of every n-tile i
+  float st[N / 8][4];
+  {
+    const float* src = p.state ? p.state + (size_t)b * p.state_batch + (size_t)h * P * N : nullptr;
+#pragma unroll
+    for (int i = 0; i < N / 8; ++i) {
+      const int r0 = 16 * warp + g4, n0 = 8 * i + 2 * t4;
+      float2 lo = make_float2(0.f, 0.f), hi = lo;
+      if (src) {
+        lo = *reinterpret_cast<const float2*>(src + (size_t)r0 * N + n0);
+        hi = *reinterpret_cast<const float2*>(src + (size_t)(r0 + 8) * N + n0);
+      }
+      st[i][0] = lo.x; st[i][1] = lo.y; st[i][2] = hi.x; st[i][3] = hi.y;
+    }
+  }
+
+  auto cp16 = [](void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+  };
+  auto load_rows = [&](__nv_bfloat16* dst, int pitch, int width16, size_t col0, int c0) {
+    // rows c0 .. c0 + Q - 1 of the call, `width16` 16-byte pieces from column col0; rows past the call are zeros
+    for (int idx = tid; idx < Q * width16; idx += kSsdThreads) {
+      const int r = idx / width16, ch = idx - r * width16;
+      __nv_bfloat16* d = dst + (size_t)r * pitch + ch * 8;
+      if (c0 + r < p.rows) cp16(d, xbc + (size_t)(c0 + r) * p.width + col0 + ch * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  for (int c0 = 0; c0 < p.rows; c0 += Q) {
+    // ---- the chunk's rows of x, B and C ----
+    load_rows(sX, PX, P / 8, (size_t)h * P, c0);
+    load_rows(sB, PN, N / 8, (size_t)inner + (size_t)grp * N, c0);
+    load_rows(sC, PN, N / 8, (size_t)inner + (size_t)(p.G + grp) * N, c0);
+    // ---- steps and their running sum (warps 0 and 1: a row each) ----
+    if (tid < Q) {
+      const int t = c0 + tid;
+      float step = 0.f;
+      if (t < valid) step = softplus_f32(__bfloat162float(dtp[(size_t)t * p.H + h]) + dt_bias);
+      float a = step * A;                                  // rows past the bound: a = 0, step = 0
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, a, off);
+        if (lane >= off) a += v;
+      }
+      s_cum[tid] = a;
+      s_step[tid] = step;
+    }
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float cum = 0.f, total = 0.f;
+    if (tid < Q) {
+      total = s_cum[31] + s_cum[Q - 1];                    // each warp scanned its own 32 rows:
+      cum = s_cum[tid] + (tid >= 32 ? s_cum[31] : 0.f);    // the first warp's total carries into the second
+    }
+    __syncthreads();
+    if (tid < Q) {
+      s_cum[tid] = cum;
+      s_ecum[tid] = __expf(cum);
+      s_w[tid] = __expf(total - cum) * s_step[tid];
+    }
+    __syncthreads();
+    const float cum_last = s_cum[Q - 1];
+    const int r_lo = 16 * warp + g4, r_hi = r_lo + 8;      // this lane's two rows of every 16-row tile
+
+    // ---- scores S = C B^T, masked and decayed into M (rows of this warp) ----
+    uint32_t m_hi[Q / 16][4], m_lo[Q / 16][4];
+    {
+      float acc[Q / 8][4];
+#pragma unroll
+      for (int i = 0; i < Q / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < N / 16; ++ks) {
+        uint32_t a[4];
+        load_a_rowmajor(a, sC, PN, 16 * warp, ks * 16, lane);
+#pragma unroll
+        for (int i2 = 0; i2 < Q / 16; ++i2) {
+          uint32_t bb[4];
+          load_b_nk(bb, sB, PN, i2 * 16, ks * 16, lane);
+          mma_bf16_16816(acc[2 * i2], a, bb[0], bb[1]);
+          mma_bf16_16816(acc[2 * i2 + 1], a, bb[2], bb[3]);
+        }
+      }
+      // The accumulator layout of two adjacent 8-column tiles is the A-fragment layout of one
+      // 16-deep step, so the masked scores go straight back into the tensor cores from
+      // registers, split into a bf16 head and a bf16 remainder (two products) to keep float32's
+      // accuracy.
+      const float cl = s_cum[r_lo], ch = s_cum[r_hi];
+#pragma unroll
+      for (int i = 0; i < Q / 8; ++i) {
+        const int j0 = 8 * i + 2 * t4, j1 = j0 + 1;
+        const float cj0 = s_cum[j0], cj1 = s_cum[j1], sj0 = s_step[j0], sj1 = s_step[j1];
+        const float m00 = j0 <= r_lo ? acc[i][0] * __expf(cl - cj0) * sj0 : 0.f;
+        const float m01 = j1 <= r_lo ? acc[i][1] * __expf(cl - cj1) * sj1 : 0.f;
+        const float m10 = j0 <= r_hi ? acc[i][2] * __expf(ch - cj0) * sj0 : 0.f;
+        const float m11 = j1 <= r_hi ? acc[i][3] * __expf(ch - cj1) * sj1 : 0.f;
+        const uint32_t h0 = pack_bf16x2(m00, m01), h1 = pack_bf16x2(m10, m11);
+        const int ks = i >> 1, half = (i & 1) * 2;        // tile i is k-columns 8 (i & 1) .. of step i / 2
+        m_hi[ks][half] = h0;
+        m_hi[ks][half + 1] = h1;
+        m_lo[ks][half] = pack_bf16x2(m00 - bf16_lo(h0), m01 - bf16_hi(h0));
+        m_lo[ks][half + 1] = pack_bf16x2(m10 - bf16_lo(h1), m11 - bf16_hi(h1));
+      }
+    }
+
+    // ---- Z = C S_prev^T for all rows of the chunk and this warp's 16 columns: the carried
+    // state is the B operand straight from the registers that hold it (the accumulator layout
+    // of two 8-column tiles is the B-fragment layout of a 16-deep step), split into a bf16
+    // head and remainder so that the read-out keeps float32's accuracy ----
+    {
+      float zt[Q / 16][2][4];
+#pragma unroll
+      for (int mt = 0; mt < Q / 16; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) { zt[mt][nt][0] = zt[mt][nt][1] = zt[mt][nt][2] = zt[mt][nt][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < N / 16; ++ks) {
+        uint32_t bh[2][2], bl[2][2];     // [column tile: rows r_lo / r_hi of the state][k half]
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+          const float* v = st[2 * ks + kh];
+          bh[0][kh] = pack_bf16x2(v[0], v[1]);
+          bh[1][kh] = pack_bf16x2(v[2], v[3]);
+          bl[0][kh] = pack_bf16x2(v[0] - bf16_lo(bh[0][kh]), v[1] - bf16_hi(bh[0][kh]));
+          bl[1][kh] = pack_bf16x2(v[2] - bf16_lo(bh[1][kh]), v[3] - bf16_hi(bh[1][kh]));
+        }
+#pragma unroll
+        for (int mt = 0; mt < Q / 16; ++mt) {
+          uint32_t a[4];
+          load_a_rowmajor(a, sC, PN, 16 * mt, ks * 16, lane);
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            mma_bf16_16816(zt[mt][nt], a, bh[nt][0], bh[nt][1]);
+            mma_bf16_16816(zt[mt][nt], a, bl[nt][0], bl[nt][1]);
+          }
+        }
+      }
+#pragma unroll
+      for (int mt = 0; mt < Q / 16; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = 16 * warp + 8 * nt + 2 * t4;
+          *reinterpret_cast<float2*>(sZ + (size_t)(16 * mt + g4) * PZ + col) = make_float2(zt[mt][nt][0], zt[mt][nt][1]);
+          *reinterpret_cast<float2*>(sZ + (size_t)(16 * mt + g4 + 8) * PZ + col) = make_float2(zt[mt][nt][2], zt[mt][nt][3]);
+        }
+    }
+    __syncthreads();
+
+    // ---- y = M X  +  exp(cum_t) Z  +  D x  (rows of this warp) ----
+    {
+      float y[P / 8][4];
+#pragma unroll
+      for (int i = 0; i < P / 8; ++i) { y[i][0] = y[i][1] = y[i][2] = y[i][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < Q / 16; ++ks) {
+#pragma unroll
+        for (int i2 = 0; i2 < P / 16; ++i2) {
+          uint32_t bb[4];
+          load_b_kn(bb, sX, PX, i2 * 16, ks * 16, lane);
+          mma_bf16_16816(y[2 * i2], m_hi[ks], bb[0], bb[1]);
+          mma_bf16_16816(y[2 * i2 + 1], m_hi[ks], bb[2], bb[3]);
+          mma_bf16_16816(y[2 * i2], m_lo[ks], bb[0], bb[1]);
+          mma_bf16_16816(y[2 * i2 + 1], m_lo[ks], bb[2], bb[3]);
+        }
+      }
+      const float el = s_ecum[r_lo], eh = s_ecum[r_hi];
+      const bool live_lo = c0 + r_lo < valid, live_hi = c0 + r_hi < valid;
+#pragma unroll
+      for (int i = 0; i < P / 8; ++i) {
+        const int p0 = 8 * i + 2 * t4;
+        const uint32_t xl = *reinterpret_cast<const uint32_t*>(sX + (size_t)r_lo * PX + p0);
+        const uint32_t xh = *reinterpret_cast<const uint32_t*>(sX + (size_t)r_hi * PX + p0);
+        const float2 zl = *reinterpret_cast<const float2*>(sZ + (size_t)r_lo * PZ + p0);
+        const float2 zh = *reinterpret_cast<const float2*>(sZ + (size_t)r_hi * PZ + p0);
+        const float v00 = fmaf(Dh, bf16_lo(xl), fmaf(el, zl.x, y[i][0]));
+        const float v01 = fmaf(Dh, bf16_hi(xl), fmaf(el, zl.y, y[i][1]));
+        const float v10 = fmaf(Dh, bf16_lo(xh), fmaf(eh, zh.x, y[i][2]));
+        const float v11 = fmaf(Dh, bf16_hi(xh), fmaf(eh, zh.y, y[i][3]));
+        *reinterpret_cast<uint32_t*>(sM + (size_t)r_lo * PQ + p0) = live_lo ? pack_bf16x2(v00, v01) : 0u;
+        *reinterpret_cast<uint32_t*>(sM + (size_t)r_hi * PQ + p0) = live_hi ? pack_bf16x2(v10, v11) : 0u;
+      }
+      __syncwarp();
+      // the warp's 16 rows of y leave as 128-byte rows
+      for (int idx = lane; idx < 16 * (P / 8); idx += 32) {
+        const int r = idx / (P / 8), ch = idx - r * (P / 8);
+        const int t = c0 + 16 * warp + r;
+        if (t < p.rows)
+          *reinterpret_cast<uint4*>(yb + (size_t)t * inner + (size_t)h * P + ch * 8) =
+              *reinterpret_cast<const uint4*>(sM + (size_t)(16 * warp + r) * PQ + ch * 8);
+      }
+    }
+    __syncthreads();   // every warp is done with C and Z
+
+    // ---- the weighted rows x_j w_j, then S = exp(cum_Q) S + X_w^T B.  The rows are rounded to
+    // bf16 as an operand; their remainders go through a second product (over C's bytes, which
+    // the chunk no longer needs), so the state keeps float32's accuracy from chunk to chunk ----
+    __nv_bfloat16* sXl = sC;
+    for (int idx = tid; idx < Q * (P / 2); idx += kSsdThreads) {
+      const int j = idx / (P / 2), pp = (idx - j * (P / 2)) * 2;
+      const uint32_t xv = *reinterpret_cast<const uint32_t*>(sX + (size_t)j * PX + pp);
+      const float w = s_w[j];
+      const float v0 = bf16_lo(xv) * w, v1 = bf16_hi(xv) * w;
+      const uint32_t hi = pack_bf16x2(v0, v1);
+      *reinterpret_cast<uint32_t*>(sM + (size_t)j * PQ + pp) = hi;
+      *reinterpret_cast<uint32_t*>(sXl + (size_t)j * PQ + pp) = pack_bf16x2(v0 - bf16_lo(hi), v1 - bf16_hi(hi));
+    }
+    __syncthreads();
+    {
+      const float decay = __expf(cum_last);
+#pragma unroll
+      for (int i = 0; i < N / 8; ++i) { st[i][0] *= decay; st[i][1] *= decay; st[i][2] *= decay; st[i][3] *= decay; }
+#pragma unroll
+      for (int ks = 0; ks < Q / 16; ++ks) {
+        uint32_t a[4], al[4];
+        load_a_transposed(a, sM, PQ, 16 * warp, ks * 16, lane);
+        load_a_transposed(al, sXl, PQ, 16 * warp, ks * 16, lane);
+#pragma unroll
+        for (int i2 = 0; i2 < N / 16; ++i2) {
+          uint32_t bb[4];
+          load_b_kn(bb, sB, PN, i2 * 16, ks * 16, lane);
+          mma_bf16_16816(st[2 * i2], a, bb[0], bb[1]);
+          mma_bf16_16816(st[2 * i2 + 1], a, bb[2], bb[3]);
+          mma_bf16_16816(st[2 * i2], al, bb[0], bb[1]);
+          mma_bf16_16816(st[2 * i2 + 1], al, bb[2], bb[3]);
+        }
+      }
+    }
+    __syncthreads();   // x, B, C and the weighted rows are free for the next chunk
+  }
+
+  if (p.final_state) {
+    float* dst = p.final_state + (size_t)b * p.state_batch + (size_t)h * P * N;
+    const int r0 = 16 * warp + g4;
+#pragma unroll
+    for (int i = 0; i < N / 8; ++i) {
+      const int n0 = 8 * i + 2 * t4;
+      *reinterpret_cast<float2*>(dst + (size_t)r0 * N + n0) = make_float2(st[i][0], st[i][1]);
+      *reinterpret_cast<float2*>(dst + (size_t)(r0 + 8) * N + n0) = make_float2(st[i][2], st[i][3]);
+    }
+  }
+}
+
+template <int N>
+static int launch_ssd(const ScanParams& p, int batch, cudaStream_t stream) {
+  static DeviceOnce configured;   // the attribute is per device
+  if (!configured.done()) {
+    if (cudaFuncSetAttribute(ssd_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SsdSmem<N>::total) != cudaSuccess)
+      return IRON_ERR_LAUNCH;
+    configured.mark();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.H, batch);
+  cfg.blockDim = dim3(kSsdThreads);
+  cfg.dynamicSmemBytes = SsdSmem<N>::total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  return cudaLaunchKernelEx(&cfg, ssd_scan_kernel<N>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+}
+
+// Calls of a prompt's length on the shapes the chunked kernel takes run on it;
+// IRON_SCAN_CHUNKED=0 keeps every call on the step-by-step kernel.
+static std::atomic<int> g_ssd_on{-1};
+static bool ssd_enabled() {
+  int on = g_ssd_on.load(std::memory_order_relaxed);
+  if (on < 0) {
+    const char* e = getenv("IRON_SCAN_CHUNKED");
+    on = (e && e[0] == '0') ? 0 : 1;
+    g_ssd_on.store(on, std::memory_order_relaxed);
+  }
+  return on != 0;
+}
+
 template <typename... Args>
 static int launch_scan_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -370,6 +710,8 @@ static int launch_scan_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaS
 }  // namespace iron
 
 using namespace iron;
+
+extern "C" void iron_set_scan_chunked(int enabled) { g_ssd_on.store(enabled ? 1 : 0, std::memory_order_relaxed); }
 
 extern "C" int iron_selective_scan_bf16(const void* xbc, const void* dt, const void* head, const void* state,
                                         void* y, void* final_state, int batch, int rows, int heads,
@@ -396,6 +738,10 @@ extern "C" int iron_selective_scan_bf16(const void* xbc, const void* dt, const v
   const dim3 block(kScanThreads);
   const dim3 grid64(heads * ((head_dim + 63) / 64), batch);
   cudaStream_t s = (cudaStream_t)stream;
+  if (head_dim == kSsdP && rows >= 32 && ssd_enabled()) {   // the chunked form on the tensor cores
+    if (state_size == 128) return launch_ssd<128>(p, batch, s);
+    if (state_size == 64) return launch_ssd<64>(p, batch, s);
+  }
   switch (state_size) {
     case 16: return launch_scan_pdl(selective_scan_kernel<16, 4>, grid64, block, s, p);
     case 32: return launch_scan_pdl(selective_scan_kernel<32, 4>, grid64, block, s, p);

@@ -74,24 +74,26 @@ def decode_qkv_rope(Wqkv, x, angles, k_cache, v_cache, q_out, *, H, G, D, positi
     return q_out
 
 
-def attn_block_supported(E: int, H: int, G: int, D: int) -> int:
-    """The cluster size the one-launch attention block runs a shape with; 0: not at all."""
-    return _lib.load().iron_decode_attn_block_supported(E, H, G, D)
+def attn_oproj_supported(E: int, H: int, G: int, D: int) -> int:
+    """Cache rows of a KV group one CTA of the one-launch attention + o_proj holds at a time;
+    0: the shape does not run on it."""
+    return _lib.load().iron_decode_attn_oproj_supported(E, H, G, D)
 
 
-def attn_block_scratch(E: int, G: int, device) -> torch.Tensor:
-    return torch.zeros(_lib.load().iron_decode_attn_block_scratch_bytes(E, G), dtype=torch.uint8, device=device)
+def attn_oproj_scratch(E: int, G: int, device) -> torch.Tensor:
+    return torch.zeros(_lib.load().iron_decode_attn_oproj_scratch_bytes(E, G), dtype=torch.uint8, device=device)
 
 
-def decode_attn_block(Wqkv, Wo, x, norm_weight, angles, k_cache, v_cache, y, *, H, G, D, scratch, position=0,
-                      d_position=None, eps=1e-5, window=None, scale=None, status=None):
-    """One decode step's attention block of a layer in one launch: RMSNorm, q/k/v, RoPE, the
-    cache writes, attention over the cache, o_proj and the residual add; ``y = x + ...``."""
-    _bf16(Wqkv, Wo, x, norm_weight, angles, k_cache, v_cache, y)
-    call("iron_decode_attn_block_bf16", _ptr(Wqkv), _ptr(Wo), _ptr(x), _ptr(norm_weight), float(eps),
-         _ptr(angles), int(position), _ptr(d_position), _ptr(k_cache), _ptr(v_cache), _ptr(y), x.numel(), H, G, D,
-         min(k_cache.shape[0], angles.shape[0]), -1 if window is None else int(window),
-         1.0 / math.sqrt(D) if scale is None else float(scale), _ptr(scratch), _ptr(status), _stream())
+def decode_attn_oproj(q, Wo, x, k_cache, v_cache, y, *, G, scratch, position=0, d_position=None, window=None,
+                      scale=None, status=None):
+    """One decode step's attention over the cache rows 0 .. position, o_proj and the residual
+    add in one launch: ``y = x + Wo @ attention(q, K, V)``.  ``q`` (H, D); caches (S, G, D)."""
+    _bf16(q, Wo, x, k_cache, v_cache, y)
+    H, D = q.shape[-2], q.shape[-1]
+    call("iron_decode_attn_oproj_bf16", _ptr(q), _ptr(Wo), _ptr(x), int(position), _ptr(d_position),
+         _ptr(k_cache), _ptr(v_cache), _ptr(y), x.numel(), H, G, D, k_cache.shape[0],
+         -1 if window is None else int(window), 1.0 / math.sqrt(D) if scale is None else float(scale),
+         _ptr(scratch), _ptr(status), _stream())
     return y
 
 

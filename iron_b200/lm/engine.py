@@ -10,9 +10,9 @@ operator steps per layer run as five kernels,
     4. RMSNorm + gate/up GEMV + SiLU + multiply                (iron_gemv_swiglu_bf16)
     5. down_proj GEMV + residual add                           (iron_gemv_bf16)
 
--- and where a layer's q/k/v and o_proj rows fit the SMs' shared memory (one sequence, one
-GPU), kernels 1-3 are one launch, a thread-block cluster per KV group
-(iron_decode_attn_block_bf16), so a layer is three dependent launches --
+-- and where a CTA's share of o_proj fits an SM's shared memory (one sequence, one GPU),
+kernels 2 and 3 are one launch, a thread-block cluster per KV group whose weights and keys
+are staged while kernel 1 still runs (iron_decode_attn_oproj_bf16) --
 
 between an embedding-row gather and the final norm + tied-head GEMV + greedy draw, all
 captured in one CUDA graph.  The per-call values (token, position) live in a small device
@@ -119,11 +119,11 @@ class LlamaEngine:
                            and E % 32 == 0 and F % 32 == 0 and V % 8 == 0 and max(E, F, H * D) <= 8192
                            and os.environ.get("IRON_DECODE_STEP", "0") == "1")
         self._fused_step_wanted = self.fused_step
-        # One sequence on one GPU runs a layer's attention block (norm, q/k/v, RoPE, cache
-        # writes, attention, o_proj, residual) as one launch where the shape's rows fit an SM's
-        # shared memory; IRON_ATTN_BLOCK=0 keeps the three separate kernels.
-        self.attn_block = (batch == 1 and tp_size == 1 and os.environ.get("IRON_ATTN_BLOCK", "1") != "0"
-                           and K.attn_block_supported(E, H, G, D) > 0)
+        # One sequence on one GPU runs a layer's attention, o_proj and residual add as one
+        # launch (a cluster per KV group) where a CTA's rows of Wo fit an SM's shared memory;
+        # IRON_ATTN_OPROJ=0 keeps the two separate kernels.
+        self.attn_oproj = (batch == 1 and tp_size == 1 and os.environ.get("IRON_ATTN_OPROJ", "1") != "0"
+                           and K.attn_oproj_supported(E, H, G, D) > 0)
 
         # ---- plan the arena: residents first, then the decode step's transients ----
         plan = ArenaPlan()
@@ -225,7 +225,7 @@ class LlamaEngine:
         self._peer_exchange_setup()
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
-        self.ab_scratch = K.attn_block_scratch(E, G, self.device) if self.attn_block else None
+        self.ab_scratch = K.attn_oproj_scratch(E, G, self.device) if self.attn_oproj else None
         self.draws = None   # (batch, S, 4) int32 draw rows once a sampler is set
         self.fuse_rope = os.environ.get("IRON_PREFILL_FUSED_ROPE", "1") != "0"
         self._chunk_launches: int | None = None
@@ -384,7 +384,7 @@ class LlamaEngine:
             return 1 + 8 * self.c.num_hidden_layers + 3
         if self.fused_step:
             return 1
-        return 1 + (3 if self.attn_block else 5) * self.c.num_hidden_layers + 2
+        return 1 + (4 if self.attn_oproj else 5) * self.c.num_hidden_layers + 2
 
     @property
     def weight_bytes_per_token(self) -> int:
@@ -454,10 +454,11 @@ class LlamaEngine:
         K.copy_rows(self.embed, x, ids=d_token, nrows=1, row_bytes=E2, src_rows=c.vocab_size)
         hints = 0 if tp else self.prefetch_hints
         for i, l in enumerate(self.layers):
-            if self.attn_block and not hints:
-                K.decode_attn_block(l["wqkv"], l["wo"], x, l["ln1"], self.angles, l["k"][0], l["v"][0], y,
-                                    H=H, G=G, D=D, scratch=self.ab_scratch, d_position=d_pos, eps=c.eps,
-                                    window=c.window, scale=c.attention_scale, status=self.status)
+            if self.attn_oproj and not hints:
+                K.decode_qkv_rope(l["wqkv"], x, self.angles, l["k"][0], l["v"][0], self.q[0],
+                                  H=H, G=G, D=D, d_position=d_pos, norm_weight=l["ln1"], eps=c.eps)
+                K.decode_attn_oproj(self.q[0], l["wo"], x, l["k"][0], l["v"][0], y, G=G, scratch=self.ab_scratch,
+                                    d_position=d_pos, window=c.window, scale=c.attention_scale, status=self.status)
                 K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
                 K.gemv(l["wd"], self.act[0], x, residual=y)
                 continue

@@ -1,7 +1,8 @@
-"""The one-launch attention block of a decode step against the chain of operator references
-(B200): RMSNorm, q/k/v GEMVs, RoPE, the cache writes, one-query attention with grouped heads,
-o_proj and the residual add (iron/lm/blocks.py:627-648, :472-502, :723-728), every operator
-rounding to bf16 as the oracle's restatements do, and against the three separate kernels.
+"""A decode step's attention + o_proj + residual add in one launch (after the fused q/k/v
+kernel) against the chain of operator references (B200): RMSNorm, q/k/v GEMVs, RoPE, the
+cache writes, one-query attention with grouped heads, o_proj and the residual add
+(iron/lm/blocks.py:627-648, :472-502, :723-728), every operator rounding to bf16 as the
+oracle's restatements do, and against the two separate kernels it replaces.
 """
 
 import numpy as np
@@ -33,7 +34,8 @@ CASES = [
     (2048, 32, 8, 64, 2304, 0, None),
     (2048, 32, 8, 64, 2304, 5, None),
     (2048, 32, 8, 64, 2304, 2100, None),
-    (2048, 32, 8, 64, 4096, 3500, None),     # more keys per CTA than one shared-memory chunk holds
+    (2048, 32, 8, 64, 4096, 3500, None),     # more keys per CTA than one shared-memory pass holds
+    (2048, 32, 8, 64, 4096, 2303, None),
     (2048, 32, 8, 64, 2304, 2047, 511),
     (512, 16, 4, 64, 256, 200, None),        # the toy decoder's shape
     (1024, 8, 4, 128, 512, 300, None),       # 128-wide heads, two query heads a group
@@ -42,12 +44,12 @@ CASES = [
 
 
 @pytest.mark.parametrize("E,H,G,D,S,pos,window", CASES)
-def test_attention_block_matches_the_operator_chain(E, H, G, D, S, pos, window):
+def test_attention_and_o_proj_in_one_launch_match_the_operator_chain(E, H, G, D, S, pos, window):
     import torch
 
     from iron_b200 import kernels as K
 
-    assert K.attn_block_supported(E, H, G, D) in (8, 16)
+    assert K.attn_oproj_supported(E, H, G, D) >= 32
     rng = np.random.default_rng(E + pos)
     x = normal(rng, (E,))
     w = {"norm": (1 + rng.standard_normal(E) / 10).astype(bfloat16),
@@ -57,31 +59,26 @@ def test_attention_block_matches_the_operator_chain(E, H, G, D, S, pos, window):
     kc, vc = normal(rng, (S, G, D)), normal(rng, (S, G, D))
     want, wk, wv = chain(x, w, angles, kc, vc, pos, H, G, D, window=window)
     d = {k: to_torch(v) for k, v in w.items()}
-    tk, tv = to_torch(kc), to_torch(vc)
+    tx, tk, tv = to_torch(x), to_torch(kc), to_torch(vc)
+    q = torch.empty(1, H, D, dtype=torch.bfloat16, device="cuda")
     y = torch.empty(E, dtype=torch.bfloat16, device="cuda")
-    scratch = K.attn_block_scratch(E, G, "cuda")
+    scratch = K.attn_oproj_scratch(E, G, "cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     dpos = torch.tensor([pos], dtype=torch.int32, device="cuda")
-    for _ in range(2):   # the scratch's counter is left ready for the next launch
-        K.decode_attn_block(d["qkv"], d["o"], to_torch(x), d["norm"], to_torch(angles), tk, tv, y, H=H, G=G, D=D,
-                            scratch=scratch, d_position=dpos, window=window, status=status)
+    for _ in range(2):   # the scratch's counters are left ready for the next launch
+        K.decode_qkv_rope(d["qkv"], tx, to_torch(angles), tk, tv, q[0], H=H, G=G, D=D, d_position=dpos,
+                          norm_weight=d["norm"])
+        K.decode_attn_oproj(q[0], d["o"], tx, tk, tv, y, G=G, scratch=scratch, d_position=dpos, window=window,
+                            status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert_bf16_bound(to_numpy(y), want, "y")
-    # the cache rows are the rotated k and v, to the bit where the projection's sum agrees
     assert_bf16_bound(to_numpy(tk[pos]), wk, "k row")
     assert_bf16_bound(to_numpy(tv[pos]), wv, "v row")
-    untouched = np.ones(S, bool)
-    untouched[pos] = False
-    assert np.array_equal(to_numpy(tk)[untouched].view(np.uint16), kc[untouched].view(np.uint16))
-    # and it is what the three separate kernels give, within the same bound
-    tk2, tv2 = to_torch(kc), to_torch(vc)
-    q = torch.empty(1, H, D, dtype=torch.bfloat16, device="cuda")
+    # and it is what the two separate kernels give, within the same bound
     att = torch.empty(1, H, D, dtype=torch.bfloat16, device="cuda")
-    K.decode_qkv_rope(d["qkv"], to_torch(x), to_torch(angles), tk2, tv2, q[0], H=H, G=G, D=D, position=pos,
-                      norm_weight=d["norm"])
-    K.mha_decode(q, tk2[None], tv2[None], att, kv_valid=pos + 1, window=window)
-    y2 = K.gemv(d["o"], att.view(-1), residual=to_torch(x))
+    K.mha_decode(q, tk[None], tv[None], att, kv_valid=pos + 1, window=window)
+    y2 = K.gemv(d["o"], att.view(-1), residual=tx)
     assert_bf16_bound(to_numpy(y), to_numpy(y2).astype(np.float32), "against the separate kernels")
 
 
@@ -90,10 +87,11 @@ def test_shapes_whose_rows_do_not_fit_an_sm_are_refused_on_the_host():
 
     from iron_b200 import _lib, kernels as K
 
-    assert K.attn_block_supported(3072, 24, 8, 128) == 0      # the 3B shape: three 128-wide heads a group
-    assert K.attn_block_supported(4096, 32, 8, 128) == 0
+    assert K.attn_oproj_supported(3072, 24, 8, 128) == 0      # the 3B shape: three 128-wide heads a group
+    assert K.attn_oproj_supported(4096, 32, 8, 128) == 0      # four 128-wide heads a group
+    assert K.attn_oproj_supported(2048, 32, 16, 64) == 0      # more groups than clusters resident at once
     z = torch.zeros(64, dtype=torch.bfloat16, device="cuda")
-    rc = _lib.load().iron_decode_attn_block_bf16(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1e-5,
-                                                 z.data_ptr(), 0, None, z.data_ptr(), z.data_ptr(), z.data_ptr(),
-                                                 3072, 24, 8, 128, 16, -1, 1.0, z.data_ptr(), None, None)
+    rc = _lib.load().iron_decode_attn_oproj_bf16(z.data_ptr(), z.data_ptr(), z.data_ptr(), 0, None, z.data_ptr(),
+                                                 z.data_ptr(), z.data_ptr(), 3072, 24, 8, 128, 16, -1, 1.0,
+                                                 z.data_ptr(), None, None)
     assert rc == -4   # IRON_ERR_UNSUPPORTED: nothing launched

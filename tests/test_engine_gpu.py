@@ -39,22 +39,22 @@ def toy_config():
         rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 64))
 
 
-@pytest.fixture(scope="module", params=["one-kernel step", "five launches a layer", "three launches a layer"])
+@pytest.fixture(scope="module", params=["one-kernel step", "five launches a layer", "four launches a layer"])
 def case(request):
     """The engine on each of its decode paths: the persistent one-kernel step, the separate
     launches per projection (what batches and tensor-parallel shards take), and the default,
-    a layer's attention block as one launch."""
+    a layer's attention and o_proj as one launch."""
     from iron_b200.lm.engine import LlamaEngine
 
     mp = pytest.MonkeyPatch()
     mp.setenv("IRON_DECODE_STEP", "1" if request.param == "one-kernel step" else "0")
-    mp.setenv("IRON_ATTN_BLOCK", "1" if request.param == "three launches a layer" else "0")
+    mp.setenv("IRON_ATTN_OPROJ", "1" if request.param == "four launches a layer" else "0")
     request.addfinalizer(mp.undo)
     weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
     with np.load(GOLDEN) as z:
         golden = {k: z[k] for k in z.files}
     engine = LlamaEngine(toy_config(), weights, kv_len_hint=64)
-    assert engine.attn_block == (request.param == "three launches a layer")
+    assert engine.attn_oproj == (request.param == "four launches a layer")
     return engine, weights, golden
 
 

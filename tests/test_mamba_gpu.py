@@ -24,6 +24,24 @@ def K():
     return kernels
 
 
+@pytest.fixture(params=["chunked", "step by step"])
+def form(request):
+    """Both forms of the scan: prompt-length calls on the 64-wide-head shapes take the chunked
+    tensor-core kernel unless it is switched off; everything else runs step by step either way."""
+    from iron_b200 import _lib
+
+    lib = _lib.load()
+    lib.iron_set_scan_chunked(1 if request.param == "chunked" else 0)
+    yield request.param
+    lib.iron_set_scan_chunked(1)
+
+
+def state_tolerance(form):
+    """Both forms keep the state in float32; the chunked form adds a chunk's rows as a bf16 head
+    and a bf16 remainder, which is float32's accuracy but another order of the sums."""
+    return Tolerance.relative(1e-4, atol=1e-4 if form == "chunked" else 1e-5)
+
+
 def trained(rows, H, P, N, G, seed=3):
     """Heads as a trained Mamba2's are (selective_scan.py:32-43): A < 0, so the state decays."""
     rng = np.random.default_rng(seed)
@@ -42,16 +60,16 @@ SCAN_CASES = [
 
 
 @pytest.mark.parametrize("rows,H,P,N,G", SCAN_CASES)
-def test_selective_scan_matches_reference(K, rows, H, P, N, G):
+def test_selective_scan_matches_reference(K, form, rows, H, P, N, G):
     xbc, dt, head, state = trained(rows, H, P, N, G)
     want_y, want_s = ops.selective_scan(xbc, dt, head, state, heads=H, head_dim=P, state_size=N, groups=G)
     y, final = K.selective_scan(to_torch(xbc), to_torch(dt), to_torch(head), to_torch(state),
                                 heads=H, head_dim=P, state_size=N, groups=G)
     assert_verdict(to_numpy(y), want_y, SCAN_TOL, what="y")
-    assert_verdict(to_numpy(final), want_s, Tolerance.relative(1e-4, atol=1e-5), what="final state")
+    assert_verdict(to_numpy(final), want_s, state_tolerance(form), what="final state")
 
 
-def test_scan_bounded_rows_and_chunked_equals_whole(K):
+def test_scan_bounded_rows_and_chunked_equals_whole(K, form):
     import torch
 
     rows, H, P, N, G = 200, 4, 64, 128, 1
@@ -63,7 +81,7 @@ def test_scan_bounded_rows_and_chunked_equals_whole(K):
     got = to_numpy(y)
     assert_verdict(got, want_y, SCAN_TOL)
     assert not got[131:].astype(np.float32).any()
-    assert_verdict(to_numpy(final), want_s, Tolerance.relative(1e-4, atol=1e-5))
+    assert_verdict(to_numpy(final), want_s, state_tolerance(form))
     # two calls, the second starting from the first's final state, equal one call
     y1, mid = K.selective_scan(to_torch(xbc[:77]), to_torch(dt[:77]), to_torch(head), to_torch(state),
                                heads=H, head_dim=P, state_size=N)
@@ -71,10 +89,14 @@ def test_scan_bounded_rows_and_chunked_equals_whole(K):
                                head_dim=P, state_size=N)
     whole, end_whole = K.selective_scan(to_torch(xbc), to_torch(dt), to_torch(head), to_torch(state),
                                         heads=H, head_dim=P, state_size=N)
-    assert torch.equal(torch.cat([y1, y2]), whole) and torch.allclose(end, end_whole, rtol=1e-5, atol=1e-6)
+    if form == "chunked":   # 77 + 123 rows cut the 64-row chunks elsewhere than 200 rows do
+        assert_verdict(to_numpy(torch.cat([y1, y2])), to_numpy(whole), SCAN_TOL)
+        assert_verdict(to_numpy(end), to_numpy(end_whole), state_tolerance(form))
+    else:
+        assert torch.equal(torch.cat([y1, y2]), whole) and torch.allclose(end, end_whole, rtol=1e-5, atol=1e-6)
 
 
-def test_granite_hybrid_layer_shape_batched(K):
+def test_granite_hybrid_layer_shape_batched(K, form):
     """d_inner 3072 = 48 heads x 64, d_state 128, 1 group; batch 2 x 512 rows of the 8 x 4096 config."""
     rng = np.random.default_rng(5001)
     B, rows, H, P, N = 2, 512, 48, 64, 128
@@ -87,7 +109,7 @@ def test_granite_hybrid_layer_shape_batched(K):
         want_y, want_s = ops.selective_scan(xbc[b], dt[b], head, np.zeros((H, P, N), np.float32), heads=H,
                                             head_dim=P, state_size=N)
         assert_verdict(to_numpy(y[b]), want_y, SCAN_TOL, what=f"y[{b}]")
-        assert_verdict(to_numpy(final[b]), want_s, Tolerance.relative(1e-4, atol=1e-5))
+        assert_verdict(to_numpy(final[b]), want_s, state_tolerance(form))
 
 
 @pytest.mark.parametrize("rows,C,Kt,decode", [(1, 3328, 4, True), (300, 3328, 4, False), (2048, 256, 4, False),
@@ -198,7 +220,7 @@ def test_one_sequence_of_the_full_layer_shape_at_4096_rows(K):
     y, final = K.selective_scan(to_torch(xbc), to_torch(dt), to_torch(head), None, heads=H, head_dim=P,
                                 state_size=N)
     assert_verdict(to_numpy(y), want_y, SCAN_TOL, what="scan, 4096 rows")
-    assert_verdict(to_numpy(final), want_s, Tolerance.relative(1e-4, atol=1e-5), what="final state")
+    assert_verdict(to_numpy(final), want_s, Tolerance.relative(1e-4, atol=1e-4), what="final state")
     w = mixer_weights(E, H, P, N, G, Kc, 43)
     mixer = MambaMixer(w, hidden_size=E, heads=H, head_dim=P, state_size=N, groups=G, kernel=Kc, batch=1,
                        rows=rows)
