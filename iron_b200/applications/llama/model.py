@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import dataclasses
+from pathlib import Path
 
 import numpy as np
 
@@ -72,6 +73,11 @@ LLAMA_3B = LlamaConfig(
 )
 
 
+#: tunables by operator shape, one file per device (``b200.json``), as the reference keeps its
+#: ``profiles/npu2.json`` beside the model (iron/applications/llama/model.py:97)
+PROFILES = Path(__file__).with_name("profiles")
+
+
 def checkpoint_shapes(c: DecoderConfig) -> dict[str, tuple[int, ...]]:
     """A Llama checkpoint's tensor names and shapes for ``c``, in the order the reference's
     random fill draws them (iron/tests/support/llama_model.py:76-98); ``lm_head.weight`` only
@@ -118,6 +124,7 @@ def _llama():
         """Llama 3 on ``config``'s shape and a checkpoint's ``weights``."""
 
         config_class = LlamaConfig
+        profile = PROFILES
 
     return Llama
 

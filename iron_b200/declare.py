@@ -470,3 +470,12 @@ class Operator(metaclass=OperatorMeta):
 
 def ceildiv(a: int, b: int) -> int:
     return -(-a // b)
+
+
+def __getattr__(name):
+    # ``Profile`` lives beside the declarations (iron/common/declare/__init__.py exports both)
+    if name == "Profile":
+        from .profile import Profile
+
+        return Profile
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

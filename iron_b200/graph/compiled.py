@@ -139,6 +139,30 @@ class Graph:
                 Graph._load_into(value, tree, full, missing, seen)
 
     # ---- recording ----
+    def resolved_profile(self):
+        """The ``Profile`` this graph's steps are made through (iron/common/graph/compiled.py:734-742):
+        ``profile`` may be one, a JSON file, or a directory holding one file per device
+        (``b200.json`` is the one read here); None where there is none."""
+        from pathlib import Path
+
+        from ..profile import Profile
+
+        held = self.__dict__.get("_profile_loaded")
+        if held is not None:
+            return held[0]
+        given = self.profile
+        loaded = None
+        if isinstance(given, Profile):
+            loaded = given
+        elif given is not None:
+            path = Path(given)
+            if path.is_dir():
+                path = path / "b200.json"
+            if path.exists():
+                loaded = Profile.load(path)
+        self.__dict__["_profile_loaded"] = (loaded,)
+        return loaded
+
     def _parameters(self):
         sig = inspect.signature(type(self).body)
         params = list(sig.parameters.values())[1:]
@@ -149,7 +173,7 @@ class Graph:
     def record(self, **shapes) -> Recording:
         """Run ``body`` on handles for inputs of ``shapes`` (``name=(shape, dtype)``)."""
         inputs, values = self._parameters()
-        rec = Recorder(self.name)
+        rec = Recorder(self.name, self.resolved_profile())
         handles, names = [], []
         for p in inputs:
             if p.name in shapes:

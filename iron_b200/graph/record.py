@@ -47,8 +47,9 @@ def carry(**values) -> Carry:
 
 
 class Recorder:
-    def __init__(self, graph_name: str = "graph"):
+    def __init__(self, graph_name: str = "graph", profile=None):
         self.graph_name = graph_name
+        self.profile = profile      # a Profile: fills the tunables a step's construction leaves open
         self.steps: list[Step] = []
         self.buffers: list[BufferRef] = []
         self._held: dict[int, BufferRef] = {}
@@ -136,7 +137,7 @@ class Recorder:
         if adopt is not None:
             solved = adopt(solved)   # a class may read a derived axis to fill a field it defaults from
         solved = {k: v for k, v in solved.items() if k not in decl.members or decl.members[k].derive is None}
-        op = cls(**solved)
+        op = cls(**solved) if self.profile is None else self.profile.make(cls, **solved)
         values: dict[str, Any] = dict(per_call_given)
         # a bound on an operand's leading axis binds the extent that axis sizes
         for name, h in ins.items():
