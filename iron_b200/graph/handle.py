@@ -88,6 +88,32 @@ class Param(Held):
     def astype(self, dtype):
         return np.asarray(self).astype(dtype)
 
+    # Outside a body a loaded param computes as its array (a model folds a scalar into a norm's
+    # weight as it loads); with a handle the handle's own arithmetic records a step.
+    def _numeric(self, other, fn):
+        if isinstance(other, Handle):
+            return NotImplemented
+        return fn(np.asarray(self), np.asarray(other) if isinstance(other, Held) else other)
+
+    def __truediv__(self, other):
+        return self._numeric(other, lambda a, b: a / b)
+
+    def __mul__(self, other):
+        return self._numeric(other, lambda a, b: a * b)
+
+    __rmul__ = __mul__
+
+    def __add__(self, other):
+        return self._numeric(other, lambda a, b: a + b)
+
+    __radd__ = __add__
+
+    def __sub__(self, other):
+        return self._numeric(other, lambda a, b: a - b)
+
+    def __neg__(self):
+        return -np.asarray(self)
+
 
 class Weight(Held):
     """A constant array a graph computes with (a RoPE table)."""
