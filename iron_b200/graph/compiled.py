@@ -65,6 +65,10 @@ def walk(node, path: str = "", seen=None):
             yield from walk(value, sub, seen)
 
 
+class StepCheckFailed(AssertionError):
+    """A step of a graph compiled with ``check=True`` wrote something outside its tolerance."""
+
+
 class MissingWeights(KeyError):
     """``load_state_dict`` found no array for some of a graph's params."""
 
@@ -203,13 +207,19 @@ class Graph:
     def _signature(shapes) -> tuple:
         return tuple((n, tuple(s), np.dtype(d).name) for n, (s, d) in shapes.items())
 
-    def compile(self, **shapes) -> "CompiledGraph":
-        """The version for inputs of ``shapes``; compiled once per signature."""
+    def compile(self, *, check: bool = False, **shapes) -> "CompiledGraph":
+        """The version for inputs of ``shapes``; compiled once per signature.
+
+        ``check=True`` gives a version that runs every step as a launch of its own and holds
+        what it wrote to the step's ``reference()`` on the very inputs the device read, inside
+        the step's ``tolerance()``, raising ``StepCheckFailed`` at the first step outside it
+        (iron/common/graph/compiled.py:556-557, iron/common/image/callable.py:785-797): the
+        way to find which kernel of a graph is wrong."""
         versions = self.__dict__.setdefault("_versions", {})
-        key = self._signature(shapes)
+        key = (self._signature(shapes), bool(check))
         if key not in versions:
             plan = self.__dict__.setdefault("_plan", ArenaPlan())
-            versions[key] = CompiledGraph(self, self.record(**shapes), plan)
+            versions[key] = CompiledGraph(self, self.record(**shapes), plan, check=check)
         return versions[key]
 
     def reference(self, *arrays, **values):
@@ -266,8 +276,10 @@ _TORCH = {"bfloat16": "bfloat16", "float32": "float32", "int32": "int32", "float
 class CompiledGraph:
     """One version of a graph on the device."""
 
-    def __init__(self, graph: Graph, recording: Recording, plan: ArenaPlan):
+    def __init__(self, graph: Graph, recording: Recording, plan: ArenaPlan, check: bool = False):
         import torch
+
+        self.check = check
 
         if not torch.cuda.is_available():
             raise RuntimeError("compile() needs a CUDA device; Graph.reference() runs on the host")
@@ -349,6 +361,51 @@ class CompiledGraph:
             bufs = {n: self._view(h) for n, h in (*step.inputs.items(), *step.outputs.items())}
             op.launch(bufs, vals)
 
+    def _launch_checked(self, vals: Mapping[str, int]) -> None:
+        """Every step alone: read its inputs back, launch it, read what it wrote, and judge that
+        against the step's numpy reference on those inputs (only the rows the call bounds)."""
+        from ..tensor import torch_to_numpy
+        from ..verify import compare
+
+        torch = self._torch
+        for step in self.recording.steps:
+            bound = {n: evaluate(e, vals) for n, e in step.values.items()}
+            op = step.op.bind(**bound) if bound else step.op
+            tol = op.tolerance()
+            if tol is None:
+                raise StepCheckFailed(f"{step.name} states no tolerance to be held to")
+            torch.cuda.synchronize()
+            ins = {b.name: torch_to_numpy(self._view(step.inputs[b.name])).copy() for b in op.inputs}
+            before = {b.name: torch_to_numpy(self._view(step.outputs[b.name])).copy() for b in op.outputs}
+            static = {n: v for n, v in step.values.items() if not isinstance(v, Expr)}
+            launch_op = step.op.bind(**static) if static else step.op
+            dvals = {f"d_{n}": self._values[self._slots[v] : self._slots[v] + 1]
+                     for n, v in step.values.items() if isinstance(v, Expr)}
+            bufs = {n: self._view(h) for n, h in (*step.inputs.items(), *step.outputs.items())}
+            launch_op.launch(bufs, dvals)
+            torch.cuda.synchronize()
+            out = op.reference(*[ins[b.name] for b in op.inputs])
+            out = out if isinstance(out, tuple) else (out,)
+            bound_fn = tol.bound(*[ins[b.name] for b in op.inputs]) if tol.kind == "bound" else None
+            for b, want in zip(op.outputs, out):
+                h = step.outputs[b.name]
+                expected = before[b.name].reshape(h.shape).copy()
+                want = np.asarray(want).reshape(h.shape)
+                rows = None if h.bound is None else evaluate(h.rows_bound(), vals)
+                if type(op).__name__ == "Copy":
+                    r0, n = bound.get("dst_row", 0), bound.get("valid", op.rows)
+                    expected[r0 : r0 + n] = want[r0 : r0 + n]
+                elif rows is None or not h.shape:
+                    expected[...] = want
+                else:
+                    expected[:rows] = want[:rows]
+                got = torch_to_numpy(self._view(h)).reshape(h.shape)
+                sel = slice(None) if rows is None or not h.shape or type(op).__name__ == "Copy" else slice(0, rows)
+                verdict = compare(got[sel], expected[sel], tol,
+                                  bound=None if bound_fn is None else np.asarray(bound_fn).reshape(h.shape)[sel])
+                if not verdict:
+                    raise StepCheckFailed(f"step {step.name}, output {b.name}: {verdict.detail}")
+
     def __call__(self, *arrays, **values):
         torch = self._torch
         from ..tensor import capturing, numpy_to_torch
@@ -379,7 +436,9 @@ class CompiledGraph:
         done = torch.cuda.Event()
         done.record()
         self._ring_done[i] = done
-        if self._cuda_graph is None:
+        if self.check:
+            self._launch_checked(vals)
+        elif self._cuda_graph is None:
             self._launch_all()                      # warm-up outside capture
             torch.cuda.synchronize()
             side = torch.cuda.Stream()

@@ -105,3 +105,31 @@ def test_llama_compiled_graphs_match_the_golden_logits_prompt_then_decode():
         want.append(int(golden[M.golden_key(tokens)].argmax()))
         tokens = np.append(tokens, want[-1])
     assert engine.complete(prompt, 4) == want
+
+
+def test_check_mode_runs_every_step_alone_and_names_the_step_that_is_wrong(monkeypatch):
+    """``compile(check=True)``: each step of the toy Llama's decode step and prompt chunk is
+    launched on its own and held to its ``reference()`` on the inputs the device read; then one
+    operator's launch is sabotaged and the check names that step."""
+    from iron_b200.applications.llama.model import Llama, Llama3RopeScaling, LlamaConfig
+    from iron_b200.graph import StepCheckFailed
+    from iron_b200.operators.silu import SiLU
+
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=512, num_hidden_layers=2, num_attention_heads=16,
+                      num_key_value_heads=4, head_dim=64, intermediate_size=2048, rope_theta=500000.0,
+                      max_seq_len=256, eps=1e-5, prefill_chunk=256,
+                      rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 64))
+    weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
+    model = Llama(cfg, weights)
+    ids = np.zeros(256, np.int32)
+    ids[:8] = np.random.default_rng(7).integers(0, 1024, 8)
+    chunk = model.compile(check=True, ids=((256,), np.int32))
+    assert chunk is not model.compile(ids=((256,), np.int32))
+    logits, carried = chunk(ids, position=7, start=0, rows=8)
+    step = model.compile(check=True)
+    logits2, carried2 = step(token=carried["token"], position=8)
+    assert carried2["position"] == 9
+    # break SiLU's launch: its output stays whatever the buffer held
+    monkeypatch.setattr(SiLU, "launch", lambda self, buffers, values: None)
+    with pytest.raises(StepCheckFailed, match="SiLU"):
+        step(token=carried["token"], position=9)
