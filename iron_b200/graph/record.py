@@ -55,7 +55,9 @@ class Recorder:
         self._held: dict[int, BufferRef] = {}
         self._consts: dict[tuple, BufferRef] = {}
         self._token = None
-        self.limits: list[tuple[Any, int, int, str]] = []   # (expr, lo, hi, what) checked per call
+        # (first row, rows moved, rows of the buffer, what): first + moved <= buffer, checked per call;
+        # a run bounded per call moves only its bound's rows, so only those must lie inside
+        self.limits: list[tuple[Any, Any, int, str]] = []
 
     # ---- context ----
     def __enter__(self):
@@ -225,7 +227,7 @@ class Recorder:
                 scaled = self._rows_of(off, cols)
                 values[name] = scaled
                 total = h.buffer.elements // cols
-                self.limits.append((scaled, 0, total - rows, f"{h.buffer.name} rows"))
+                self.limits.append((scaled, values.get("valid", rows), total, f"{h.buffer.name} rows"))
             else:
                 if off % cols:
                     raise TypeError("a copied view starts on a row boundary")
@@ -263,10 +265,10 @@ class Recording:
 
     def check_limits(self, values: Mapping[str, int]) -> None:
         """Refuse a call whose per-call indices or bounds leave their buffers, before any dispatch."""
-        for expr, lo, hi, what in self.limits:
-            v = evaluate(expr, values)
-            if not lo <= v <= hi:
-                raise IndexError(f"{what}: {v} is outside {lo}..{hi} for {dict(values)}")
+        for first, moved, total, what in self.limits:
+            v, n = evaluate(first, values), evaluate(moved, values)
+            if v < 0 or n < 0 or v + n > total:
+                raise IndexError(f"{what}: rows {v}..{v + n} are outside 0..{total} for {dict(values)}")
         for step in self.steps:
             for name, e in step.values.items():
                 f = type(step.op).declaration.per_calls.get(name)

@@ -108,8 +108,11 @@ class CausalLM(Graph):
             self.lm_head.weight = self.model.embed_tokens.weight
         self.load_state_dict(weights)
         self._weights = weights
-        self._held = 0   # positions the caches hold (device path)
-        self._held_ref = 0
+        # the session whose tokens the caches hold, and the one ``history_logits`` / ``generate`` run in
+        from .session import Session
+
+        self.holder = None
+        self.session = Session(self)
 
     def body(self, ids=None, *, token: Carried[np.int32] = np.int32(0), position: Carried[np.int32] = np.int32(0),
              start: Scratchpad[np.int32] = np.int32(0), rows: Scratchpad[np.int32] = np.int32(1)):
@@ -125,7 +128,8 @@ class CausalLM(Graph):
         if prompt:
             x = Copy.step(x[rows - 1]).reshape(1, c.hidden_size)   # the last row's logits alone
         logits = self.head(x)
-        drawn = Sample.step(logits.reshape(c.vocab_size), self.draws, self.drawn, at=position, vocab=c.vocab_size)
+        drawn = Sample.step(logits.reshape(c.vocab_size), self.draws, self.drawn, row=position, at=position,
+                            vocab=c.vocab_size)
         return logits, carry(token=drawn[position], position=position + 1)
 
     def lookup(self, ids):
@@ -171,6 +175,79 @@ class CausalLM(Graph):
         logits = logits if isinstance(logits, np.ndarray) else logits.numpy()
         return np.asarray(logits, np.float32).reshape(-1), carried
 
+    #: ``OnHost`` turns this on: the versions are stood in by the graph's host reference
+    on_host = False
+
+    @property
+    def recurrent(self) -> list:
+        """Each state a layer carries from position to position that restarts only at some
+        positions (iron/lm/causal.py:229-243): the mixers' ``Checkpoints``."""
+        found = {}
+        for layer in self.model.layers:
+            for _, value in self._walk_checkpoints(layer):
+                found.setdefault(id(value), value)
+        return list(found.values())
+
+    @staticmethod
+    def _walk_checkpoints(node, seen=None):
+        seen = set() if seen is None else seen
+        if id(node) in seen:
+            return
+        seen.add(id(node))
+        if isinstance(node, Checkpoints):
+            yield None, node
+            return
+        children = []
+        if isinstance(node, Graph):
+            children = [v for k, v in vars(node).items() if not k.startswith("_")]
+        elif isinstance(node, (list, tuple)):
+            children = list(node)
+        for child in children:
+            if isinstance(child, (Graph, Checkpoints, list, tuple)):
+                yield from CausalLM._walk_checkpoints(child, seen)
+
+    def call_version(self, ids=None, **values):
+        """Run one call -- the prompt chunk when ``ids`` is given, else the decode step -- on the
+        device (compiled versions) or on the host (``on_host``); ``(float32 logits, carried)``."""
+        if self.on_host:
+            logits, carried = self.reference(ids, **values) if ids is not None else self.reference(**values)
+        elif ids is not None:
+            logits, carried = self.compile(ids=((self.config.prefill_chunk,), np.int32))(ids, **values)
+        else:
+            logits, carried = self.compile()(**values)
+        logits = logits if isinstance(logits, np.ndarray) else logits.numpy()
+        return np.asarray(logits, np.float32).reshape(-1), carried
+
+    def write_draws(self, first: int, count: int, sampler) -> None:
+        """Fill the draw rows of positions ``first .. first + count`` from ``sampler``'s
+        uniforms (rows of zeros draw greedily), as iron/lm/session.py:83-92 writes them."""
+        rows = np.zeros((self.config.max_seq_len, ROW_WORDS), np.int32)
+        if sampler is not None and sampler.temperature != 0:
+            rows[first : first + count] = sampler.rows(count)
+        if self.on_host:
+            self.draws.host = rows.reshape(-1).copy()
+        else:
+            for version in self.__dict__.get("_versions", {}).values():
+                version.write(self.draws, rows)
+            if not self.__dict__.get("_versions"):
+                self.compile().write(self.draws, rows)
+
+    def history_logits(self, tokens) -> np.ndarray:
+        """Logits after the whole history ``tokens``, running only what the caches do not hold
+        (``Session.logits``)."""
+        return self.session.logits(tokens)
+
+    def generate(self, tokens, max_tokens: int, sampler=None) -> list[int]:
+        """``max_tokens`` tokens drawn after ``tokens`` (greedy without a sampler)."""
+        return list(self.session.draw(tokens, max_tokens, sampler))
+
+    def stream(self, tokens, max_tokens: int, sampler=None):
+        """``generate`` as an iterator, each token yielded as it is drawn."""
+        return self.session.draw(tokens, max_tokens, sampler)
+
+    def forget(self, position: int) -> None:
+        self.session.forget(position)
+
     def logits(self, tokens, start: int = 0) -> np.ndarray:
         """Float32 logits after the last of ``tokens`` run at positions ``start...`` on the device."""
         return self._run(tokens, start, on_host=False)[0]
@@ -184,3 +261,20 @@ class CausalLM(Graph):
         from .engine import LlamaEngine
 
         return LlamaEngine(self.config, self._weights, **kwargs)
+
+
+class OnHost:
+    """A model with its versions stood in by its graph's host reference (iron/lm/model.py:667-695):
+    mixed in before the model's own class, it compiles nothing and needs no GPU --
+
+        class HostLlama(OnHost, Llama): pass
+    """
+
+    on_host = True
+
+    def logits(self, tokens, start: int | None = None) -> np.ndarray:
+        """With ``start``: the tokens run at those positions; without: the whole history, resuming
+        from what the caches hold (``Session.logits``), as the reference's ``Model.logits`` does."""
+        if start is None:
+            return self.session.logits(tokens)
+        return self._run(tokens, start, on_host=True)[0]
