@@ -54,11 +54,13 @@ def peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
 
 
-def timed_loops(run, rewind, steps: int, barrier, min_seconds: float = 0.5, max_loops: int = 64) -> list[float]:
+def timed_loops(run, rewind, steps: int, barrier, min_seconds: float = 0.5, max_loops: int = 64,
+                agree=None) -> list[float]:
     """Time ``run()`` (which launches exactly ``steps`` steps) with CUDA events, a barrier and a
     synchronisation on both sides, again and again until ``min_seconds`` have been timed;
-    ``rewind()`` puts the inputs back between loops, outside the timed region.  Returns every
-    loop's milliseconds."""
+    ``rewind()`` puts the inputs back between loops, outside the timed region.  ``agree`` turns a
+    rank's timed total into the one every rank stops by (the maximum over the ranks), so that
+    all ranks run the same number of loops.  Returns every loop's milliseconds."""
     import torch
 
     out: list[float] = []
@@ -71,7 +73,8 @@ def timed_loops(run, rewind, steps: int, barrier, min_seconds: float = 0.5, max_
         stop.record()
         barrier()
         out.append(start.elapsed_time(stop))
-        if sum(out) >= min_seconds * 1e3 or len(out) >= max_loops:
+        total = sum(out) if agree is None else agree(sum(out))
+        if total >= min_seconds * 1e3 or len(out) >= max_loops:
             return out
 
 
@@ -288,6 +291,11 @@ def make_barrier(world: int):
     return barrier
 
 
+def make_agree(world: int, device):
+    """The maximum of a number over the ranks (every rank gets the same answer)."""
+    return lambda x: max_over_ranks([x], world, device)[0]
+
+
 def max_over_ranks(values, world: int, device):
     import torch
     import torch.distributed as dist
@@ -335,7 +343,7 @@ def measure_tp(args, rank: int, world: int, device, nb: int, steps: int) -> dict
     rewind()
     for _ in range(warm):
         engine.step()
-    loops = timed_loops(run, rewind, steps, make_barrier(world))
+    loops = timed_loops(run, rewind, steps, make_barrier(world), agree=make_agree(world, device))
     (ms,) = max_over_ranks([median(loops)], world, device)
     engine.check()
     pk = peaks()
@@ -391,7 +399,8 @@ def measure_batch(args, rank: int, world: int, device, total: int, steps: int, e
     for _ in range(warm):
         engine.step()
     with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as clocks:
-        loops = timed_loops(run, lambda: engine.set_batch(first, positions), steps, barrier)
+        loops = timed_loops(run, lambda: engine.set_batch(first, positions), steps, barrier,
+                            agree=make_agree(world, device))
     ms_e2e = None
     if e2e:
         # host-facing: every step's tokens go in from pinned host memory and come back
@@ -408,7 +417,7 @@ def measure_batch(args, rank: int, world: int, device, total: int, steps: int, e
         rewind_host()
         for i in range(warm):
             state["toks"] = engine.decode_batch(state["toks"], [CONTEXT + i] * len(mine))
-        ms_e2e = median(timed_loops(run_host, rewind_host, steps, barrier))
+        ms_e2e = median(timed_loops(run_host, rewind_host, steps, barrier, agree=make_agree(world, device)))
     ms, ms_e2e = max_over_ranks([median(loops), ms_e2e or 0.0], world, device)
     engine.check()
     pk = peaks()
@@ -745,7 +754,10 @@ def main() -> None:
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+
+        # a rank that failed must not leave the others in a collective for long
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     if rank == 0:
         build()
     if world > 1:
@@ -820,7 +832,7 @@ def main() -> None:
     for _ in range(warm):
         engine.step()
     with ClockSampler(local) as clocks:
-        loops = timed_loops(run, lambda: engine.set_call(1, CONTEXT), steps, barrier)
+        loops = timed_loops(run, lambda: engine.set_call(1, CONTEXT), steps, barrier, agree=make_agree(world, device))
 
         # ---- host-facing call: token from pinned host memory in, drawn token out ----
         def run_host():
@@ -831,7 +843,7 @@ def main() -> None:
         tok = 1
         for i in range(warm):
             tok = engine.decode(tok, CONTEXT + i)
-        loops_e2e = timed_loops(run_host, lambda: None, steps, barrier)
+        loops_e2e = timed_loops(run_host, lambda: None, steps, barrier, agree=make_agree(world, device))
     ms, ms_e2e = max_over_ranks([median(loops), median(loops_e2e)], world, device)
     pk = peaks()
     peak, kind = pk["hbm_gbs"], pk["kind"]
