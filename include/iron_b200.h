@@ -204,6 +204,19 @@ int iron_argmax_bf16(const void* logits, int n, int* token_out, const int* d_out
                      int out_rows, int* carry_token, int* carry_position, void* workspace,
                      iron_stream_t stream);
 
+/* The greedy draw when the output head is split by vocabulary rows across ranks (the
+ * reference keeps the head whole on one device; a later row of its plan shards it): each
+ * rank reduces its rows' logits to one 64-bit key -- the value made monotone in the high
+ * word, the complement of the GLOBAL row index (index_offset + local index) in the low word
+ * -- with iron_argmax_key_bf16; the keys of all ranks are gathered (any all-gather) and
+ * iron_argmax_pick takes their maximum, which is the first index of the largest logit over
+ * the whole vocabulary (iron/lm/generation.py:97-99), and stores and carries it exactly as
+ * iron_argmax_bf16 does.  key_out and keys are 8-byte aligned. */
+int iron_argmax_key_bf16(const void* logits, int n, int index_offset, void* key_out, void* workspace,
+                         iron_stream_t stream);
+int iron_argmax_pick(const void* keys, int count, int* token_out, const int* d_out_index, int out_rows,
+                     int* carry_token, int* carry_position, iron_stream_t stream);
+
 /* The same greedy draw for callers that cannot give the library a workspace.  It has no
  * counterpart in the reference.  A caller may be unable to allocate device memory at all: a
  * thread that must never enter the CUDA allocator (which can lock or synchronise), a plugin

@@ -69,6 +69,8 @@ SIGNATURES: dict[str, tuple] = {
     "iron_copy_rows": (_I, [_P, _P, _P, _I, _P, _L, _L, _L, _I, _I, _P, _I, _P, _P]),
     "iron_argmax_workspace_bytes": (_Z, [_I]),
     "iron_argmax_bf16": (_I, [_P, _I, _P, _P, _I, _P, _P, _P, _P]),
+    "iron_argmax_key_bf16": (_I, [_P, _I, _I, _P, _P, _P]),
+    "iron_argmax_pick": (_I, [_P, _I, _P, _P, _I, _P, _P, _P]),
     "iron_argmax_noalloc_max_n": (_I, []),
     "iron_argmax_bf16_noalloc": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "iron_tp_buffer_bytes": (_Z, [_I, _I]),

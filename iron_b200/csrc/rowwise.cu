@@ -326,7 +326,8 @@ constexpr int kArgmaxBlocks = kSMs * 2;
 __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int n,
                                                      int* token_out, const int* d_out_index,
                                                      int out_rows, int* carry_token, int* carry_position,
-                                                     unsigned long long* workspace) {
+                                                     unsigned long long* workspace, int index_offset,
+                                                     unsigned long long* key_out) {
   __shared__ unsigned long long sred[8];
   __shared__ bool last;
   pdl_wait();
@@ -339,10 +340,10 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __rest
     float f[8];
     unpack8(ld_cached(reinterpret_cast<const uint4*>(logits) + i), f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) best = umax64(best, argmax_key(f[j], i * 8 + j));
+    for (int j = 0; j < 8; ++j) best = umax64(best, argmax_key(f[j], index_offset + i * 8 + j));
   }
   for (int i = (nvec << 3) + blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
-    best = umax64(best, argmax_key(__bfloat162float(logits[i]), i));
+    best = umax64(best, argmax_key(__bfloat162float(logits[i]), index_offset + i));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) best = umax64(best, __shfl_xor_sync(0xffffffffu, best, o));
   if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5] = best;
@@ -366,6 +367,11 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* __rest
     __syncthreads();
     if (threadIdx.x == 0) {
       for (int w = 1; w < 8; ++w) b = umax64(b, sred[w]);
+      if (key_out) {   // a shard's candidate: the draw is made from every shard's key
+        *key_out = b;
+        *counter = 0;
+        return;
+      }
       const int tok = (int)(~(uint32_t)(b & 0xffffffffull));
       // out_rows > 0 bounds the row written; when the row written IS the carried position
       // (a decoder's loop: d_out_index and carry_position are one word) the position stops
@@ -541,7 +547,45 @@ extern "C" int iron_argmax_bf16(const void* logits, int n, int* token_out,
   grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
   return launch_pdl(argmax_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
                     (const __nv_bfloat16*)logits, n, token_out, d_out_index, out_rows, carry_token,
-                    carry_position, (unsigned long long*)workspace);
+                    carry_position, (unsigned long long*)workspace, 0, (unsigned long long*)nullptr);
+}
+
+// The greedy draw over a vocabulary split across ranks: every rank reduces its rows of the
+// logits to one 64-bit key (value, then lowest global index), the keys are gathered, and the
+// largest key names the token -- the same first-maximum rule as over the whole row.
+__global__ void argmax_pick_kernel(const unsigned long long* __restrict__ keys, int count, int* token_out,
+                                   const int* d_out_index, int out_rows, int* carry_token, int* carry_position) {
+  pdl_wait();
+  pdl_launch();
+  if (threadIdx.x != 0) return;
+  unsigned long long b = 0;
+  for (int i = 0; i < count; ++i) b = umax64(b, keys[i]);
+  const int tok = (int)(~(uint32_t)(b & 0xffffffffull));
+  const int at = d_out_index ? *d_out_index : 0;
+  if (out_rows <= 0 || (at >= 0 && at < out_rows)) token_out[at] = tok;
+  if (carry_token) *carry_token = tok;
+  const bool tied = out_rows > 0 && d_out_index == carry_position;
+  if (carry_position && (!tied || *carry_position < out_rows)) *carry_position += 1;
+}
+
+extern "C" int iron_argmax_key_bf16(const void* logits, int n, int index_offset, void* key_out, void* workspace,
+                                    iron_stream_t stream) {
+  if (n <= 0 || index_offset < 0 || !key_out || !workspace) return IRON_ERR_SHAPE;
+  if (!aligned16(logits) || (reinterpret_cast<uintptr_t>(workspace) & 7) || (reinterpret_cast<uintptr_t>(key_out) & 7))
+    return IRON_ERR_ALIGN;
+  int grid = (n / 8 + 255) / 256;
+  grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
+  return launch_pdl(argmax_kernel, dim3(grid), dim3(256), (cudaStream_t)stream, (const __nv_bfloat16*)logits, n,
+                    (int*)nullptr, (const int*)nullptr, 0, (int*)nullptr, (int*)nullptr,
+                    (unsigned long long*)workspace, index_offset, (unsigned long long*)key_out);
+}
+
+extern "C" int iron_argmax_pick(const void* keys, int count, int* token_out, const int* d_out_index, int out_rows,
+                                int* carry_token, int* carry_position, iron_stream_t stream) {
+  if (count <= 0 || !keys || !token_out) return IRON_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(keys) & 7) return IRON_ERR_ALIGN;
+  return launch_pdl(argmax_pick_kernel, dim3(1), dim3(32), (cudaStream_t)stream, (const unsigned long long*)keys,
+                    count, token_out, d_out_index, out_rows, carry_token, carry_position);
 }
 
 extern "C" int iron_rope_kv_write_bf16(void* qkv, long long pitch, const void* angles, void* k_cache,
@@ -599,5 +643,5 @@ extern "C" int iron_argmax_bf16_noalloc(const void* logits, int n, int* token_ou
   int grid = (n / 8 + 255) / 256;
   grid = grid < 1 ? 1 : (grid > kArgmaxBlocks ? kArgmaxBlocks : grid);
   return launch_pdl(argmax_kernel, dim3(grid), dim3(256), s, (const __nv_bfloat16*)logits, n, token_out,
-                    d_out_index, 0, carry_token, carry_position, scratch);
+                    d_out_index, 0, carry_token, carry_position, scratch, 0, (unsigned long long*)nullptr);
 }

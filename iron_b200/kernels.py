@@ -197,6 +197,22 @@ def argmax(logits, token_out, workspace, *, d_out_index=None, carry_token=None,
     return token_out
 
 
+def argmax_key(logits, key_out, workspace, *, index_offset=0):
+    """One shard's candidate for the greedy draw: ``key_out`` (one int64) receives the 64-bit
+    key of the largest of ``logits``, whose rows start at global row ``index_offset``."""
+    _bf16(logits)
+    call("iron_argmax_key_bf16", _ptr(logits), logits.numel(), int(index_offset), _ptr(key_out), _ptr(workspace),
+         _stream())
+    return key_out
+
+
+def argmax_pick(keys, token_out, *, d_out_index=None, carry_token=None, carry_position=None):
+    """The draw from every shard's key: the largest names the token (first index of the maximum)."""
+    call("iron_argmax_pick", _ptr(keys), keys.numel(), _ptr(token_out), _ptr(d_out_index), token_out.numel(),
+         _ptr(carry_token), _ptr(carry_position), _stream())
+    return token_out
+
+
 def mha_decode_splits(batch, G, kv_len_hint) -> int:
     """The cluster size (key splits) suggested for a context of ``kv_len_hint`` keys."""
     return _lib.load().iron_mha_decode_splits(batch, G, kv_len_hint)

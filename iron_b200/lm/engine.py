@@ -225,6 +225,17 @@ class LlamaEngine:
         self._peer_exchange_setup()
         self.nsplit = K.mha_decode_splits(batch, G, self.kv_len_hint)
         self.argmax_ws = K.argmax_workspace(self.device)
+        # Under tensor parallelism the output head is split by vocabulary rows as well (one
+        # sequence, greedy draw): a rank multiplies its V / t rows, reduces them to one 64-bit
+        # (value, index) key, the keys are gathered and the largest names the token -- the head
+        # is most of a rank's bytes once the layers are split.  IRON_TP_SHARD_HEAD=0 keeps every
+        # rank on the whole head.
+        self.head_sharded = (tp_size > 1 and batch == 1 and V % (8 * tp_size) == 0
+                             and os.environ.get("IRON_TP_SHARD_HEAD", "1") != "0")
+        if self.head_sharded:
+            self.head_rows = slice(tp_rank * (V // tp_size), (tp_rank + 1) * (V // tp_size))
+            self.head_key = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self.head_keys = torch.zeros(tp_size, dtype=torch.int64, device=self.device)
         self.ab_scratch = K.attn_oproj_scratch(E, G, self.device) if self.attn_oproj else None
         self.draws = None   # (batch, S, 4) int32 draw rows once a sampler is set
         self.fuse_rope = os.environ.get("IRON_PREFILL_FUSED_ROPE", "1") != "0"
@@ -256,6 +267,7 @@ class LlamaEngine:
         # the position the next replayed step runs at (the largest over a batch), mirrored on
         # the host so that a replay past the end of the caches is refused before any launch
         self._next_position = 0
+        self._last_call_sharded = False
 
     # ------------------------------------------------------------------ weights
     @classmethod
@@ -393,7 +405,8 @@ class LlamaEngine:
         E, F, V = c.hidden_size, c.intermediate_size, c.vocab_size
         Q, KV = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
         layer = ((Q + 2 * KV) * E + E * Q + 3 * F * E) * 2
-        return c.num_hidden_layers * layer // self.tp_size + V * E * 2
+        head = V * E * 2 // (self.tp_size if getattr(self, "head_sharded", False) else 1)
+        return c.num_hidden_layers * layer // self.tp_size + head
 
     def _batch_launches(self) -> None:
         """Launch one decode step of every sequence of the batch: row b reads
@@ -492,6 +505,15 @@ class LlamaEngine:
             K.gemv(l["wo"], self.att[0].view(-1), y, residual=x)
             K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
             K.gemv(l["wd"], self.act[0], x, residual=y)
+        if self.head_sharded and self.draws is None:
+            import torch.distributed as dist
+
+            rows = self.head_rows
+            K.gemv(self.head[rows], x, self.logits_buf[0, rows], norm_weight=self.norm, eps=c.eps)
+            K.argmax_key(self.logits_buf[0, rows], self.head_key, self.argmax_ws, index_offset=rows.start)
+            dist.all_gather_into_tensor(self.head_keys, self.head_key, group=self.tp_group)
+            K.argmax_pick(self.head_keys, self.drawn[0], d_out_index=d_pos, carry_token=d_token, carry_position=d_pos)
+            return
         K.gemv(self.head, x, self.logits_buf[0], norm_weight=self.norm, eps=c.eps)
         self._draw(0, d_token, d_pos)
 
@@ -604,6 +626,7 @@ class LlamaEngine:
         self.set_call(0, start + n - 1)
         self._draw(seq, self.values[0:1], self.values[1:2])
         self._next_position = start + n
+        self._last_call_sharded = False
         self._chunk_launches = launches
 
     def prefill(self, tokens, start: int = 0, seq: int = 0) -> np.ndarray:
@@ -732,6 +755,7 @@ class LlamaEngine:
         self.capture()
         self._advance()
         self._graph.replay()
+        self._last_call_sharded = self.head_sharded and self.draws is None
 
     def decode(self, token: int, position: int) -> int:
         """One decode step from the host: token in, drawn token out (both cross PCIe)."""
@@ -827,7 +851,15 @@ class LlamaEngine:
         return self.logits_buf.float().cpu().numpy()
 
     def logits(self) -> np.ndarray:
-        """The last step's logits as float32 on the host."""
+        """The last step's logits as float32 on the host (with a vocabulary-split head, every
+        rank's rows are gathered first: a collective, every rank calls it)."""
+        if self.head_sharded and self._last_call_sharded:
+            import torch.distributed as dist
+
+            rows = self.head_rows
+            whole = torch.empty_like(self.logits_buf[0])
+            dist.all_gather_into_tensor(whole, self.logits_buf[0, rows].contiguous(), group=self.tp_group)
+            return whole.float().cpu().numpy()
         return self.logits_buf[0].float().cpu().numpy()
 
     def generate(self, token: int, position: int, steps: int) -> list[int]:

@@ -37,6 +37,9 @@ def _work(rank: int, size: int, out):
     weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
     prompt = np.random.default_rng(7).integers(0, 1024, 8)
     tp = LlamaEngine(toy_config(), weights, device=f"cuda:{rank}", kv_len_hint=64, tp_rank=rank, tp_size=size)
+    # the output head is split by vocabulary rows too unless switched off: a rank then streams
+    # half of it and the greedy token comes from the two ranks' (value, index) keys
+    assert tp.head_sharded == (os.environ.get("IRON_TP_SHARD_HEAD", "1") != "0")
     logits = [tp.prefill(prompt)]
     drawn = tp.complete(prompt, 5)
     logits.append(tp.logits())
@@ -72,9 +75,9 @@ def _work(rank: int, size: int, out):
         out.put(("ok", rank, None))
 
 
-def _rank(rank: int, size: int, port: int, out, peer: str):
+def _rank(rank: int, size: int, port: int, out, peer: str, shard_head: str):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      IRON_TP_PEER=peer, TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+                      IRON_TP_PEER=peer, IRON_TP_SHARD_HEAD=shard_head, TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     try:
         _work(rank, size, out)
     except BaseException:  # noqa: BLE001 -- report and leave; the parent ends the peer
@@ -85,8 +88,9 @@ def _rank(rank: int, size: int, port: int, out, peer: str):
         os._exit(0)   # no collective teardown: the peer may already be gone
 
 
-@pytest.mark.parametrize("peer", ["1", "0"], ids=["peer-memory exchange", "nccl exchange"])
-def test_two_way_tensor_parallel_matches_one_gpu(peer):
+@pytest.mark.parametrize("peer,shard_head", [("1", "1"), ("0", "1"), ("1", "0")],
+                         ids=["peer-memory exchange", "nccl exchange", "whole head on every rank"])
+def test_two_way_tensor_parallel_matches_one_gpu(peer, shard_head):
     import queue
 
     import torch
@@ -97,7 +101,7 @@ def test_two_way_tensor_parallel_matches_one_gpu(peer):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, out, peer), daemon=True) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, out, peer, shard_head), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
     results = {}
