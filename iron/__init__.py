@@ -59,10 +59,14 @@ class _AliasLoader(importlib.abc.Loader):
         self.target = target
 
     def create_module(self, spec):
-        return importlib.import_module(self.target)   # the module object itself, not a copy
+        module = importlib.import_module(self.target)   # the module object itself, not a copy
+        self.own_spec = module.__spec__
+        return module
 
     def exec_module(self, module):
-        pass
+        # the import system has just stamped the alias's spec on the module: put its own back, so
+        # that its relative imports keep resolving against the package it lives in
+        module.__spec__ = self.own_spec
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder):

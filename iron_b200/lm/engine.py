@@ -662,7 +662,7 @@ class LlamaEngine:
         self._next_position = n
         self._advance(steps - 1)
         for _ in range(steps - 1):
-            self._graph.replay()
+            self._replay()
         out = self.drawn[0, n - 1 : n - 1 + steps].cpu().tolist()
         self.check()
         return out
@@ -754,6 +754,10 @@ class LlamaEngine:
         ``IndexError`` at the end of the caches, before anything is launched."""
         self.capture()
         self._advance()
+        self._replay()
+
+    def _replay(self) -> None:
+        """One replay of the captured step; notes whether its logits are split over the ranks."""
         self._graph.replay()
         self._last_call_sharded = self.head_sharded and self.draws is None
 
@@ -870,7 +874,7 @@ class LlamaEngine:
         self.capture()
         self._advance(steps)
         for _ in range(steps):
-            self._graph.replay()
+            self._replay()
         out = self.drawn[0, position : position + steps].cpu()
         self.check()
         return out.tolist()
