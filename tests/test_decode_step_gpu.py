@@ -32,8 +32,12 @@ def test_a_long_context_agrees_with_the_separate_launches(monkeypatch):
         a = fused.feed(tokens[lo:at], lo)
         b = separate.feed(tokens[lo:at], lo)
         # the key splits fold in a different order: a few bf16 ulps on the logits (each path is held to 2 % of the largest logit against the oracle)
-        assert np.abs(a - b).max() <= 0.02 * np.abs(b).max(), f"after {at} tokens"
-        assert int(a.argmax()) == int(b.argmax())
+        bound = float(np.abs(a - b).max())
+        assert bound <= 0.02 * np.abs(b).max(), f"after {at} tokens"
+        # the same greedy token wherever the leader is further ahead than the two paths differ
+        top = np.sort(b)[-2:]
+        if top[1] - top[0] > 2 * bound:
+            assert int(a.argmax()) == int(b.argmax()), f"after {at} tokens"
     for l_f, l_s in zip(fused.layers, separate.layers):
         k_f, k_s = l_f["k"][0, :200].float(), l_s["k"][0, :200].float()
         assert (k_f - k_s).abs().max().item() <= 0.02 * k_s.abs().max().item()
