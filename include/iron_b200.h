@@ -114,6 +114,14 @@ int iron_rmsnorm_bf16(const void* x, const void* weight, void* y, int rows, int 
                       float eps, int valid_rows, const int* d_valid_rows,
                       iron_stream_t stream);
 
+/* RMSNorm of x * silu(gate) in one launch -- the SiLU, ElementwiseMul and RMSNorm steps that end
+ * a Mamba2 mixer (iron/applications/granite_hybrid/model.py:131-135): g = bf16(x * bf16(silu(gate)))
+ * element by element, then RMSNorm of g exactly as iron_rmsnorm_bf16.  x, gate, y (rows, cols);
+ * cols % 8 == 0 and cols <= 8192. */
+int iron_rmsnorm_gated_bf16(const void* x, const void* gate, const void* weight, void* y,
+                            int rows, int cols, float eps, int valid_rows,
+                            const int* d_valid_rows, iron_stream_t stream);
+
 /* RoPE -- iron/operators/rope.py:58 (reference :167-184).  x, y (rows, cols); angles
  * (angle_rows, cols) packed cos/sin; row r uses angle row
  * angle_offset + r / (rows / angle_rows).  two_halves != 0 pairs column i with

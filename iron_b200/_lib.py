@@ -60,6 +60,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "iron_gemm_swiglu_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "iron_rmsnorm_bf16": (_I, [_P, _P, _P, _I, _I, _F, _I, _P, _P]),
+    "iron_rmsnorm_gated_bf16": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _P, _P]),
     "iron_rope_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
     "iron_rope_kv_write_bf16": (_I, [_P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P, _P]),
     "iron_elementwise_bf16": (_I, [_I, _P, _P, _P, _L, _I, _F, _P]),

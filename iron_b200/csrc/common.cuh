@@ -126,8 +126,10 @@ __device__ __forceinline__ void prefetch_l2_slice(const PrefetchHint& h, int cta
   }
 }
 
-// SiLU as the reference's chain computes it: f32 x*sigmoid(x), rounded once to bf16.
-__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+// SiLU as the reference's chain computes it: f32 x*sigmoid(x), rounded once to bf16 by the
+// caller.  The hardware's exp2 and reciprocal (a few float32 ulps) are far inside that rounding;
+// a huge negative x gives exp = inf and the quotient 0, the limit.
+__device__ __forceinline__ float silu_f32(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // Programmatic dependent launch can be switched off process-wide (iron_set_pdl): every
 // launch helper asks here how many launch attributes to attach.

@@ -47,6 +47,69 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
   }
 }
 
+// RMSNorm of x * silu(gate), the tail of a Mamba2 mixer, in one pass over HBM: the product is
+// rounded to bf16 as the separate SiLU and multiply steps round it (silu first, then the
+// product), held in registers across the row sum, normalised with the norm's own two
+// roundings.  One CTA per row; up to kGatedChunks 16-byte chunks a thread stay in registers.
+constexpr int kGatedChunks = 4;
+__global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ gate,
+                                                            const __nv_bfloat16* __restrict__ w,
+                                                            __nv_bfloat16* __restrict__ y, int rows, int cols,
+                                                            float eps, int valid, const int* d_valid) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
+  if (d_valid) valid = min(*d_valid, rows);
+  const int nch = cols >> 3;
+  for (int r = blockIdx.x; r < valid; r += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(gate + (size_t)r * cols);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)r * cols);
+    uint4 xv[kGatedChunks], gv[kGatedChunks];
+#pragma unroll
+    for (int u = 0; u < kGatedChunks; ++u) {
+      const int i = threadIdx.x + u * 256;
+      if (i < nch) { xv[u] = ld_stream(xr + i); gv[u] = ld_stream(gr + i); }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < kGatedChunks; ++u) {
+      const int i = threadIdx.x + u * 256;
+      if (i < nch) {
+        float f[8], g[8];
+        unpack8(xv[u], f);
+        unpack8(gv[u], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          f[j] = round_bf16(__fmul_rn(round_bf16(silu_f32(g[j])), f[j]));
+          ss = fmaf(f[j], f[j], ss);
+        }
+        xv[u] = pack8(f);    // exact: the values are bf16 already
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(tot / (float)cols + eps);
+#pragma unroll
+    for (int u = 0; u < kGatedChunks; ++u) {
+      const int i = threadIdx.x + u * 256;
+      if (i < nch) {
+        float f[8];
+        unpack8(xv[u], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv);
+        if (w) {
+          float g[8];
+          unpack8(ld_cached(reinterpret_cast<const uint4*>(w) + i), g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = f[j] * g[j];
+        }
+        yr[i] = pack8(f);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- LayerNorm
 // One CTA per row: mean, then the biased variance about it, then the two roundings.
 __global__ void __launch_bounds__(256) layernorm_kernel(const __nv_bfloat16* __restrict__ x,
@@ -441,6 +504,21 @@ extern "C" int iron_rmsnorm_bf16(const void* x, const void* weight, void* y, int
   return launch_pdl(rmsnorm_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
                     (const __nv_bfloat16*)x, (const __nv_bfloat16*)weight, (__nv_bfloat16*)y, rows,
                     cols, eps, valid_rows, d_valid_rows);
+}
+
+extern "C" int iron_rmsnorm_gated_bf16(const void* x, const void* gate, const void* weight, void* y, int rows,
+                                       int cols, float eps, int valid_rows, const int* d_valid_rows,
+                                       iron_stream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7) || cols > 256 * 8 * kGatedChunks) return IRON_ERR_SHAPE;
+  if (valid_rows < 0 || valid_rows > rows) return IRON_ERR_SHAPE;
+  if (!x || !gate || !y) return IRON_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(gate) || !aligned16(y) || (weight && !aligned16(weight))) return IRON_ERR_ALIGN;
+  if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
+  const int upper = d_valid_rows ? rows : valid_rows;
+  const int grid = upper < kSMs * 8 ? upper : kSMs * 8;
+  return launch_pdl(rmsnorm_gated_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
+                    (const __nv_bfloat16*)x, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)weight,
+                    (__nv_bfloat16*)y, rows, cols, eps, valid_rows, d_valid_rows);
 }
 
 extern "C" int iron_layernorm_bf16(const void* x, const void* weight, void* y, int rows, int cols, float eps,

@@ -382,26 +382,28 @@ constexpr int kSsdThreads = 128;
 
 template <int N>
 struct SsdSmem {
-  static constexpr int PX = kSsdP + 8, PN = N + 8, PQ = kSsdQ + 8;   // row pitches in elements
+  static constexpr int PX = kSsdP + 8, PN = N + 8;                   // row pitches in elements
   static constexpr size_t off_x = 0;
   static constexpr size_t off_b = off_x + (size_t)kSsdQ * PX * 2;
   static constexpr size_t off_c = off_b + (size_t)kSsdQ * PN * 2;
-  static constexpr size_t off_m = off_c + (size_t)kSsdQ * PN * 2;    // y tiles, then the weighted rows of x
   static constexpr int PZ = kSsdP + 4;                              // floats
-  static constexpr size_t off_z = off_m + (size_t)kSsdQ * PQ * 2;    // C S_prev^T, float32
+  static constexpr size_t off_z = off_c + (size_t)kSsdQ * PN * 2;    // C S_prev^T, float32; then a warp's rows of y
   static constexpr size_t off_f = off_z + (size_t)kSsdQ * PZ * 4;    // cum, step, w, exp(cum): 4 x Q floats
   static constexpr size_t total = off_f + 4 * kSsdQ * sizeof(float);
 };
 
+#ifndef SSD_DROP
+#define SSD_DROP 0   // bit 0: masked scores, bit 1: weighted rows, bit 2: state -- as one bf16 operand only
+#endif
+
 template <int N>
 __global__ void __launch_bounds__(kSsdThreads, 3) ssd_scan_kernel(const ScanParams p) {
   using S = SsdSmem<N>;
-  constexpr int Q = kSsdQ, P = kSsdP, PX = S::PX, PN = S::PN, PQ = S::PQ, PZ = S::PZ;
+  constexpr int Q = kSsdQ, P = kSsdP, PX = S::PX, PN = S::PN, PZ = S::PZ;
   extern __shared__ __align__(128) unsigned char ssd_smem[];
   __nv_bfloat16* sX = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_x);
   __nv_bfloat16* sB = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_b);
   __nv_bfloat16* sC = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_c);
-  __nv_bfloat16* sM = reinterpret_cast<__nv_bfloat16*>(ssd_smem + S::off_m);
   float* sZ = reinterpret_cast<float*>(ssd_smem + S::off_z);
   float* s_cum = reinterpret_cast<float*>(ssd_smem + S::off_f);
   float* s_step = s_cum + Q;
@@ -450,42 +452,93 @@ __global__ void __launch_bounds__(kSsdThreads, 3) ssd_scan_kernel(const ScanPara
       else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
   };
+  // a float32 pair as a bf16 head and the bf16 of what the head left over
+  auto split = [](float v0, float v1, uint32_t& hi, uint32_t& lo) {
+    hi = pack_bf16x2(v0, v1);
+    lo = pack_bf16x2(v0 - bf16_lo(hi), v1 - bf16_hi(hi));
+  };
 
+  const int r_lo = 16 * warp + g4, r_hi = r_lo + 8;        // this lane's two rows of every 16-row tile
   for (int c0 = 0; c0 < p.rows; c0 += Q) {
-    // ---- the chunk's rows of x, B and C ----
+    // ---- the chunk's rows of x, B and C; meanwhile warp 0 turns the chunk's steps into their
+    // running sum (lane l: rows l and l + 32) and the decays every product below needs ----
     load_rows(sX, PX, P / 8, (size_t)h * P, c0);
     load_rows(sB, PN, N / 8, (size_t)inner + (size_t)grp * N, c0);
     load_rows(sC, PN, N / 8, (size_t)inner + (size_t)(p.G + grp) * N, c0);
-    // ---- steps and their running sum (warps 0 and 1: a row each) ----
-    if (tid < Q) {
-      const int t = c0 + tid;
-      float step = 0.f;
-      if (t < valid) step = softplus_f32(__bfloat162float(dtp[(size_t)t * p.H + h]) + dt_bias);
-      float a = step * A;                                  // rows past the bound: a = 0, step = 0
+    if (warp == 0) {
+      float step[2], cum[2];
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float v = __shfl_up_sync(0xffffffffu, a, off);
-        if (lane >= off) a += v;
+      for (int u = 0; u < 2; ++u) {
+        const int t = c0 + lane + 32 * u;
+        step[u] = t < valid ? softplus_f32(__bfloat162float(dtp[(size_t)t * p.H + h]) + dt_bias) : 0.f;
+        float a = step[u] * A;                             // rows past the bound: a = 0, step = 0
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const float v = __shfl_up_sync(0xffffffffu, a, off);
+          if (lane >= off) a += v;
+        }
+        cum[u] = a;
       }
-      s_cum[tid] = a;
-      s_step[tid] = step;
+      cum[1] += __shfl_sync(0xffffffffu, cum[0], 31);     // the first half's total carries into the second
+      const float total = __shfl_sync(0xffffffffu, cum[1], 31);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r = lane + 32 * u;
+        s_cum[r] = cum[u];
+        s_step[r] = step[u];
+        s_ecum[r] = __expf(cum[u]);
+        s_w[r] = __expf(total - cum[u]) * step[u];
+      }
     }
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    float cum = 0.f, total = 0.f;
-    if (tid < Q) {
-      total = s_cum[31] + s_cum[Q - 1];                    // each warp scanned its own 32 rows:
-      cum = s_cum[tid] + (tid >= 32 ? s_cum[31] : 0.f);    // the first warp's total carries into the second
+
+    // ---- Z = C S_prev^T for all rows of the chunk and this warp's 16 columns: the carried
+    // state is the B operand straight from the registers that hold it (the accumulator layout
+    // of two 8-column tiles is the B-fragment layout of a 16-deep step), split into a bf16
+    // head and remainder so that the read-out keeps float32's accuracy.  Products that add
+    // into the same accumulator are issued as far apart as the registers allow ----
+    {
+      float zt[Q / 16][2][4];
+#pragma unroll
+      for (int mt = 0; mt < Q / 16; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) { zt[mt][nt][0] = zt[mt][nt][1] = zt[mt][nt][2] = zt[mt][nt][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < N / 16; ++ks) {
+        uint32_t bh[2][2], bl[2][2];     // [column tile: rows r_lo / r_hi of the state][k half]
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+          const float* v = st[2 * ks + kh];
+          split(v[0], v[1], bh[0][kh], bl[0][kh]);
+          split(v[2], v[3], bh[1][kh], bl[1][kh]);
+        }
+#pragma unroll
+        for (int mp = 0; mp < Q / 32; ++mp) {
+          uint32_t a0[4], a1[4];
+          load_a_rowmajor(a0, sC, PN, 32 * mp, ks * 16, lane);
+          load_a_rowmajor(a1, sC, PN, 32 * mp + 16, ks * 16, lane);
+          mma_bf16_16816(zt[2 * mp][0], a0, bh[0][0], bh[0][1]);
+          mma_bf16_16816(zt[2 * mp][1], a0, bh[1][0], bh[1][1]);
+          mma_bf16_16816(zt[2 * mp + 1][0], a1, bh[0][0], bh[0][1]);
+          mma_bf16_16816(zt[2 * mp + 1][1], a1, bh[1][0], bh[1][1]);
+          if (!(SSD_DROP & 4)) {
+            mma_bf16_16816(zt[2 * mp][0], a0, bl[0][0], bl[0][1]);
+            mma_bf16_16816(zt[2 * mp][1], a0, bl[1][0], bl[1][1]);
+            mma_bf16_16816(zt[2 * mp + 1][0], a1, bl[0][0], bl[0][1]);
+            mma_bf16_16816(zt[2 * mp + 1][1], a1, bl[1][0], bl[1][1]);
+          }
+        }
+      }
+#pragma unroll
+      for (int mt = 0; mt < Q / 16; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = 16 * warp + 8 * nt + 2 * t4;
+          *reinterpret_cast<float2*>(sZ + (size_t)(16 * mt + g4) * PZ + col) = make_float2(zt[mt][nt][0], zt[mt][nt][1]);
+          *reinterpret_cast<float2*>(sZ + (size_t)(16 * mt + g4 + 8) * PZ + col) = make_float2(zt[mt][nt][2], zt[mt][nt][3]);
+        }
     }
-    __syncthreads();
-    if (tid < Q) {
-      s_cum[tid] = cum;
-      s_ecum[tid] = __expf(cum);
-      s_w[tid] = __expf(total - cum) * s_step[tid];
-    }
-    __syncthreads();
-    const float cum_last = s_cum[Q - 1];
-    const int r_lo = 16 * warp + g4, r_hi = r_lo + 8;      // this lane's two rows of every 16-row tile
 
     // ---- scores S = C B^T, masked and decayed into M (rows of this warp) ----
     uint32_t m_hi[Q / 16][4], m_lo[Q / 16][4];
@@ -513,62 +566,18 @@ __global__ void __launch_bounds__(kSsdThreads, 3) ssd_scan_kernel(const ScanPara
 #pragma unroll
       for (int i = 0; i < Q / 8; ++i) {
         const int j0 = 8 * i + 2 * t4, j1 = j0 + 1;
-        const float cj0 = s_cum[j0], cj1 = s_cum[j1], sj0 = s_step[j0], sj1 = s_step[j1];
-        const float m00 = j0 <= r_lo ? acc[i][0] * __expf(cl - cj0) * sj0 : 0.f;
-        const float m01 = j1 <= r_lo ? acc[i][1] * __expf(cl - cj1) * sj1 : 0.f;
-        const float m10 = j0 <= r_hi ? acc[i][2] * __expf(ch - cj0) * sj0 : 0.f;
-        const float m11 = j1 <= r_hi ? acc[i][3] * __expf(ch - cj1) * sj1 : 0.f;
-        const uint32_t h0 = pack_bf16x2(m00, m01), h1 = pack_bf16x2(m10, m11);
+        const float2 cj = *reinterpret_cast<const float2*>(s_cum + j0);
+        const float2 sj = *reinterpret_cast<const float2*>(s_step + j0);
+        const float m00 = j0 <= r_lo ? acc[i][0] * __expf(cl - cj.x) * sj.x : 0.f;
+        const float m01 = j1 <= r_lo ? acc[i][1] * __expf(cl - cj.y) * sj.y : 0.f;
+        const float m10 = j0 <= r_hi ? acc[i][2] * __expf(ch - cj.x) * sj.x : 0.f;
+        const float m11 = j1 <= r_hi ? acc[i][3] * __expf(ch - cj.y) * sj.y : 0.f;
         const int ks = i >> 1, half = (i & 1) * 2;        // tile i is k-columns 8 (i & 1) .. of step i / 2
-        m_hi[ks][half] = h0;
-        m_hi[ks][half + 1] = h1;
-        m_lo[ks][half] = pack_bf16x2(m00 - bf16_lo(h0), m01 - bf16_hi(h0));
-        m_lo[ks][half + 1] = pack_bf16x2(m10 - bf16_lo(h1), m11 - bf16_hi(h1));
+        split(m00, m01, m_hi[ks][half], m_lo[ks][half]);
+        split(m10, m11, m_hi[ks][half + 1], m_lo[ks][half + 1]);
       }
     }
-
-    // ---- Z = C S_prev^T for all rows of the chunk and this warp's 16 columns: the carried
-    // state is the B operand straight from the registers that hold it (the accumulator layout
-    // of two 8-column tiles is the B-fragment layout of a 16-deep step), split into a bf16
-    // head and remainder so that the read-out keeps float32's accuracy ----
-    {
-      float zt[Q / 16][2][4];
-#pragma unroll
-      for (int mt = 0; mt < Q / 16; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) { zt[mt][nt][0] = zt[mt][nt][1] = zt[mt][nt][2] = zt[mt][nt][3] = 0.f; }
-#pragma unroll
-      for (int ks = 0; ks < N / 16; ++ks) {
-        uint32_t bh[2][2], bl[2][2];     // [column tile: rows r_lo / r_hi of the state][k half]
-#pragma unroll
-        for (int kh = 0; kh < 2; ++kh) {
-          const float* v = st[2 * ks + kh];
-          bh[0][kh] = pack_bf16x2(v[0], v[1]);
-          bh[1][kh] = pack_bf16x2(v[2], v[3]);
-          bl[0][kh] = pack_bf16x2(v[0] - bf16_lo(bh[0][kh]), v[1] - bf16_hi(bh[0][kh]));
-          bl[1][kh] = pack_bf16x2(v[2] - bf16_lo(bh[1][kh]), v[3] - bf16_hi(bh[1][kh]));
-        }
-#pragma unroll
-        for (int mt = 0; mt < Q / 16; ++mt) {
-          uint32_t a[4];
-          load_a_rowmajor(a, sC, PN, 16 * mt, ks * 16, lane);
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            mma_bf16_16816(zt[mt][nt], a, bh[nt][0], bh[nt][1]);
-            mma_bf16_16816(zt[mt][nt], a, bl[nt][0], bl[nt][1]);
-          }
-        }
-      }
-#pragma unroll
-      for (int mt = 0; mt < Q / 16; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const int col = 16 * warp + 8 * nt + 2 * t4;
-          *reinterpret_cast<float2*>(sZ + (size_t)(16 * mt + g4) * PZ + col) = make_float2(zt[mt][nt][0], zt[mt][nt][1]);
-          *reinterpret_cast<float2*>(sZ + (size_t)(16 * mt + g4 + 8) * PZ + col) = make_float2(zt[mt][nt][2], zt[mt][nt][3]);
-        }
-    }
-    __syncthreads();
+    __syncthreads();   // Z is whole
 
     // ---- y = M X  +  exp(cum_t) Z  +  D x  (rows of this warp) ----
     {
@@ -578,17 +587,25 @@ __global__ void __launch_bounds__(kSsdThreads, 3) ssd_scan_kernel(const ScanPara
 #pragma unroll
       for (int ks = 0; ks < Q / 16; ++ks) {
 #pragma unroll
-        for (int i2 = 0; i2 < P / 16; ++i2) {
-          uint32_t bb[4];
-          load_b_kn(bb, sX, PX, i2 * 16, ks * 16, lane);
-          mma_bf16_16816(y[2 * i2], m_hi[ks], bb[0], bb[1]);
-          mma_bf16_16816(y[2 * i2 + 1], m_hi[ks], bb[2], bb[3]);
-          mma_bf16_16816(y[2 * i2], m_lo[ks], bb[0], bb[1]);
-          mma_bf16_16816(y[2 * i2 + 1], m_lo[ks], bb[2], bb[3]);
+        for (int ip = 0; ip < P / 32; ++ip) {
+          uint32_t b0[4], b1[4];
+          load_b_kn(b0, sX, PX, ip * 32, ks * 16, lane);
+          load_b_kn(b1, sX, PX, ip * 32 + 16, ks * 16, lane);
+          mma_bf16_16816(y[4 * ip], m_hi[ks], b0[0], b0[1]);
+          mma_bf16_16816(y[4 * ip + 1], m_hi[ks], b0[2], b0[3]);
+          mma_bf16_16816(y[4 * ip + 2], m_hi[ks], b1[0], b1[1]);
+          mma_bf16_16816(y[4 * ip + 3], m_hi[ks], b1[2], b1[3]);
+          if (!(SSD_DROP & 1)) {
+            mma_bf16_16816(y[4 * ip], m_lo[ks], b0[0], b0[1]);
+            mma_bf16_16816(y[4 * ip + 1], m_lo[ks], b0[2], b0[3]);
+            mma_bf16_16816(y[4 * ip + 2], m_lo[ks], b1[0], b1[1]);
+            mma_bf16_16816(y[4 * ip + 3], m_lo[ks], b1[2], b1[3]);
+          }
         }
       }
       const float el = s_ecum[r_lo], eh = s_ecum[r_hi];
       const bool live_lo = c0 + r_lo < valid, live_hi = c0 + r_hi < valid;
+      uint32_t out_lo[P / 8], out_hi[P / 8];
 #pragma unroll
       for (int i = 0; i < P / 8; ++i) {
         const int p0 = 8 * i + 2 * t4;
@@ -600,56 +617,67 @@ __global__ void __launch_bounds__(kSsdThreads, 3) ssd_scan_kernel(const ScanPara
         const float v01 = fmaf(Dh, bf16_hi(xl), fmaf(el, zl.y, y[i][1]));
         const float v10 = fmaf(Dh, bf16_lo(xh), fmaf(eh, zh.x, y[i][2]));
         const float v11 = fmaf(Dh, bf16_hi(xh), fmaf(eh, zh.y, y[i][3]));
-        *reinterpret_cast<uint32_t*>(sM + (size_t)r_lo * PQ + p0) = live_lo ? pack_bf16x2(v00, v01) : 0u;
-        *reinterpret_cast<uint32_t*>(sM + (size_t)r_hi * PQ + p0) = live_hi ? pack_bf16x2(v10, v11) : 0u;
+        out_lo[i] = live_lo ? pack_bf16x2(v00, v01) : 0u;
+        out_hi[i] = live_hi ? pack_bf16x2(v10, v11) : 0u;
+      }
+      // The warp's 16 rows of y are staged over its own rows of Z (which only it reads, and has
+      // read) and leave as 128-byte rows.
+      __syncwarp();
+      __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(sZ);
+      constexpr int PS = PZ * 2;                           // the same row pitch, in bf16 elements
+#pragma unroll
+      for (int i = 0; i < P / 8; ++i) {
+        const int p0 = 8 * i + 2 * t4;
+        *reinterpret_cast<uint32_t*>(stage + (size_t)r_lo * PS + p0) = out_lo[i];
+        *reinterpret_cast<uint32_t*>(stage + (size_t)r_hi * PS + p0) = out_hi[i];
       }
       __syncwarp();
-      // the warp's 16 rows of y leave as 128-byte rows
       for (int idx = lane; idx < 16 * (P / 8); idx += 32) {
         const int r = idx / (P / 8), ch = idx - r * (P / 8);
         const int t = c0 + 16 * warp + r;
         if (t < p.rows)
           *reinterpret_cast<uint4*>(yb + (size_t)t * inner + (size_t)h * P + ch * 8) =
-              *reinterpret_cast<const uint4*>(sM + (size_t)(16 * warp + r) * PQ + ch * 8);
+              *reinterpret_cast<const uint4*>(stage + (size_t)(16 * warp + r) * PS + ch * 8);
       }
     }
-    __syncthreads();   // every warp is done with C and Z
 
-    // ---- the weighted rows x_j w_j, then S = exp(cum_Q) S + X_w^T B.  The rows are rounded to
-    // bf16 as an operand; their remainders go through a second product (over C's bytes, which
-    // the chunk no longer needs), so the state keeps float32's accuracy from chunk to chunk ----
-    __nv_bfloat16* sXl = sC;
-    for (int idx = tid; idx < Q * (P / 2); idx += kSsdThreads) {
-      const int j = idx / (P / 2), pp = (idx - j * (P / 2)) * 2;
-      const uint32_t xv = *reinterpret_cast<const uint32_t*>(sX + (size_t)j * PX + pp);
-      const float w = s_w[j];
-      const float v0 = bf16_lo(xv) * w, v1 = bf16_hi(xv) * w;
-      const uint32_t hi = pack_bf16x2(v0, v1);
-      *reinterpret_cast<uint32_t*>(sM + (size_t)j * PQ + pp) = hi;
-      *reinterpret_cast<uint32_t*>(sXl + (size_t)j * PQ + pp) = pack_bf16x2(v0 - bf16_lo(hi), v1 - bf16_hi(hi));
-    }
-    __syncthreads();
+    // ---- S = exp(cum_Q) S + X_w^T B.  The weighted rows x_j w_j are made in registers from
+    // the transposed fragments of x (a register holds rows j, j + 1 of one column), rounded to
+    // bf16 as an operand, their remainders going through a second product, so the state keeps
+    // float32's accuracy from chunk to chunk ----
     {
-      const float decay = __expf(cum_last);
+      const float decay = s_ecum[Q - 1];
 #pragma unroll
       for (int i = 0; i < N / 8; ++i) { st[i][0] *= decay; st[i][1] *= decay; st[i][2] *= decay; st[i][3] *= decay; }
 #pragma unroll
       for (int ks = 0; ks < Q / 16; ++ks) {
-        uint32_t a[4], al[4];
-        load_a_transposed(a, sM, PQ, 16 * warp, ks * 16, lane);
-        load_a_transposed(al, sXl, PQ, 16 * warp, ks * 16, lane);
+        uint32_t raw[4], a[4], al[4];
+        load_a_transposed(raw, sX, PX, 16 * warp, ks * 16, lane);
+        const float2 w0 = *reinterpret_cast<const float2*>(s_w + ks * 16 + 2 * t4);
+        const float2 w1 = *reinterpret_cast<const float2*>(s_w + ks * 16 + 8 + 2 * t4);
+        split(bf16_lo(raw[0]) * w0.x, bf16_hi(raw[0]) * w0.y, a[0], al[0]);
+        split(bf16_lo(raw[1]) * w0.x, bf16_hi(raw[1]) * w0.y, a[1], al[1]);
+        split(bf16_lo(raw[2]) * w1.x, bf16_hi(raw[2]) * w1.y, a[2], al[2]);
+        split(bf16_lo(raw[3]) * w1.x, bf16_hi(raw[3]) * w1.y, a[3], al[3]);
 #pragma unroll
-        for (int i2 = 0; i2 < N / 16; ++i2) {
-          uint32_t bb[4];
-          load_b_kn(bb, sB, PN, i2 * 16, ks * 16, lane);
-          mma_bf16_16816(st[2 * i2], a, bb[0], bb[1]);
-          mma_bf16_16816(st[2 * i2 + 1], a, bb[2], bb[3]);
-          mma_bf16_16816(st[2 * i2], al, bb[0], bb[1]);
-          mma_bf16_16816(st[2 * i2 + 1], al, bb[2], bb[3]);
+        for (int ip = 0; ip < N / 32; ++ip) {
+          uint32_t b0[4], b1[4];
+          load_b_kn(b0, sB, PN, ip * 32, ks * 16, lane);
+          load_b_kn(b1, sB, PN, ip * 32 + 16, ks * 16, lane);
+          mma_bf16_16816(st[4 * ip], a, b0[0], b0[1]);
+          mma_bf16_16816(st[4 * ip + 1], a, b0[2], b0[3]);
+          mma_bf16_16816(st[4 * ip + 2], a, b1[0], b1[1]);
+          mma_bf16_16816(st[4 * ip + 3], a, b1[2], b1[3]);
+          if (!(SSD_DROP & 2)) {
+            mma_bf16_16816(st[4 * ip], al, b0[0], b0[1]);
+            mma_bf16_16816(st[4 * ip + 1], al, b0[2], b0[3]);
+            mma_bf16_16816(st[4 * ip + 2], al, b1[0], b1[1]);
+            mma_bf16_16816(st[4 * ip + 3], al, b1[2], b1[3]);
+          }
         }
       }
     }
-    __syncthreads();   // x, B, C and the weighted rows are free for the next chunk
+    __syncthreads();   // x, B, C, Z and the decays are free for the next chunk
   }
 
   if (p.final_state) {

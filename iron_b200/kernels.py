@@ -108,6 +108,20 @@ def rms_norm(x, weight=None, out=None, *, eps=1e-5, valid=None, d_valid=None):
     return out
 
 
+def rms_norm_gated(x, gate, weight=None, out=None, *, eps=1e-5, valid=None, d_valid=None):
+    """RMSNorm of ``x * silu(gate)`` (each step rounded as the separate operators round) in one launch."""
+    _bf16(x, gate, weight)
+    if x.shape != gate.shape:
+        raise ValueError(f"x {tuple(x.shape)} and gate {tuple(gate.shape)} differ in shape")
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty_like(x)
+    call("iron_rmsnorm_gated_bf16", _ptr(x), _ptr(gate), _ptr(weight), _ptr(out), rows, cols, float(eps),
+         rows if valid is None else valid, _ptr(d_valid), _stream())
+    return out
+
+
 def layer_norm(x, weight=None, out=None, *, eps=1e-5, valid=None, d_valid=None):
     """Each row minus its mean over its standard deviation (biased), rounded, times ``weight``."""
     _bf16(x, weight)

@@ -6,14 +6,13 @@ projections on row slices of ``in_proj``, the causal convolution as a chain of r
 products and sums (iron/functional.py:147-180) plus a bias add, SiLU, the scan
 (iron/operators/selective_scan.py:46), SiLU of the gate, a product, RMSNorm over ``d_inner``
 and ``out_proj``: about twenty steps.  Here a call of ``rows`` positions for ``batch``
-independent sequences is eight launches:
+independent sequences is seven launches:
 
     1-3. gate, x/B/C and dt projections              (iron_gemm_bf16, tcgen05)
     4.   causal convolution + bias + SiLU            (iron_causal_conv1d_bf16)
     5.   selective scan                              (iron_selective_scan_bf16)
-    6.   y * silu(gate)                              (iron_elementwise_bf16)
-    7.   RMSNorm over d_inner                        (iron_rmsnorm_bf16)
-    8.   out_proj                                    (iron_gemm_bf16)
+    6.   RMSNorm over d_inner of y * silu(gate)      (iron_rmsnorm_gated_bf16)
+    7.   out_proj                                    (iron_gemm_bf16)
 
 with every rounding of the recorded steps kept (each projection, the convolution's chain, the
 activation, the product and the norm's two roundings round to bf16 where the reference's
@@ -80,12 +79,12 @@ class MambaMixer:
         new = lambda *shape, dtype=BF16: torch.empty(shape, dtype=dtype, device=dev)
         self.gate, self.xbc, self.dt = new(n, self.inner), new(n, self.channels), new(n, heads)
         self.conv_out, self.y, self.out = new(n, self.channels), new(n, self.inner), new(n, hidden_size)
-        self.gated, self.normed = new(n, self.inner), new(n, self.inner)
+        self.normed = new(n, self.inner)
         self.conv_state = torch.zeros(batch, kernel - 1, self.channels, dtype=BF16, device=dev)
         self.ssm_state = torch.zeros(batch, heads, head_dim, state_size, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    launches_per_call = 8
+    launches_per_call = 7
 
     def reset(self) -> None:
         """Forget every sequence: zero convolution rows and scan states."""
@@ -112,8 +111,7 @@ class MambaMixer:
         y = self.y[:n].view(B, R, self.inner)
         K.selective_scan(conv, dt.view(B, R, self.H), self.head, self.ssm_state, heads=self.H, head_dim=self.P,
                          state_size=self.N, groups=self.G, y=y, final=self.ssm_state)
-        K.elementwise("silu_mul", gate, self.y[:n], self.gated[:n])      # y * silu(gate)
-        K.rms_norm(self.gated[:n], self.norm_w, self.normed[:n], eps=self.eps)
+        K.rms_norm_gated(self.y[:n], gate, self.norm_w, self.normed[:n], eps=self.eps)
         out = self.out[:n]
         K.gemm(self.normed[:n], self.w_out, out, b_col_maj=True, status=self.status)
         return out.view(B, R, self.E)

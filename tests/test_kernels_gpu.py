@@ -131,6 +131,18 @@ def test_rmsnorm(K, rows, cols, weighted):
     assert_verdict(got, want, Tolerance.bf16_ulps(1), what="rmsnorm")
 
 
+@pytest.mark.parametrize("rows,cols", [(5, 3072), (3, 64), (300, 8192), (2, 1032)])
+def test_rmsnorm_of_a_gated_product_is_the_three_steps_in_one(K, rows, cols):
+    """x * silu(gate), then RMSNorm: each of the three recorded steps rounds to bf16."""
+    rng = np.random.default_rng(rows + cols)
+    x, gate, w = normal(rng, (rows, cols), 2.0), normal(rng, (rows, cols), 2.0), normal(rng, (cols,))
+    want = ops.rms_norm(ops.mul(x, ops.silu(gate)), w, 1e-5)
+    got = to_numpy(K.rms_norm_gated(to_torch(x), to_torch(gate), to_torch(w), eps=1e-5))
+    assert_verdict(got, want, Tolerance.bf16_ulps(2), what="gated rmsnorm")
+    with pytest.raises(Exception):
+        K.rms_norm_gated(to_torch(normal(rng, (2, 8200))), to_torch(normal(rng, (2, 8200))))
+
+
 @pytest.mark.parametrize("rows,cols,angle_rows,two_halves", [
     (32, 512, 8, True), (32, 512, 32, True), (32, 128, 8, False), (64, 128, 16, True),
     (4096, 512, 8, True), (40, 64, 1, True), (2048 * 8, 64, 2048, True)])
