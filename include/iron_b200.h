@@ -434,6 +434,29 @@ int iron_tp_allreduce_bf16(const void* part, const void* residual, void* y, int 
                            const void* const* h_peer_buffers, int rank, int world,
                            unsigned int* d_seq, int* d_status, iron_stream_t stream);
 
+/* The same exchange folded into the GEMVs on either side of it, so that it costs no launch of
+ * its own.  Each call below attaches the exchange to the NEXT GEMV-family launch this host thread
+ * makes (iron_gemv_bf16, iron_gemv_swiglu_bf16, iron_decode_qkv_rope_bf16) and is consumed by it,
+ * whatever that launch returns.
+ *   iron_tp_push_next: the next iron_gemv_bf16 (no residual, one batch) stores every rounded row
+ *     into slot [parity][rank] of EVERY rank's buffer instead of y (y must still be a valid
+ *     pointer), and each of its CTAs then adds the rows it wrote to an arrival count on every rank.
+ *   iron_tp_pull_next: the next launch takes its activation vector not from x but from the
+ *     exchange: every CTA waits (at most 2 s, then IRON_ERR_TIMEOUT in *d_status) until every rank's
+ *     count covers the K-element vector and builds x = bf16(bf16(sum over ranks, in rank order)
+ *     + residual); one CTA also stores it to x_out (the next residual).  Any fused RMSNorm then
+ *     applies to that x.  The last CTA to finish advances d_state to the next exchange.
+ * Buffers, h_peer_buffers, rank, world and slot_elems are as for iron_tp_allreduce_bf16 (the
+ * counts live in the buffers' first 256 bytes next to that kernel's flags); d_state is four
+ * device words private to the rank, zeroed once: a sequence number, the rows consumed per parity
+ * and a CTA count.  A push and the pull that consumes it form one exchange; all ranks make the
+ * same sequence of exchanges, and an engine uses either these or iron_tp_allreduce_bf16 on one
+ * set of buffers, not both.  No counterpart in the reference (it is single-device). */
+int iron_tp_push_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,
+                      unsigned int* d_state, int* d_status);
+int iron_tp_pull_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,
+                      unsigned int* d_state, int* d_status, const void* residual, void* x_out);
+
 /* ------------------------------------------------------------------------------------
  * Batched decode: every row of the batch is another sequence at its own position with its
  * own KV cache -- the reference runs such sequences one Session at a time

@@ -21,6 +21,17 @@ namespace iron {
 
 enum { GEMV_PLAIN = 0, GEMV_SWIGLU = 1, GEMV_QKV = 2 };
 
+// A tensor-parallel exchange attached to a launch (iron_tp_push_next / iron_tp_pull_next).
+enum { TP_NONE = 0, TP_PUSH = 1, TP_PULL = 2 };
+struct TpLink {
+  int mode, world, rank, slot_elems;
+  unsigned char* peer[8];         // every rank's exchange buffer as this rank addresses it
+  unsigned int* state;            // this rank's own: [0] sequence number, [1] [2] rows consumed per parity, [3] CTAs done
+  int* status;
+  const __nv_bfloat16* residual;  // pull: added to the ranks' sum (may be null)
+  __nv_bfloat16* x_out;           // pull: where CTA 0 stores the vector it built (may be null)
+};
+
 struct GemvParams {
   const __nv_bfloat16* A;     // PLAIN/QKV: the matrix; SWIGLU: gate
   const __nv_bfloat16* A2;    // SWIGLU: up
@@ -40,7 +51,111 @@ struct GemvParams {
   int position, H, G, D;
   int cache_rows;             // rows of the caches and of the angle table: the position is held below it
   PrefetchHint hint;          // weights a later kernel will stream (may be empty)
+  TpLink tp;                  // tensor-parallel exchange this launch feeds or is fed by (mode 0: none)
 };
+
+// ---- a tensor-parallel exchange folded into the GEMVs on either side of it -----------------
+// A row-parallel projection leaves every rank a partial vector that must be summed over the
+// ranks and added to the residual stream before the next kernel reads it.  Instead of a
+// kernel of its own, the producing GEMV stores each rounded row straight into slot
+// [parity][rank] of EVERY rank's exchange buffer (plain stores to peer memory) and, once per
+// CTA, adds the rows it wrote to an arrival count on every rank (system-scope release); the
+// consuming GEMV, which has been streaming its first weights since before the producer ended,
+// waits (bounded) until every rank's count covers the vector, then every CTA builds
+//   x = bf16(bf16(sum over ranks, in rank order, f32) + residual)
+// in shared memory where it would otherwise have staged x, and CTA 0 also stores it as the
+// next residual.  Slots alternate by the parity of the exchange's sequence number: a rank can
+// be at most one exchange ahead of its slowest peer.  Counts only grow.  The sequence number
+// and the two running totals live in this rank's own memory and are advanced by the last CTA
+// of the consuming kernel to finish.
+constexpr int kTpCountOffset = 128;                      // bytes: counts [2][world] after the flags
+constexpr int kTpSlotOffset = 256;
+constexpr unsigned long long kTpLinkWaitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned int tpl_ld_acquire(const unsigned int* q) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(q) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tpl_red_release(unsigned int* q, unsigned int v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(q), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long tpl_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// One rounded row value of the producing GEMV into every rank's slot.
+__device__ __forceinline__ void tp_push_row(const TpLink& tp, unsigned int par, int row, float v) {
+  const __nv_bfloat16 b = __float2bfloat16_rn(v);
+  for (int r = 0; r < tp.world; ++r) {
+    __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(tp.peer[r] + kTpSlotOffset) +
+                          ((size_t)par * tp.world + tp.rank) * tp.slot_elems;
+    slot[row] = b;
+  }
+}
+// After a CTA's last row: make the rows visible everywhere, then count them in on every rank.
+__device__ __forceinline__ void tp_push_done(const TpLink& tp, unsigned int par, const int* s_rows) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < tp.world && *s_rows > 0)
+    tpl_red_release(reinterpret_cast<unsigned int*>(tp.peer[threadIdx.x] + kTpCountOffset) + par * tp.world + tp.rank,
+                    (unsigned int)*s_rows);
+}
+// The consuming side: wait for every rank's rows of exchange `seq`, then x into `xs` (n / 8 chunks).
+__device__ __forceinline__ void tp_pull_x(const TpLink& tp, uint4* xs, int n, int nthreads) {
+  const int tid = threadIdx.x;
+  const unsigned int seq = tp.state[0], par = seq & 1u;
+  const unsigned int want = tp.state[1 + par] + (unsigned int)n;
+  if (tid < tp.world) {
+    const unsigned int* cnt = reinterpret_cast<const unsigned int*>(tp.peer[tp.rank] + kTpCountOffset) + par * tp.world + tid;
+    if ((int)(tpl_ld_acquire(cnt) - want) < 0) {
+      const unsigned long long t0 = tpl_ns();
+      for (unsigned int it = 1;; ++it) {
+        if ((int)(tpl_ld_acquire(cnt) - want) >= 0) break;
+        if ((it & 63u) == 0 && tpl_ns() - t0 > kTpLinkWaitNs) {
+          if (tp.status) *reinterpret_cast<volatile int*>(tp.status) = IRON_ERR_TIMEOUT;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const size_t slot16 = (size_t)tp.slot_elems >> 3;
+  const uint4* mine = reinterpret_cast<const uint4*>(tp.peer[tp.rank] + kTpSlotOffset) + (size_t)par * tp.world * slot16;
+  const uint4* res = reinterpret_cast<const uint4*>(tp.residual);
+  uint4* out = blockIdx.x == 0 && blockIdx.y == 0 ? reinterpret_cast<uint4*>(tp.x_out) : nullptr;
+  for (int i = tid; i < (n >> 3); i += nthreads) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < tp.world; ++r) {
+      float f[8];
+      unpack8(__ldcv(mine + (size_t)r * slot16 + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    if (res) {
+      float f[8];
+      unpack8(ld_cached(res + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(round_bf16(acc[j]), f[j]);
+    }
+    const uint4 v = pack8(acc);
+    xs[i] = v;
+    if (out) out[i] = v;
+  }
+}
+// The last CTA of the consuming kernel to finish moves this rank on to the next exchange.
+__device__ __forceinline__ void tp_pull_done(const TpLink& tp, int n) {
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  const unsigned int ctas = gridDim.x * gridDim.y;
+  __threadfence();
+  if (atomicAdd(tp.state + 3, 1u) != ctas - 1) return;
+  const unsigned int seq = tp.state[0];
+  tp.state[3] = 0;
+  tp.state[1 + (seq & 1u)] += (unsigned int)n;
+  tp.state[0] = seq + 1u;
+}
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
@@ -81,6 +196,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   uint4* xs = smem;                                   // nch chunks of 8 bf16
   float* red = reinterpret_cast<float*>(smem + nch);  // 32 floats for block_sum
   float* part = red + 32;                             // kWarps x 2 partial sums
+  __shared__ int tp_rows;                             // rows this CTA pushed into an exchange
 
   pdl_launch();
   if (threadIdx.x == 0 && blockIdx.y == 0) prefetch_l2_slice(p.hint, blockIdx.x, gridDim.x);
@@ -113,14 +229,22 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
 
   // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
+  unsigned int tp_par = 0;
+  if (p.tp.mode == TP_PUSH) {
+    tp_par = p.tp.state[0] & 1u;
+    if (tid == 0) tp_rows = 0;
+  }
 
-  // ---- stage x (optionally RMS-normalised) into shared memory ----
+  // ---- stage x (optionally RMS-normalised) into shared memory; fed by an exchange, x is
+  // the ranks' sum plus the residual ----
   {
     const uint4* xg = reinterpret_cast<const uint4*>(p.x + (size_t)batch * K);
     float ss = 0.f;
+    if (p.tp.mode == TP_PULL) tp_pull_x(p.tp, xs, K, kThreads);
     for (int i = tid; i < nch; i += kThreads) {
-      uint4 v = ld_cached(xg + i);
-      xs[i] = v;
+      uint4 v;
+      if (p.tp.mode == TP_PULL) v = xs[i];           // written by this thread just above
+      else { v = ld_cached(xg + i); xs[i] = v; }
       if (p.norm_mode) {
         float f[8];
         unpack8(v, f);
@@ -175,7 +299,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
       __syncthreads();
     }
     if (live && ks == 0 && lane == 0) {
-      if (MODE == GEMV_PLAIN) {
+      if (MODE == GEMV_PLAIN && p.tp.mode == TP_PUSH) {
+        tp_push_row(p.tp, tp_par, ra, acc0);
+        if (rb < p.rows) tp_push_row(p.tp, tp_par, rb, acc1);
+        atomicAdd(&tp_rows, rb < p.rows ? 2 : 1);
+      } else if (MODE == GEMV_PLAIN) {
         __nv_bfloat16* y = p.y + (size_t)batch * p.M;
         float v0 = round_bf16(acc0), v1 = round_bf16(acc1);
         if (p.residual) {
@@ -210,6 +338,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     }
     live = live_n; ra = ra_n; rb = rb_n; qa = qa_n; qb = qb_n;
   }
+  if (p.tp.mode == TP_PUSH) tp_push_done(p.tp, tp_par, &tp_rows);
+  if (p.tp.mode == TP_PULL) tp_pull_done(p.tp, K);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -306,7 +436,9 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
   uint4* xs = reinterpret_cast<uint4*>(ring_smem + kRingBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring_smem + kRingBytes + (size_t)kRingMaxK * 2);
   float* red = reinterpret_cast<float*>(bars + kRingWarps * kRingSlots);
+  __shared__ int tp_rows;                             // rows this CTA pushed into an exchange
   if (tid == 0) {
+    tp_rows = 0;
     for (int i = 0; i < kRingWarps * kRingSlots; ++i) ring_mbar_init(bars + i);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -347,12 +479,15 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
 
   // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
+  const unsigned int tp_par = p.tp.mode == TP_PUSH ? (p.tp.state[0] & 1u) : 0u;
   {
     const uint4* xg = reinterpret_cast<const uint4*>(p.x);
     float ss = 0.f;
+    if (p.tp.mode == TP_PULL) tp_pull_x(p.tp, xs, K, kRingThreads);
     for (int i = tid; i < nch; i += kRingThreads) {
-      const uint4 v = ld_cached(xg + i);
-      xs[i] = v;
+      uint4 v;
+      if (p.tp.mode == TP_PULL) v = xs[i];           // written by this thread just above
+      else { v = ld_cached(xg + i); xs[i] = v; }
       if (p.norm_mode) {
         float f[8];
         unpack8(v, f);
@@ -438,7 +573,12 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
 #pragma unroll
       for (int u = 0; u < 4; ++u) { pa[u] = 0.f; pb[u] = 0.f; }
       if (lane != 0) continue;
-      if (MODE == RING_ROW || MODE == RING_PAIR) {
+      if ((MODE == RING_ROW || MODE == RING_PAIR) && p.tp.mode == TP_PUSH) {
+        tp_push_row(p.tp, tp_par, ra, acc0);
+        const bool two = MODE == RING_PAIR && rb < p.rows;
+        if (two) tp_push_row(p.tp, tp_par, rb, acc1);
+        atomicAdd(&tp_rows, two ? 2 : 1);
+      } else if (MODE == RING_ROW || MODE == RING_PAIR) {
         float v0 = round_bf16(acc0), v1 = round_bf16(acc1);
         if (p.residual) {
           v0 = __fadd_rn(v0, __bfloat162float(p.residual[ra]));
@@ -479,6 +619,8 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
       while (!ring_try_wait(bar, (uint32_t)(idx / kRingSlots) & 1u) && ring_ns() - t0 < kRingWaitNs) {}
     }
   }
+  if (p.tp.mode == TP_PUSH) tp_push_done(p.tp, tp_par, &tp_rows);
+  if (p.tp.mode == TP_PULL) tp_pull_done(p.tp, K);
 }
 
 // Which shapes go to the TMA-fed kernel (IRON_GEMV_RING, a bit mask; -1 = unset).
@@ -575,8 +717,38 @@ static int launch_gemv_w(GemvParams& p, int npairs, int batches, cudaStream_t st
 
 static bool aligned32(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; }
 
+// The exchange the next GEMV-family launch of this thread takes part in (consumed by it).
+static thread_local TpLink g_next_link = {};
+static TpLink take_tp_link() {
+  TpLink l = g_next_link;
+  g_next_link = TpLink{};
+  return l;
+}
+static int set_tp_link(int mode, const void* const* h_peer_buffers, int rank, int world, int slot_elems,
+                       unsigned int* d_state, int* d_status, const void* residual, void* x_out) {
+  g_next_link = TpLink{};
+  if (world <= 0 || world > 8 || rank < 0 || rank >= world) return IRON_ERR_SHAPE;
+  if (slot_elems <= 0 || (slot_elems & 7) || !h_peer_buffers || !d_state) return IRON_ERR_SHAPE;
+  if ((residual && !aligned16(residual)) || (x_out && !aligned16(x_out))) return IRON_ERR_ALIGN;
+  TpLink l = {};
+  l.mode = mode; l.world = world; l.rank = rank; l.slot_elems = slot_elems;
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_buffers[r] || !aligned16(h_peer_buffers[r])) return IRON_ERR_ALIGN;
+    l.peer[r] = static_cast<unsigned char*>(const_cast<void*>(h_peer_buffers[r]));
+  }
+  l.state = d_state; l.status = d_status;
+  l.residual = (const __nv_bfloat16*)residual; l.x_out = (__nv_bfloat16*)x_out;
+  g_next_link = l;
+  return IRON_OK;
+}
+
 template <int MODE>
 static int launch_gemv(GemvParams& p, int npairs, int batches, cudaStream_t stream) {
+  if (p.tp.mode != TP_NONE) {
+    if (batches != 1 || p.repeat != 1) return IRON_ERR_UNSUPPORTED;
+    if (p.tp.mode == TP_PUSH && (MODE != GEMV_PLAIN || p.residual || p.rows > p.tp.slot_elems)) return IRON_ERR_UNSUPPORTED;
+    if (p.tp.mode == TP_PULL && p.K > p.tp.slot_elems) return IRON_ERR_SHAPE;
+  }
   // Which shapes stream through the TMA-fed kernel: IRON_GEMV_RING is a bit mask (1 gate/up,
   // 2 large plain matrices, 4 q/k/v, 8 small plain matrices); unset = 3.  Measured on the
   // Llama-3.2-1B decode step: gate/up 12.3 us against 14.5 us register-streamed; the whole
@@ -611,28 +783,42 @@ extern "C" int iron_gemv_bf16(const void* A, const void* x, void* y, int M, int 
                               int repeat, int valid_rows, int norm_mode,
                               const void* norm_weight, float eps, const void* residual,
                               iron_stream_t stream) {
+  const TpLink link = take_tp_link();   // consumed by this call whatever it returns
   int rc = check_common(A, x, y, M, K);
   if (rc) return rc;
   if (batches <= 0 || repeat <= 0 || batches % repeat) return IRON_ERR_SHAPE;
   if (valid_rows < 0 || valid_rows > M) return IRON_ERR_SHAPE;
   if (norm_mode < 0 || norm_mode > 2 || (norm_mode == 2 && !norm_weight)) return IRON_ERR_SHAPE;
   if (norm_mode == 2 && !aligned16(norm_weight)) return IRON_ERR_ALIGN;
-  if (valid_rows == 0) return IRON_OK;
+  if (valid_rows == 0) return link.mode == TP_NONE ? IRON_OK : IRON_ERR_UNSUPPORTED;
   GemvParams p = {};
+  p.tp = link;
   p.A = (const __nv_bfloat16*)A; p.x = (const __nv_bfloat16*)x; p.y = (__nv_bfloat16*)y;
   p.residual = (const __nv_bfloat16*)residual; p.norm_w = (const __nv_bfloat16*)norm_weight;
   p.M = M; p.K = K; p.repeat = repeat; p.rows = valid_rows; p.norm_mode = norm_mode; p.eps = eps;
   return launch_gemv<GEMV_PLAIN>(p, (valid_rows + 1) / 2, batches, (cudaStream_t)stream);
 }
 
+extern "C" int iron_tp_push_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,
+                                 unsigned int* d_state, int* d_status) {
+  return set_tp_link(TP_PUSH, h_peer_buffers, rank, world, slot_elems, d_state, d_status, nullptr, nullptr);
+}
+
+extern "C" int iron_tp_pull_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,
+                                 unsigned int* d_state, int* d_status, const void* residual, void* x_out) {
+  return set_tp_link(TP_PULL, h_peer_buffers, rank, world, slot_elems, d_state, d_status, residual, x_out);
+}
+
 extern "C" int iron_gemv_swiglu_bf16(const void* Wg, const void* Wu, const void* x, void* y,
                                      int M, int K, int norm_mode, const void* norm_weight,
                                      float eps, iron_stream_t stream) {
+  const TpLink link = take_tp_link();
   int rc = check_common(Wg, x, y, M, K);
   if (rc) return rc;
   if (!aligned16(Wu)) return IRON_ERR_ALIGN;
   if (norm_mode < 0 || norm_mode > 2 || (norm_mode == 2 && !norm_weight)) return IRON_ERR_SHAPE;
   GemvParams p = {};
+  p.tp = link;
   p.A = (const __nv_bfloat16*)Wg; p.A2 = (const __nv_bfloat16*)Wu;
   p.x = (const __nv_bfloat16*)x; p.y = (__nv_bfloat16*)y;
   p.norm_w = (const __nv_bfloat16*)norm_weight;
@@ -645,6 +831,7 @@ extern "C" int iron_decode_qkv_rope_bf16(const void* Wqkv, const void* x, int K,
                                          int position, const int* d_position, void* q_out,
                                          void* k_cache, void* v_cache, int H, int G, int D,
                                          int cache_rows, iron_stream_t stream) {
+  const TpLink link = take_tp_link();
   if (H <= 0 || G <= 0 || D <= 0 || (D & 15) || cache_rows <= 0) return IRON_ERR_SHAPE;
   const int M = (H + 2 * G) * D;
   int rc = check_common(Wqkv, x, q_out, M, K);
@@ -653,6 +840,7 @@ extern "C" int iron_decode_qkv_rope_bf16(const void* Wqkv, const void* x, int K,
   if (norm_mode < 0 || norm_mode > 2 || (norm_mode == 2 && !norm_weight)) return IRON_ERR_SHAPE;
   if (!d_position && (position < 0 || position >= cache_rows)) return IRON_ERR_SHAPE;
   GemvParams p = {};
+  p.tp = link;
   p.A = (const __nv_bfloat16*)Wqkv; p.x = (const __nv_bfloat16*)x; p.y = (__nv_bfloat16*)q_out;
   p.norm_w = (const __nv_bfloat16*)norm_weight;
   p.M = M; p.K = K; p.repeat = 1; p.rows = M; p.norm_mode = norm_mode; p.eps = eps;

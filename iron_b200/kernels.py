@@ -541,6 +541,19 @@ def tp_buffer_bytes(world: int, slot_elems: int) -> int:
     return _lib.load().iron_tp_buffer_bytes(world, slot_elems)
 
 
+def tp_push_next(*, peer_buffers, slot_elems, rank, world, state, status=None) -> None:
+    """The next ``gemv`` call stores its rows into every rank's exchange buffer instead of ``y``."""
+    call("iron_tp_push_next", peer_buffers, rank, world, slot_elems, _ptr(state), _ptr(status))
+
+
+def tp_pull_next(*, peer_buffers, slot_elems, rank, world, state, status=None, residual=None, x_out=None) -> None:
+    """The next GEMV-family call takes ``x = sum over ranks + residual`` from the exchange (and
+    stores it to ``x_out``) instead of reading its ``x`` argument."""
+    _bf16(residual, x_out)
+    call("iron_tp_pull_next", peer_buffers, rank, world, slot_elems, _ptr(state), _ptr(status),
+         _ptr(residual), _ptr(x_out))
+
+
 def tp_allreduce(part, y, *, residual=None, peer_buffers, slot_elems, rank, world, seq, status=None):
     """Sum ``part`` over the tensor-parallel ranks through peer memory, add ``residual``.
 

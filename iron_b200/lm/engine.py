@@ -344,6 +344,7 @@ class LlamaEngine:
         (torch symmetric memory over NVLink peer access), for the decode step's fused
         all-reduce + residual add.  IRON_TP_PEER=0 keeps the NCCL all-reduce."""
         self.peer_buffers = None
+        self.tp_fused = False
         if self.tp_size == 1 or os.environ.get("IRON_TP_PEER", "1") == "0":
             return
         import ctypes
@@ -364,6 +365,10 @@ class LlamaEngine:
         ptrs = [int(q) for q in self._peer_handle.buffer_ptrs]
         self.peer_buffers = (ctypes.c_void_p * self.tp_size)(*ptrs)
         self.peer_seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # a one-sequence step folds each exchange into the GEMVs on either side of it
+        # (IRON_TP_FUSED=0 keeps the all-reduce kernel of its own)
+        self.tp_fused = self.batch == 1 and os.environ.get("IRON_TP_FUSED", "1") != "0"
+        self.peer_state = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize()
         dist.barrier(group=group)   # every rank's buffer is zeroed before anyone stores into it
 
@@ -372,6 +377,9 @@ class LlamaEngine:
         """How a decode step's partial sums meet under tensor parallelism."""
         if self.tp_size == 1:
             return "none"
+        if self.tp_fused:
+            return ("peer memory, no launch of its own (the producing GEMV stores its rows into every rank's slot, "
+                    "the consuming GEMV waits, bounded, and sums in rank order)")
         if self.peer_buffers is not None and self.c.hidden_size * self.batch <= self.peer_slot_elems:
             return "peer-memory kernel (stores to every rank's slot, bounded flag wait, rank-ordered f32 sum)"
         return "nccl all-reduce"
@@ -390,13 +398,18 @@ class LlamaEngine:
     # ------------------------------------------------------------------ decode step
     @property
     def launches_per_step(self) -> int:
-        """Kernels one decode step launches: one persistent kernel, or gather, five per
-        layer, head, draw; a batched step takes gather, eight per layer, norm, head, draw."""
+        """This package's kernels in one decode step: one persistent kernel, or gather, four or
+        five per layer, head, draw; a batched step takes gather, eight per layer, norm, head, draw.
+        Tensor parallelism adds two exchange kernels a layer unless the exchanges ride on the GEMVs,
+        and a key and a pick in place of the draw when the head is split."""
         if self.batch > 1:
             return 1 + 8 * self.c.num_hidden_layers + 3
         if self.fused_step:
             return 1
-        return 1 + (4 if self.attn_oproj else 5) * self.c.num_hidden_layers + 2
+        per_layer = 4 if self.attn_oproj else 5
+        if self.tp_size > 1 and self.peer_buffers is not None and not self.tp_fused:
+            per_layer += 2
+        return 1 + per_layer * self.c.num_hidden_layers + (3 if self.head_sharded else 2)
 
     @property
     def weight_bytes_per_token(self) -> int:
@@ -466,7 +479,28 @@ class LlamaEngine:
         tp = self.tp_size > 1
         K.copy_rows(self.embed, x, ids=d_token, nrows=1, row_bytes=E2, src_rows=c.vocab_size)
         hints = 0 if tp else self.prefetch_hints
-        for i, l in enumerate(self.layers):
+        if tp and self.tp_fused:
+            # Each exchange rides on its neighbours: the row-parallel GEMV pushes its rows to every
+            # rank, the next GEMV pulls the ranks' sum plus the residual as its input.
+            link = dict(peer_buffers=self.peer_buffers, slot_elems=self.peer_slot_elems, rank=self.tp_rank,
+                        world=self.tp_size, state=self.peer_state, status=self.status)
+            pushed = False
+            for l in self.layers:
+                if pushed:
+                    K.tp_pull_next(**link, residual=y, x_out=x)
+                K.decode_qkv_rope(l["wqkv"], x, self.angles, l["k"][0], l["v"][0], self.q[0],
+                                  H=H, G=G, D=D, d_position=d_pos, norm_weight=l["ln1"], eps=c.eps)
+                K.mha_decode(self.q, l["k"], l["v"], self.att, d_kv_valid=d_pos, kv_valid_add=1,
+                             window=c.window, scale=c.attention_scale, nsplit=self.nsplit, stable_prefix=True)
+                K.tp_push_next(**link)
+                K.gemv(l["wo"], self.att[0].view(-1), part)
+                K.tp_pull_next(**link, residual=x, x_out=y)
+                K.gemv_swiglu(l["wg"], l["wu"], y, self.act[0], norm_weight=l["ln2"], eps=c.eps)
+                K.tp_push_next(**link)
+                K.gemv(l["wd"], self.act[0], part)
+                pushed = True
+            K.tp_pull_next(**link, residual=y, x_out=x)   # consumed by the head projection below
+        for i, l in enumerate(self.layers if not (tp and self.tp_fused) else ()):
             if self.attn_oproj and not hints:
                 K.decode_qkv_rope(l["wqkv"], x, self.angles, l["k"][0], l["v"][0], self.q[0],
                                   H=H, G=G, D=D, d_position=d_pos, norm_weight=l["ln1"], eps=c.eps)

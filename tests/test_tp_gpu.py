@@ -1,6 +1,6 @@
 """Tensor-parallel decode and prefill on two GPUs against the single-GPU engine, with the
-decode step's exchange through peer memory (one fused all-reduce + residual kernel per
-rank) and through NCCL.
+decode step's exchange through peer memory -- folded into the GEMVs on either side of it, or
+as one all-reduce + residual kernel per rank -- and through NCCL.
 
 The ranks are child processes.  A rank that fails reports its traceback through the queue
 and leaves at once (between steps, nothing of its own in flight); the parent then ends the
@@ -40,6 +40,7 @@ def _work(rank: int, size: int, out):
     # the output head is split by vocabulary rows too unless switched off: a rank then streams
     # half of it and the greedy token comes from the two ranks' (value, index) keys
     assert tp.head_sharded == (os.environ.get("IRON_TP_SHARD_HEAD", "1") != "0")
+    assert tp.tp_fused == (os.environ["IRON_TP_PEER"] == "1" and os.environ["IRON_TP_FUSED"] == "1")
     logits = [tp.prefill(prompt)]
     drawn = tp.complete(prompt, 5)
     logits.append(tp.logits())
@@ -75,8 +76,8 @@ def _work(rank: int, size: int, out):
         out.put(("ok", rank, None))
 
 
-def _rank(rank: int, size: int, port: int, out, peer: str, shard_head: str):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+def _rank(rank: int, size: int, port: int, out, peer: str, shard_head: str, fused: str):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", IRON_TP_FUSED=fused,
                       IRON_TP_PEER=peer, IRON_TP_SHARD_HEAD=shard_head, TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     try:
         _work(rank, size, out)
@@ -88,9 +89,10 @@ def _rank(rank: int, size: int, port: int, out, peer: str, shard_head: str):
         os._exit(0)   # no collective teardown: the peer may already be gone
 
 
-@pytest.mark.parametrize("peer,shard_head", [("1", "1"), ("0", "1"), ("1", "0")],
-                         ids=["peer-memory exchange", "nccl exchange", "whole head on every rank"])
-def test_two_way_tensor_parallel_matches_one_gpu(peer, shard_head):
+@pytest.mark.parametrize("peer,shard_head,fused", [("1", "1", "1"), ("0", "1", "1"), ("1", "0", "1"), ("1", "1", "0")],
+                         ids=["exchange folded into the GEMVs", "nccl exchange", "whole head on every rank",
+                              "exchange kernel of its own"])
+def test_two_way_tensor_parallel_matches_one_gpu(peer, shard_head, fused):
     import queue
 
     import torch
@@ -101,7 +103,7 @@ def test_two_way_tensor_parallel_matches_one_gpu(peer, shard_head):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, out, peer, shard_head), daemon=True) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, out, peer, shard_head, fused), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
     results = {}
