@@ -440,18 +440,21 @@ int iron_tp_allreduce_bf16(const void* part, const void* residual, void* y, int 
  * whatever that launch returns.
  *   iron_tp_push_next: the next iron_gemv_bf16 (no residual, one batch) stores every rounded row
  *     into slot [parity][rank] of EVERY rank's buffer instead of y (y must still be a valid
- *     pointer), and each of its CTAs then adds the rows it wrote to an arrival count on every rank.
+ *     pointer), as one 32-bit word: the bf16 value and a 16-bit tag of the exchange's number.  A
+ *     word arrives whole, so the tag says its value is there: no fence, no flag, no count.
  *   iron_tp_pull_next: the next launch takes its activation vector not from x but from the
- *     exchange: every CTA waits (at most 2 s, then IRON_ERR_TIMEOUT in *d_status) until every rank's
- *     count covers the K-element vector and builds x = bf16(bf16(sum over ranks, in rank order)
- *     + residual); one CTA also stores it to x_out (the next residual).  Any fused RMSNorm then
- *     applies to that x.  The last CTA to finish advances d_state to the next exchange.
+ *     exchange: every CTA reads all ranks' rows, re-reading words whose tag is not yet this
+ *     exchange's (at most 2 s, then IRON_ERR_TIMEOUT in *d_status and zero for what is missing),
+ *     and builds x = bf16(bf16(sum over ranks, in rank order) + residual); one CTA also stores it
+ *     to x_out (the next residual).  Any fused RMSNorm then applies to that x.  The last CTA to
+ *     finish advances d_state to the next exchange.
  * Buffers, h_peer_buffers, rank, world and slot_elems are as for iron_tp_allreduce_bf16 (the
- * counts live in the buffers' first 256 bytes next to that kernel's flags); d_state is four
- * device words private to the rank, zeroed once: a sequence number, the rows consumed per parity
- * and a CTA count.  A push and the pull that consumes it form one exchange; all ranks make the
- * same sequence of exchanges, and an engine uses either these or iron_tp_allreduce_bf16 on one
- * set of buffers, not both.  No counterpart in the reference (it is single-device). */
+ * tagged words use the buffers' whole length, that kernel's bf16 slots the first half); d_state is
+ * eight device words private to the rank, zeroed once (the exchange's sequence number, a CTA
+ * count).  A push and the pull that consumes it form one exchange; all ranks make the same
+ * sequence of exchanges, and an engine uses either these or iron_tp_allreduce_bf16 on one set
+ * of buffers, not both.  The tensors named here must outlive the launch that consumes the call.
+ * No counterpart in the reference (it is single-device). */
 int iron_tp_push_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,
                       unsigned int* d_state, int* d_status);
 int iron_tp_pull_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,

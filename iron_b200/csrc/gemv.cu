@@ -26,7 +26,7 @@ enum { TP_NONE = 0, TP_PUSH = 1, TP_PULL = 2 };
 struct TpLink {
   int mode, world, rank, slot_elems;
   unsigned char* peer[8];         // every rank's exchange buffer as this rank addresses it
-  unsigned int* state;            // this rank's own: [0] sequence number, [1] [2] rows consumed per parity, [3] CTAs done
+  unsigned int* state;            // this rank's own: [0] the exchange's sequence number, [1] consuming CTAs done
   int* status;
   const __nv_bfloat16* residual;  // pull: added to the ranks' sum (may be null)
   __nv_bfloat16* x_out;           // pull: where CTA 0 stores the vector it built (may be null)
@@ -58,80 +58,73 @@ struct GemvParams {
 // A row-parallel projection leaves every rank a partial vector that must be summed over the
 // ranks and added to the residual stream before the next kernel reads it.  Instead of a
 // kernel of its own, the producing GEMV stores each rounded row straight into slot
-// [parity][rank] of EVERY rank's exchange buffer (plain stores to peer memory) and, once per
-// CTA, adds the rows it wrote to an arrival count on every rank (system-scope release); the
-// consuming GEMV, which has been streaming its first weights since before the producer ended,
-// waits (bounded) until every rank's count covers the vector, then every CTA builds
+// [parity][rank] of EVERY rank's exchange buffer as one 32-bit word: the bf16 value and, in the
+// upper half, a 16-bit tag of the exchange's sequence number.  A word arrives whole, so the tag
+// says that its value is there: no fence and no separate flag (a system-scope fence costs
+// ~5 us on this machine, more than the rest of the exchange).  The consuming GEMV, which has
+// been streaming its first weights since before the producer ended, reads the slots of all
+// ranks (16 bytes = four rows at a time), re-reading (bounded) any word whose tag is not yet
+// this exchange's, and every CTA builds
 //   x = bf16(bf16(sum over ranks, in rank order, f32) + residual)
-// in shared memory where it would otherwise have staged x, and CTA 0 also stores it as the
-// next residual.  Slots alternate by the parity of the exchange's sequence number: a rank can
-// be at most one exchange ahead of its slowest peer.  Counts only grow.  The sequence number
-// and the two running totals live in this rank's own memory and are advanced by the last CTA
-// of the consuming kernel to finish.
-constexpr int kTpCountOffset = 128;                      // bytes: counts [2][world] after the flags
-constexpr int kTpSlotOffset = 256;
+// in shared memory where it would otherwise have staged x; CTA 0 also stores it as the next
+// residual.  Slots alternate by the parity of the sequence number: a rank can be at most one
+// exchange ahead of its slowest peer, so a slot is never overwritten before it is read.  The
+// sequence number lives in this rank's own memory and is advanced by the last CTA of the
+// consuming kernel to finish.
+constexpr int kTpSlotOffset = 256;                       // bytes: the tagged slots follow the all-reduce kernel's flags
 constexpr unsigned long long kTpLinkWaitNs = 2000000000ull;
 
-__device__ __forceinline__ unsigned int tpl_ld_acquire(const unsigned int* q) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(q) : "memory");
-  return v;
-}
-__device__ __forceinline__ void tpl_red_release(unsigned int* q, unsigned int v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(q), "r"(v) : "memory");
-}
 __device__ __forceinline__ unsigned long long tpl_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ unsigned int tp_tag(unsigned int seq) { return ((seq >> 1) + 1u) & 0xffffu; }
+__device__ __forceinline__ uint32_t* tp_slot(const TpLink& tp, int owner, unsigned int par, int rank) {
+  return reinterpret_cast<uint32_t*>(tp.peer[owner] + kTpSlotOffset) + ((size_t)par * tp.world + rank) * tp.slot_elems;
+}
 // One rounded row value of the producing GEMV into every rank's slot.
-__device__ __forceinline__ void tp_push_row(const TpLink& tp, unsigned int par, int row, float v) {
-  const __nv_bfloat16 b = __float2bfloat16_rn(v);
-  for (int r = 0; r < tp.world; ++r) {
-    __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(tp.peer[r] + kTpSlotOffset) +
-                          ((size_t)par * tp.world + tp.rank) * tp.slot_elems;
-    slot[row] = b;
-  }
+__device__ __forceinline__ void tp_push_row(const TpLink& tp, unsigned int seq, int row, float v) {
+  const uint32_t word = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v)) | (tp_tag(seq) << 16);
+  for (int r = 0; r < tp.world; ++r)
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(tp_slot(tp, r, seq & 1u, tp.rank) + row), "r"(word) : "memory");
 }
-// After a CTA's last row: make the rows visible everywhere, then count them in on every rank.
-__device__ __forceinline__ void tp_push_done(const TpLink& tp, unsigned int par, const int* s_rows) {
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < tp.world && *s_rows > 0)
-    tpl_red_release(reinterpret_cast<unsigned int*>(tp.peer[threadIdx.x] + kTpCountOffset) + par * tp.world + tp.rank,
-                    (unsigned int)*s_rows);
-}
-// The consuming side: wait for every rank's rows of exchange `seq`, then x into `xs` (n / 8 chunks).
+// The consuming side: x (n elements, n % 8 == 0) into `xs`, from the ranks' rows of the running exchange.
 __device__ __forceinline__ void tp_pull_x(const TpLink& tp, uint4* xs, int n, int nthreads) {
   const int tid = threadIdx.x;
-  const unsigned int seq = tp.state[0], par = seq & 1u;
-  const unsigned int want = tp.state[1 + par] + (unsigned int)n;
-  if (tid < tp.world) {
-    const unsigned int* cnt = reinterpret_cast<const unsigned int*>(tp.peer[tp.rank] + kTpCountOffset) + par * tp.world + tid;
-    if ((int)(tpl_ld_acquire(cnt) - want) < 0) {
-      const unsigned long long t0 = tpl_ns();
-      for (unsigned int it = 1;; ++it) {
-        if ((int)(tpl_ld_acquire(cnt) - want) >= 0) break;
-        if ((it & 63u) == 0 && tpl_ns() - t0 > kTpLinkWaitNs) {
-          if (tp.status) *reinterpret_cast<volatile int*>(tp.status) = IRON_ERR_TIMEOUT;
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  const size_t slot16 = (size_t)tp.slot_elems >> 3;
-  const uint4* mine = reinterpret_cast<const uint4*>(tp.peer[tp.rank] + kTpSlotOffset) + (size_t)par * tp.world * slot16;
+  const unsigned int seq = tp.state[0], tag = tp_tag(seq);
   const uint4* res = reinterpret_cast<const uint4*>(tp.residual);
   uint4* out = blockIdx.x == 0 && blockIdx.y == 0 ? reinterpret_cast<uint4*>(tp.x_out) : nullptr;
+  unsigned long long t0 = 0;
+  bool gave_up = false;
   for (int i = tid; i < (n >> 3); i += nthreads) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int r = 0; r < tp.world; ++r) {
-      float f[8];
-      unpack8(__ldcv(mine + (size_t)r * slot16 + i), f);
+      const uint32_t* src = tp_slot(tp, tp.rank, seq & 1u, r) + 8 * i;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      for (int h = 0; h < 2; ++h) {
+        uint32_t w0, w1, w2, w3;
+        for (unsigned int it = 0;; ++it) {
+          asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "l"(src + 4 * h) : "memory");
+          if (((w0 >> 16) == tag) & ((w1 >> 16) == tag) & ((w2 >> 16) == tag) & ((w3 >> 16) == tag)) break;
+          if (gave_up) break;
+          if ((it & 63u) == 63u) {
+            const unsigned long long now = tpl_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kTpLinkWaitNs) {
+              gave_up = true;
+              if (tp.status) *reinterpret_cast<volatile int*>(tp.status) = IRON_ERR_TIMEOUT;
+              break;
+            }
+          }
+        }
+        // a word that never arrived (after the limit) counts as zero
+        acc[4 * h + 0] += (w0 >> 16) == tag ? __uint_as_float(w0 << 16) : 0.f;
+        acc[4 * h + 1] += (w1 >> 16) == tag ? __uint_as_float(w1 << 16) : 0.f;
+        acc[4 * h + 2] += (w2 >> 16) == tag ? __uint_as_float(w2 << 16) : 0.f;
+        acc[4 * h + 3] += (w3 >> 16) == tag ? __uint_as_float(w3 << 16) : 0.f;
+      }
     }
     if (res) {
       float f[8];
@@ -145,16 +138,13 @@ __device__ __forceinline__ void tp_pull_x(const TpLink& tp, uint4* xs, int n, in
   }
 }
 // The last CTA of the consuming kernel to finish moves this rank on to the next exchange.
-__device__ __forceinline__ void tp_pull_done(const TpLink& tp, int n) {
+__device__ __forceinline__ void tp_pull_done(const TpLink& tp) {
   __syncthreads();
   if (threadIdx.x != 0) return;
   const unsigned int ctas = gridDim.x * gridDim.y;
-  __threadfence();
-  if (atomicAdd(tp.state + 3, 1u) != ctas - 1) return;
-  const unsigned int seq = tp.state[0];
-  tp.state[3] = 0;
-  tp.state[1 + (seq & 1u)] += (unsigned int)n;
-  tp.state[0] = seq + 1u;
+  if (atomicAdd(tp.state + 1, 1u) != ctas - 1) return;
+  tp.state[1] = 0;
+  tp.state[0] = tp.state[0] + 1u;
 }
 
 constexpr int kThreads = 256;
@@ -196,7 +186,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   uint4* xs = smem;                                   // nch chunks of 8 bf16
   float* red = reinterpret_cast<float*>(smem + nch);  // 32 floats for block_sum
   float* part = red + 32;                             // kWarps x 2 partial sums
-  __shared__ int tp_rows;                             // rows this CTA pushed into an exchange
 
   pdl_launch();
   if (threadIdx.x == 0 && blockIdx.y == 0) prefetch_l2_slice(p.hint, blockIdx.x, gridDim.x);
@@ -229,11 +218,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
 
   // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
-  unsigned int tp_par = 0;
-  if (p.tp.mode == TP_PUSH) {
-    tp_par = p.tp.state[0] & 1u;
-    if (tid == 0) tp_rows = 0;
-  }
+  const unsigned int tp_seq = p.tp.mode == TP_PUSH ? p.tp.state[0] : 0u;
 
   // ---- stage x (optionally RMS-normalised) into shared memory; fed by an exchange, x is
   // the ranks' sum plus the residual ----
@@ -300,9 +285,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     }
     if (live && ks == 0 && lane == 0) {
       if (MODE == GEMV_PLAIN && p.tp.mode == TP_PUSH) {
-        tp_push_row(p.tp, tp_par, ra, acc0);
-        if (rb < p.rows) tp_push_row(p.tp, tp_par, rb, acc1);
-        atomicAdd(&tp_rows, rb < p.rows ? 2 : 1);
+        tp_push_row(p.tp, tp_seq, ra, acc0);
+        if (rb < p.rows) tp_push_row(p.tp, tp_seq, rb, acc1);
       } else if (MODE == GEMV_PLAIN) {
         __nv_bfloat16* y = p.y + (size_t)batch * p.M;
         float v0 = round_bf16(acc0), v1 = round_bf16(acc1);
@@ -338,8 +322,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     }
     live = live_n; ra = ra_n; rb = rb_n; qa = qa_n; qb = qb_n;
   }
-  if (p.tp.mode == TP_PUSH) tp_push_done(p.tp, tp_par, &tp_rows);
-  if (p.tp.mode == TP_PULL) tp_pull_done(p.tp, K);
+  if (p.tp.mode == TP_PULL) tp_pull_done(p.tp);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -436,9 +419,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
   uint4* xs = reinterpret_cast<uint4*>(ring_smem + kRingBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring_smem + kRingBytes + (size_t)kRingMaxK * 2);
   float* red = reinterpret_cast<float*>(bars + kRingWarps * kRingSlots);
-  __shared__ int tp_rows;                             // rows this CTA pushed into an exchange
   if (tid == 0) {
-    tp_rows = 0;
     for (int i = 0; i < kRingWarps * kRingSlots; ++i) ring_mbar_init(bars + i);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -479,7 +460,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
 
   // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
-  const unsigned int tp_par = p.tp.mode == TP_PUSH ? (p.tp.state[0] & 1u) : 0u;
+  const unsigned int tp_seq = p.tp.mode == TP_PUSH ? p.tp.state[0] : 0u;
   {
     const uint4* xg = reinterpret_cast<const uint4*>(p.x);
     float ss = 0.f;
@@ -574,10 +555,8 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
       for (int u = 0; u < 4; ++u) { pa[u] = 0.f; pb[u] = 0.f; }
       if (lane != 0) continue;
       if ((MODE == RING_ROW || MODE == RING_PAIR) && p.tp.mode == TP_PUSH) {
-        tp_push_row(p.tp, tp_par, ra, acc0);
-        const bool two = MODE == RING_PAIR && rb < p.rows;
-        if (two) tp_push_row(p.tp, tp_par, rb, acc1);
-        atomicAdd(&tp_rows, two ? 2 : 1);
+        tp_push_row(p.tp, tp_seq, ra, acc0);
+        if (MODE == RING_PAIR && rb < p.rows) tp_push_row(p.tp, tp_seq, rb, acc1);
       } else if (MODE == RING_ROW || MODE == RING_PAIR) {
         float v0 = round_bf16(acc0), v1 = round_bf16(acc1);
         if (p.residual) {
@@ -619,8 +598,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
       while (!ring_try_wait(bar, (uint32_t)(idx / kRingSlots) & 1u) && ring_ns() - t0 < kRingWaitNs) {}
     }
   }
-  if (p.tp.mode == TP_PUSH) tp_push_done(p.tp, tp_par, &tp_rows);
-  if (p.tp.mode == TP_PULL) tp_pull_done(p.tp, K);
+  if (p.tp.mode == TP_PULL) tp_pull_done(p.tp);
 }
 
 // Which shapes go to the TMA-fed kernel (IRON_GEMV_RING, a bit mask; -1 = unset).

@@ -111,7 +111,9 @@ using namespace iron;
 
 extern "C" size_t iron_tp_buffer_bytes(int world, int slot_elems) {
   if (world <= 0 || world > kTpMaxWorld || slot_elems <= 0) return 0;
-  return kTpFlagBytes + (size_t)2 * world * slot_elems * sizeof(__nv_bfloat16);
+  // room for the tagged 32-bit words of an exchange folded into the GEMVs (gemv.cu); this kernel's bf16
+  // slots take the first half
+  return kTpFlagBytes + (size_t)2 * world * slot_elems * sizeof(uint32_t);
 }
 
 extern "C" int iron_tp_allreduce_bf16(const void* part, const void* residual, void* y, int n, int slot_elems,

@@ -368,7 +368,7 @@ class LlamaEngine:
         # a one-sequence step folds each exchange into the GEMVs on either side of it
         # (IRON_TP_FUSED=0 keeps the all-reduce kernel of its own)
         self.tp_fused = self.batch == 1 and os.environ.get("IRON_TP_FUSED", "1") != "0"
-        self.peer_state = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.peer_state = torch.zeros(8, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize()
         dist.barrier(group=group)   # every rank's buffer is zeroed before anyone stores into it
 

@@ -43,7 +43,7 @@ def test_a_flag_nobody_raises_ends_in_a_timeout_status_not_a_hang():
     # the context is intact: the same call with every flag present completes at once
     status.zero_()
     # play rank 1 by hand for the second all-reduce (sequence 1, parity 1): its slot and flag in `mine`
-    slots = mine[256:].view(torch.bfloat16).view(2, 2, n)
+    slots = mine[256 : 256 + 2 * 2 * n * 2].view(torch.bfloat16).view(2, 2, n)   # this kernel's bf16 slots
     slots[1, 1] = 2.0
     mine[:256].view(torch.int32)[1 * 2 + 1] = 2
     torch.cuda.synchronize()

@@ -31,13 +31,13 @@ def K():
 
 
 class Rank:
-    """One rank's side of the exchange: its buffer, its four state words, its status word."""
+    """One rank's side of the exchange: its buffer, its eight state words, its status word."""
 
     def __init__(self, K, world, n):
         import torch
 
         self.buffer = torch.zeros(K.tp_buffer_bytes(world, n), dtype=torch.uint8, device="cuda")
-        self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self.state = torch.zeros(8, dtype=torch.int32, device="cuda")
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
 
@@ -118,7 +118,7 @@ def test_a_rank_exchanging_with_itself_reproduces_the_separate_steps(K, E, inner
     want = ops.gemv(head, ops.rms_norm(ops.gemv(wo, att), ln, 1e-5))
     assert_verdict(to_numpy(logits), want, Tolerance.bf16_ulps(2), what="plain GEMV fed by an exchange")
     torch.cuda.synchronize()
-    assert me[0].state.tolist() == [3, 2 * E, E, 0] and int(me[0].status.item()) == 0
+    assert me[0].state.tolist()[:2] == [3, 0] and int(me[0].status.item()) == 0
 
 
 def test_two_ranks_on_one_gpu_sum_in_rank_order(K):
@@ -148,7 +148,7 @@ def test_two_ranks_on_one_gpu_sum_in_rank_order(K):
             want_act = ops.mul(ops.silu(ops.gemv(wg, want)), ops.gemv(wu, want))
             assert_verdict(to_numpy(act), want_act, Tolerance.bf16_ulps(2), what="two ranks' sum")
     assert all(int(r.status.item()) == 0 for r in ranks)
-    assert ranks[0].state.tolist() == ranks[1].state.tolist() == [2, E, E, 0]
+    assert ranks[0].state.tolist()[:2] == ranks[1].state.tolist()[:2] == [2, 0]
 
 
 def test_what_the_exchange_refuses(K):
@@ -171,7 +171,7 @@ def test_what_the_exchange_refuses(K):
     with pytest.raises(IronError):                      # the vector does not fit a slot
         K.gemv(A, v)
     torch.cuda.synchronize()
-    assert me[0].state.tolist() == [0, 0, 0, 0]
+    assert me[0].state.tolist() == [0] * 8
 
 
 def test_a_rank_that_never_pushes_ends_the_pull_in_a_timeout_status(K):
