@@ -339,9 +339,15 @@ int iron_decode_attn_oproj_bf16(const void* q, const void* Wo, const void* x, in
  * tensor cores (64-row chunks: scores C B^T, decay-masked scores times x, C times the
  * carried state, the state update, as bf16 products with float32 accumulation and a float32
  * state): the same function within the operator's tolerance (iron/operators/
- * selective_scan.py:353-356), not bit for bit the step-by-step kernel.  iron_set_scan_chunked(0)
- * (or IRON_SCAN_CHUNKED=0 in the environment) keeps every call step by step. */
-void iron_set_scan_chunked(int enabled);
+ * selective_scan.py:353-356), not bit for bit the step-by-step kernel.  With 128 states and at
+ * least 128 rows the chunks are 128 rows and the four products run as tcgen05.mma with
+ * tensor-memory accumulators (TMA-fed operands; the float32 operands enter as a bf16 head and
+ * remainder).  iron_set_scan_chunked(mode), or IRON_SCAN_CHUNKED in the environment: 2 (default)
+ * tcgen05 where the shape fits, 1 warp MMAs only, 0 every call step by step.
+ * iron_selective_scan_status_word names the device word that receives IRON_ERR_TIMEOUT when a
+ * bounded pipeline wait of the tcgen05 kernel gives up (NULL: none; per device). */
+void iron_set_scan_chunked(int mode);
+void iron_selective_scan_status_word(int* d_status);
 int iron_selective_scan_bf16(const void* xbc, const void* dt, const void* head,
                              const void* state, void* y, void* final_state, int batch,
                              int rows, int heads, int head_dim, int state_size, int groups,

@@ -93,6 +93,7 @@ SIGNATURES: dict[str, tuple] = {
         [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _P, _I, _I, _I, _F, _I, _I, _P],
     ),
     "iron_set_scan_chunked": (None, [_I]),
+    "iron_selective_scan_status_word": (None, [_P]),
     "iron_selective_scan_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "iron_causal_conv1d_bf16": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P]),
     "iron_gemm_qkv_rope_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),

@@ -15,29 +15,12 @@
 // (each product and each partial sum rounded to bf16), optional bias and SiLU fused.
 #include "common.cuh"
 #include "mma.cuh"
+#include "scan.cuh"
 
 namespace iron {
 
 constexpr int kScanThreads = 128;
 constexpr int kTB = 16;   // time steps staged per block
-
-struct ScanParams {
-  const __nv_bfloat16* xbc;   // (B, rows, width): x (H*P) | B (G*N) | C (G*N)
-  const __nv_bfloat16* dt;    // (B, rows, H)
-  const float* head;          // (H, 3): dt_bias, A, D
-  const float* state;         // (B, H, P, N) or null: zeros
-  __nv_bfloat16* y;           // (B, rows, H*P)
-  float* final_state;         // (B, H, P, N) or null
-  int rows, H, P, G, width;
-  int valid;
-  const int* d_valid;
-  long long xbc_batch, dt_batch, y_batch, state_batch;  // element strides
-};
-
-__device__ __forceinline__ float softplus_f32(float v) {
-  // logaddexp(0, v) = max(v, 0) + log1p(exp(-|v|))
-  return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v)));
-}
 
 // TPP threads share a pair of state rows (4 or 8); a CTA covers kPT = 2 * 128 / TPP rows of a head.
 template <int N, int TPP>
@@ -711,18 +694,22 @@ static int launch_ssd(const ScanParams& p, int batch, cudaStream_t stream) {
   return cudaLaunchKernelEx(&cfg, ssd_scan_kernel<N>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
-// Calls of a prompt's length on the shapes the chunked kernel takes run on it;
-// IRON_SCAN_CHUNKED=0 keeps every call on the step-by-step kernel.
+// Calls of a prompt's length on the shapes the chunked kernels take run on them: 2 (the default)
+// = the tcgen05 kernel where its shape fits (64-wide heads, 128 states, 128 rows or more), else
+// the warp-MMA kernel; 1 = the warp-MMA kernel only; 0 (IRON_SCAN_CHUNKED=0) keeps every call on
+// the step-by-step kernel.
 static std::atomic<int> g_ssd_on{-1};
-static bool ssd_enabled() {
+static int ssd_mode() {
   int on = g_ssd_on.load(std::memory_order_relaxed);
   if (on < 0) {
     const char* e = getenv("IRON_SCAN_CHUNKED");
-    on = (e && e[0] == '0') ? 0 : 1;
+    on = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
     g_ssd_on.store(on, std::memory_order_relaxed);
   }
-  return on != 0;
+  return on;
 }
+static bool ssd_enabled() { return ssd_mode() != 0; }
+static int* g_scan_status[64] = {};   // one status word per device
 
 template <typename... Args>
 static int launch_scan_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
@@ -739,7 +726,13 @@ static int launch_scan_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaS
 
 using namespace iron;
 
-extern "C" void iron_set_scan_chunked(int enabled) { g_ssd_on.store(enabled ? 1 : 0, std::memory_order_relaxed); }
+extern "C" void iron_set_scan_chunked(int mode) {
+  g_ssd_on.store(mode < 0 ? 0 : (mode > 2 ? 2 : mode), std::memory_order_relaxed);
+}
+extern "C" void iron_selective_scan_status_word(int* d_status) {
+  const int dev = current_device();
+  if (dev >= 0) g_scan_status[dev] = d_status;
+}
 
 extern "C" int iron_selective_scan_bf16(const void* xbc, const void* dt, const void* head, const void* state,
                                         void* y, void* final_state, int batch, int rows, int heads,
@@ -766,7 +759,12 @@ extern "C" int iron_selective_scan_bf16(const void* xbc, const void* dt, const v
   const dim3 block(kScanThreads);
   const dim3 grid64(heads * ((head_dim + 63) / 64), batch);
   cudaStream_t s = (cudaStream_t)stream;
-  if (head_dim == kSsdP && rows >= 32 && ssd_enabled()) {   // the chunked form on the tensor cores
+  if (head_dim == kSsdP && state_size == 128 && rows >= 128 && ssd_mode() == 2) {   // tcgen05, 128-row chunks
+    const int dev = current_device();
+    const int rc = launch_ssd_tc(p, batch, s, dev >= 0 ? g_scan_status[dev] : nullptr);
+    if (rc != IRON_ERR_UNSUPPORTED) return rc;
+  }
+  if (head_dim == kSsdP && rows >= 32 && ssd_enabled()) {   // the chunked form on warp MMAs
     if (state_size == 128) return launch_ssd<128>(p, batch, s);
     if (state_size == 64) return launch_ssd<64>(p, batch, s);
   }

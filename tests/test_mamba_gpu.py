@@ -24,22 +24,24 @@ def K():
     return kernels
 
 
-@pytest.fixture(params=["chunked", "step by step"])
+@pytest.fixture(params=["chunked, tensor memory", "chunked, warp MMAs", "step by step"])
 def form(request):
-    """Both forms of the scan: prompt-length calls on the 64-wide-head shapes take the chunked
-    tensor-core kernel unless it is switched off; everything else runs step by step either way."""
+    """The forms of the scan: prompt-length calls on the 64-wide-head shapes take a chunked
+    tensor-core kernel unless it is switched off -- tcgen05 with 128-row chunks where there are 128
+    states and 128 rows, warp MMAs with 64-row chunks otherwise -- everything else runs step by step."""
     from iron_b200 import _lib
 
     lib = _lib.load()
-    lib.iron_set_scan_chunked(1 if request.param == "chunked" else 0)
-    yield request.param
-    lib.iron_set_scan_chunked(1)
+    mode = {"chunked, tensor memory": 2, "chunked, warp MMAs": 1, "step by step": 0}[request.param]
+    lib.iron_set_scan_chunked(mode)
+    yield "chunked" if mode else "step by step"
+    lib.iron_set_scan_chunked(2)
 
 
 def state_tolerance(form):
     """Both forms keep the state in float32; the chunked form adds a chunk's rows as a bf16 head
     and a bf16 remainder, which is float32's accuracy but another order of the sums."""
-    return Tolerance.relative(1e-4, atol=1e-4 if form == "chunked" else 1e-5)
+    return Tolerance.relative(2e-4 if form == "chunked" else 1e-4, atol=2e-4 if form == "chunked" else 1e-5)
 
 
 def trained(rows, H, P, N, G, seed=3):
@@ -56,6 +58,7 @@ SCAN_CASES = [
     # rows, heads, head_dim, state_size, groups
     (5, 2, 16, 16, 1), (8, 4, 32, 32, 2), (1, 2, 16, 128, 1), (3, 2, 16, 64, 1),
     (64, 16, 64, 64, 2), (2048, 8, 64, 16, 1), (300, 6, 64, 128, 1), (100, 4, 128, 32, 4),
+    (128, 3, 64, 128, 1), (1000, 8, 64, 128, 2), (129, 2, 64, 128, 2),
 ]
 
 
