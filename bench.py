@@ -677,8 +677,13 @@ def run_mamba2(args, device) -> None:
     conv_bytes = B * 2 * R * C * 2
     proj_flops = 2 * B * R * E * (inner + C + H) + 2 * B * R * inner * E
     scan_gbs, conv_gbs = scan_bytes / scan_us / 1e3, conv_bytes / conv_us / 1e3
-    chunked = os.environ.get("IRON_SCAN_CHUNKED", "1") != "0" and R >= 32
-    scan_kernel = "ssd_scan_kernel (64-row chunks on the tensor cores)" if chunked else "selective_scan_kernel"
+    mode = os.environ.get("IRON_SCAN_CHUNKED", "2")[:1]
+    if mode == "2" and R >= 128:
+        scan_kernel = "ssd_scan_tc_kernel (128-row chunks, tcgen05 products with tensor-memory accumulators)"
+    elif mode in "12" and R >= 32:
+        scan_kernel = "ssd_scan_kernel (64-row chunks, warp MMAs)"
+    else:
+        scan_kernel = "selective_scan_kernel (step by step)"
     # CPU: the sequential numpy scan on a bounded sample of one sequence
     from iron_b200.tensor import torch_to_numpy as to_numpy
     from oracle import ops

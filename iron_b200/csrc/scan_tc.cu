@@ -20,12 +20,15 @@
 // of the scores, of y and of x; row n of the transposed state, whose 64 float32 values stay in
 // its registers from chunk to chunk.
 //
-// Roles (448 threads).  Warps 0-3, the state warps: the chunk's steps and their running sum
-// (published for the others), the weighted rows -> [P4], then S = decay S + dS and its split
-// -> [P3 of the next chunk].  Warps 4-11, the row warps, two per tensor-memory lane quarter:
-// the masked scores of columns 0-63 / 64-127 -> [P2], then 32 of the row's 64 outputs each.
-// Warp 12 issues the MMAs, warp 13 the TMA loads.  One warp alone on a scheduler runs these
-// dependent chains at a fifth of an instruction per clock; three a scheduler overlap them.
+// Roles (512 threads).  Warps 0-3, the state warps: a chunk's steps and their running sum,
+// published one chunk ahead, then S = decay S + dS and its split -> [P3 of the next chunk].
+// Warps 4-11, the row warps, two per tensor-memory lane quarter: the masked scores of columns
+// 0-63 / 64-127, written over the scores in tensor memory -> [P2], then 32 of the row's 64
+// outputs each; the four of them with the least below the diagonal also make the next chunk's
+// weighted rows -> [P4].  Warps 12, 13 and 15 issue the MMAs (a product family each: these
+// products are small, and what they wait for is their issue), warp 14 the TMA loads.  One warp
+// alone on a scheduler runs these dependent chains at a fifth of an instruction per clock; three
+// or four a scheduler overlap them.
 // B and C are single-buffered and reloaded as soon as their last product has read them (a
 // commit), early in the chunk; x is double-buffered.  Every wait is bounded (2 s ->
 // IRON_ERR_TIMEOUT in the status word); the state warps leave their loop together.
@@ -40,8 +43,8 @@ constexpr int kTcQ = 128;            // rows per chunk
 constexpr int kTcP = 64;             // head_dim
 constexpr int kTcNs = 128;           // states
 constexpr int kTcSub = 16384;        // one 128-row x 128-byte swizzled tile
-constexpr int kTcThreads = 480;      // 12 compute warps, two MMA warps, the TMA warp
-constexpr int kTcMmaWarp = 12, kTcMmaWarp2 = 13, kTcTmaWarp = 14;
+constexpr int kTcThreads = 512;      // 12 compute warps, three MMA warps, the TMA warp
+constexpr int kTcMmaWarp = 15, kTcMmaWarp2 = 13, kTcTmaWarp = 14, kTcMmaWarp3 = 12;   // P2 | P3, P4 | TMA | P1
 
 struct SsdTcSmem {
   static constexpr int kX = 0;                         // 2 x (Q x P)            x of chunk c, c + 1
@@ -101,6 +104,20 @@ __device__ __forceinline__ float ssd_lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// softplus(v) = max(v, 0) + log1p(exp(-|v|)) in a dozen instructions: e = exp(-|v|) <= 1 on the
+// hardware's exp2, and log1p(e) = 2 atanh(z), z = e / (2 + e) <= 1/3, as its odd series up to z^13
+// (the next term is below 2e-8 of the value).
+__device__ __forceinline__ float ssd_softplus(float v) {
+  const float e = ssd_ex2(-fabsf(v) * 1.4426950408889634f);
+  const float z = __fdividef(e, 2.0f + e), w = z * z;
+  float poly = fmaf(w, 1.0f / 13.0f, 1.0f / 11.0f);
+  poly = fmaf(w, poly, 1.0f / 9.0f);
+  poly = fmaf(w, poly, 1.0f / 7.0f);
+  poly = fmaf(w, poly, 1.0f / 5.0f);
+  poly = fmaf(w, poly, 1.0f / 3.0f);
+  poly = fmaf(w, poly, 1.0f);
+  return fmaxf(v, 0.f) + 2.0f * z * poly;
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -130,6 +147,31 @@ __device__ __forceinline__ void tcgen05_mma_bf16_ta(uint32_t d_tmem, uint32_t a_
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The MMAs as the issuing thread sees them: a descriptor is two 32-bit halves, and a K step moves
+// only the low one (the 14-bit address field, in 16-byte units, never carries), so a step costs
+// the issuer one add.  It issues ~one instruction per ten clocks next to three compute warps on
+// its scheduler, and these products are small: what they wait for is their issue.
+__device__ __forceinline__ void ssd_mma_ss(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void ssd_mma_ts(uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Row r's 16-byte chunk c of a 128-byte-swizzled tile.
 __device__ __forceinline__ uint4* tile_chunk(uint8_t* tile, int r, int c) {
   return reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4));
@@ -143,6 +185,12 @@ __device__ long long g_ssd_trace[4 * 64 * 16];
 #define SSD_MARK(who, i)
 #define SSD_MMARK(i)
 #endif
+
+// One copy of the bounded wait for the whole kernel: fifteen warps run five different roles out of
+// one instruction cache, and the code's size is what they wait for first.
+__device__ __noinline__ bool ssd_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_relaxed(bar, parity, abort_flag, 20);
+}
 
 enum {
   BAR_XFULL = 0,   // [2]  TMA: x of a chunk
@@ -177,7 +225,7 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
     for (int i = 0; i < L::kNumBars; ++i) {
       int count = 1;                                                        // a TMA transaction or a commit
       if (i == BAR_STATE || (i >= BAR_SCAN && i < BAR_SCAN + 3)) count = 128;   // the state warps
-      if (i == BAR_BFREE || i == BAR_CFREE) count = 2;                        // a commit from each MMA warp
+      if (i == BAR_BFREE || i == BAR_CFREE) count = 2;                        // a commit from each MMA warp that reads the tile
       if (i == BAR_XW) count = 128;                                           // the four row warps that weight x
       if (i == BAR_XFREE || i == BAR_XFREE + 1 || i == BAR_M || i == BAR_E) count = 256;   // the row warps
       mbar_init(bars + i, count);
@@ -213,83 +261,106 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
       for (int c = 0; c < chunks; ++c) {
         const int row = c * Q, s = c & 1;
         // x: the buffer's last reader was the output step of chunk c - 2
-        if (c >= 2 && !mbar_wait_relaxed(bars + BAR_XFREE + s, ((c - 2) >> 1) & 1, abort_flag)) break;
+        if (c >= 2 && !ssd_wait(bars + BAR_XFREE + s, ((c - 2) >> 1) & 1, abort_flag)) break;
         mbar_expect_tx(bars + BAR_XFULL + s, kTcSub);
         tma_load_3d(smem + L::kX + s * kTcSub, &map_xbc, col_x, row, b, bars + BAR_XFULL + s);
-        if (c >= 1 && !mbar_wait_relaxed(bars + BAR_CFREE, (c - 1) & 1, abort_flag)) break;
+        if (c >= 1 && !ssd_wait(bars + BAR_CFREE, (c - 1) & 1, abort_flag)) break;
         mbar_expect_tx(bars + BAR_CFULL, 2 * kTcSub);
         tma_load_3d(smem + L::kC, &map_xbc, col_c, row, b, bars + BAR_CFULL);
         tma_load_3d(smem + L::kC + kTcSub, &map_xbc, col_c + 64, row, b, bars + BAR_CFULL);
-        if (c >= 1 && !mbar_wait_relaxed(bars + BAR_BFREE, (c - 1) & 1, abort_flag)) break;
+        if (c >= 1 && !ssd_wait(bars + BAR_BFREE, (c - 1) & 1, abort_flag)) break;
         mbar_expect_tx(bars + BAR_BFULL, 2 * kTcSub);
         tma_load_3d(smem + L::kB, &map_xbc, col_b, row, b, bars + BAR_BFULL);
         tma_load_3d(smem + L::kB + kTcSub, &map_xbc, col_b + 64, row, b, bars + BAR_BFULL);
       }
     }
-  } else if (warp == kTcMmaWarp || warp == kTcMmaWarp2) {
+  } else if (warp == kTcMmaWarp || warp == kTcMmaWarp2 || warp == kTcMmaWarp3) {
     // ---------------- MMA issuers ----------------
-    // One thread takes ~70 clocks to issue a tcgen05.mma, more than these small products take to
-    // run, so there are two issuers -- the scores and P2 here, the two state products there -- and
-    // the products are as wide as they can be: head and remainder of the state (and of the
-    // weighted rows) are the two 64-column halves of ONE N-major operand, 128 columns a product.
+    // Three of them, one product family each -- P2 | P3 and P4 | P1 -- because these products are
+    // small and what they wait for is their issue: alone, a thread issues one 64-column product per
+    // 46 clocks (32 of arithmetic), next to busy compute warps on its scheduler one per ~140.  P2
+    // is the one the rows wait for, so its issuer sits on the scheduler of the lane quarter whose
+    // row warps have the most to mask and nothing to do once they have signalled (warp 15, with
+    // warps 3, 7 and 11).  And the products are as wide as they can be:
+    // head and remainder of the state (and of the weighted rows) are the two 64-column halves of
+    // ONE N-major operand, 128 columns a product.
     if (lane == 0) {
       constexpr uint32_t idesc_s = ssd_idesc(128, false, false);   // C (K-major) x B (K-major)
       constexpr uint32_t idesc_y = ssd_idesc(P, false, true);      // M (tensor memory) x X (N-major)
       constexpr uint32_t idesc_z = ssd_idesc(128, false, true);    // C (K-major) x state, head | remainder (N-major)
       constexpr uint32_t idesc_d = ssd_idesc(128, true, true);     // B (M-major) x X_w, head | remainder (N-major)
+      auto lo32 = [](uint64_t d) { return (uint32_t)d; };
+      auto hi32 = [](uint64_t d) { return (uint32_t)(d >> 32); };
       const uint64_t c_desc = make_desc(smem_u32(smem + L::kC), 16, 1024);
       const uint64_t b_desc = make_desc(smem_u32(smem + L::kB), 16, 1024);
       const uint64_t bt_desc = make_desc(smem_u32(smem + L::kB), kTcSub, 1024);   // 64-state chunks one tile apart
       const uint64_t st_desc = make_desc(smem_u32(smem + L::kShi), kTcSub, 1024);   // head tile, remainder tile
       const uint64_t xw_desc = make_desc(smem_u32(smem + L::kXwHi), kTcSub, 1024);
+      const uint64_t x_desc0 = make_desc(smem_u32(smem + L::kX), kTcSub, 1024);
       // K-major operand, step k of 8: tile k / 4, 32 bytes per step; M-/N-major: 16 rows of 128 bytes per step
-      auto kmaj = [](int k) { return (uint64_t)(((k >> 2) * kTcSub + (k & 3) * 32) >> 4); };
-      auto nmaj = [](int k) { return (uint64_t)((k * 16 * 128) >> 4); };
+      auto kmaj = [](int k) { return (uint32_t)(((k >> 2) * kTcSub + (k & 3) * 32) >> 4); };
+      auto nmaj = [](int k) { return (uint32_t)((k * 16 * 128) >> 4); };
       if (warp == kTcMmaWarp) {
+#pragma unroll 1
         for (int c = 0; c < chunks; ++c) {
           const uint32_t ph = c & 1;
-          const uint64_t x_desc = make_desc(smem_u32(smem + L::kX + (c & 1) * kTcSub), kTcSub, 1024);
-          // P1: the scores.  Their columns held the last chunk's masked scores, which P2 of that chunk --
-          // issued by this thread, so ahead of this product in the pipe -- has read.
-          if (!mbar_wait(bars + BAR_BFULL, ph, abort_flag) || !mbar_wait(bars + BAR_CFULL, ph, abort_flag)) break;
-          tcgen05_fence_after();
-#pragma unroll
-          for (int k = 0; k < N / 16; ++k)
-            tcgen05_mma_bf16(tmem_base + kColS, c_desc + kmaj(k), b_desc + kmaj(k), idesc_s, k != 0);
-          tcgen05_commit(bars + BAR_S);
-          tcgen05_commit(bars + BAR_CFREE);
-          tcgen05_commit(bars + BAR_BFREE);
+          const uint32_t x_lo = lo32(x_desc0) + (uint32_t)(((c & 1) * kTcSub) >> 4);
           // P2: the masked scores (heads, remainders: two accumulators, step by step in turn) times x;
           // Y is free once the last chunk's output rows have been read
-          if (!mbar_wait(bars + BAR_M, ph, abort_flag)) break;
-          if (c >= 1 && !mbar_wait(bars + BAR_E, (c - 1) & 1, abort_flag)) break;
+          if (!ssd_wait(bars + BAR_M, ph, abort_flag)) break;
+          if (c >= 1 && !ssd_wait(bars + BAR_E, (c - 1) & 1, abort_flag)) break;
+          if (!ssd_wait(bars + BAR_XFULL + (c & 1), (c >> 1) & 1, abort_flag)) break;
           tcgen05_fence_after();
+          SSD_MMARK(2)
 #pragma unroll
           for (int k = 0; k < Q / 16; ++k) {
             const uint32_t m_col = tmem_base + kColS + 32 * (k >> 1) + 8 * (k & 1);
-            tcgen05_mma_bf16_ta(tmem_base + kColY, m_col, x_desc + nmaj(k), idesc_y, k != 0);
-            tcgen05_mma_bf16_ta(tmem_base + kColY2, m_col + 16, x_desc + nmaj(k), idesc_y, k != 0);
+            ssd_mma_ts(tmem_base + kColY, m_col, x_lo + nmaj(k), hi32(x_desc0), idesc_y, k != 0);
+            ssd_mma_ts(tmem_base + kColY2, m_col + 16, x_lo + nmaj(k), hi32(x_desc0), idesc_y, k != 0);
           }
+          SSD_MMARK(3)
           tcgen05_commit(bars + BAR_Y);
         }
-      } else {
+      } else if (warp == kTcMmaWarp2) {
+#pragma unroll 1
         for (int c = 0; c < chunks; ++c) {
           const uint32_t ph = c & 1;
           // P3, the read-out of the carried state (written at the end of the last chunk), and P4, the
           // state's update, transposed, step by step in turn.  Z is free once the last chunk's output
           // rows have been read, dS once the state warps have written the state.
-          if (!mbar_wait(bars + BAR_BFULL, ph, abort_flag) || !mbar_wait(bars + BAR_CFULL, ph, abort_flag)) break;
-          if (!mbar_wait(bars + BAR_STATE, ph, abort_flag)) break;
-          if (c >= 1 && !mbar_wait(bars + BAR_E, (c - 1) & 1, abort_flag)) break;
-          if (!mbar_wait(bars + BAR_XW, ph, abort_flag)) break;
+          if (!ssd_wait(bars + BAR_BFULL, ph, abort_flag) || !ssd_wait(bars + BAR_CFULL, ph, abort_flag)) break;
+          if (!ssd_wait(bars + BAR_STATE, ph, abort_flag)) break;
+          if (c >= 1 && !ssd_wait(bars + BAR_E, (c - 1) & 1, abort_flag)) break;
+          if (!ssd_wait(bars + BAR_XW, ph, abort_flag)) break;
           tcgen05_fence_after();
+          SSD_MMARK(0)
 #pragma unroll
           for (int k = 0; k < N / 16; ++k) {
-            tcgen05_mma_bf16(tmem_base + kColZ, c_desc + kmaj(k), st_desc + nmaj(k), idesc_z, k != 0);
-            tcgen05_mma_bf16(tmem_base + kColD, bt_desc + nmaj(k), xw_desc + nmaj(k), idesc_d, k != 0);
+            ssd_mma_ss(tmem_base + kColZ, lo32(c_desc) + kmaj(k), hi32(c_desc), lo32(st_desc) + nmaj(k), hi32(st_desc),
+                       idesc_z, k != 0);
+            ssd_mma_ss(tmem_base + kColD, lo32(bt_desc) + nmaj(k), hi32(bt_desc), lo32(xw_desc) + nmaj(k), hi32(xw_desc),
+                       idesc_d, k != 0);
           }
+          SSD_MMARK(1)
           tcgen05_commit(bars + BAR_Z);
           tcgen05_commit(bars + BAR_D);
+          tcgen05_commit(bars + BAR_CFREE);
+          tcgen05_commit(bars + BAR_BFREE);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          const uint32_t ph = c & 1;
+          // P1: the scores.  Their columns held the last chunk's masked scores, which P2 of that chunk
+          // must have read.
+          if (!ssd_wait(bars + BAR_BFULL, ph, abort_flag) || !ssd_wait(bars + BAR_CFULL, ph, abort_flag)) break;
+          if (c >= 1 && !ssd_wait(bars + BAR_Y, (c - 1) & 1, abort_flag)) break;
+          tcgen05_fence_after();
+#pragma unroll
+          for (int k = 0; k < N / 16; ++k)
+            ssd_mma_ss(tmem_base + kColS, lo32(c_desc) + kmaj(k), hi32(c_desc), lo32(b_desc) + kmaj(k), hi32(b_desc),
+                       idesc_s, k != 0);
+          tcgen05_commit(bars + BAR_S);
           tcgen05_commit(bars + BAR_CFREE);
           tcgen05_commit(bars + BAR_BFREE);
         }
@@ -333,15 +404,13 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
       proxy_fence();
       mbar_arrive(bars + BAR_STATE);
     };
-    write_state();
-
     // The running sum of chunk c is made while chunk c - 1's update product is in flight (it needs
     // only dt), and published in buffer c % 3: the row warps may still be reading chunk c - 2's.
     bool ok = true;
     float dt_next = r < p.rows ? __bfloat162float(dtp[(size_t)r * p.H]) : 0.f;
     auto publish_scan = [&](int c) -> float {      // returns the chunk's decay exp(cum_Q); leaves `ok` the same in every thread
       const int t = c * Q + r;
-      const float step = t < valid ? softplus_f32(dt_next + dt_bias) : 0.f;   // rows past the bound: a = 0, step = 0
+      const float step = t < valid ? ssd_softplus(dt_next + dt_bias) : 0.f;   // rows past the bound: a = 0, step = 0
       if (c + 1 < chunks && t + Q < p.rows) dt_next = __bfloat162float(dtp[(size_t)(t + Q) * p.H]);
       float cum = step * A;
 #pragma unroll
@@ -371,9 +440,12 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
       mbar_arrive(bars + BAR_SCAN + c % 3);
       return ssd_ex2(total);
     };
-    float decay = publish_scan(0);
-    bool all_ok = ok;                                  // the same in every state thread: they leave together
-    for (int c = 0; c < chunks && all_ok; ++c) {
+    // Iteration -1 publishes the first chunk's sums and writes the incoming state; iteration c
+    // publishes chunk c + 1's (one call site each: the kernel's code must stay small).
+    float decay = 0.f;
+    bool all_ok = true;                                // the same in every state thread: they leave together
+#pragma unroll 1
+    for (int c = -1; c < chunks && all_ok; ++c) {
       const uint32_t ph = c & 1;
       float decay_next = 0.f;
       SSD_MARK(0, 0)
@@ -382,25 +454,27 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
         all_ok = ok;
         if (!all_ok) break;
       }
-      // ---- S = exp(cum_Q) S + dS, split for the next chunk's read-out (P3 has read the old one) ----
-      SSD_MARK(0, 1)
-      ok = ok && mbar_wait(bars + BAR_D, ph, abort_flag);
-      tcgen05_fence_after();
-      SSD_MARK(0, 4)
+      if (c >= 0) {
+        // ---- S = exp(cum_Q) S + dS, split for the next chunk's read-out (P3 has read the old one) ----
+        SSD_MARK(0, 1)
+        ok = ok && ssd_wait(bars + BAR_D, ph, abort_flag);
+        tcgen05_fence_after();
+        SSD_MARK(0, 4)
 #pragma unroll
-      for (int part = 0; part < 4; ++part) {
-        uint32_t v[16], v2[16];
-        tmem_ld16(lane_base + kColD + 16 * part, v);
-        tmem_ld16(lane_base + kColD + 64 + 16 * part, v2);     // the remainders' product
-        tmem_ld_wait();
+        for (int part = 0; part < 4; ++part) {
+          uint32_t v[16], v2[16];
+          tmem_ld16(lane_base + kColD + 16 * part, v);
+          tmem_ld16(lane_base + kColD + 64 + 16 * part, v2);     // the remainders' product
+          tmem_ld_wait();
 #pragma unroll
-        for (int q = 0; q < 16; ++q)
-          st[16 * part + q] = fmaf(decay, st[16 * part + q], __uint_as_float(v[q]) + __uint_as_float(v2[q]));
+          for (int q = 0; q < 16; ++q)
+            st[16 * part + q] = fmaf(decay, st[16 * part + q], __uint_as_float(v[q]) + __uint_as_float(v2[q]));
+        }
+        tcgen05_fence_before();
+        SSD_MARK(0, 5)
+        ok = ok && ssd_wait(bars + BAR_Z, ph, abort_flag);
+        SSD_MARK(0, 6)
       }
-      tcgen05_fence_before();
-      SSD_MARK(0, 5)
-      ok = ok && mbar_wait(bars + BAR_Z, ph, abort_flag);
-      SSD_MARK(0, 6)
       write_state();
       SSD_MARK(0, 7)
       decay = decay_next;
@@ -463,9 +537,9 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
     auto weigh_rows = [&](int c) {
       const int s = c & 1;
       uint8_t* x_tile = smem + L::kX + s * kTcSub;
-      ok = ok && mbar_wait(bars + BAR_SCAN + c % 3, (c / 3) & 1, abort_flag);
-      ok = ok && mbar_wait(bars + BAR_XFULL + s, (c >> 1) & 1, abort_flag);
-      if (c >= 1) ok = ok && mbar_wait(bars + BAR_D, (c - 1) & 1, abort_flag);
+      ok = ok && ssd_wait(bars + BAR_SCAN + c % 3, (c / 3) & 1, abort_flag);
+      ok = ok && ssd_wait(bars + BAR_XFULL + s, (c >> 1) & 1, abort_flag);
+      if (c >= 1) ok = ok && ssd_wait(bars + BAR_D, (c - 1) & 1, abort_flag);
       const float* g_all = s_g + (c % 3) * Q;
       const float total = s_cum[(c % 3) * Q + Q - 1];
       {
@@ -493,43 +567,48 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
       proxy_fence();
       mbar_arrive(bars + BAR_XW);
     };
-    if (weights_x) weigh_rows(0);
-    for (int c = 0; c < chunks && ok; ++c) {
+#pragma unroll 1
+    for (int c = -1; c < chunks && ok; ++c) {
+      // iteration -1 only weighs the first chunk's rows (one call site: the code must stay small)
       const uint32_t ph = c & 1;
       const int s = c & 1, t = c * Q + r;
       uint8_t* x_tile = smem + L::kX + s * kTcSub;
-      SSD_MARK(1 + side, 0)
-      ok = ok && mbar_wait(bars + BAR_SCAN + c % 3, (c / 3) & 1, abort_flag);
-      const float* g_all = s_g + (c % 3) * Q;
-      const float cum_r = s_cum[(c % 3) * Q + r];
-      // ---- the masked scores of this side's columns -> P2 ----
-      SSD_MARK(1 + side, 1)
-      ok = ok && mbar_wait(bars + BAR_S, ph, abort_flag);
-      tcgen05_fence_after();
-      SSD_MARK(1 + side, 2)
-      mask_batch(2 * side, cum_r, g_all);
-      mask_batch(2 * side + 1, cum_r, g_all);
-      tmem_st_wait();
-      tcgen05_fence_before();
-      mbar_arrive(bars + BAR_M);
-      SSD_MARK(1 + side, 3)
+      float cum_r = 0.f;
+      if (c >= 0) {
+        SSD_MARK(1 + side, 0)
+        ok = ok && ssd_wait(bars + BAR_SCAN + c % 3, (c / 3) & 1, abort_flag);
+        const float* g_all = s_g + (c % 3) * Q;
+        cum_r = s_cum[(c % 3) * Q + r];
+        // ---- the masked scores of this side's columns -> P2 ----
+        SSD_MARK(1 + side, 1)
+        ok = ok && ssd_wait(bars + BAR_S, ph, abort_flag);
+        tcgen05_fence_after();
+        SSD_MARK(1 + side, 2)
+#pragma unroll 1
+        for (int i = 0; i < 2; ++i) mask_batch(2 * side + i, cum_r, g_all);
+        tmem_st_wait();
+        tcgen05_fence_before();
+        mbar_arrive(bars + BAR_M);
+        SSD_MARK(1 + side, 3)
+      }
       if (weights_x && c + 1 < chunks) weigh_rows(c + 1);   // after the signal: P2 does not wait for this
+      if (c < 0) continue;
 
       // ---- y_r = Y_r + exp(cum_r) Z_r + D x_r, this side's 32 columns ----
-      ok = ok && mbar_wait(bars + BAR_XFULL + s, (c >> 1) & 1, abort_flag);
-      uint4 xr[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) xr[q] = *tile_chunk(x_tile, r, 4 * side + q);
+      ok = ok && ssd_wait(bars + BAR_XFULL + s, (c >> 1) & 1, abort_flag);
       const float e_r = ssd_ex2(cum_r);
       SSD_MARK(1 + side, 4)
-      ok = ok && mbar_wait(bars + BAR_Z, ph, abort_flag);
+      ok = ok && ssd_wait(bars + BAR_Z, ph, abort_flag);
       SSD_MARK(1 + side, 5)
-      ok = ok && mbar_wait(bars + BAR_Y, ph, abort_flag);
+      ok = ok && ssd_wait(bars + BAR_Y, ph, abort_flag);
       tcgen05_fence_after();
       SSD_MARK(1 + side, 6)
-#pragma unroll
+#pragma unroll 1
       for (int hh = 0; hh < 2; ++hh) {          // 16 of this side's 32 columns at a time
         const int col = 32 * side + 16 * hh;
+        uint4 xr[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) xr[q] = *tile_chunk(x_tile, r, 4 * side + 2 * hh + q);
         uint32_t y1[16], y2[16], z1[16], z2[16];
         tmem_ld16(lane_base + kColY + col, y1);
         tmem_ld16(lane_base + kColY2 + col, y2);
@@ -540,7 +619,7 @@ ssd_scan_tc_kernel(const __grid_constant__ CUtensorMap map_xbc, const ScanParams
         uint4 out[2];
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const uint4 xq = xr[2 * hh + q];
+          const uint4 xq = xr[q];
           const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w};
           uint32_t o[4];
 #pragma unroll
