@@ -705,10 +705,15 @@ def run_mamba2(args, device) -> None:
         "roofline": {"bound": "hbm", "kernel": scan_kernel, "achieved": round(scan_gbs, 1),
                      "peak": pk["hbm_gbs"], "peak_kind": pk["kind"], "unit": "GB/s",
                      "frac": round(scan_gbs / pk["hbm_gbs"], 4), "bytes_per_launch": scan_bytes,
-                     "us_per_launch": round(scan_us, 1), "traffic": None},
+                     "us_per_launch": round(scan_us, 1),
+                     # dram bytes of one launch at this shape under ncu (the summary named beside it)
+                     "traffic": 392400000 if (mode == "2" and (B, R) == (8, 4096)) else None,
+                     "traffic_from": "profiles/ssd_scan_tc_mamba2_ncu.md"},
         "conv_roofline": {"bound": "hbm", "kernel": "causal_conv_kernel (+ bias + SiLU)", "achieved": round(conv_gbs, 1),
                           "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(conv_gbs / pk["hbm_gbs"], 4),
-                          "bytes_per_launch": conv_bytes, "us_per_launch": round(conv_us, 1)},
+                          "bytes_per_launch": conv_bytes, "us_per_launch": round(conv_us, 1),
+                          "traffic": 399600000 if (B, R) == (8, 4096) else None,
+                          "traffic_from": "profiles/causal_conv_mamba2_ncu.md"},
         "layer": {"us": round(layer_us, 1), "launches": MambaMixer.launches_per_call,
                   "projection_tflop": round(proj_flops / 1e12, 3),
                   "projection_floor_us": round(proj_flops / pk["bf16_tflops_sustained"] / 1e6, 1)},
