@@ -22,6 +22,18 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w 
 __device__ __forceinline__ float round_bf16(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
+// The same rounding (to nearest even) on the integer pipe, and the packing of two values that
+// are bf16 already: the conversion instructions share the special-function unit with exp2 and
+// the reciprocal, which an HBM-bound kernel with several roundings an element runs out of first.
+__device__ __forceinline__ float round_bf16_alu(float x) {
+  uint32_t u = __float_as_uint(x);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return x;   // NaN
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return __uint_as_float(u & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2_exact(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
 __device__ __forceinline__ uint16_t f2bf(float x) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(x));
 }

@@ -216,6 +216,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   Item cur;
   issue<WIDE>(cur, qa, qb, ch_lo, lane, ch_hi, live && ch_lo < ch_hi);
 
+  // The norm's weights do not depend on the previous kernel either: this thread's first chunk
+  // of them is on its way before the wait (a second L2 round trip off the critical path).
+  uint4 norm_w0 = make_uint4(0, 0, 0, 0);
+  if (p.norm_mode == 2 && tid < nch) norm_w0 = ld_cached(reinterpret_cast<const uint4*>(p.norm_w) + tid);
   // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
   const unsigned int tp_seq = p.tp.mode == TP_PUSH ? p.tp.state[0] : 0u;
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv);
         if (p.norm_mode == 2) {
           float w[8];
-          unpack8(ld_cached(wg + i), w);
+          unpack8(i == tid ? norm_w0 : ld_cached(wg + i), w);
 #pragma unroll
           for (int j = 0; j < 8; ++j) f[j] = f[j] * w[j];
         }
@@ -458,6 +462,10 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
   };
   for (int i = 0; i < kRingSlots; ++i) issue_next();
 
+  // The norm's weights do not depend on the previous kernel either: this thread's first chunk
+  // of them is on its way before the wait.
+  uint4 norm_w0 = make_uint4(0, 0, 0, 0);
+  if (p.norm_mode == 2 && tid < nch) norm_w0 = ld_cached(reinterpret_cast<const uint4*>(p.norm_w) + tid);
   // The activation vector is the previous kernel's output: wait for it now.
   pdl_wait();
   const unsigned int tp_seq = p.tp.mode == TP_PUSH ? p.tp.state[0] : 0u;
@@ -487,7 +495,7 @@ __global__ void __launch_bounds__(kRingThreads, kRingCtasPerSm) gemv_ring_kernel
         for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv);
         if (p.norm_mode == 2) {
           float w[8];
-          unpack8(ld_cached(wg + i), w);
+          unpack8(i == tid ? norm_w0 : ld_cached(wg + i), w);
 #pragma unroll
           for (int j = 0; j < 8; ++j) f[j] = f[j] * w[j];
         }

@@ -82,10 +82,11 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __nv_bfloat16*
         unpack8(gv[u], g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          f[j] = round_bf16(__fmul_rn(round_bf16(silu_f32(g[j])), f[j]));
+          f[j] = round_bf16_alu(__fmul_rn(round_bf16_alu(silu_f32(g[j])), f[j]));
           ss = fmaf(f[j], f[j], ss);
         }
-        xv[u] = pack8(f);    // exact: the values are bf16 already
+        xv[u] = make_uint4(pack_bf16x2_exact(f[0], f[1]), pack_bf16x2_exact(f[2], f[3]),
+                           pack_bf16x2_exact(f[4], f[5]), pack_bf16x2_exact(f[6], f[7]));
       }
     }
     const float tot = block_sum(ss, red);
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __nv_bfloat16*
         float f[8];
         unpack8(xv[u], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = round_bf16(f[j] * inv);
+        for (int j = 0; j < 8; ++j) f[j] = round_bf16_alu(f[j] * inv);
         if (w) {
           float g[8];
           unpack8(ld_cached(reinterpret_cast<const uint4*>(w) + i), g);
