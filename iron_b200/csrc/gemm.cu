@@ -738,6 +738,10 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 
+// The weight-streaming form for a decode batch (gemm_skinny.cu).
+int launch_gemm_skinny(const void* X, const void* W, const void* W2, void* C, const void* residual, int rows, int N,
+                       int K, int ldx, int ldw, int ldc, int* d_status, cudaStream_t stream);
+
 // A 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows `pitch` elements apart.
 static bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
                      uint32_t box_inner, uint32_t box_outer) {
@@ -863,6 +867,13 @@ extern "C" int iron_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
   if (valid_k == 0) return IRON_ERR_SHAPE;
 
+  // a decode batch against weights as stored: the weight-streaming kernel with the operands swapped
+  if (valid_rows >= 1 && valid_rows <= 64 && !d_valid_rows && b_col_maj && !c_col_maj && !out_f32 &&
+      epilogue == EPI_NONE && (ldb & 7) == 0) {
+    const int rc = launch_gemm_skinny(A, B, nullptr, C, residual, valid_rows, N, valid_k, lda, ldb, ldc, d_status,
+                                      (cudaStream_t)stream);
+    if (rc != IRON_ERR_UNSUPPORTED) return rc;
+  }
   // BN: the widest tile that still yields at least one wave of CTAs
   const int m_tiles = (M + BM - 1) / BM;
   int bn = 256;
@@ -947,6 +958,11 @@ extern "C" int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* 
   if ((lda & 7) || (ldb & 7)) return IRON_ERR_ALIGN;
   if (lda < K || ldb < K || ldc < N) return IRON_ERR_SHAPE;
   if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
+  if (valid_rows >= 1 && valid_rows <= 64 && !d_valid_rows) {
+    const int rc = launch_gemm_skinny(A, Wg, Wu, C, nullptr, valid_rows, N, K, lda, ldb, ldc, d_status,
+                                      (cudaStream_t)stream);
+    if (rc != IRON_ERR_UNSUPPORTED) return rc;
+  }
   // One 128 x BN accumulator = BN/2 output columns: the gate half and the up half.  The
   // widest tile that still gives at least half a wave of CTAs.
   const int max_rows = d_valid_rows ? M : valid_rows;

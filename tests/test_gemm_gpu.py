@@ -49,6 +49,35 @@ def test_gemm_matches_reference(K, M, N, Kd, b_col_maj):
     check(got, A, B, want, b_col_maj, what=f"{M}x{N}x{Kd} b_col_maj={b_col_maj}")
 
 
+SKINNY = [
+    # rows, N, K: a decode batch against weights as stored -- the weight-streaming kernel with the
+    # operands swapped: split along K over clusters of 8, 4, 2 CTAs, one CTA a tile, ragged edges
+    (64, 2048, 2048), (64, 2048, 8192), (33, 3072, 2048), (5, 4096, 1024), (1, 2048, 2048),
+    (64, 8192, 2048), (17, 200, 136), (64, 18944, 512), (8, 1000, 72),
+]
+
+
+@pytest.mark.parametrize("rows,N,Kd", SKINNY)
+@pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
+def test_a_decode_batch_streams_the_weights(K, rows, N, Kd, residual):
+    import torch
+
+    rng = np.random.default_rng(rows + N + Kd)
+    A = normal(rng, (rows, Kd), 1 / np.sqrt(Kd))
+    W = normal(rng, (N, Kd), 1.0)
+    res = normal(rng, (rows, N), 1.0) if residual else None
+    want = ops.gemm(A, W, b_col_maj=True)
+    if residual:
+        want = ops.add(want, res)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = to_numpy(K.gemm(to_torch(A), to_torch(W), b_col_maj=True, residual=to_torch(res) if residual else None,
+                          status=status))
+    bound = ops.gemm_bound(A, W, b_col_maj=True) + (np.abs(res.astype(np.float32)) * 2 ** -8 if residual else 0)
+    v = compare(got, want, Tolerance.bounded(lambda *a: bound), bound=bound)
+    assert v, f"{rows}x{N}x{Kd}: {v.detail}"
+    assert int(status.item()) == 0
+
+
 def test_gemm_2048_cubed_within_the_bf16_output_bound(K):
     rng = np.random.default_rng(1001)
     A = normal(rng, (2048, 2048), 1 / np.sqrt(2048))
