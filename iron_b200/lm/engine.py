@@ -842,10 +842,13 @@ class LlamaEngine:
             raise IndexError(f"a position is outside the {self.c.max_seq_len}-row caches")
         if tokens.min() < 0 or tokens.max() >= self.c.vocab_size:
             raise IndexError(f"a token is outside the {self.c.vocab_size}-row vocabulary")
-        host = torch.from_numpy(np.stack([tokens, positions]).astype(np.int32)).pin_memory()
+        if getattr(self, "_h_set_batch", None) is None:      # one pinned staging buffer for the engine's life
+            self._h_set_batch = torch.empty((2, self.batch), dtype=torch.int32).pin_memory()
+        host = self._h_set_batch
+        host.copy_(torch.from_numpy(np.stack([tokens, positions]).astype(np.int32)))
         self.b_tokens.copy_(host[0], non_blocking=True)
         self.b_pos.copy_(host[1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the pinned staging buffer is released here
+        torch.cuda.current_stream().synchronize()   # the staging buffer may be rewritten after this
         self._next_position = int(positions.max())
 
     def decode_batch(self, tokens, positions) -> list[int]:
