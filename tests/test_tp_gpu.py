@@ -1,4 +1,4 @@
-"""Tensor-parallel decode and prefill on two GPUs against the single-GPU engine, with the
+"""Tensor-parallel decode and prefill on two (and four) GPUs against the single-GPU engine, with the
 decode step's exchange through peer memory -- folded into the GEMVs on either side of it, or
 as one all-reduce + residual kernel per rank -- and through NCCL.
 
@@ -89,26 +89,28 @@ def _rank(rank: int, size: int, port: int, out, peer: str, shard_head: str, fuse
         os._exit(0)   # no collective teardown: the peer may already be gone
 
 
-@pytest.mark.parametrize("peer,shard_head,fused", [("1", "1", "1"), ("0", "1", "1"), ("1", "0", "1"), ("1", "1", "0")],
+@pytest.mark.parametrize("size,peer,shard_head,fused",
+                         [(2, "1", "1", "1"), (2, "0", "1", "1"), (2, "1", "0", "1"), (2, "1", "1", "0"), (4, "1", "1", "1")],
                          ids=["exchange folded into the GEMVs", "nccl exchange", "whole head on every rank",
-                              "exchange kernel of its own"])
-def test_two_way_tensor_parallel_matches_one_gpu(peer, shard_head, fused):
+                              "exchange kernel of its own", "four ranks"])
+def test_tensor_parallel_matches_one_gpu(size, peer, shard_head, fused):
     import queue
 
     import torch
     import torch.multiprocessing as mp
 
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < size:
+        pytest.skip(f"needs {size} GPUs")
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, out, peer, shard_head, fused), daemon=True) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, size, port, out, peer, shard_head, fused), daemon=True)
+             for r in range(size)]
     for p in procs:
         p.start()
     results = {}
     try:
-        for _ in range(2):
+        for _ in range(size):
             try:
                 kind, rank, payload = out.get(timeout=240)
             except queue.Empty:
