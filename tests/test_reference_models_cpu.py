@@ -11,6 +11,7 @@ Skipped where the reference checkout is not mounted.
 """
 
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
@@ -20,7 +21,8 @@ import pytest
 from oracle import model as M
 from tests.test_oracle_golden import assert_close
 
-REFERENCE = Path("/root/reference")
+# a checkout of amd/IRON: IRON_REFERENCE, or a `reference` directory beside this repository
+REFERENCE = Path(os.environ.get("IRON_REFERENCE") or Path(__file__).resolve().parents[2] / "reference")
 pytestmark = pytest.mark.skipif(not (REFERENCE / "iron" / "applications").is_dir(),
                                 reason="the reference checkout is not mounted")
 GOLDENS = Path(__file__).parent / "golden"
