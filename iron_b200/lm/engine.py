@@ -356,7 +356,7 @@ class LlamaEngine:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         # one slot holds a decode step's rows: the vector of one sequence, or a few sequences'
         # (one CTA moves a slot: larger batches take NCCL)
-        self.peer_slot_elems = self.c.hidden_size * min(self.batch, 4)
+        self.peer_slot_elems = self.c.hidden_size * min(self.batch, 8)
         nbytes = K.tp_buffer_bytes(self.tp_size, self.peer_slot_elems)
         group = self.tp_group if self.tp_group is not None else dist.group.WORLD
         self._peer_mem = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
