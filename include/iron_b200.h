@@ -289,6 +289,42 @@ int iron_gemm_swiglu_bf16(const void* A, const void* Wg, const void* Wu, void* C
                           const int* d_valid_rows, int* d_status, iron_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * The projections of a BATCHED decode step (1 to 64 sequences, one row each), with the layer's
+ * RMSNorm, RoPE and cache write folded into them -- iron/lm/blocks.py's `Attention.body` and
+ * `GatedMLP.body` chains RMSNorm, ProjectionGEMM, RoPE, cache write ... ProjectionGEMM + residual,
+ * RMSNorm, ProjectionGEMM x 2, SiLU, ElementwiseMul, ProjectionGEMM + residual as five launches
+ * a layer instead of eight.
+ *
+ * iron_gemm_rows_bf16: C (rows, N; pitch ldc) = X (rows <= 64, K; pitch ldx) . W^T, W (N, K; pitch
+ * ldw) as a checkpoint stores it; the weights cross HBM once.
+ *   W2 != NULL        the gated pair: C = bf16(silu(bf16(X . W^T))) * bf16(X . W2^T), no residual.
+ *   residual          (rows, N; pitch ldc) added after the product's rounding.
+ *   d_rowsq_out       with a residual: this call also leaves, per row, the sum of squares of the
+ *                     bf16 values it wrote, as iron_gemm_rows_parts(rows, N, K, 0) partial sums in
+ *                     fixed slots of a float[64][320] buffer (row-major; no atomics).
+ *   norm_weight, d_rowsq_in, rowsq_parts, eps
+ *                     RMSNorm of X before the product (iron/operators/rms_norm.py): the sums the
+ *                     call that PRODUCED X left; X is normalised on its way into shared memory with
+ *                     the norm's own two roundings, bf16(bf16(x / rms) * weight).  K % 64 == 0.
+ * IRON_ERR_UNSUPPORTED for a product this kernel does not take (more than 296 tiles of 128 rows).
+ *
+ * iron_gemm_rows_qkv_rope_bf16: the q/k/v projection of such a step (Wqkv ((H + 2G) D, K), rows
+ * q | k | v), the optional folded RMSNorm as above, then per row RoPE of q and k with the angle
+ * row (interleaved cos, sin; two-halves pairing) of d_positions[row], q to q_out (rows, H, D),
+ * k and v to row d_positions[row] of that sequence's caches ((rows, S, G, D), sequences
+ * kv_batch_stride elements apart).  D 64 or 128, H D and G D multiples of 128. */
+int iron_gemm_rows_parts(int rows, int N, int K, int gated);
+int iron_gemm_rows_bf16(const void* X, const void* W, const void* W2, void* C, const void* residual,
+                        int rows, int N, int K, int ldx, int ldw, int ldc, const void* norm_weight,
+                        const float* d_rowsq_in, int rowsq_parts, float eps, float* d_rowsq_out,
+                        int* d_status, iron_stream_t stream);
+int iron_gemm_rows_qkv_rope_bf16(const void* X, const void* Wqkv, int rows, int K, int ldx, int ldw,
+                                 const void* norm_weight, const float* d_rowsq_in, int rowsq_parts,
+                                 float eps, const void* angles, const int* d_positions, void* q_out,
+                                 void* k_cache, void* v_cache, long long kv_batch_stride, int H, int G,
+                                 int D, int S, int* d_status, iron_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * One decode step's attention, o_proj and residual add of a layer in one launch -- the
  * reference's steps MHA (iron/operators/mha.py:191 as iron/lm/blocks.py:487-502 calls it: one
  * query row per head over the cache rows 0 .. position, grouped heads, an optional window),

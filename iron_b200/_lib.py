@@ -78,6 +78,12 @@ SIGNATURES: dict[str, tuple] = {
     "iron_tp_allreduce_bf16": (_I, [_P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P]),
     "iron_tp_push_next": (_I, [_P, _I, _I, _I, _P, _P]),
     "iron_tp_pull_next": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "iron_gemm_rows_parts": (_I, [_I, _I, _I, _I]),
+    "iron_gemm_rows_bf16": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P]),
+    "iron_gemm_rows_qkv_rope_bf16": (
+        _I,
+        [_P, _P, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P, _P],
+    ),
     "iron_rope_kv_scatter_bf16": (_I, [_P, _L, _P, _P, _P, _P, _L, _I, _P, _I, _I, _I, _I, _P]),
     "iron_argmax_rows_bf16": (_I, [_P, _L, _I, _I, _P, _P, _P, _I, _P]),
     "iron_decode_step_workspace_bytes": (_Z, [_I, _I, _I, _I]),

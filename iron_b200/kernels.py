@@ -507,6 +507,67 @@ def rope_kv_scatter(qkv, angles, q_out, k_cache, v_cache, positions, *, H, G, D)
          _ptr(v_cache), k_cache.stride(0), rows, _ptr(positions), H, G, D, S, _stream())
 
 
+ROWSQ_PITCH = 320   # floats between the rows of a sums-of-squares buffer (iron_gemm_rows_bf16)
+
+
+def rowsq_buffer(device=None):
+    """The (64, 320) float32 buffer a projection leaves its rows' sums of squares in."""
+    return torch.zeros((64, ROWSQ_PITCH), dtype=torch.float32, device=device or "cuda")
+
+
+def gemm_rows_parts(rows: int, N: int, K: int, gated: bool = False) -> int:
+    """How many partial sums per row ``gemm_rows(..., rowsq_out=...)`` of this shape leaves
+    (0: the weight-streaming kernel does not take the shape)."""
+    return int(_lib.load().iron_gemm_rows_parts(rows, N, K, int(gated)))
+
+
+def _norm_args(norm_weight, rowsq_in, rowsq_parts):
+    if (norm_weight is None) != (rowsq_in is None):
+        raise ValueError("a folded RMSNorm takes both its weight and the producing call's sums of squares")
+    if rowsq_in is not None and (rowsq_in.dtype != torch.float32 or rowsq_in.shape != (64, ROWSQ_PITCH)):
+        raise TypeError("rowsq buffers are (64, 320) float32")
+    return _ptr(norm_weight), _ptr(rowsq_in), int(rowsq_parts)
+
+
+def gemm_rows(X, W, out=None, *, W2=None, residual=None, norm_weight=None, rowsq_in=None, rowsq_parts=0,
+              eps=1e-5, rowsq_out=None, status=None):
+    """``X @ W.T`` for a decode batch (up to 64 rows) against weights as stored, optionally with
+    the RMSNorm before it folded in (``norm_weight``, ``rowsq_in``, ``rowsq_parts``: the sums of
+    squares the call that produced ``X`` left through its ``rowsq_out``), as the gated pair
+    (``W2``), or with a residual."""
+    _bf16(X, W)
+    rows, Kd = X.shape
+    N = W.shape[0]
+    if W.shape[1] != Kd or (W2 is not None and W2.shape != W.shape):
+        raise ValueError(f"gemm_rows: X {tuple(X.shape)} and W {tuple(W.shape)} do not chain")
+    if out is None:
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=X.device)
+    if residual is not None and residual.stride(0) != out.stride(0):
+        raise ValueError("the residual has the output's pitch")
+    if rowsq_out is not None and (rowsq_out.dtype != torch.float32 or rowsq_out.shape != (64, ROWSQ_PITCH)):
+        raise TypeError("rowsq buffers are (64, 320) float32")
+    nw, sq, parts = _norm_args(norm_weight, rowsq_in, rowsq_parts)
+    call("iron_gemm_rows_bf16", _ptr(X), _ptr(W), _ptr(W2), _ptr(out), _ptr(residual), rows, N, Kd, X.stride(0),
+         W.stride(0), out.stride(0), nw, sq, parts, float(eps), _ptr(rowsq_out), _ptr(status), _stream())
+    return out
+
+
+def gemm_rows_qkv_rope(X, Wqkv, angles, q_out, k_cache, v_cache, positions, *, H, G, D, norm_weight=None,
+                       rowsq_in=None, rowsq_parts=0, eps=1e-5, status=None):
+    """The q/k/v projection of a batched decode step with RoPE and the cache write (and
+    optionally the RMSNorm before it) folded in; arguments as ``rope_kv_scatter``."""
+    _bf16(X, Wqkv, angles, q_out, k_cache, v_cache)
+    rows, Kd = X.shape
+    if Wqkv.shape != ((H + 2 * G) * D, Kd):
+        raise ValueError(f"gemm_rows_qkv_rope: Wqkv {tuple(Wqkv.shape)} is not ({(H + 2 * G) * D}, {Kd})")
+    if positions.dtype != torch.int32:
+        raise TypeError("positions are int32")
+    nw, sq, parts = _norm_args(norm_weight, rowsq_in, rowsq_parts)
+    call("iron_gemm_rows_qkv_rope_bf16", _ptr(X), _ptr(Wqkv), rows, Kd, X.stride(0), Wqkv.stride(0), nw, sq, parts,
+         float(eps), _ptr(angles), _ptr(positions), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0),
+         H, G, D, k_cache.shape[1], _ptr(status), _stream())
+
+
 def sample_k_max() -> int:
     """The largest top-k the device draws."""
     return _lib.load().iron_sample_k_max()

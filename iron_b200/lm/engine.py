@@ -220,6 +220,18 @@ class LlamaEngine:
             self.b_att = view("b.att", (batch, H, D))
             self.b_gate, self.b_up = view("b.gate", (batch, F)), view("b.up", (batch, F))
             self.b_part = view("b.part", (batch, E))
+        # A batched step's projections take their neighbours into the launch (RMSNorm before, RoPE and
+        # the cache write after) where the weight-streaming kernel covers the shapes: five launches a
+        # layer instead of eight.  IRON_BATCH_FOLD=0 keeps the separate kernels.
+        self.rows_folded = (1 < batch <= 64 and tp_size == 1 and E % 64 == 0 and D in (64, 128)
+                            and (H * D) % 128 == 0 and (G * D) % 128 == 0
+                            and os.environ.get("IRON_BATCH_FOLD", "1") != "0"
+                            and os.environ.get("IRON_GEMM_SKINNY", "1") != "0"
+                            and min(K.gemm_rows_parts(batch, E, H * D), K.gemm_rows_parts(batch, E, F),
+                                    K.gemm_rows_parts(batch, QKV, E), K.gemm_rows_parts(batch, F, E, True)) > 0)
+        if self.rows_folded:
+            self.b_sq_x, self.b_sq_y = K.rowsq_buffer(self.device), K.rowsq_buffer(self.device)
+            self.b_parts_o, self.b_parts_d = K.gemm_rows_parts(batch, E, H * D), K.gemm_rows_parts(batch, E, F)
 
         self._load(weights, release)
         self._peer_exchange_setup()
@@ -403,6 +415,8 @@ class LlamaEngine:
         Tensor parallelism adds two exchange kernels a layer unless the exchanges ride on the GEMVs,
         and a key and a pick in place of the draw when the head is split."""
         if self.batch > 1:
+            if self.rows_folded:
+                return 2 + 5 * self.c.num_hidden_layers + 3
             return 1 + 8 * self.c.num_hidden_layers + 3
         if self.fused_step:
             return 1
@@ -432,7 +446,23 @@ class LlamaEngine:
         x, h, y = self.b_x, self.b_h, self.b_y
         tp, part = self.tp_size > 1, self.b_part
         K.copy_rows(self.embed, x, ids=self.b_tokens, nrows=n, row_bytes=E * 2, src_rows=V)
-        for l in self.layers:
+        if self.rows_folded:
+            sq_x, sq_y = self.b_sq_x, self.b_sq_y
+            for i, l in enumerate(self.layers):
+                rope = dict(H=H, G=G, D=D, eps=c.eps, status=self.status)
+                if i == 0:    # the embedding rows come with no sums of squares: the first norm is a launch
+                    K.rms_norm(x, l["ln1"], h, eps=c.eps)
+                    K.gemm_rows_qkv_rope(h, l["wqkv"], self.angles, self.b_q, l["k"], l["v"], self.b_pos, **rope)
+                else:
+                    K.gemm_rows_qkv_rope(x, l["wqkv"], self.angles, self.b_q, l["k"], l["v"], self.b_pos,
+                                         norm_weight=l["ln1"], rowsq_in=sq_x, rowsq_parts=self.b_parts_d, **rope)
+                K.mha_decode(self.b_q, l["k"], l["v"], self.b_att, d_kv_valid=self.b_pos, per_batch=True,
+                             kv_valid_add=1, window=c.window, scale=c.attention_scale)
+                K.gemm_rows(self.b_att.view(n, H * D), l["wo"], y, residual=x, rowsq_out=sq_y, status=self.status)
+                K.gemm_rows(y, l["wg"], self.b_gate, W2=l["wu"], norm_weight=l["ln2"], rowsq_in=sq_y,
+                            rowsq_parts=self.b_parts_o, eps=c.eps, status=self.status)
+                K.gemm_rows(self.b_gate, l["wd"], x, residual=y, rowsq_out=sq_x, status=self.status)
+        for l in (() if self.rows_folded else self.layers):
             K.rms_norm(x, l["ln1"], h, eps=c.eps)
             K.gemm(h, l["wqkv"], self.b_qkv, b_col_maj=True, status=self.status)
             K.rope_kv_scatter(self.b_qkv, self.angles, self.b_q, l["k"], l["v"], self.b_pos, H=H, G=G, D=D)
