@@ -107,6 +107,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   // this CTA's share of the k blocks
   const int per = (p.num_kb + S - 1) / S;
   const int kb_lo = min(p.num_kb, rank * per), kb_hi = min(p.num_kb, kb_lo + per);
+  const int nkb = kb_hi - kb_lo;
+  auto kblock = [&](int i) { return kb_lo + i; };    // the i-th k block this CTA takes
   const int rows_w = p.dual ? 64 : 128;          // output features a tile covers
   const int n0 = tile * rows_w;
 
@@ -150,15 +152,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const bool own_x = p.sq_in != nullptr;       // X on its own barrier
       const uint32_t w_bytes = own_x ? kSkWBytes : kSkStage;
       int pre = 0;
-      for (int kb = kb_lo; kb < kb_hi && pre < stages; ++kb, ++pre) {
+      for (; pre < nkb && pre < stages; ++pre) {
         mbar_expect_tx(full + pre, w_bytes);
-        load_w(pre, kb);
+        load_w(pre, kblock(pre));
       }
       pdl_wait();
       int s = 0;
       uint32_t phase = 0;
       int issued = 0;
-      for (int kb = kb_lo; kb < kb_hi; ++kb, ++issued) {
+      for (; issued < nkb; ++issued) {
+        const int kb = kblock(issued);
         if (issued >= pre) {
           if (!mbar_wait(empty + s, phase ^ 1, abort_flag)) break;
           mbar_expect_tx(full + s, w_bytes);
@@ -177,14 +180,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+      for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(full + s, phase, abort_flag) || (p.sq_in && !mbar_wait(ready + s, phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t w_addr = smem_u32(smem + s * kSkStage);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           tcgen05_mma_bf16(tmem_base, make_desc(w_addr + k * 32, 16, 1024), make_desc(w_addr + kSkWBytes + k * 32, 16, 1024),
-                           idesc, kb != kb_lo || k != 0);
+                           idesc, i != 0 || k != 0);
         tcgen05_commit(empty + s);
         if (++s == stages) { s = 0; phase ^= 1; }
       }
@@ -231,7 +234,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const float inv = 1.0f / sqrtf((s0 + s1) / (float)p.K + p.eps);
       int s = 0;
       uint32_t phase = 0;
-      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+      for (int i = 0; i < nkb; ++i) {
+        const int kb = kblock(i);
         uint4 gw[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) gw[j] = *reinterpret_cast<const uint4*>(norm_sm + (kb - kb_lo) * 128 + kh * 64 + j * 16);
