@@ -304,14 +304,19 @@ extern "C" int iron_mha_decode_bf16(const void* Q, const void* K, const void* V,
   if ((kv_batch_stride & 7) || (kv_seq_stride & 7) || (kv_head_stride & 7)) return IRON_ERR_ALIGN;
   if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return IRON_ERR_ALIGN;
   const int group = H / G;
-  // A batch of a few sequences or more (one CTA per sequence and KV head, at least 32)
-  // goes to the tensor-core kernel: the group's query heads are the rows of one MMA tile.
-  // IRON_MHA_DECODE_TC=0 keeps the SIMT kernel.
+  // A batch of two sequences or more (at least 16 (sequence, KV head) pairs; IRON_MHA_DECODE_TC_MIN)
+  // goes to the tensor-core kernel: the group's query heads are the rows of one MMA tile, and
+  // the keys are split over a cluster while the pairs alone do not fill the machine.  One
+  // sequence (8 pairs) measured faster on the SIMT kernel.  IRON_MHA_DECODE_TC=0 keeps the SIMT kernel.
   static const bool use_tc = [] {
     const char* e = getenv("IRON_MHA_DECODE_TC");
     return !(e && e[0] == '0');
   }();
-  if (use_tc && group > 1 && (long long)batch * G >= 32) {
+  static const int tc_min = [] {
+    const char* e = getenv("IRON_MHA_DECODE_TC_MIN");
+    return e ? atoi(e) : 16;
+  }();
+  if (use_tc && group > 1 && (long long)batch * G >= tc_min) {
     const int rc = mha_decode_tc(Q, K, V, O, batch, H, G, D, kv_max, kv_batch_stride, kv_seq_stride,
                                  kv_head_stride, kv_valid, d_kv_valid, d_kv_valid_stride, kv_valid_add, window,
                                  scale, (cudaStream_t)stream);

@@ -11,6 +11,13 @@
 //   exp2 domain, O += P V (D/8 column tiles); the four warps' (max, sum, O) are merged
 //   through shared memory at the end.
 // Rows of the tile beyond the group are zero queries whose results are dropped.
+//
+// A batch that does not fill the machine that way (8 sequences x 8 KV heads = 64 CTAs on 148 SMs) is
+// split along the keys as well: a thread-block cluster of 2, 4 or 8 CTAs shares one (sequence, KV head),
+// each takes a contiguous run of key tiles, leaves its (O, max, sum) in its shared memory, and after one
+// cluster barrier every CTA merges its slice of the outputs over distributed shared memory.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace iron {
@@ -29,6 +36,7 @@ struct DecodeTcParams {
   int kv_max;
   int window;               // < 0: none
   float scale_log2;
+  int nsplit;               // CTAs (a cluster along z) that share the keys of one (sequence, KV head)
 };
 
 constexpr int kDtThreads = 128;
@@ -90,7 +98,12 @@ __global__ void __launch_bounds__(kDtThreads) mha_decode_tc_kernel(const DecodeT
   if (p.d_kv_valid) kv_valid = p.d_kv_valid[b * p.d_kv_valid_stride] + p.kv_valid_add;
   kv_valid = max(0, min(kv_valid, p.kv_max));
   const int lo = (p.window >= 0) ? max(0, kv_valid - 1 - p.window) : 0;
-  const int j_lo = lo / kDtKeys, j_hi = (kv_valid + kDtKeys - 1) / kDtKeys;
+  int j_lo = lo / kDtKeys, j_hi = (kv_valid + kDtKeys - 1) / kDtKeys;
+  if (p.nsplit > 1) {   // this CTA's run of key tiles
+    const int per = (j_hi - j_lo + p.nsplit - 1) / p.nsplit;
+    j_lo = min(j_hi, j_lo + (int)blockIdx.z * per);
+    j_hi = min(j_hi, j_lo + per);
+  }
 
   const __nv_bfloat16* Qb = p.Q + ((size_t)b * p.H + (size_t)kvh * p.group) * D;
   const __nv_bfloat16* Kb = p.K + (size_t)b * p.kv_batch_stride + (size_t)kvh * p.kv_head_stride;
@@ -227,28 +240,85 @@ __global__ void __launch_bounds__(kDtThreads) mha_decode_tc_kernel(const DecodeT
     if (t == 0) { dst[D] = m_run[r]; dst[D + 1] = l; }
   }
   __syncthreads();
-  for (int idx = tid; idx < p.group * D; idx += kDtThreads) {
-    const int row = idx / D, d = idx - row * D;
+  if (p.nsplit == 1) {
+    for (int idx = tid; idx < p.group * D; idx += kDtThreads) {
+      const int row = idx / D, d = idx - row * D;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, part[((size_t)w * 16 + row) * kRow + D]);
+      float acc = 0.f, L = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float* src = part + ((size_t)w * 16 + row) * kRow;
+        const float c = (src[D] == -INFINITY) ? 0.f : dt_ex2(src[D] - M);
+        acc = fmaf(src[d], c, acc);
+        L = fmaf(src[D + 1], c, L);
+      }
+      p.O[((size_t)b * p.H + (size_t)kvh * p.group + row) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    return;
+  }
+  // ---- keys split over the cluster: this CTA's (O, max, sum) per query head, behind the warps' partials ----
+  float* mine = part + 4 * 16 * kRow;
+  for (int idx = tid; idx < p.group * kRow; idx += kDtThreads) {
+    const int row = idx / kRow, d = idx - row * kRow;
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, part[((size_t)w * 16 + row) * kRow + D]);
-    float acc = 0.f, L = 0.f;
+    float v = 0.f;
+    if (d == D) v = M;
+    else {
+      const int col = d < D ? d : D + 1;      // an output, or the sum
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float* src = part + ((size_t)w * 16 + row) * kRow;
-      const float c = (src[D] == -INFINITY) ? 0.f : dt_ex2(src[D] - M);
-      acc = fmaf(src[d], c, acc);
-      L = fmaf(src[D + 1], c, L);
+      for (int w = 0; w < 4; ++w) {
+        const float* src = part + ((size_t)w * 16 + row) * kRow;
+        const float c = (src[D] == -INFINITY) ? 0.f : dt_ex2(src[D] - M);
+        v = fmaf(src[col], c, v);
+      }
     }
-    p.O[((size_t)b * p.H + (size_t)kvh * p.group + row) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    mine[idx] = v;
   }
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  {
+    const int total = p.group * D, per = (total + p.nsplit - 1) / p.nsplit;
+    const int begin = (int)blockIdx.z * per, end = min(total, begin + per);
+    const float* theirs[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) theirs[r] = r < p.nsplit ? cluster.map_shared_rank(mine, r) : mine;
+    for (int idx = begin + tid; idx < end; idx += kDtThreads) {
+      const int row = idx / D, d = idx - row * D;
+      float mr[8], ar[8], lr[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.nsplit) {
+          const float* src = theirs[r] + (size_t)row * kRow;
+          mr[r] = src[D]; ar[r] = src[d]; lr[r] = src[D + 1];
+        }
+      float M = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.nsplit) M = fmaxf(M, mr[r]);
+      float acc = 0.f, L = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.nsplit) {
+          const float c = (mr[r] == -INFINITY) ? 0.f : dt_ex2(mr[r] - M);
+          acc = fmaf(ar[r], c, acc);
+          L = fmaf(lr[r], c, L);
+        }
+      p.O[((size_t)b * p.H + (size_t)kvh * p.group + row) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+  }
+  cluster.sync();   // nobody leaves while a peer still reads its partial
 }
 
 template <int D>
 static int launch_decode_tc(const DecodeTcParams& p, int batch, cudaStream_t stream) {
   // Q tile + double-buffered K and V tiles; the merge reuses the same bytes
   constexpr int kTiles = 16 * D * 2 + 4 * kDtKeys * D * 2;
-  constexpr int kMerge = 4 * 16 * (D + 2) * 4;
+  constexpr int kMerge = 5 * 16 * (D + 2) * 4;   // the four warps' partials and the CTA's own
   constexpr int kSmem = kTiles > kMerge ? kTiles : kMerge;
   static DeviceOnce configured;   // the attribute is per device
   if (!configured.done()) {
@@ -258,12 +328,19 @@ static int launch_decode_tc(const DecodeTcParams& p, int batch, cudaStream_t str
     configured.mark();
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.G, batch, 1);
+  cfg.gridDim = dim3(p.G, batch, p.nsplit);
   cfg.blockDim = dim3(kDtThreads);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   fill_pdl_attr(cfg, attr);
+  if (p.nsplit > 1) {
+    cudaLaunchAttribute& c = attr[cfg.numAttrs++];
+    c.id = cudaLaunchAttributeClusterDimension;
+    c.val.clusterDim.x = 1;
+    c.val.clusterDim.y = 1;
+    c.val.clusterDim.z = p.nsplit;
+  }
   return cudaLaunchKernelEx(&cfg, mha_decode_tc_kernel<D>, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
@@ -284,6 +361,10 @@ int mha_decode_tc(const void* Q, const void* K, const void* V, void* O, int batc
   p.kv_valid = kv_valid; p.d_kv_valid = d_kv_valid; p.d_kv_valid_stride = d_kv_valid_stride;
   p.kv_valid_add = kv_valid_add; p.kv_max = kv_max; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  // split the keys while the machine is not yet full and a CTA keeps at least four tiles of the longest run
+  p.nsplit = 1;
+  const int tiles = (kv_max + kDtKeys - 1) / kDtKeys;
+  while (p.nsplit < 8 && (long long)batch * G * p.nsplit * 2 <= 2 * kSMs && tiles / (p.nsplit * 2) >= 4) p.nsplit *= 2;
   return D == 64 ? launch_decode_tc<64>(p, batch, stream) : launch_decode_tc<128>(p, batch, stream);
 }
 

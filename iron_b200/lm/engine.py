@@ -220,16 +220,20 @@ class LlamaEngine:
             self.b_att = view("b.att", (batch, H, D))
             self.b_gate, self.b_up = view("b.gate", (batch, F)), view("b.up", (batch, F))
             self.b_part = view("b.part", (batch, E))
-        # A batched step's projections take their neighbours into the launch (RMSNorm before, RoPE and
-        # the cache write after) where the weight-streaming kernel covers the shapes: five launches a
-        # layer instead of eight.  IRON_BATCH_FOLD=0 keeps the separate kernels.
-        self.rows_folded = (1 < batch <= 64 and tp_size == 1 and E % 64 == 0 and D in (64, 128)
-                            and (H * D) % 128 == 0 and (G * D) % 128 == 0
-                            and os.environ.get("IRON_BATCH_FOLD", "1") != "0"
-                            and os.environ.get("IRON_GEMM_SKINNY", "1") != "0"
-                            and min(K.gemm_rows_parts(batch, E, H * D), K.gemm_rows_parts(batch, E, F),
-                                    K.gemm_rows_parts(batch, QKV, E), K.gemm_rows_parts(batch, F, E, True)) > 0)
-        if self.rows_folded:
+        # A batched step's projections can take their neighbours into the launch where the
+        # weight-streaming kernel covers the shapes: RoPE and the cache write after q/k/v
+        # (IRON_BATCH_FOLD=rope), the RMSNorms before q/k/v and gate/up (=norm), both (=1).  Off unless
+        # asked for: measured, the step is as long either way (the norm's latency moves into the
+        # projection), and 128-wide heads at small batches lose a few percent.
+        fold = os.environ.get("IRON_BATCH_FOLD", "0")
+        foldable = (1 < batch <= 64 and tp_size == 1 and E % 64 == 0 and E <= 8192 and D in (64, 128)
+                    and (H * D) % 128 == 0 and (G * D) % 128 == 0
+                    and os.environ.get("IRON_GEMM_SKINNY", "1") != "0"
+                    and min(K.gemm_rows_parts(batch, E, H * D), K.gemm_rows_parts(batch, E, F),
+                            K.gemm_rows_parts(batch, QKV, E), K.gemm_rows_parts(batch, F, E, True)) > 0)
+        self.fold_norm = foldable and fold in ("1", "norm")
+        self.fold_rope = foldable and fold in ("1", "rope")
+        if self.fold_norm:
             self.b_sq_x, self.b_sq_y = K.rowsq_buffer(self.device), K.rowsq_buffer(self.device)
             self.b_parts_o, self.b_parts_d = K.gemm_rows_parts(batch, E, H * D), K.gemm_rows_parts(batch, E, F)
 
@@ -415,9 +419,8 @@ class LlamaEngine:
         Tensor parallelism adds two exchange kernels a layer unless the exchanges ride on the GEMVs,
         and a key and a pick in place of the draw when the head is split."""
         if self.batch > 1:
-            if self.rows_folded:
-                return 2 + 5 * self.c.num_hidden_layers + 3
-            return 1 + 8 * self.c.num_hidden_layers + 3
+            per_layer = 8 - (1 if self.fold_rope else 0) - (2 if self.fold_norm else 0)
+            return 1 + per_layer * self.c.num_hidden_layers + (1 if self.fold_norm else 0) + 3
         if self.fused_step:
             return 1
         per_layer = 4 if self.attn_oproj else 5
@@ -446,38 +449,43 @@ class LlamaEngine:
         x, h, y = self.b_x, self.b_h, self.b_y
         tp, part = self.tp_size > 1, self.b_part
         K.copy_rows(self.embed, x, ids=self.b_tokens, nrows=n, row_bytes=E * 2, src_rows=V)
-        if self.rows_folded:
-            sq_x, sq_y = self.b_sq_x, self.b_sq_y
-            for i, l in enumerate(self.layers):
-                rope = dict(H=H, G=G, D=D, eps=c.eps, status=self.status)
-                if i == 0:    # the embedding rows come with no sums of squares: the first norm is a launch
-                    K.rms_norm(x, l["ln1"], h, eps=c.eps)
-                    K.gemm_rows_qkv_rope(h, l["wqkv"], self.angles, self.b_q, l["k"], l["v"], self.b_pos, **rope)
+        fold_norm, fold_rope = self.fold_norm, self.fold_rope
+        for i, l in enumerate(self.layers):
+            # the layer's input is normalised inside the q/k/v projection when the projection before it left
+            # the rows' sums of squares (the embedding rows come with none: the first norm is a launch)
+            normed = dict(norm_weight=l["ln1"], rowsq_in=self.b_sq_x, rowsq_parts=self.b_parts_d,
+                          eps=c.eps) if fold_norm and i > 0 else None
+            if normed is None:
+                K.rms_norm(x, l["ln1"], h, eps=c.eps)
+            if fold_rope:
+                K.gemm_rows_qkv_rope(h if normed is None else x, l["wqkv"], self.angles, self.b_q, l["k"], l["v"],
+                                     self.b_pos, H=H, G=G, D=D, status=self.status, **(normed or {}))
+            else:
+                if normed is None:
+                    K.gemm(h, l["wqkv"], self.b_qkv, b_col_maj=True, status=self.status)
                 else:
-                    K.gemm_rows_qkv_rope(x, l["wqkv"], self.angles, self.b_q, l["k"], l["v"], self.b_pos,
-                                         norm_weight=l["ln1"], rowsq_in=sq_x, rowsq_parts=self.b_parts_d, **rope)
-                K.mha_decode(self.b_q, l["k"], l["v"], self.b_att, d_kv_valid=self.b_pos, per_batch=True,
-                             kv_valid_add=1, window=c.window, scale=c.attention_scale)
-                K.gemm_rows(self.b_att.view(n, H * D), l["wo"], y, residual=x, rowsq_out=sq_y, status=self.status)
-                K.gemm_rows(y, l["wg"], self.b_gate, W2=l["wu"], norm_weight=l["ln2"], rowsq_in=sq_y,
-                            rowsq_parts=self.b_parts_o, eps=c.eps, status=self.status)
-                K.gemm_rows(self.b_gate, l["wd"], x, residual=y, rowsq_out=sq_x, status=self.status)
-        for l in (() if self.rows_folded else self.layers):
-            K.rms_norm(x, l["ln1"], h, eps=c.eps)
-            K.gemm(h, l["wqkv"], self.b_qkv, b_col_maj=True, status=self.status)
-            K.rope_kv_scatter(self.b_qkv, self.angles, self.b_q, l["k"], l["v"], self.b_pos, H=H, G=G, D=D)
+                    K.gemm_rows(x, l["wqkv"], self.b_qkv, status=self.status, **normed)
+                K.rope_kv_scatter(self.b_qkv, self.angles, self.b_q, l["k"], l["v"], self.b_pos, H=H, G=G, D=D)
             K.mha_decode(self.b_q, l["k"], l["v"], self.b_att, d_kv_valid=self.b_pos, per_batch=True,
                          kv_valid_add=1, window=c.window, scale=c.attention_scale)
             if tp:   # row-parallel: this rank's partial sums meet the others', then the residual
                 K.gemm(self.b_att.view(n, H * D), l["wo"], part, b_col_maj=True, status=self.status)
                 self._reduce_add(part, x, y)
+            elif fold_norm:
+                K.gemm_rows(self.b_att.view(n, H * D), l["wo"], y, residual=x, rowsq_out=self.b_sq_y, status=self.status)
             else:
                 K.gemm(self.b_att.view(n, H * D), l["wo"], y, b_col_maj=True, residual=x, status=self.status)
-            K.rms_norm(y, l["ln2"], h, eps=c.eps)
-            K.gemm_swiglu(h, l["wg"], l["wu"], self.b_gate, status=self.status)
+            if fold_norm:
+                K.gemm_rows(y, l["wg"], self.b_gate, W2=l["wu"], norm_weight=l["ln2"], rowsq_in=self.b_sq_y,
+                            rowsq_parts=self.b_parts_o, eps=c.eps, status=self.status)
+            else:
+                K.rms_norm(y, l["ln2"], h, eps=c.eps)
+                K.gemm_swiglu(h, l["wg"], l["wu"], self.b_gate, status=self.status)
             if tp:
                 K.gemm(self.b_gate, l["wd"], part, b_col_maj=True, status=self.status)
                 self._reduce_add(part, y, x)
+            elif fold_norm:
+                K.gemm_rows(self.b_gate, l["wd"], x, residual=y, rowsq_out=self.b_sq_x, status=self.status)
             else:
                 K.gemm(self.b_gate, l["wd"], x, b_col_maj=True, residual=y, status=self.status)
         K.rms_norm(x, self.norm, h, eps=c.eps)

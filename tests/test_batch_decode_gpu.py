@@ -10,16 +10,20 @@ from tests.test_engine_gpu import close_to_oracle, toy_config
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def engines():
+# the layer's RMSNorms, RoPE and cache write as launches of their own, or inside the projections
+@pytest.fixture(scope="module", params=["0", "1", "norm", "rope"],
+                ids=["separate kernels", "norm and rope folded in", "norm folded in", "rope folded in"])
+def engines(request):
     from iron_b200.lm.engine import LlamaEngine
 
     weights = M.filled_random(M.llama_shapes(M.SCALED), 0)
     mp = pytest.MonkeyPatch()
     mp.setenv("IRON_DECODE_STEP", "0")
+    mp.setenv("IRON_BATCH_FOLD", request.param)
     batched = LlamaEngine(toy_config(), weights, batch=3, kv_len_hint=64)
     single = LlamaEngine(toy_config(), weights, batch=1, kv_len_hint=64)
     mp.undo()
+    assert batched.fold_norm == (request.param in ("1", "norm")) and batched.fold_rope == (request.param in ("1", "rope"))
     return batched, single, weights
 
 

@@ -290,6 +290,9 @@ def test_mha_decode_batched_with_per_sequence_lengths_on_device(K):
     (64, 24, 8, 128, 200, None),    # 128-wide heads, groups of 3
     (300, 5, 1, 64, 130, 40),       # groups of 5, one KV head, a sliding window
     (38, 32, 8, 64, 129, None),
+    (8, 24, 8, 128, 2304, None),    # 64 pairs do not fill the machine: the keys are split over clusters of four
+    (8, 32, 8, 64, 1100, 300),      # clusters of four, a sliding window that leaves some splits empty
+    (16, 8, 2, 128, 4608, None),    # clusters of eight
 ])
 def test_mha_decode_large_batches_on_the_tensor_cores(K, B, H, G, D, S, window):
     """A batch that fills the machine takes the MMA kernel: every sequence has its own
