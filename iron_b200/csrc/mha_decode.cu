@@ -269,7 +269,11 @@ static int launch_decode(const DecodeParams& p, int B, cudaStream_t stream) {
                                                                               : IRON_ERR_LAUNCH;
 }
 
-// the tensor-core kernel for batches that fill the machine (mha_decode_tc.cu)
+// the resident form for a few sequences and the tensor-core kernel for batches (mha_decode_tc.cu)
+int mha_decode_resident(const void* Q, const void* K, const void* V, void* O, int batch, int H, int G, int D,
+                        int kv_max, long long kv_batch_stride, long long kv_seq_stride, long long kv_head_stride,
+                        int kv_valid, const int* d_kv_valid, int d_kv_valid_stride, int kv_valid_add, int window,
+                        float scale, int stable_prefix, cudaStream_t stream);
 int mha_decode_tc(const void* Q, const void* K, const void* V, void* O, int batch, int H, int G, int D, int kv_max,
                   long long kv_batch_stride, long long kv_seq_stride, long long kv_head_stride, int kv_valid,
                   const int* d_kv_valid, int d_kv_valid_stride, int kv_valid_add, int window, float scale,
@@ -312,10 +316,22 @@ extern "C" int iron_mha_decode_bf16(const void* Q, const void* K, const void* V,
     const char* e = getenv("IRON_MHA_DECODE_TC");
     return !(e && e[0] == '0');
   }();
+  // fewer pairs than that: every CTA holds its share of the keys in shared memory (IRON_MHA_DECODE_RESIDENT=0
+  // keeps the SIMT kernel)
+  static const bool use_resident = [] {
+    const char* e = getenv("IRON_MHA_DECODE_RESIDENT");
+    return !(e && e[0] == '0');
+  }();
   static const int tc_min = [] {
     const char* e = getenv("IRON_MHA_DECODE_TC_MIN");
     return e ? atoi(e) : 16;
   }();
+  if (use_tc && use_resident && group > 1 && (long long)batch * G < tc_min) {
+    const int rc = mha_decode_resident(Q, K, V, O, batch, H, G, D, kv_max, kv_batch_stride, kv_seq_stride,
+                                       kv_head_stride, kv_valid, d_kv_valid, d_kv_valid_stride, kv_valid_add, window,
+                                       scale, stable_prefix, (cudaStream_t)stream);
+    if (rc != IRON_ERR_UNSUPPORTED) return rc;
+  }
   if (use_tc && group > 1 && (long long)batch * G >= tc_min) {
     const int rc = mha_decode_tc(Q, K, V, O, batch, H, G, D, kv_max, kv_batch_stride, kv_seq_stride,
                                  kv_head_stride, kv_valid, d_kv_valid, d_kv_valid_stride, kv_valid_add, window,

@@ -262,9 +262,11 @@ def test_mha_decode_matches_reference(K, H, G, D, S, n, window, nsplit):
                    kv_interleaved=True, q_tokens=1, kv_tokens=n)
     ns = nsplit
     tq, tk, tv = to_torch(q), to_torch(k), to_torch(v)
-    for _ in range(2):
-        got = to_numpy(K.mha_decode(tq, tk, tv, kv_valid=n, window=window, nsplit=ns))
-        assert_verdict(got, want, MHA_TOL, what="mha decode")
+    # twice each (the resident form's arrival counters must be back at zero), and with the promise that only
+    # the newest row is fresh (its keys are then asked for ahead of the dependency wait, that row after it)
+    for stable in (False, True, False, True):
+        got = to_numpy(K.mha_decode(tq, tk, tv, kv_valid=n, window=window, nsplit=ns, stable_prefix=stable))
+        assert_verdict(got, want, MHA_TOL, what=f"mha decode, stable_prefix={stable}")
         assert_bf16_bound(got, want, "mha decode")
 
 
