@@ -497,6 +497,16 @@ int iron_tp_allreduce_bf16(const void* part, const void* residual, void* y, int 
  * sequence of exchanges, and an engine uses either these or iron_tp_allreduce_bf16 on one set
  * of buffers, not both.  The tensors named here must outlive the launch that consumes the call.
  * No counterpart in the reference (it is single-device). */
+/* The all-reduce as one launch of many CTAs without a fence or a flag: the values travel as the
+ * tagged 32-bit words described above (the same slots and d_state as iron_tp_push_next /
+ * iron_tp_pull_next), every CTA stores its run of the elements to every rank and re-reads the own
+ * buffer until every rank's words of that run carry this exchange's tag (at most 2 s, then
+ * IRON_ERR_TIMEOUT in *d_status and zero for what is missing).  For the few rows of a decode
+ * batch (n = rows x hidden <= slot_elems); arguments as iron_tp_allreduce_bf16 with d_state in
+ * place of d_seq. */
+int iron_tp_allreduce_tagged_bf16(const void* part, const void* residual, void* y, int n, int slot_elems,
+                                  const void* const* h_peer_buffers, int rank, int world,
+                                  unsigned int* d_state, int* d_status, iron_stream_t stream);
 int iron_tp_push_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,
                       unsigned int* d_state, int* d_status);
 int iron_tp_pull_next(const void* const* h_peer_buffers, int rank, int world, int slot_elems,

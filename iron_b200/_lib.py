@@ -76,6 +76,7 @@ SIGNATURES: dict[str, tuple] = {
     "iron_argmax_bf16_noalloc": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "iron_tp_buffer_bytes": (_Z, [_I, _I]),
     "iron_tp_allreduce_bf16": (_I, [_P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P]),
+    "iron_tp_allreduce_tagged_bf16": (_I, [_P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P]),
     "iron_tp_push_next": (_I, [_P, _I, _I, _I, _P, _P]),
     "iron_tp_pull_next": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "iron_gemm_rows_parts": (_I, [_I, _I, _I, _I]),

@@ -105,6 +105,83 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const TpParams p) {
   if (tid == 0) *p.d_seq = seq + 1u;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same all-reduce without a fence or a flag, for a few rows (a decode batch): every value
+// travels as one 32-bit word -- the bf16 partial and a 16-bit tag of the exchange's number -- and a
+// word arrives whole, so its tag says that its value is there.  Many CTAs, each taking a run of
+// the elements: store the words into slot [parity][rank] of every rank, then read every rank's
+// words of that run from the own buffer, again while a tag is not yet this exchange's (at most 2 s).
+// The last CTA to finish advances the rank's exchange number.  Slots and tags are those of the
+// exchange folded into the GEMVs (gemv.cu); an engine uses one of the three forms on a buffer.
+struct TpTaggedParams {
+  const __nv_bfloat16* part;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* y;
+  int n, slot_elems, rank, world;
+  unsigned char* peer[kTpMaxWorld];
+  unsigned int* state;            // [0] exchange number, [1] CTAs that have finished this launch
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) tp_allreduce_tagged_kernel(const TpTaggedParams p) {
+  pdl_wait();
+  pdl_launch();
+  const unsigned int seq = p.state[0], par = seq & 1u, tag = ((seq >> 1) + 1u) & 0xffffu;
+  const int n4 = p.n >> 2;
+  const size_t base = ((size_t)par * p.world) * p.slot_elems;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    // 1. four partials as tagged words into slot [par][rank] of every rank
+    const uint2 raw = *reinterpret_cast<const uint2*>(p.part + 4 * (size_t)i);
+    const uint32_t t = tag << 16;
+    const uint4 words = make_uint4((raw.x & 0xffffu) | t, (raw.x >> 16) | t, (raw.y & 0xffffu) | t, (raw.y >> 16) | t);
+    for (int r = 0; r < p.world; ++r) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(p.peer[r] + kTpFlagBytes) + base + (size_t)p.rank * p.slot_elems + 4 * (size_t)i;
+      asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(words.x), "r"(words.y),
+                   "r"(words.z), "r"(words.w) : "memory");
+    }
+  }
+  bool gave_up = false;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    // 2. every rank's four words from the own buffer, in rank order
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < p.world; ++r) {
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + kTpFlagBytes) + base + (size_t)r * p.slot_elems + 4 * (size_t)i;
+      uint4 w;
+      unsigned long long t0 = 0;
+      for (unsigned int it = 1;; ++it) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
+        if ((w.x >> 16) == tag && (w.y >> 16) == tag && (w.z >> 16) == tag && (w.w >> 16) == tag) break;
+        if (gave_up) break;
+        if ((it & 63u) == 0) {
+          const unsigned long long now = tp_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > kTpWaitNs) { gave_up = true; break; }
+        }
+      }
+      // a word that never came counts as zero
+      acc[0] += (w.x >> 16) == tag ? __uint_as_float(w.x << 16) : 0.f;
+      acc[1] += (w.y >> 16) == tag ? __uint_as_float(w.y << 16) : 0.f;
+      acc[2] += (w.z >> 16) == tag ? __uint_as_float(w.z << 16) : 0.f;
+      acc[3] += (w.w >> 16) == tag ? __uint_as_float(w.w << 16) : 0.f;
+    }
+    if (p.residual) {
+      const uint2 rr = *reinterpret_cast<const uint2*>(p.residual + 4 * (size_t)i);
+      acc[0] = __fadd_rn(round_bf16(acc[0]), bf16_lo(rr.x)); acc[1] = __fadd_rn(round_bf16(acc[1]), bf16_hi(rr.x));
+      acc[2] = __fadd_rn(round_bf16(acc[2]), bf16_lo(rr.y)); acc[3] = __fadd_rn(round_bf16(acc[3]), bf16_hi(rr.y));
+    }
+    *reinterpret_cast<uint2*>(p.y + 4 * (size_t)i) = make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]));
+  }
+  if (gave_up && p.status) *reinterpret_cast<volatile int*>(p.status) = IRON_ERR_TIMEOUT;
+  // 3. the last CTA advances the exchange number (the next launch reads it after this one has ended)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(&p.state[1], 1u) == gridDim.x - 1) {
+      p.state[1] = 0;
+      p.state[0] = seq + 1u;
+    }
+  }
+}
+
 }  // namespace iron
 
 using namespace iron;
@@ -138,4 +215,31 @@ extern "C" int iron_tp_allreduce_bf16(const void* part, const void* residual, vo
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
   return cudaLaunchKernelEx(&cfg, tp_allreduce_kernel, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+}
+
+extern "C" int iron_tp_allreduce_tagged_bf16(const void* part, const void* residual, void* y, int n, int slot_elems,
+                                             const void* const* h_peer_buffers, int rank, int world,
+                                             unsigned int* d_state, int* d_status, iron_stream_t stream) {
+  if (world <= 0 || world > kTpMaxWorld || rank < 0 || rank >= world) return IRON_ERR_SHAPE;
+  if (n <= 0 || (n & 7) || slot_elems < n || (slot_elems & 7)) return IRON_ERR_SHAPE;
+  if (!part || !y || !h_peer_buffers || !d_state) return IRON_ERR_SHAPE;
+  if (!aligned16(part) || !aligned16(y) || (residual && !aligned16(residual))) return IRON_ERR_ALIGN;
+  TpTaggedParams p = {};
+  p.part = (const __nv_bfloat16*)part; p.residual = (const __nv_bfloat16*)residual; p.y = (__nv_bfloat16*)y;
+  p.n = n; p.slot_elems = slot_elems; p.rank = rank; p.world = world;
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_buffers[r] || !aligned16(h_peer_buffers[r])) return IRON_ERR_ALIGN;
+    p.peer[r] = static_cast<unsigned char*>(const_cast<void*>(h_peer_buffers[r]));
+  }
+  p.state = d_state; p.status = d_status;
+  const int groups = n / 4;
+  int ctas = (groups + 255) / 256;
+  if (ctas > 32) ctas = 32;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(256);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  fill_pdl_attr(cfg, attr);
+  return cudaLaunchKernelEx(&cfg, tp_allreduce_tagged_kernel, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }

@@ -615,6 +615,15 @@ def tp_pull_next(*, peer_buffers, slot_elems, rank, world, state, status=None, r
          _ptr(residual), _ptr(x_out))
 
 
+def tp_allreduce_tagged(part, y, *, residual=None, peer_buffers, slot_elems, rank, world, state, status=None):
+    """``tp_allreduce`` as one launch of many CTAs over tagged 32-bit words (no fence, no flag);
+    ``state``: the rank's eight device words of ``tp_push_next`` / ``tp_pull_next``."""
+    _bf16(part, y)
+    call("iron_tp_allreduce_tagged_bf16", _ptr(part), _ptr(residual), _ptr(y), part.numel(), slot_elems,
+         peer_buffers, rank, world, _ptr(state), _ptr(status), _stream())
+    return y
+
+
 def tp_allreduce(part, y, *, residual=None, peer_buffers, slot_elems, rank, world, seq, status=None):
     """Sum ``part`` over the tensor-parallel ranks through peer memory, add ``residual``.
 

@@ -385,6 +385,9 @@ class LlamaEngine:
         # (IRON_TP_FUSED=0 keeps the all-reduce kernel of its own)
         self.tp_fused = self.batch == 1 and os.environ.get("IRON_TP_FUSED", "1") != "0"
         self.peer_state = torch.zeros(8, dtype=torch.int32, device=self.device)
+        # an exchange that is a launch of its own: many CTAs over tagged words (IRON_TP_TAGGED=0: the one-CTA
+        # kernel with a fence and flags)
+        self.tp_tagged = os.environ.get("IRON_TP_TAGGED", "1") != "0"
         torch.cuda.synchronize()
         dist.barrier(group=group)   # every rank's buffer is zeroed before anyone stores into it
 
@@ -397,13 +400,21 @@ class LlamaEngine:
             return ("peer memory, no launch of its own (the producing GEMV stores its rows into every rank's slot, "
                     "the consuming GEMV waits, bounded, and sums in rank order)")
         if self.peer_buffers is not None and self.c.hidden_size * self.batch <= self.peer_slot_elems:
+            if self.tp_tagged:
+                return ("peer-memory kernel (tagged 32-bit words to every rank's slot, bounded re-reads, "
+                        "rank-ordered f32 sum; no fence, no flag)")
             return "peer-memory kernel (stores to every rank's slot, bounded flag wait, rank-ordered f32 sum)"
         return "nccl all-reduce"
 
     def _reduce_add(self, part: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> None:
         """out = residual + (sum of ``part`` over the ranks): one kernel over peer memory
         for a decode step's vector, NCCL and an add otherwise."""
-        if self.peer_buffers is not None and part.numel() <= self.peer_slot_elems and part.is_contiguous():
+        if (self.peer_buffers is not None and part.numel() <= self.peer_slot_elems and part.is_contiguous()
+                and self.tp_tagged):
+            K.tp_allreduce_tagged(part, out, residual=residual, peer_buffers=self.peer_buffers,
+                                  slot_elems=self.peer_slot_elems, rank=self.tp_rank, world=self.tp_size,
+                                  state=self.peer_state, status=self.status)
+        elif self.peer_buffers is not None and part.numel() <= self.peer_slot_elems and part.is_contiguous():
             K.tp_allreduce(part, out, residual=residual, peer_buffers=self.peer_buffers,
                            slot_elems=self.peer_slot_elems, rank=self.tp_rank, world=self.tp_size,
                            seq=self.peer_seq, status=self.status)

@@ -198,3 +198,47 @@ def test_a_rank_that_never_pushes_ends_the_pull_in_a_timeout_status(K):
     assert_verdict(to_numpy(out), want, Tolerance.bf16_ulps(2), what="after the timeout")
     # and the context is intact
     assert torch.equal(K.gemv(A, v), K.gemv(A, v))
+
+
+@pytest.mark.parametrize("rows,E", [(1, 512), (8, 3072), (3, 200)], ids=["one row", "eight rows of 3072", "ragged"])
+def test_the_all_reduce_over_tagged_words_with_one_rank_is_the_residual_add(K, rows, E):
+    """World of one, four exchanges in a row (both parities twice, the state advancing): a batch's
+    rows as one launch of many CTAs -- y = bf16(bf16(part) + residual)."""
+    import torch
+
+    rng = np.random.default_rng(rows * E)
+    n = rows * E
+    me = [Rank(K, 1, n)]
+    for round_ in range(4):
+        part, res = normal(rng, (rows, E)), normal(rng, (rows, E))
+        y = torch.empty(rows, E, dtype=torch.bfloat16, device="cuda")
+        K.tp_allreduce_tagged(to_torch(part), y, residual=to_torch(res), **link(me, 0, n))
+        want = (part.astype(np.float32) + res.astype(np.float32)).astype(bfloat16)
+        assert np.array_equal(to_numpy(y).view(np.uint16), want.view(np.uint16)), round_
+        assert me[0].state.tolist()[:2] == [round_ + 1, 0]
+    # without a residual: the partial itself
+    part = normal(rng, (rows, E))
+    y = torch.empty(rows, E, dtype=torch.bfloat16, device="cuda")
+    K.tp_allreduce_tagged(to_torch(part), y, **link(me, 0, n))
+    assert np.array_equal(to_numpy(y).view(np.uint16), part.view(np.uint16))
+    assert int(me[0].status.item()) == 0
+
+
+def test_the_all_reduce_over_tagged_words_gives_up_on_an_absent_rank(K):
+    import torch
+
+    n = 4 * 512
+    ranks = [Rank(K, 2, n), Rank(K, 2, n)]
+    rng = np.random.default_rng(5)
+    part, res = normal(rng, (4, 512)), normal(rng, (4, 512))
+    y = torch.empty(4, 512, dtype=torch.bfloat16, device="cuda")
+    t0 = time.perf_counter()
+    K.tp_allreduce_tagged(to_torch(part), y, residual=to_torch(res), **link(ranks, 0, n))   # rank 1 never calls
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert int(ranks[0].status.item()) == -6            # IRON_ERR_TIMEOUT, reported not raised
+    assert 1.0 < waited < 10.0
+    assert ranks[0].state.tolist()[:2] == [1, 0]        # the kernel ran to its end
+    # it went on with what it had: its own rows plus the absent rank's zeros
+    want = (part.astype(np.float32) + res.astype(np.float32)).astype(bfloat16)
+    assert np.array_equal(to_numpy(y).view(np.uint16), want.view(np.uint16))
