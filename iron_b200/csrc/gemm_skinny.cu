@@ -81,10 +81,16 @@ __device__ __forceinline__ uint32_t norm_pair(uint32_t x, uint32_t w, float inv)
   return *reinterpret_cast<const uint32_t*>(&y);
 }
 
+// kFolds = false is the plain product: the folded forms' branches are compiled out of it (they cost it
+// 4 to 15 % when they were not).
+template <bool kFolds>
 __global__ void __launch_bounds__(kSkThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                    const __grid_constant__ CUtensorMap map_x, const SkinnyParams p) {
   extern __shared__ uint8_t sk_raw[];
+  const float* const sq_in = kFolds ? p.sq_in : nullptr;
+  float* const sq_out = kFolds ? p.sq_out : nullptr;
+  const int rope_half = kFolds ? p.rope_half : 0;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sk_raw) + 1023) & ~uintptr_t(1023));
   float* part = reinterpret_cast<float*>(smem);     // [batch row][feature], over the stages
   const int stages = p.stages;
@@ -114,7 +120,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(full + s, 1); mbar_init(empty + s, 1); mbar_init(x_full + s, 1); mbar_init(ready + s, 4);
+      mbar_init(full + s, 1); mbar_init(empty + s, 1);
+      if (kFolds) { mbar_init(x_full + s, 1); mbar_init(ready + s, 4); }
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -149,7 +156,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // ---------------- producer ----------------
     if (lane == 0) {
       // the weights do not depend on the kernel before: the first stages' tiles go out ahead of the wait
-      const bool own_x = p.sq_in != nullptr;       // X on its own barrier
+      const bool own_x = sq_in != nullptr;       // X on its own barrier
       const uint32_t w_bytes = own_x ? kSkWBytes : kSkStage;
       int pre = 0;
       for (; pre < nkb && pre < stages; ++pre) {
@@ -181,7 +188,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       uint32_t phase = 0;
       bool ok = true;
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(full + s, phase, abort_flag) || (p.sq_in && !mbar_wait(ready + s, phase, abort_flag))) { ok = false; break; }
+        if (!mbar_wait(full + s, phase, abort_flag) || (sq_in && !mbar_wait(ready + s, phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t w_addr = smem_u32(smem + s * kSkStage);
 #pragma unroll
@@ -195,24 +202,24 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
   } else {
     // ---------------- output warps: park this CTA's partial tile, row = tensor-memory lane ----------------
-    if (p.sq_in) {   // the norm weight is a constant: staged ahead of the dependency wait
+    if (sq_in) {   // the norm weight is a constant: staged ahead of the dependency wait
       const uint4* src = reinterpret_cast<const uint4*>(p.norm_w + (size_t)kb_lo * 64);
       for (int i = threadIdx.x - 64; i < (kb_hi - kb_lo) * 8; i += 128) reinterpret_cast<uint4*>(norm_sm)[i] = ld_cached(src + i);
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     pdl_wait();
-    if (p.rope_half) {    // the positions of this thread's first two items, fetched while the products run
+    if (rope_half) {    // the positions of this thread's first two items, fetched while the products run
       const int fq = (64 / S) >> 2, total = fq * p.rows, t = threadIdx.x - 64;
       if (t < total) pos_first0 = p.positions[t / fq];
       if (t + 128 < total) pos_first1 = p.positions[(t + 128) / fq];
     }
-    if (p.sq_in) {
+    if (sq_in) {
       // ---- the B operand, normalised in place: thread (row b, half kh) owns 32 of a k block's 64 values ----
       const int t = threadIdx.x - 64, b = t >> 1, kh = t & 1;
       float sum = 0.f;
       if (b < p.rows) {
         // sixteen 16-byte loads in flight at a time (a load is ~700 clocks away): 128 slots take one round
-        const float* slots = p.sq_in + (size_t)b * kRowSqPitch;
+        const float* slots = sq_in + (size_t)b * kRowSqPitch;
         for (int base = kh * 4; base < p.sq_parts; base += 128) {
           float4 v[16];
 #pragma unroll
@@ -283,8 +290,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // the ranks in order: all of a group's loads are issued before any is used (a remote one takes ~500
     // clocks).  A thread's second run of four is the up half of a gated tile or the rotation partners. ----
     const int t = threadIdx.x - 64;                 // 0 .. 127
-    const bool two = p.dual || p.rope_half;
-    const int second = p.dual ? 64 : p.rope_half;   // distance of the second run
+    const bool two = p.dual || rope_half;
+    const int second = p.dual ? 64 : rope_half;   // distance of the second run
     const int firsts = two ? 64 : 128;              // first runs' features in a tile
     const int feats = firsts / S, fq = feats >> 2, total = fq * p.rows;
     const float* src[8];
@@ -294,7 +301,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const int g = g0 + t;
       const int b = g / fq, first = rank * feats + 4 * (g - b * fq);
       // a rotation pair's low element: head (first / half) of the tile, element (first % half)
-      const int f = p.rope_half ? (first / p.rope_half) * p.D + first % p.rope_half : first;
+      const int f = rope_half ? (first / rope_half) * p.D + first % rope_half : first;
       const int col = n0 + f;
       const bool act = g < total && col < p.N;
       float sq = 0.f;
@@ -302,7 +309,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         float4 va[8], vb[8];
         int pos = 0;
         uint4 turn = make_uint4(0u, 0u, 0u, 0u);
-        if (p.rope_half) {     // the angle chunk is asked for before the partial tiles
+        if (rope_half) {     // the angle chunk is asked for before the partial tiles
           const int it = g0 >> 7;
           pos = it == 0 ? pos_first0 : it == 1 ? pos_first1 : p.positions[b];
           pos = max(0, min(pos, p.S - 1));
@@ -324,7 +331,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[e] = round_bf16(acc[e]);
-        if (p.rope_half) {
+        if (rope_half) {
           // q and k heads turn by the angle row of this sequence's position; q goes out densely, k and v
           // into row `position` of the sequence's caches (the values the separate kernels would read and write)
           float w[4];
@@ -347,7 +354,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           else if (hh < p.H + p.G) dst = p.k_cache + (size_t)b * p.kv_batch_stride + ((size_t)pos * p.G + (hh - p.H)) * p.D;
           else dst = p.v_cache + (size_t)b * p.kv_batch_stride + ((size_t)pos * p.G + (hh - p.H - p.G)) * p.D;
           *reinterpret_cast<uint2*>(dst + i0) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
-          *reinterpret_cast<uint2*>(dst + i0 + p.rope_half) = make_uint2(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]));
+          *reinterpret_cast<uint2*>(dst + i0 + rope_half) = make_uint2(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]));
         } else {
           if (p.dual) {
 #pragma unroll
@@ -360,7 +367,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
               v[0] = __fadd_rn(v[0], bf16_lo(rr.x)); v[1] = __fadd_rn(v[1], bf16_hi(rr.x));
               v[2] = __fadd_rn(v[2], bf16_lo(rr.y)); v[3] = __fadd_rn(v[3], bf16_hi(rr.y));
             }
-            if (p.sq_out) {
+            if (sq_out) {
 #pragma unroll
               for (int e = 0; e < 4; ++e) { v[e] = round_bf16(v[e]); sq = fmaf(v[e], v[e], sq); }
             }
@@ -376,10 +383,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           }
         }
       }
-      if (p.sq_out) {
+      if (sq_out) {
         // the fq threads of a batch row are neighbours in a warp: one slot per (row, CTA), in a fixed order
         for (int m = 1; m < fq; m <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, m);
-        if (g < total && g == b * fq) p.sq_out[(size_t)b * kRowSqPitch + blockIdx.x] = sq;
+        if (g < total && g == b * fq) sq_out[(size_t)b * kRowSqPitch + blockIdx.x] = sq;
       }
     }
   }
@@ -478,9 +485,11 @@ static int launch_skinny(const void* X, const void* W, const void* W2, void* C, 
     p.q_out = (__nv_bfloat16*)fold.q_out; p.k_cache = (__nv_bfloat16*)fold.k_cache; p.v_cache = (__nv_bfloat16*)fold.v_cache;
     p.kv_batch_stride = fold.kv_batch_stride; p.H = fold.H; p.G = fold.G; p.D = fold.D; p.S = fold.S;
   }
+  const bool folds = fold.norm_w || fold.sq_out || fold.angles;
   static DeviceOnce configured;   // the attribute is per device
   if (!configured.done()) {
-    if (cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemDeep + kSkNormBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemDeep) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemDeep + kSkNormBytes) != cudaSuccess)
       return IRON_ERR_LAUNCH;
     configured.mark();
   }
@@ -500,7 +509,9 @@ static int launch_skinny(const void* X, const void* W, const void* W2, void* C, 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1 + pdl_attr_count();
-  return cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, mw, mw2, mx, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+  const cudaError_t e = folds ? cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<true>, mw, mw2, mx, p)
+                              : cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<false>, mw, mw2, mx, p);
+  return e == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
 int launch_gemm_skinny(const void* X, const void* W, const void* W2, void* C, const void* residual, int rows, int N,
