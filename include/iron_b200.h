@@ -419,7 +419,14 @@ int iron_causal_conv1d_bf16(const void* x, const void* taps, const void* bias,
  * one); partial results meet in distributed shared memory, so no workspace is needed.
  * stable_prefix != 0 promises that the kernel launched just before this one on the
  * stream wrote at most row n-1 of K and V (true of a decode step), which lets the key
- * loads start before that kernel has finished. */
+ * loads start before that kernel has finished.
+ * Grouped heads (H > G, D 64 or 128) take tensor-core forms that choose their own split: from
+ * 16 (sequence, KV head) pairs on, one CTA a pair with the keys split over a cluster while the
+ * pairs do not fill the machine; below that, every CTA holds its share of a cache of up to
+ * about 100 K key rows x pairs in shared memory and the last CTA of a pair folds the partials
+ * through a scratch the library owns (1.2 MB per GPU, held until exit): calls of that form that
+ * OVERLAP on one GPU (two streams) would race; calls of one stream do not.
+ * IRON_MHA_DECODE_RESIDENT=0 / IRON_MHA_DECODE_TC=0 keep the cluster kernel described first. */
 int iron_mha_decode_splits(int batch, int G, int kv_len_hint);
 int iron_mha_decode_bf16(const void* Q, const void* K, const void* V, void* O, int batch,
                          int H, int G, int D, int kv_max, long long kv_batch_stride,

@@ -736,12 +736,15 @@ static int launch_gemv(GemvParams& p, int npairs, int batches, cudaStream_t stre
     if (p.tp.mode == TP_PULL && p.K > p.tp.slot_elems) return IRON_ERR_SHAPE;
   }
   // Which shapes stream through the TMA-fed kernel: IRON_GEMV_RING is a bit mask (1 gate/up,
-  // 2 large plain matrices, 4 q/k/v, 8 small plain matrices); unset = 3.  Measured on the
-  // Llama-3.2-1B decode step: gate/up 12.3 us against 14.5 us register-streamed; the whole
-  // step 695 us with mask 3, 710 us with 0, 704 us with 15 (the small matrices gain nothing).
+  // 2 large plain matrices, 4 q/k/v, 8 small plain matrices); unset = by size: gate/up always, q/k/v
+  // from 24 MB, plain matrices from 16 MB.  Measured on the Llama-3.2-1B decode step: gate/up 12.3 us
+  // against 14.5 us register-streamed; the whole step 695 us with mask 3, 710 us with 0, 704 us with
+  // 15 (its 12.6 MB q/k/v matrix gains nothing); on the 3B step (31.5 MB q/k/v, 18.9 MB o_proj)
+  // 1.686 ms with mask 3, 1.651 with 7, 1.648 with 15.
   const int policy = ring_policy();
-  const int mask = policy >= 0 ? policy : 3;
   const long long bytes = (long long)p.rows * p.K * 2 * (MODE == GEMV_SWIGLU ? 2 : 1);
+  const int by_size = 1 | (bytes >= (24ll << 20) ? 4 : 0) | (bytes >= (16ll << 20) ? 2 | 8 : 0);
+  const int mask = policy >= 0 ? policy : by_size;
   if (mask && batches == 1 && p.repeat == 1 && p.K <= kRingMaxK) {
     if (MODE == GEMV_SWIGLU && (mask & 1)) return launch_ring<RING_SWIGLU>(p, p.rows, stream);
     if (MODE == GEMV_QKV && (mask & 4)) return launch_ring<RING_QKV>(p, p.rows >> 1, stream);
