@@ -52,6 +52,19 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 // product), held in registers across the row sum, normalised with the norm's own two
 // roundings.  One CTA per row; up to kGatedChunks 16-byte chunks a thread stay in registers.
 constexpr int kGatedChunks = 4;
+// Two gate values -> bf16x2 of silu (f32 arithmetic, one rounding), times two packed bf16 x (the product of
+// two bf16 values is exact in f32, so the bf16 multiply's single rounding is the separate steps' rounding).
+__device__ __forceinline__ uint32_t gated_pair(uint32_t g, uint32_t x) {
+  const __nv_bfloat162 s = __floats2bfloat162_rn(silu_f32(bf16_lo(g)), silu_f32(bf16_hi(g)));
+  const __nv_bfloat162 y = __hmul2(s, *reinterpret_cast<const __nv_bfloat162*>(&x));
+  return *reinterpret_cast<const uint32_t*>(&y);
+}
+// Two packed bf16 values scaled by `inv` in f32 and rounded, times two packed bf16 weights (w == nullptr: none).
+__device__ __forceinline__ uint32_t scaled_pair(uint32_t v, float inv, const uint32_t* w) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(bf16_lo(v) * inv, bf16_hi(v) * inv);
+  if (w) h = __hmul2(h, *reinterpret_cast<const __nv_bfloat162*>(w));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ gate,
                                                             const __nv_bfloat16* __restrict__ w,
@@ -61,7 +74,7 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __nv_bfloat16*
   pdl_wait();
   pdl_launch();
   if (d_valid) valid = min(*d_valid, rows);
-  const int nch = cols >> 3;
+  const int nch = cols >> 3, nt = blockDim.x;
   for (int r = blockIdx.x; r < valid; r += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * cols);
     const uint4* gr = reinterpret_cast<const uint4*>(gate + (size_t)r * cols);
@@ -69,43 +82,32 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const __nv_bfloat16*
     uint4 xv[kGatedChunks], gv[kGatedChunks];
 #pragma unroll
     for (int u = 0; u < kGatedChunks; ++u) {
-      const int i = threadIdx.x + u * 256;
+      const int i = threadIdx.x + u * nt;
       if (i < nch) { xv[u] = ld_stream(xr + i); gv[u] = ld_stream(gr + i); }
     }
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < kGatedChunks; ++u) {
-      const int i = threadIdx.x + u * 256;
+      const int i = threadIdx.x + u * nt;
       if (i < nch) {
-        float f[8], g[8];
+        xv[u] = make_uint4(gated_pair(gv[u].x, xv[u].x), gated_pair(gv[u].y, xv[u].y), gated_pair(gv[u].z, xv[u].z),
+                           gated_pair(gv[u].w, xv[u].w));
+        float f[8];
         unpack8(xv[u], f);
-        unpack8(gv[u], g);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          f[j] = round_bf16_alu(__fmul_rn(round_bf16_alu(silu_f32(g[j])), f[j]));
-          ss = fmaf(f[j], f[j], ss);
-        }
-        xv[u] = make_uint4(pack_bf16x2_exact(f[0], f[1]), pack_bf16x2_exact(f[2], f[3]),
-                           pack_bf16x2_exact(f[4], f[5]), pack_bf16x2_exact(f[6], f[7]));
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
       }
     }
     const float tot = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(tot / (float)cols + eps);
 #pragma unroll
     for (int u = 0; u < kGatedChunks; ++u) {
-      const int i = threadIdx.x + u * 256;
+      const int i = threadIdx.x + u * nt;
       if (i < nch) {
-        float f[8];
-        unpack8(xv[u], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = round_bf16_alu(f[j] * inv);
-        if (w) {
-          float g[8];
-          unpack8(ld_cached(reinterpret_cast<const uint4*>(w) + i), g);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = f[j] * g[j];
-        }
-        yr[i] = pack8(f);
+        uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+        if (w) wv = ld_cached(reinterpret_cast<const uint4*>(w) + i);
+        yr[i] = make_uint4(scaled_pair(xv[u].x, inv, w ? &wv.x : nullptr), scaled_pair(xv[u].y, inv, w ? &wv.y : nullptr),
+                           scaled_pair(xv[u].z, inv, w ? &wv.z : nullptr), scaled_pair(xv[u].w, inv, w ? &wv.w : nullptr));
       }
     }
   }
@@ -516,8 +518,11 @@ extern "C" int iron_rmsnorm_gated_bf16(const void* x, const void* gate, const vo
   if (!aligned16(x) || !aligned16(gate) || !aligned16(y) || (weight && !aligned16(weight))) return IRON_ERR_ALIGN;
   if (valid_rows == 0 && !d_valid_rows) return IRON_OK;
   const int upper = d_valid_rows ? rows : valid_rows;
-  const int grid = upper < kSMs * 8 ? upper : kSMs * 8;
-  return launch_pdl(rmsnorm_gated_kernel, dim3(grid), dim3(256), (cudaStream_t)stream,
+  // 128 threads when they cover the row with up to four chunks each (a 3072-wide row is three chunks a thread)
+  const int threads = (cols >> 3) <= 128 * kGatedChunks ? 128 : 256;
+  const int full = kSMs * (2048 / threads);
+  const int grid = upper < full ? upper : full;
+  return launch_pdl(rmsnorm_gated_kernel, dim3(grid), dim3(threads), (cudaStream_t)stream,
                     (const __nv_bfloat16*)x, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)weight,
                     (__nv_bfloat16*)y, rows, cols, eps, valid_rows, d_valid_rows);
 }
