@@ -546,7 +546,8 @@ extern "C" int iron_gemm_rows_bf16(const void* X, const void* W, const void* W2,
   if (rows < 0 || rows > 64 || N <= 0 || K <= 0 || (K & 7)) return IRON_ERR_SHAPE;
   if (!X || !W || !C) return IRON_ERR_SHAPE;
   if (ldx < K || ldw < K || ldc < N || (ldx & 7) || (ldw & 7)) return IRON_ERR_SHAPE;
-  if (!aligned16(X) || !aligned16(W) || (W2 && !aligned16(W2))) return IRON_ERR_ALIGN;
+  if (!aligned16(X) || !aligned16(W) || (W2 && !aligned16(W2)) || !aligned16(C) || (residual && !aligned16(residual)))
+    return IRON_ERR_ALIGN;
   if (W2 && residual) return IRON_ERR_SHAPE;                        // the gated form has no residual
   if (d_rowsq_out && (W2 || !residual || !aligned16(d_rowsq_out))) return IRON_ERR_SHAPE;   // sums of the residual stream only
   const int rc = check_norm(X, norm_weight, d_rowsq_in, rowsq_parts, K, ldx);

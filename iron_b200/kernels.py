@@ -542,8 +542,8 @@ def gemm_rows(X, W, out=None, *, W2=None, residual=None, norm_weight=None, rowsq
         raise ValueError(f"gemm_rows: X {tuple(X.shape)} and W {tuple(W.shape)} do not chain")
     if out is None:
         out = torch.empty((rows, N), dtype=torch.bfloat16, device=X.device)
-    if residual is not None and residual.stride(0) != out.stride(0):
-        raise ValueError("the residual has the output's pitch")
+    if residual is not None and (residual.shape != out.shape or residual.stride(0) != out.stride(0)):
+        raise ValueError("the residual has the output's shape and pitch")
     if rowsq_out is not None and (rowsq_out.dtype != torch.float32 or rowsq_out.shape != (64, ROWSQ_PITCH)):
         raise TypeError("rowsq buffers are (64, 320) float32")
     nw, sq, parts = _norm_args(norm_weight, rowsq_in, rowsq_parts)
