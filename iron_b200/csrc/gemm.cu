@@ -99,13 +99,16 @@ __device__ __forceinline__ float epilogue_apply(int mode, float c) {
 
 // The output stage for 32 consecutive columns of one row: round, activation, residual,
 // store (bf16 or f32; C row-major or transposed).
+template <bool kSlim = false>
 __device__ __forceinline__ void output_chunk(const GemmParams& p, float* v, int row, int col0) {
-  if (!p.out_f32) {
+  const bool out_f32 = kSlim ? false : p.out_f32 != 0, c_transposed = kSlim ? false : p.c_transposed != 0;
+  const int epilogue = kSlim ? EPI_NONE : p.epilogue;
+  if (!out_f32) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = epilogue_apply(p.epilogue, round_bf16(v[j]));
+    for (int j = 0; j < 32; ++j) v[j] = epilogue_apply(epilogue, round_bf16(v[j]));
   }
   const bool full_chunk = col0 + 32 <= p.N;
-  if (!p.c_transposed) {
+  if (!c_transposed) {
     const size_t off = (size_t)row * p.ldc + col0;
     if (p.residual) {
       // 16-byte loads need every row of the residual to start on an 8-element boundary
@@ -118,18 +121,21 @@ __device__ __forceinline__ void output_chunk(const GemmParams& p, float* v, int 
           for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(round_bf16(v[q * 8 + j]), f[j]);
         }
       } else {
-        for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-          v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(p.residual[off + j]));
+#pragma unroll
+        for (int j = 0; j < 32; ++j)   // unrolled with a predicate: v stays in registers
+          if (col0 + j < p.N) v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(p.residual[off + j]));
       }
     }
-    if (p.out_f32) {
+    if (out_f32) {
       float* dst = reinterpret_cast<float*>(p.C) + off;
       if (full_chunk && (p.ldc & 3) == 0) {
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
       } else {
-        for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) dst[j] = v[j];
       }
     } else {
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
@@ -137,16 +143,20 @@ __device__ __forceinline__ void output_chunk(const GemmParams& p, float* v, int 
 #pragma unroll
         for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = pack8(v + q * 8);
       } else {
-        for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
       }
     }
   } else {
     // C is (N, M): lanes hold consecutive rows, so each column is a coalesced run.
-    for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (col0 + j >= p.N) break;
       const size_t off = (size_t)(col0 + j) * p.ldc + row;
       float x = v[j];
       if (p.residual) x = __fadd_rn(round_bf16(x), __bfloat162float(p.residual[off]));
-      if (p.out_f32) reinterpret_cast<float*>(p.C)[off] = x;
+      if (out_f32) reinterpret_cast<float*>(p.C)[off] = x;
       else reinterpret_cast<__nv_bfloat16*>(p.C)[off] = __float2bfloat16_rn(x);
     }
   }
@@ -470,11 +480,15 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int PBN>
+// kSlim: the plain product (bf16 row-major C, optional residual, no activation, no gated pair, no RoPE) as an
+// instantiation of its own: the other output stages are compiled out of it.
+template <int PBN, bool kSlim = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
   constexpr int kPairBN = PBN;
+  const int dual = kSlim ? 0 : p.dual;
+  const __nv_bfloat16* const rope_angles = kSlim ? nullptr : p.rope_angles;
   constexpr int kPairStageBytes = PairCfg<PBN>::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -511,7 +525,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int BNO = p.dual ? kPairBN / 2 : kPairBN;
+  const int BNO = dual ? kPairBN / 2 : kPairBN;
   const int num_kb = (p.K + BK - 1) / BK;
   pdl_launch();
   // With the row count known at launch, the first tile's weight (B) copies do not depend on the
@@ -525,7 +539,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint8_t* b_dst = smem + pre * kPairStageBytes + kPairABytes;
         const uint32_t bar = map_to_rank(smem_u32(full + pre), 0);
         if (rank == 0) mbar_expect_tx(full + pre, 2 * kPairStageBytes);
-        if (p.dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
+        if (dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
         else tma_load_2d_pair(b_dst, &map_b, kb * BK, n0 + (int)rank * (kPairBN / 2), bar);
       }
     }
@@ -560,7 +574,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           if (rank == 0) mbar_expect_tx(full + s, 2 * kPairStageBytes);
           tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, bar);
-          if (p.dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
+          if (dual) tma_load_2d_pair(b_dst, rank == 0 ? &map_b : &map_b2, kb * BK, n0, bar);
           else tma_load_2d_pair(b_dst, &map_b, kb * BK, n0 + (int)rank * (kPairBN / 2), bar);
           ++issued;
           if (++s == kPairStages) { s = 0; phase ^= 1; }
@@ -629,7 +643,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tcgen05_fence_after();
       const int row = m0 + group * 32 + lane;
       const bool row_live = row < valid;
-      if (p.rope_angles) {
+      if (rope_angles) {
         // A tile holds whole heads (BNO % D == 0).  Per head and per run of 32 rotation pairs:
         // element i and element i + D/2, rounded to bf16 as the projection's output is, then
         // turned with the products and the sum each rounded once -- the arithmetic of the
@@ -654,7 +668,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               b[j] = round_bf16(__uint_as_float(rb[j]));
             }
             if (hh < H + G) {
-              const __nv_bfloat16* ar = p.rope_angles + (size_t)(p.rope_angle_start + row) * D + 2 * (s * 32);
+              const __nv_bfloat16* ar = rope_angles + (size_t)(p.rope_angle_start + row) * D + 2 * (s * 32);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 float cs[16];
@@ -693,7 +707,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.dual) {
+        if (dual) {
           tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * kPairAccStride + kPairBN / 2 + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
@@ -701,7 +715,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             v[j] = __fmul_rn(round_bf16(silu_f32(round_bf16(v[j]))), round_bf16(__uint_as_float(r[j])));
         }
         if (!row_live || col0 >= p.N) continue;
-        output_chunk(p, v, row, col0);
+        output_chunk<kSlim>(p, v, row, col0);
       }
       tcgen05_fence_before();
       mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + acc), 0));
@@ -817,8 +831,10 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
   constexpr int kPairSmem = PairCfg<PBN>::kSmem;
   static DeviceOnce configured;   // the attribute is per device
   if (!configured.done()) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel<PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_pair_kernel<PBN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gemm_pair_kernel<PBN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
+            cudaSuccess)
       return IRON_ERR_LAUNCH;
     configured.mark();
   }
@@ -832,7 +848,11 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
-  return cudaLaunchKernelEx(&cfg, gemm_pair_kernel<PBN>, ma, mb, mb2, p) == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
+  static const bool slim_on = [] { const char* e = getenv("IRON_GEMM_SLIM"); return !(e && e[0] == '0'); }();
+  const bool slim = slim_on && !p.dual && !p.rope_angles && !p.out_f32 && !p.c_transposed && p.epilogue == EPI_NONE;
+  const cudaError_t e = slim ? cudaLaunchKernelEx(&cfg, gemm_pair_kernel<PBN, true>, ma, mb, mb2, p)
+                             : cudaLaunchKernelEx(&cfg, gemm_pair_kernel<PBN, false>, ma, mb, mb2, p);
+  return e == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
 // The pair form takes K-major B (weights as stored) and problems with more than one
