@@ -162,11 +162,13 @@ __device__ __forceinline__ void output_chunk(const GemmParams& p, float* v, int 
   }
 }
 
-template <int BN, bool SPLIT>
+// kSlim: as for the pair kernel below, the plain product as an instantiation of its own.
+template <int BN, bool SPLIT, bool kSlim = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
   using Cfg = GemmCfg<BN, SPLIT>;
+  const int dual = kSlim ? 0 : p.dual;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* staging = reinterpret_cast<float*>(smem);
@@ -206,7 +208,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   unsigned int crank = 0, csize = 1;
   // Output columns per tile: in the gated form one accumulator holds BN/2 columns of the
   // first product and the matching BN/2 columns of the second.
-  const int BNO = p.dual ? BN / 2 : BN;
+  const int BNO = dual ? BN / 2 : BN;
   const int num_kb = (p.K + BK - 1) / BK;
   auto setup = [&](int rows) {
     valid = max(rows, 0);
@@ -239,7 +241,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         mbar_expect_tx(full + pre, Cfg::kStageBytes);
         uint8_t* b_dst = smem + pre * Cfg::kStageBytes + Cfg::kABytes;
         tma_load_2d(b_dst, &map_b, kb * BK, n0, full + pre);
-        if (p.dual) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b2, kb * BK, n0, full + pre);
+        if (dual) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b2, kb * BK, n0, full + pre);
       }
     }
   }
@@ -268,7 +270,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           mbar_expect_tx(full + s, Cfg::kStageBytes);
           tma_load_2d(a_dst, &map_a, kb * BK, m0, full + s);
-          if (p.dual) {
+          if (dual) {
             tma_load_2d(b_dst, &map_b, kb * BK, n0, full + s);
             tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b2, kb * BK, n0, full + s);
           } else if (!p.b_n_major) {
@@ -354,7 +356,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.dual) {
+        if (dual) {
           // the second product's columns sit BN/2 further in the accumulator
           tmem_ld32(tmem_base + ((uint32_t)(group * 32) << 16) + acc * BN + BN / 2 + c * 32, r);
           tmem_ld_wait();
@@ -383,7 +385,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
-        output_chunk(p, v, row, col0);
+        output_chunk<kSlim>(p, v, row, col0);
       }
       tcgen05_fence_before();
       mbar_arrive(acc_empty + acc);
@@ -776,7 +778,9 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   using Cfg = GemmCfg<BN>;
   static DeviceOnce configured;   // the attribute is per device
   if (!configured.done()) {
-    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_bf16_kernel<BN, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmem) != cudaSuccess)
       return IRON_ERR_LAUNCH;
     configured.mark();
@@ -790,8 +794,11 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   fill_pdl_attr(cfg, attr);
-  return cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, false>, ma, mb, mb2, p) == cudaSuccess ? IRON_OK
-                                                                                             : IRON_ERR_LAUNCH;
+  static const bool slim_on = [] { const char* e = getenv("IRON_GEMM_SLIM"); return !(e && e[0] == '0'); }();
+  const bool slim = slim_on && !p.dual && !p.out_f32 && !p.c_transposed && p.epilogue == EPI_NONE;
+  const cudaError_t e = slim ? cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, false, true>, ma, mb, mb2, p)
+                             : cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, false, false>, ma, mb, mb2, p);
+  return e == cudaSuccess ? IRON_OK : IRON_ERR_LAUNCH;
 }
 
 // One tile per cluster of `splits` CTAs, each taking a slice of K.
