@@ -796,12 +796,20 @@ extern "C" int iron_causal_conv1d_bf16(const void* x, const void* taps, const vo
   p.hist_batch = (long long)(kernel - 1) * channels;
   // rows are cut into segments so a long prompt fills the machine; each segment re-reads
   // the K-1 rows before it
-  const int cgroups = (channels / 8 + 127) / 128;
-  int segs = (16 * kSMs + cgroups * batch - 1) / (cgroups * batch);
+  // a thread takes 8 channels; the block is the multiple of 32 threads (up to 128) that wastes the fewest
+  // lanes on the last block of a row (3328 channels = 416 threads' worth: 13 blocks of 32, none idle)
+  const int c8s = channels / 8;
+  int threads = 128, idle = (128 - c8s % 128) % 128;
+  for (int t = 96; t >= 32; t -= 32) {
+    const int waste = (t - c8s % t) % t;
+    if (waste < idle) { threads = t; idle = waste; }
+  }
+  const int cgroups = (c8s + threads - 1) / threads;
+  int segs = (16 * kSMs * (128 / threads) + cgroups * batch - 1) / (cgroups * batch);
   segs = segs < 1 ? 1 : segs;
   const int max_segs = (rows + 31) / 32;
   if (segs > max_segs) segs = max_segs;
-  const dim3 grid(cgroups, segs, batch), block(128);
+  const dim3 grid(cgroups, segs, batch), block(threads);
   cudaStream_t s = (cudaStream_t)stream;
   switch (kernel) {
     case 2: return launch_scan_pdl(causal_conv_kernel<2>, grid, block, s, p);
