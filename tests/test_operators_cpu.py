@@ -153,6 +153,19 @@ def test_host_refusals_come_before_any_launch():
         K.gemm(A, W, b_col_maj=True, residual=torch.zeros(256, 104, dtype=torch.bfloat16)[:, :100])
     with pytest.raises(ValueError, match="residual"):
         K.gemm(A, W, b_col_maj=True, residual=torch.zeros(100, 256, dtype=torch.bfloat16))
+    # the decode-batch projections with folded neighbours: a norm needs both its weight and the sums, sums and
+    # residuals have fixed layouts, the q/k/v weight has (H + 2G) D rows
+    X, ln = torch.zeros(4, 64, dtype=torch.bfloat16), torch.ones(64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="RMSNorm"):
+        K.gemm_rows(X, W, norm_weight=ln)
+    with pytest.raises(TypeError, match="rowsq"):
+        K.gemm_rows(X, W, norm_weight=ln, rowsq_in=torch.zeros(64, 64), rowsq_parts=1)
+    with pytest.raises(ValueError, match="residual"):
+        K.gemm_rows(X, W, residual=torch.zeros(4, 104, dtype=torch.bfloat16)[:, :100])
+    with pytest.raises(ValueError, match="do not chain"):
+        K.gemm_rows(X, torch.zeros(100, 32, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="Wqkv"):
+        K.gemm_rows_qkv_rope(X, W, ln, X, X, X, torch.zeros(4, dtype=torch.int32), H=1, G=1, D=64)
     base = LlamaConfig(vocab_size=64, hidden_size=64, num_hidden_layers=1, num_attention_heads=1,
                        num_key_value_heads=1, head_dim=64, intermediate_size=64, rope_theta=1e4, max_seq_len=8)
     for change in (dict(attention_bias=True), dict(mlp_bias=True), dict(hidden_act="gelu")):
