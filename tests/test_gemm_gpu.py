@@ -148,7 +148,7 @@ def test_no_pipeline_wait_gave_up(K):
     assert int(status.item()) == 0
 
 
-@pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (2048, 8192, 2048), (64, 8192, 2048), (200, 328, 136), (7, 2048, 512)])
+@pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (2048, 8192, 2048), (64, 8192, 2048), (200, 328, 136), (7, 2048, 512), (5, 328, 136), (33, 5000, 320)])
 def test_gated_two_weight_form_matches_the_chain_of_references(K, M, N, Kd):
     """gate GEMM, up GEMM, SiLU, product -- each rounded as the separate operators round."""
     rng = np.random.default_rng(1010)
